@@ -1,0 +1,439 @@
+#!/usr/bin/env python
+"""Benchmark of the preprocessing hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--no-extras]
+
+Headline workload (one "step" = one pass of the resampler over one batch): bf16 trajectory
+resampling, B=4096 rows per GPU, S=500, D=256, T=250 sorted-uniform target times per row, seeded
+synthetic inputs resident in HBM.  ``value`` is GB/s over the bytes a resampler must move (the
+smaller of "every tensor once" and "touched source rows + times + output").  Under torchrun each
+rank owns its own B=4096 shard (weak scaling, no data-path collective); the time is the max over
+ranks of the CUDA-event time of the K timed steps.
+
+The line also carries: the HBM roofline of the resample kernel measured live, the end-to-end rate
+from pinned host buffers through the public API, the CPU oracle timed on the host cores
+(``cpu_baseline``), SM clocks sampled during the run, and — unless ``--no-extras`` — fusion and
+voxelisation figures for the other headline configurations.
+
+``--impl reference`` times the CPU restatement of the reference's torch path (the oracle port,
+all host threads) on a bounded sample of the same workload and prints the same line shape.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+HEADLINE = dict(B=4096, S=500, D=256, T=250)
+METRIC = "resample_throughput"
+UNIT = "GB/s"
+
+
+# ----------------------------------------------------------------------------- helpers
+
+def measured_peak_gbs():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region runs."""
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(prefix="clocks_", suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, smax, reasons, power = [], [], set(), []
+        try:
+            for line in open(self.path):
+                p = [x.strip() for x in line.split(",")]
+                if len(p) < 9 or not p[0].isdigit() or int(p[0]) != self.gpu_index:
+                    continue
+                try:
+                    sm.append(float(p[1])); smax.append(float(p[2])); power.append(float(p[3]))
+                except ValueError:
+                    continue
+                for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), p[5:9]):
+                    if v.lower().startswith("active"):
+                        reasons.add(name)
+            os.unlink(self.path)
+        except Exception:
+            pass
+        # samples under load: the upper half by power draw
+        if sm:
+            order = sorted(range(len(sm)), key=lambda i: power[i])
+            loaded = [sm[i] for i in order[len(order) // 2:]]
+        else:
+            loaded = []
+        return {"sm_mhz": statistics.median(loaded) if loaded else None,
+                "sm_max_mhz": max(smax) if smax else None, "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def physical_gpu_index(local_rank: int) -> int:
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+    if vis:
+        try:
+            return int(vis.split(",")[local_rank])
+        except Exception:
+            return local_rank
+    return local_rank
+
+
+def dist_setup(n_gpus: int):
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29500")
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    else:
+        torch.cuda.set_device(local)
+    return rank, world, local
+
+
+def max_over_ranks(ms: float, world: int, dev) -> float:
+    if world == 1:
+        return ms
+    import torch.distributed as dist
+    t = torch.tensor([ms], dtype=torch.float64, device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def barrier(world: int):
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+    torch.cuda.synchronize()
+
+
+def timed_region(step, steps: int, warmup: int, world: int, dev):
+    """W untimed steps, then K steps between events; returns (max-over-ranks total ms, per-step ms list)."""
+    for _ in range(warmup):
+        step()
+    barrier(world)
+    evs = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+    evs[0].record()
+    for k in range(steps):
+        step()
+        evs[k + 1].record()
+    torch.cuda.synchronize()
+    barrier(world)
+    total = evs[0].elapsed_time(evs[-1])
+    per = [evs[k].elapsed_time(evs[k + 1]) for k in range(steps)]
+    return max_over_ranks(total, world, dev), per
+
+
+class L2Flush:
+    """Writes a buffer larger than L2 so the next timed call starts from DRAM."""
+    def __init__(self, dev, nbytes=256 << 20):
+        self.buf = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+
+    def __call__(self):
+        self.buf.zero_()
+
+
+def time_cold(fn, iters: int, warmup: int, flush: L2Flush):
+    """Median and mean of per-call CUDA-event times with an L2 flush before every call (ms)."""
+    for _ in range(warmup):
+        flush(); fn()
+    ts = []
+    for _ in range(iters):
+        flush()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(); fn(); b.record()
+        b.synchronize()
+        ts.append(a.elapsed_time(b))
+    return statistics.median(ts), sum(ts) / len(ts)
+
+
+# ----------------------------------------------------------------------------- reference arm
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import oracle
+    from robogoat_b200 import workloads
+    threads = oracle.max_threads()
+    B_s = 256                                  # bounded sample: 1/16 of the headline batch per step
+    src, st, tt = workloads.resample_inputs(B=B_s, dtype=torch.bfloat16, irregular_targets=True, seed=0,
+                                            S=HEADLINE["S"], D=HEADLINE["D"], T=HEADLINE["T"])
+    left, right, _ = oracle.brackets(st, tt)
+    nbytes = min(workloads.resample_bytes(B_s, HEADLINE["S"], HEADLINE["T"], HEADLINE["D"], 2),
+                 workloads.resample_touched_bytes(left, right, HEADLINE["S"], HEADLINE["D"], 2))
+    for _ in range(max(args.warmup, 1)):
+        oracle.resample_trajectories(src, st, tt, threads=threads)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        oracle.resample_trajectories(src, st, tt, threads=threads)
+    dt = time.perf_counter() - t0
+    gbs = nbytes * args.steps / dt / 1e9
+    sample = f"B={B_s} rows of the B=4096 headline batch per step (same S, D, T, generator), oracle port, {threads} threads"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": gbs, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "resample bf16 B=4096 S=500 D=256 T=250 (timed on a B=256 sample, rate is size independent)",
+                   "bytes_per_step": nbytes},
+        "cpu_baseline": {"value": gbs, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": gbs, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ----------------------------------------------------------------------------- our arm
+
+def run_ours(args):
+    from robogoat_b200 import _lib, ops, workloads
+    import robocache
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU path to measure)")
+    L = _lib.load()
+    rank, world, local = dist_setup(args.gpus)
+    dev = torch.device("cuda", local)
+    B, S, D, T = HEADLINE["B"], HEADLINE["S"], HEADLINE["D"], HEADLINE["T"]
+
+    src, st, tt = workloads.resample_inputs(B=B, S=S, D=D, T=T, dtype=torch.bfloat16, irregular_targets=True,
+                                            seed=rank, device=dev)
+    out = torch.empty((B, T, D), dtype=torch.bfloat16, device=dev)
+    left, right, _ = ops.resample_brackets_cuda(st, tt)
+    algo_bytes = workloads.resample_bytes(B, S, T, D, 2)
+    touched_bytes = workloads.resample_touched_bytes(left, right, S, D, 2)
+    step_bytes = min(algo_bytes, touched_bytes)
+    del left, right
+    stream = torch.cuda.current_stream(dev).cuda_stream
+
+    def step():
+        rc = L.rc_resample(src.data_ptr(), st.data_ptr(), tt.data_ptr(), out.data_ptr(), B, S, T, D, _lib.RC_DTYPE_BF16,
+                           local, stream)
+        if rc != 0:
+            raise RuntimeError(f"rc_resample failed: {rc}")
+
+    sampler = ClockSampler(physical_gpu_index(local))
+    if rank == 0:
+        sampler.start()
+    total_ms, per = timed_region(step, args.steps, args.warmup, world, dev)
+    # keep the kernel running long enough for the clock sampler to see it under load
+    if rank == 0:
+        t_end = time.time() + 1.0
+        while time.time() < t_end:
+            for _ in range(50):
+                step()
+            torch.cuda.synchronize()
+    clocks = sampler.stop() if rank == 0 else None
+    barrier(world)
+
+    ms_per_step = total_ms / args.steps
+    value = step_bytes * world / (ms_per_step * 1e-3) / 1e9
+    kernel_ms = statistics.mean(per)
+    peak, peak_kind = measured_peak_gbs()
+    achieved = step_bytes / (kernel_ms * 1e-3) / 1e9
+    roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                "traffic": None, "peak_source": f"of {peak_kind}", "kernel": "interp_kernel<bf16,16B,staged>",
+                "kernel_ms": kernel_ms, "bytes_algorithmic_all_tensors_once": algo_bytes,
+                "bytes_touched_rows": touched_bytes, "achieved_all_tensors_once": algo_bytes / (kernel_ms * 1e-3) / 1e9}
+
+    # ---- end to end through the public API: pinned host inputs -> device -> op -> pinned host output
+    e2e_steps = max(3, min(args.steps, 10))
+    h_src, h_st, h_tt = src.cpu().pin_memory(), st.cpu().pin_memory(), tt.cpu().pin_memory()
+    h_out = torch.empty((B, T, D), dtype=torch.bfloat16).pin_memory()
+
+    def e2e_step():
+        d_out = robocache.resample_trajectories(h_src.to(dev, non_blocking=True), h_st.to(dev, non_blocking=True),
+                                                h_tt.to(dev, non_blocking=True))
+        h_out.copy_(d_out, non_blocking=True)
+
+    e2e_ms, _ = timed_region(e2e_step, e2e_steps, 2, world, dev)
+    e2e_val = step_bytes * world / (e2e_ms / e2e_steps * 1e-3) / 1e9
+    h2d = h_src.numel() * 2 + h_st.numel() * 4 + h_tt.numel() * 4
+    d2h = h_out.numel() * 2
+    ok = torch.equal(h_out.view(torch.int16), out.cpu().view(torch.int16))
+    e2e = {"value": e2e_val, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps,
+           "ms_per_step": e2e_ms / e2e_steps, "matches_device_run": bool(ok)}
+    del h_src, h_out
+
+    cpu_baseline = None
+    extras = {}
+    if rank == 0:
+        cpu_baseline = cpu_baseline_leg(world)
+    if not args.no_extras:
+        try:
+            extras = run_extras(L, dev, local, rank, world, peak)
+        except Exception as e:  # the headline line must survive a failing side measurement
+            extras = {"error": repr(e)}
+    barrier(world)
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic",
+            "config": {"workload": "resample bf16 B=4096 S=500 D=256 T=250 sorted-uniform targets, per GPU",
+                       "global_batch": B * world, "parallelism": f"batch-shard x{world}, no collective",
+                       "l2": "inputs (1.06 GB) and output (0.52 GB) exceed the 126 MB L2; no flush needed",
+                       "bytes_per_step_per_gpu": step_bytes, "bytes_convention": "min(all tensors once, touched rows + times + output)"},
+            "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e, "gpu_launches": args.steps, "clocks": clocks,
+            "extras": extras,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        import torch.distributed as dist
+        dist.destroy_process_group()
+
+
+def cpu_baseline_leg(world: int):
+    """Oracle port on the host cores, bounded sample (rank 0, N=1 only)."""
+    if world != 1:
+        return None
+    import oracle
+    from robogoat_b200 import workloads
+    threads = oracle.max_threads()
+    B_s = 512
+    src, st, tt = workloads.resample_inputs(B=B_s, dtype=torch.bfloat16, irregular_targets=True, seed=0,
+                                            S=HEADLINE["S"], D=HEADLINE["D"], T=HEADLINE["T"])
+    left, right, _ = oracle.brackets(st, tt)
+    nbytes = min(workloads.resample_bytes(B_s, HEADLINE["S"], HEADLINE["T"], HEADLINE["D"], 2),
+                 workloads.resample_touched_bytes(left, right, HEADLINE["S"], HEADLINE["D"], 2))
+    oracle.resample_trajectories(src, st, tt, threads=threads)
+    reps, t0 = 0, time.perf_counter()
+    while time.perf_counter() - t0 < 10.0 and reps < 200:
+        oracle.resample_trajectories(src, st, tt, threads=threads)
+        reps += 1
+    dt = (time.perf_counter() - t0) / reps
+    return {"value": nbytes / dt / 1e9, "unit": UNIT, "cores": threads, "kind": "port",
+            "sample": f"B={B_s} rows of the headline batch, {reps} passes (~10 s), oracle port with OpenMP over rows",
+            "host_cores": os.cpu_count()}
+
+
+def run_extras(L, dev, local, rank, world, peak):
+    """Fusion and voxelisation figures for the other headline configurations (device-resident inputs)."""
+    from robogoat_b200 import _lib, ops, workloads
+    import robocache
+    ex = {}
+    flush = L2Flush(dev)
+
+    # fusion throughput, B=16384 per GPU, bf16
+    Bf = 16384
+    a = workloads.fusion_inputs(B=Bf, dtype=torch.bfloat16, seed=rank, device=dev)
+    fb = workloads.fusion_bytes(Bf, 50, 2)
+    f = lambda: ops.fuse_multimodal_cuda(*a)
+    for _ in range(5):
+        f()
+    barrier(world)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    iters = 50
+    e0.record()
+    for _ in range(iters):
+        f()
+    e1.record(); torch.cuda.synchronize()
+    ms = max_over_ranks(e0.elapsed_time(e1) / iters, world, dev)
+    ex["fusion_bf16_B16384"] = {"ms": ms, "GB/s": fb * world / (ms * 1e-3) / 1e9, "frac_of_hbm_peak": fb / (ms * 1e-3) / 1e9 / peak,
+                                "bytes_per_gpu": fb, "timing": "50 back-to-back calls incl. output allocation, inputs 0.8 GB > L2"}
+    del a
+    # fusion latency, B=4
+    a4 = workloads.fusion_inputs(B=4, dtype=torch.bfloat16, seed=rank, device=dev)
+    med, mean = time_cold(lambda: ops.fuse_multimodal_cuda(*a4), 200, 20, flush)
+    ex["fusion_bf16_B4_latency_us"] = {"median": med * 1e3, "mean": mean * 1e3, "timing": "per-call events, L2 flushed before each call"}
+
+    # voxel occupancy, 500k points, 128^3
+    pts = workloads.voxel_uniform_inputs(500_000, seed=rank, device=dev)
+    kw = workloads.VOXEL_OCCUPANCY_GEOMETRY
+    med, mean = time_cold(lambda: robocache.voxelize_pointcloud(pts, mode="occupancy", **kw), 200, 20, flush)
+    ex["voxel_occupancy_500k_128"] = {"median_us": med * 1e3, "Gpts/s": 500_000 / (med * 1e-3) / 1e9,
+                                      "timing": "per-call events incl. grid allocation and zero-fill, L2 flushed before each call"}
+    del pts
+
+    # voxel count + mean at scale: N = 2^26 points per GPU, 512^3, F=4
+    N = 1 << 26
+    pts, feats = workloads.voxel_mixture_inputs(N, seed=rank, device=dev)
+    kw = workloads.VOXEL_MIXTURE_GEOMETRY
+    for mode in ("count", "mean"):
+        fn = (lambda: robocache.voxelize_pointcloud(pts, feats if mode == "mean" else None, mode=mode, **kw))
+        for _ in range(3):
+            r = fn(); del r
+        barrier(world)
+        iters = 10
+        e0.record()
+        for _ in range(iters):
+            r = fn(); del r
+        e1.record(); torch.cuda.synchronize()
+        ms = max_over_ranks(e0.elapsed_time(e1) / iters, world, dev)
+        ex[f"voxel_{mode}_64M_512"] = {"ms": ms, "Gpts/s_per_gpu": N / (ms * 1e-3) / 1e9,
+                                       "timing": "10 back-to-back calls incl. zero-fill (and normalise for mean); working set > L2"}
+    if world > 1:
+        from robogoat_b200 import sharding
+        fn = lambda: sharding.voxelize_sharded(pts, feats, mode="mean", **kw)
+        for _ in range(2):
+            r = fn(); del r
+        barrier(world)
+        e0.record()
+        for _ in range(5):
+            r = fn(); del r
+        e1.record(); torch.cuda.synchronize()
+        ms = max_over_ranks(e0.elapsed_time(e1) / 5, world, dev)
+        ex["voxel_mean_sharded_with_grid_reduce"] = {"ms": ms, "Gpts/s_total": N * world / (ms * 1e-3) / 1e9,
+                                                     "note": "point shards + NCCL sum of partial grids + slab normalise"}
+    return ex
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-extras", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,133 @@
+/*
+ * robocache_b200.h — C ABI of the B200 (sm_100a) preprocessing library.
+ *
+ * One shared object, plain pointers and sizes, no torch types.  Each entry point names
+ * the reference interface it replaces (paths are relative to the reference project).
+ *
+ * Conventions
+ *   - All data pointers are DEVICE pointers on `device`, unless a name ends in _host.
+ *   - `stream` is a cudaStream_t passed as void* (NULL = the legacy default stream).
+ *     Calls only enqueue work; they never synchronise and never allocate.
+ *   - Tensors are dense row-major.  Timestamps are fp32.
+ *   - Every function returns an rc_status (0 = ok).  rc_strerror() names a code;
+ *     rc_last_cuda_error() gives the cudaError_t behind RC_ERR_CUDA for this thread.
+ *   - The library is re-entrant and keeps no state between calls.
+ */
+#ifndef ROBOCACHE_B200_H
+#define ROBOCACHE_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define RC_ABI_VERSION 1
+
+/* exported symbols (the library is built with hidden default visibility) */
+#if defined(__GNUC__)
+#define RC_API __attribute__((visibility("default")))
+#else
+#define RC_API
+#endif
+#define RC_MAX_STREAMS 8
+
+typedef enum rc_status {
+    RC_OK = 0,
+    RC_ERR_NULL_POINTER = 1,   /* a required pointer is NULL */
+    RC_ERR_BAD_SHAPE = 2,      /* negative size, S == 0 with T > 0, too many streams, ... */
+    RC_ERR_BAD_DTYPE = 3,      /* dtype is not RC_DTYPE_F32 / RC_DTYPE_BF16 */
+    RC_ERR_BAD_ALIGNMENT = 4,  /* a pointer is not aligned to its element size */
+    RC_ERR_BAD_MODE = 5,       /* unknown voxel mode, or features missing for mean mode */
+    RC_ERR_CUDA = 6,           /* a CUDA runtime call failed; see rc_last_cuda_error() */
+    RC_ERR_TOO_LARGE = 7,      /* a size exceeds what the kernels index (see each call) */
+    RC_ERR_BAD_DEVICE = 8,     /* device index out of range */
+    RC_ERR_BAD_VALUE = 9       /* voxel_size <= 0 or not finite */
+} rc_status;
+
+typedef enum rc_dtype { RC_DTYPE_F32 = 0, RC_DTYPE_BF16 = 1 } rc_dtype;
+
+/* numbering of the reference's VoxelMode, robocache/csrc/cuda/voxelize_kernel.cu:20-25 */
+typedef enum rc_voxel_mode {
+    RC_VOXEL_COUNT = 0,        /* int32 points per voxel */
+    RC_VOXEL_OCCUPANCY = 1,    /* int32 0/1 */
+    RC_VOXEL_MEAN = 2,         /* fp32 [.., F] feature mean + int32 counts */
+    RC_VOXEL_MAX = 3,          /* fp32 [.., F] feature maximum, empty voxels 0 */
+    RC_VOXEL_OCCUPANCY_U8 = 4  /* uint8 0/1 (harness format; payload of the multi-GPU max-reduce) */
+} rc_voxel_mode;
+
+/* flags of rc_voxelize */
+#define RC_VOXEL_ZERO_INIT   1u  /* clear grid (and counts) on `stream` before binning */
+#define RC_VOXEL_NO_NORMALIZE 2u /* mean mode: leave feature SUMS in grid (multi-GPU partials) */
+#define RC_VOXEL_WARP_AGGREGATE 4u /* merge equal voxel ids inside a warp before the atomic */
+
+/* one timestamped feature stream: data [B,S,D] (dtype of the call), times [B,S] fp32 */
+typedef struct rc_stream_desc {
+    const void*  data;
+    const float* times;
+    int64_t      S;
+    int64_t      D;
+} rc_stream_desc;
+
+/*
+ * Timestamp-aligned resampling: out[b,t,:] = lerp of the two source rows that bracket
+ * target_times[b,t] (lower-bound search, clamped at both ends).
+ * Replaces launch_resample_bf16 / launch_resample_fp32
+ * (robocache/csrc/cuda/resample_kernel.cu:127-174) behind
+ * resample_trajectories_cuda (robocache/csrc/cpp/resample_ops.cpp:31-90).
+ * src [B,S,D], source_times [B,S], target_times [B,T], out [B,T,D]; out dtype = dtype.
+ * Limits: S and T below 2^31; S >= 1 when T > 0.
+ */
+RC_API int rc_resample(const void* src, const float* source_times, const float* target_times, void* out,
+                int64_t B, int64_t S, int64_t T, int64_t D, int dtype, int device, void* stream);
+
+/*
+ * N-stream temporal fusion in one launch: every stream is resampled to target_times and
+ * written into its column slice of out [B,T,sum(D_k)] (slice order = stream order).
+ * Replaces multimodal_fusion_cuda (robocache/csrc/cuda/multimodal_kernel.cu:201-251) behind
+ * fuse_multimodal_cuda (robocache/csrc/cpp/multimodal_ops.cpp:28-119); n_streams = 3 there.
+ */
+RC_API int rc_fuse(const rc_stream_desc* streams, int n_streams, const float* target_times, void* out,
+            int64_t B, int64_t T, int dtype, int device, void* stream);
+
+/*
+ * Bracket rows and weights only (no feature traffic): left/right int32 [B,T], weight fp32 [B,T].
+ * Plays the role of compute_all_indices
+ * (robocache/kernels/cutlass/trajectory_resample_bulk.cu:37-95); used for the bit-exact
+ * bracket check.  Any of the three outputs may be NULL.
+ */
+RC_API int rc_resample_brackets(const float* source_times, const float* target_times, int64_t B, int64_t S,
+                         int64_t T, int32_t* left, int32_t* right, float* weight, int device,
+                         void* stream);
+
+/*
+ * Point-cloud voxelisation.  points [N,3] fp32, features [N,F] fp32 (mean / max modes).
+ * A point is binned at floor((p - grid_min) / voxel_size) per axis (fp32, IEEE) and dropped
+ * if any axis falls outside the grid; flat voxel id = vz*gx*gy + vy*gx + vx.
+ *   grid   : int32 [gx*gy*gz] (count, occupancy), uint8 (occupancy_u8), fp32 [gx*gy*gz*F] (mean, max)
+ *   counts : int32 [gx*gy*gz], required for mean mode, ignored otherwise
+ * Replaces voxelize_cuda (robocache/csrc/cuda/voxelize_kernel.cu:210-277) behind
+ * voxelize_pointcloud_cuda (robocache/csrc/cpp/voxelize_ops.cpp:31-133).
+ * Limits: gx*gy*gz*max(F,1) below 2^40; each grid extent below 2^24.
+ */
+RC_API int rc_voxelize(const float* points, const float* features, void* grid, int32_t* counts, int64_t N,
+                int32_t F, const float grid_min_host[3], float voxel_size,
+                const int32_t grid_size_host[3], int mode, uint32_t flags, int device, void* stream);
+
+/*
+ * Second pass of mean mode on voxels [voxel_begin, voxel_end): grid[v,:] *= 1.0f / counts[v]
+ * where counts[v] > 0.  Replaces normalize_mean_kernel
+ * (robocache/csrc/cuda/voxelize_kernel.cu:145-163); the range lets each rank of the
+ * multi-GPU harness normalise only its own slab after the partial grids are reduced.
+ */
+RC_API int rc_voxel_normalize(float* grid, const int32_t* counts, int64_t voxel_begin, int64_t voxel_end,
+                       int32_t F, int device, void* stream);
+
+RC_API const char* rc_strerror(int status);
+RC_API int rc_last_cuda_error(void);
+RC_API int rc_abi_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ROBOCACHE_B200_H */

@@ -1,0 +1,95 @@
+"""ctypes binding of ``librobocache_b200.so`` (declared in ``include/robocache_b200.h``).
+
+Loading is explicit and loud: a missing library raises, nothing falls back to a CPU or
+torch implementation.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import threading
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG, "lib", "librobocache_b200.so")
+
+RC_OK = 0
+RC_DTYPE_F32 = 0
+RC_DTYPE_BF16 = 1
+RC_MAX_STREAMS = 8
+
+VOXEL_COUNT = 0
+VOXEL_OCCUPANCY = 1
+VOXEL_MEAN = 2
+VOXEL_MAX = 3
+VOXEL_OCCUPANCY_U8 = 4
+
+VOXEL_ZERO_INIT = 1
+VOXEL_NO_NORMALIZE = 2
+VOXEL_WARP_AGGREGATE = 4
+
+# every symbol the header declares; the CPU test-suite checks the built library exports them all
+EXPORTED_SYMBOLS = (
+    "rc_resample", "rc_fuse", "rc_resample_brackets", "rc_voxelize", "rc_voxel_normalize",
+    "rc_strerror", "rc_last_cuda_error", "rc_abi_version",
+)
+
+
+class StreamDesc(ctypes.Structure):
+    _fields_ = [("data", ctypes.c_void_p), ("times", ctypes.c_void_p),
+                ("S", ctypes.c_int64), ("D", ctypes.c_int64)]
+
+
+class LibraryNotBuilt(RuntimeError):
+    pass
+
+
+_lock = threading.Lock()
+_lib = None
+
+
+def _declare(L: ctypes.CDLL) -> None:
+    vp, i64, i32, ci, f32, u32 = (ctypes.c_void_p, ctypes.c_int64, ctypes.c_int32, ctypes.c_int,
+                                  ctypes.c_float, ctypes.c_uint32)
+    L.rc_resample.argtypes = [vp, vp, vp, vp, i64, i64, i64, i64, ci, ci, vp]
+    L.rc_fuse.argtypes = [ctypes.POINTER(StreamDesc), ci, vp, vp, i64, i64, ci, ci, vp]
+    L.rc_resample_brackets.argtypes = [vp, vp, i64, i64, i64, vp, vp, vp, ci, vp]
+    L.rc_voxelize.argtypes = [vp, vp, vp, vp, i64, i32, ctypes.POINTER(f32), f32,
+                              ctypes.POINTER(i32), ci, u32, ci, vp]
+    L.rc_voxel_normalize.argtypes = [vp, vp, i64, i64, i32, ci, vp]
+    for name in ("rc_resample", "rc_fuse", "rc_resample_brackets", "rc_voxelize", "rc_voxel_normalize",
+                 "rc_last_cuda_error", "rc_abi_version"):
+        getattr(L, name).restype = ci
+    L.rc_strerror.argtypes = [ci]
+    L.rc_strerror.restype = ctypes.c_char_p
+
+
+def load() -> ctypes.CDLL:
+    """The CUDA library, loaded once.  Raises LibraryNotBuilt if it has not been compiled."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    with _lock:
+        if _lib is None:
+            if not os.path.exists(LIB_PATH):
+                raise LibraryNotBuilt(
+                    f"RoboCache CUDA kernels not available: {LIB_PATH} is missing. "
+                    "Build it with `python -m robogoat_b200.build`; there is no CPU fallback.")
+            L = ctypes.CDLL(LIB_PATH)
+            _declare(L)
+            _lib = L
+    return _lib
+
+
+def is_built() -> bool:
+    return os.path.exists(LIB_PATH)
+
+
+def check(status: int, what: str) -> None:
+    """Turn a non-zero rc_status into the exception the reference's bindings would raise."""
+    if status == RC_OK:
+        return
+    L = load()
+    msg = L.rc_strerror(status).decode()
+    if status == 6:
+        msg += f" (cudaError {L.rc_last_cuda_error()})"
+    raise RuntimeError(f"{what}: {msg}")

@@ -1,0 +1,50 @@
+// Status strings, ABI version and the per-device SM-count cache.
+#include "rc_common.cuh"
+
+#include <atomic>
+
+namespace rc {
+
+thread_local int g_last_cuda_error = 0;
+
+// SM count per device, filled on first use (immutable hardware facts, not call state).
+static std::atomic<int> g_sm_count[64];
+
+int sm_count(int device) {
+    if (device < 0 || device >= 64) return 148;
+    int v = g_sm_count[device].load(std::memory_order_relaxed);
+    if (v > 0) return v;
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || n <= 0) {
+        cudaGetLastError();
+        n = 148;
+    }
+    g_sm_count[device].store(n, std::memory_order_relaxed);
+    return n;
+}
+
+}  // namespace rc
+
+extern "C" {
+
+const char* rc_strerror(int status) {
+    switch (status) {
+        case RC_OK: return "ok";
+        case RC_ERR_NULL_POINTER: return "a required pointer is NULL";
+        case RC_ERR_BAD_SHAPE: return "bad shape";
+        case RC_ERR_BAD_DTYPE: return "Unsupported dtype. Use float32 or bfloat16.";
+        case RC_ERR_BAD_ALIGNMENT: return "pointer is not aligned to its element size";
+        case RC_ERR_BAD_MODE: return "invalid voxel mode or missing features";
+        case RC_ERR_CUDA: return "CUDA runtime error";
+        case RC_ERR_TOO_LARGE: return "size exceeds the supported range";
+        case RC_ERR_BAD_DEVICE: return "device index out of range";
+        case RC_ERR_BAD_VALUE: return "voxel_size must be positive";
+        default: return "unknown status";
+    }
+}
+
+int rc_last_cuda_error(void) { return rc::g_last_cuda_error; }
+
+int rc_abi_version(void) { return RC_ABI_VERSION; }
+
+}  // extern "C"

@@ -1,0 +1,333 @@
+// Point-cloud voxelisation for sm_100a: sort-free binning (pass 1) and mean normalisation
+// (pass 2).
+//
+// Pass 1.  A warp takes 128 consecutive points.  Their packed xyz (1536 contiguous bytes)
+// is fetched with three fully coalesced 16-byte loads per lane, parked in the warp's slice
+// of shared memory and read back as point (i*32 + lane), i = 0..3 — a stride of three
+// words, which is bank-conflict free — so that every later access of the warp (feature
+// rows, atomics) is issued for 32 consecutive points.  The voxel id follows the
+// reference's arithmetic exactly, in IEEE fp32:
+//   v = floor((p - grid_min) / voxel_size) per axis, dropped unless 0 <= v < g on every axis,
+//   id = vz*gx*gy + vy*gx + vx
+//   (robocache/csrc/cuda/voxelize_kernel.cu:43-61, robocache/validation/cpu_reference.hpp:151-174)
+// Scatter: count -> one reduction (no return value) per point or per group of equal ids in
+// the warp; occupancy -> a plain store of 1 (every writer stores the same value, no atomic
+// needed); mean -> one 16-byte vector reduction per 4 feature channels plus the count.
+//
+// Pass 2 reads the count plane four voxels per thread and scales the feature sums of
+// occupied voxels by 1.0f / count (robocache/csrc/cuda/voxelize_kernel.cu:145-163).
+#include "rc_common.cuh"
+
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kPointsPerLane = 4;
+constexpr int kPointsPerWarp = 32 * kPointsPerLane;            // 128
+constexpr int kPointsPerBlock = kThreads * kPointsPerLane;     // 1024
+
+struct VoxelGeom {
+    float minx, miny, minz, vs;
+    int gx, gy, gz;
+    float fgx, fgy, fgz;
+};
+
+// flat voxel id, or -1 for a dropped point (NaN and infinities fail the range test)
+__device__ __forceinline__ long long voxel_id(float x, float y, float z, const VoxelGeom& g) {
+    const float fx = floorf(__fdiv_rn(__fsub_rn(x, g.minx), g.vs));
+    const float fy = floorf(__fdiv_rn(__fsub_rn(y, g.miny), g.vs));
+    const float fz = floorf(__fdiv_rn(__fsub_rn(z, g.minz), g.vs));
+    const bool in = (fx >= 0.0f) && (fx < g.fgx) && (fy >= 0.0f) && (fy < g.fgy) && (fz >= 0.0f) && (fz < g.fgz);
+    if (!in) return -1;
+    return (static_cast<long long>(fz) * g.gy + static_cast<long long>(fy)) * g.gx + static_cast<long long>(fx);
+}
+
+__device__ __forceinline__ void red_add_v4(float* addr, float4 v) {
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};"
+                 :: "l"(addr), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+}
+__device__ __forceinline__ void red_add_v2(float* addr, float2 v) {
+    asm volatile("red.global.add.v2.f32 [%0], {%1, %2};" :: "l"(addr), "f"(v.x), "f"(v.y) : "memory");
+}
+
+// ordered-integer image of a float: larger float <=> larger signed int
+__device__ __forceinline__ int float_ordered(float f) {
+    const int i = __float_as_int(f);
+    return (i >= 0) ? i : (i ^ 0x7fffffff);
+}
+
+enum : int { kCount = 0, kOccupancy = 1, kMean = 2, kMax = 3, kOccupancyU8 = 4 };
+
+// Loads the xyz of the warp's 128-point tile starting at `base` into registers:
+// point i of the lane is (base + i*32 + lane).  ALIGNED: the tile is full and 16-byte aligned.
+__device__ __forceinline__ void load_tile(const float* __restrict__ pts, long long base, long long N,
+                                          bool full_aligned, float* s_warp, int lane,
+                                          float (&x)[kPointsPerLane], float (&y)[kPointsPerLane],
+                                          float (&z)[kPointsPerLane]) {
+    if (full_aligned) {
+        const float4* src = reinterpret_cast<const float4*>(pts + base * 3);
+        float4* dst = reinterpret_cast<float4*>(s_warp);
+#pragma unroll
+        for (int k = 0; k < 3; ++k) dst[k * 32 + lane] = __ldcs(src + k * 32 + lane);
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < kPointsPerLane; ++i) {
+            const float* q = s_warp + (i * 32 + lane) * 3;
+            x[i] = q[0]; y[i] = q[1]; z[i] = q[2];
+        }
+        __syncwarp();
+    } else {
+#pragma unroll
+        for (int i = 0; i < kPointsPerLane; ++i) {
+            const long long pi = base + i * 32 + lane;
+            if (pi < N) {
+                x[i] = __ldg(pts + pi * 3 + 0);
+                y[i] = __ldg(pts + pi * 3 + 1);
+                z[i] = __ldg(pts + pi * 3 + 2);
+            } else {
+                x[i] = y[i] = z[i] = __int_as_float(0x7fc00000);  // NaN: dropped
+            }
+        }
+    }
+}
+
+template <int MODE, bool AGG>
+__global__ void __launch_bounds__(kThreads)
+voxel_bin_kernel(const float* __restrict__ pts, const float* __restrict__ feats, void* __restrict__ grid_v,
+                 int* __restrict__ counts, long long N, int F, VoxelGeom g, bool pts_aligned) {
+    __shared__ __align__(16) float s_xyz[kThreads / 32][kPointsPerWarp * 3];
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    const long long base = (static_cast<long long>(blockIdx.x) * (kThreads / 32) + warp) * kPointsPerWarp;
+    if (base >= N) return;
+
+    float x[kPointsPerLane], y[kPointsPerLane], z[kPointsPerLane];
+    load_tile(pts, base, N, pts_aligned && (base + kPointsPerWarp <= N), s_xyz[warp], lane, x, y, z);
+
+    long long id[kPointsPerLane];
+#pragma unroll
+    for (int i = 0; i < kPointsPerLane; ++i) id[i] = voxel_id(x[i], y[i], z[i], g);
+
+    if (MODE == kOccupancy) {
+        int* grid = static_cast<int*>(grid_v);
+#pragma unroll
+        for (int i = 0; i < kPointsPerLane; ++i)
+            if (id[i] >= 0) grid[id[i]] = 1;
+    } else if (MODE == kOccupancyU8) {
+        unsigned char* grid = static_cast<unsigned char*>(grid_v);
+#pragma unroll
+        for (int i = 0; i < kPointsPerLane; ++i)
+            if (id[i] >= 0) grid[id[i]] = 1;
+    } else if (MODE == kCount) {
+        int* grid = static_cast<int*>(grid_v);
+#pragma unroll
+        for (int i = 0; i < kPointsPerLane; ++i) {
+            if (AGG) {
+                // lanes holding the same voxel elect their lowest lane to add the group size
+                const unsigned int peers = __match_any_sync(0xffffffffu, id[i]);
+                if (id[i] >= 0 && lane == (__ffs(peers) - 1)) atomicAdd(grid + id[i], __popc(peers));
+            } else {
+                if (id[i] >= 0) atomicAdd(grid + id[i], 1);
+            }
+        }
+    } else if (MODE == kMean) {
+        float* grid = static_cast<float*>(grid_v);
+#pragma unroll
+        for (int i = 0; i < kPointsPerLane; ++i) {
+            const long long pi = base + i * 32 + lane;
+            if (id[i] < 0) continue;
+            const float* f = feats + pi * F;
+            float* o = grid + id[i] * F;
+            if ((F & 3) == 0) {
+                for (int c = 0; c < F; c += 4) red_add_v4(o + c, __ldcs(reinterpret_cast<const float4*>(f + c)));
+            } else if ((F & 1) == 0) {
+                for (int c = 0; c < F; c += 2) red_add_v2(o + c, __ldcs(reinterpret_cast<const float2*>(f + c)));
+            } else {
+                for (int c = 0; c < F; ++c) atomicAdd(o + c, __ldg(f + c));
+            }
+            atomicAdd(counts + id[i], 1);
+        }
+    } else {  // kMax: running maximum kept as an ordered integer, decoded by the fix-up pass
+        int* grid = static_cast<int*>(grid_v);
+#pragma unroll
+        for (int i = 0; i < kPointsPerLane; ++i) {
+            const long long pi = base + i * 32 + lane;
+            if (id[i] < 0) continue;
+            for (int c = 0; c < F; ++c) atomicMax(grid + id[i] * F + c, float_ordered(__ldg(feats + pi * F + c)));
+        }
+    }
+}
+
+// mean pass 2, wide form: four voxels per thread; counts + v0 is 16-byte aligned, (v1 - v0) % 4 == 0
+template <bool VEC4>
+__global__ void __launch_bounds__(kThreads)
+voxel_normalize_wide_kernel(float* __restrict__ grid, const int* __restrict__ counts, long long v0, long long v1, int F) {
+    const long long v = v0 + (blockIdx.x * static_cast<long long>(kThreads) + threadIdx.x) * 4;
+    if (v >= v1) return;
+    const int4 c = __ldcs(reinterpret_cast<const int4*>(counts + v));
+    const int cc[4] = {c.x, c.y, c.z, c.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        if (cc[k] <= 0) continue;  // empty voxels stay exactly 0
+        const float inv = __fdiv_rn(1.0f, static_cast<float>(cc[k]));
+        float* o = grid + (v + k) * F;
+        if (VEC4) {
+            for (int f = 0; f < F; f += 4) {
+                float4 s = *reinterpret_cast<float4*>(o + f);
+                s.x = __fmul_rn(s.x, inv); s.y = __fmul_rn(s.y, inv);
+                s.z = __fmul_rn(s.z, inv); s.w = __fmul_rn(s.w, inv);
+                *reinterpret_cast<float4*>(o + f) = s;
+            }
+        } else {
+            for (int f = 0; f < F; ++f) o[f] = __fmul_rn(o[f], inv);
+        }
+    }
+}
+
+// mean pass 2, one voxel per thread: ragged ends of a range and unaligned buffers
+__global__ void __launch_bounds__(kThreads)
+voxel_normalize_scalar_kernel(float* __restrict__ grid, const int* __restrict__ counts, long long v0, long long v1, int F) {
+    const long long v = v0 + blockIdx.x * static_cast<long long>(kThreads) + threadIdx.x;
+    if (v >= v1) return;
+    const int c = counts[v];
+    if (c <= 0) return;
+    const float inv = __fdiv_rn(1.0f, static_cast<float>(c));
+    for (int f = 0; f < F; ++f) grid[v * F + f] = __fmul_rn(grid[v * F + f], inv);
+}
+
+// max mode set-up and fix-up: the grid holds ordered integers while points are binned
+constexpr int kMaxEmpty = static_cast<int>(0x80000000u);
+__global__ void __launch_bounds__(kThreads) voxel_max_fill_kernel(int* __restrict__ grid, long long n) {
+    for (long long i = blockIdx.x * static_cast<long long>(kThreads) + threadIdx.x; i < n;
+         i += static_cast<long long>(gridDim.x) * kThreads)
+        grid[i] = kMaxEmpty;
+}
+__global__ void __launch_bounds__(kThreads) voxel_max_decode_kernel(int* __restrict__ grid, long long n) {
+    for (long long i = blockIdx.x * static_cast<long long>(kThreads) + threadIdx.x; i < n;
+         i += static_cast<long long>(gridDim.x) * kThreads) {
+        const int o = grid[i];
+        grid[i] = (o == kMaxEmpty) ? 0 : ((o >= 0) ? o : (o ^ 0x7fffffff));  // empty voxel -> 0.0f
+    }
+}
+
+template <int MODE>
+void launch_bin(bool agg, unsigned int blocks, cudaStream_t st, const float* pts, const float* feats, void* grid,
+                int* counts, long long N, int F, const VoxelGeom& g, bool aligned) {
+    if (agg) voxel_bin_kernel<MODE, true><<<blocks, kThreads, 0, st>>>(pts, feats, grid, counts, N, F, g, aligned);
+    else     voxel_bin_kernel<MODE, false><<<blocks, kThreads, 0, st>>>(pts, feats, grid, counts, N, F, g, aligned);
+}
+
+}  // namespace
+
+extern "C" {
+
+int rc_voxel_normalize(float* grid, const int32_t* counts, int64_t voxel_begin, int64_t voxel_end,
+                       int32_t F, int device, void* stream) {
+    if (voxel_begin < 0 || voxel_end < voxel_begin || F < 0) return RC_ERR_BAD_SHAPE;
+    if (voxel_end == voxel_begin || F == 0) return RC_OK;
+    if (grid == nullptr || counts == nullptr) return RC_ERR_NULL_POINTER;
+    if (!rc::aligned_to(grid, 4) || !rc::aligned_to(counts, 4)) return RC_ERR_BAD_ALIGNMENT;
+    rc::DeviceScope scope(device);
+    if (scope.status() != RC_OK) return scope.status();
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    // [voxel_begin, head) and [body_end, voxel_end) go voxel by voxel; the body, whose count
+    // pointer is 16-byte aligned and whose length is a multiple of four, goes four per thread
+    long long head = voxel_begin;
+    while (head < voxel_end && !rc::aligned_to(counts + head, 16)) ++head;
+    const long long body_end = head + ((voxel_end - head) & ~3ll);
+    auto scalar = [&](long long a, long long b) {
+        if (b > a) {
+            const long long blocks = (b - a + kThreads - 1) / kThreads;
+            voxel_normalize_scalar_kernel<<<static_cast<unsigned int>(blocks), kThreads, 0, st>>>(grid, counts, a, b, F);
+        }
+    };
+    if ((voxel_end - voxel_begin + kThreads - 1) / kThreads >= (1ll << 31)) return RC_ERR_TOO_LARGE;
+    scalar(voxel_begin, head);
+    if (body_end > head) {
+        const long long blocks = ((body_end - head) / 4 + kThreads - 1) / kThreads;
+        const unsigned int nb = static_cast<unsigned int>(blocks);
+        if ((F & 3) == 0 && rc::aligned_to(grid, 16))
+            voxel_normalize_wide_kernel<true><<<nb, kThreads, 0, st>>>(grid, counts, head, body_end, F);
+        else
+            voxel_normalize_wide_kernel<false><<<nb, kThreads, 0, st>>>(grid, counts, head, body_end, F);
+    }
+    scalar(body_end, voxel_end);
+    return rc::check_launch();
+}
+
+int rc_voxelize(const float* points, const float* features, void* grid, int32_t* counts, int64_t N,
+                int32_t F, const float grid_min_host[3], float voxel_size,
+                const int32_t grid_size_host[3], int mode, uint32_t flags, int device, void* stream) {
+    if (mode < RC_VOXEL_COUNT || mode > RC_VOXEL_OCCUPANCY_U8) return RC_ERR_BAD_MODE;
+    if (grid_min_host == nullptr || grid_size_host == nullptr || grid == nullptr) return RC_ERR_NULL_POINTER;
+    if (N < 0 || F < 0) return RC_ERR_BAD_SHAPE;
+    if (!(voxel_size > 0.0f) || !(voxel_size <= 3.0e38f)) return RC_ERR_BAD_VALUE;
+    const bool feat_mode = (mode == RC_VOXEL_MEAN || mode == RC_VOXEL_MAX);
+    VoxelGeom g;
+    g.minx = grid_min_host[0]; g.miny = grid_min_host[1]; g.minz = grid_min_host[2];
+    g.vs = voxel_size;
+    g.gx = grid_size_host[0]; g.gy = grid_size_host[1]; g.gz = grid_size_host[2];
+    if (g.gx < 0 || g.gy < 0 || g.gz < 0) return RC_ERR_BAD_SHAPE;
+    if (g.gx >= (1 << 24) || g.gy >= (1 << 24) || g.gz >= (1 << 24)) return RC_ERR_TOO_LARGE;
+    g.fgx = static_cast<float>(g.gx); g.fgy = static_cast<float>(g.gy); g.fgz = static_cast<float>(g.gz);
+    const long long V = static_cast<long long>(g.gx) * g.gy * g.gz;  // < 2^72 impossible: each < 2^24 -> check below
+    if (static_cast<double>(g.gx) * g.gy * g.gz * (feat_mode ? (F > 0 ? F : 1) : 1) >= 1099511627776.0)
+        return RC_ERR_TOO_LARGE;
+    if (feat_mode && N > 0 && F > 0 && features == nullptr) return RC_ERR_BAD_MODE;
+    if (mode == RC_VOXEL_MEAN && counts == nullptr) return RC_ERR_NULL_POINTER;
+    if (N > 0 && points == nullptr) return RC_ERR_NULL_POINTER;
+    if (!rc::aligned_to(points, 4) || !rc::aligned_to(features, 4) || !rc::aligned_to(counts, 4))
+        return RC_ERR_BAD_ALIGNMENT;
+    if (mode != RC_VOXEL_OCCUPANCY_U8 && !rc::aligned_to(grid, 4)) return RC_ERR_BAD_ALIGNMENT;
+
+    rc::DeviceScope scope(device);
+    if (scope.status() != RC_OK) return scope.status();
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+
+    const long long cells = feat_mode ? V * F : V;
+    const size_t cell_bytes = (mode == RC_VOXEL_OCCUPANCY_U8) ? 1 : 4;
+    const long long fill_blocks_ll = (cells + kThreads - 1) / kThreads;
+    const unsigned int fill_blocks =
+        static_cast<unsigned int>(fill_blocks_ll < 64ll * rc::sm_count(device) ? (fill_blocks_ll > 0 ? fill_blocks_ll : 1)
+                                                                           : 64ll * rc::sm_count(device));
+    if (mode == RC_VOXEL_MAX) {
+        // max mode always starts from "empty": the caller's buffer content is never an operand
+        if (cells > 0) voxel_max_fill_kernel<<<fill_blocks, kThreads, 0, st>>>(static_cast<int*>(grid), cells);
+    } else if (flags & RC_VOXEL_ZERO_INIT) {
+        if (cells > 0) RC_CUDA_TRY(cudaMemsetAsync(grid, 0, static_cast<size_t>(cells) * cell_bytes, st));
+        if (mode == RC_VOXEL_MEAN && V > 0) RC_CUDA_TRY(cudaMemsetAsync(counts, 0, static_cast<size_t>(V) * 4, st));
+    }
+
+    if (N > 0 && V > 0 && !(feat_mode && F == 0)) {
+        const long long blocks = (N + kPointsPerBlock - 1) / kPointsPerBlock;
+        if (blocks >= (1ll << 31)) return RC_ERR_TOO_LARGE;
+        const unsigned int nb = static_cast<unsigned int>(blocks);
+        const bool aligned = rc::aligned_to(points, 16);
+        const bool agg = (flags & RC_VOXEL_WARP_AGGREGATE) != 0;
+        // vector feature accesses need the feature rows and grid cells aligned to their width
+        int Fk = F;
+        if (feat_mode) {
+            const bool a16 = rc::aligned_to(features, 16) && rc::aligned_to(grid, 16);
+            const bool a8 = rc::aligned_to(features, 8) && rc::aligned_to(grid, 8);
+            if ((F & 3) == 0 && !a16) return RC_ERR_BAD_ALIGNMENT;
+            if ((F & 3) != 0 && (F & 1) == 0 && !a8) return RC_ERR_BAD_ALIGNMENT;
+        }
+        switch (mode) {
+            case RC_VOXEL_COUNT: launch_bin<kCount>(agg, nb, st, points, features, grid, counts, N, Fk, g, aligned); break;
+            case RC_VOXEL_OCCUPANCY: launch_bin<kOccupancy>(false, nb, st, points, features, grid, counts, N, Fk, g, aligned); break;
+            case RC_VOXEL_OCCUPANCY_U8: launch_bin<kOccupancyU8>(false, nb, st, points, features, grid, counts, N, Fk, g, aligned); break;
+            case RC_VOXEL_MEAN: launch_bin<kMean>(false, nb, st, points, features, grid, counts, N, Fk, g, aligned); break;
+            default: launch_bin<kMax>(false, nb, st, points, features, grid, counts, N, Fk, g, aligned); break;
+        }
+    }
+    if (mode == RC_VOXEL_MAX && cells > 0) {
+        voxel_max_decode_kernel<<<fill_blocks, kThreads, 0, st>>>(static_cast<int*>(grid), cells);
+    }
+    int rc_launch = rc::check_launch();
+    if (rc_launch != RC_OK) return rc_launch;
+    if (mode == RC_VOXEL_MEAN && !(flags & RC_VOXEL_NO_NORMALIZE) && V > 0 && F > 0) {
+        return rc_voxel_normalize(static_cast<float*>(grid), counts, 0, V, F, device, stream);
+    }
+    return RC_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,227 @@
+"""Binding layer: validates torch tensors, allocates outputs and calls the C ABI.
+
+These three functions mirror the reference's pybind11 entry points, with the same
+checks and error texts:
+
+* ``resample_trajectories_cuda``  — robocache/csrc/cpp/resample_ops.cpp:31-90
+* ``fuse_multimodal_cuda``        — robocache/csrc/cpp/multimodal_ops.cpp:28-119
+* ``voxelize_pointcloud_cuda``    — robocache/csrc/cpp/voxelize_ops.cpp:31-133
+
+Outputs are allocated here with torch (device memory and streams are torch's job); the
+kernels run on torch's current stream of the tensors' device.  There is no CPU path.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import List, Optional, Sequence
+
+import torch
+
+from . import _lib
+
+_MODES = {"count": _lib.VOXEL_COUNT, "occupancy": _lib.VOXEL_OCCUPANCY, "mean": _lib.VOXEL_MEAN,
+          "max": _lib.VOXEL_MAX}
+
+
+def _check(cond: bool, msg: str) -> None:
+    if not cond:
+        raise RuntimeError(msg)
+
+
+def _stream_ptr(device: torch.device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _dtype_code(dtype: torch.dtype) -> int:
+    if dtype == torch.bfloat16:
+        return _lib.RC_DTYPE_BF16
+    if dtype == torch.float32:
+        return _lib.RC_DTYPE_F32
+    raise RuntimeError("Unsupported dtype. Use float32 or bfloat16.")
+
+
+def _times(t: torch.Tensor) -> torch.Tensor:
+    return t.to(torch.float32).contiguous()
+
+
+def resample_trajectories_cuda(source_data: torch.Tensor, source_times: torch.Tensor,
+                               target_times: torch.Tensor) -> torch.Tensor:
+    """[B,S,D] x [B,S] x [B,T] -> [B,T,D], dtype of ``source_data`` (fp32 or bf16)."""
+    _check(source_data.is_cuda, "source_data must be CUDA tensor")
+    _check(source_times.is_cuda, "source_times must be CUDA tensor")
+    _check(target_times.is_cuda, "target_times must be CUDA tensor")
+    _check(source_data.dim() == 3, "source_data must be 3D [B, S, D]")
+    _check(source_times.dim() == 2, "source_times must be 2D [B, S]")
+    _check(target_times.dim() == 2, "target_times must be 2D [B, T]")
+    B, S, D = source_data.shape
+    T = target_times.shape[1]
+    _check(source_times.shape[0] == B, "Batch size mismatch")
+    _check(source_times.shape[1] == S, "Source length mismatch")
+    _check(target_times.shape[0] == B, "Batch size mismatch")
+    _check(source_times.device == source_data.device and target_times.device == source_data.device,
+           "all tensors must be on the same CUDA device")
+    code = _dtype_code(source_data.dtype)
+    _check(S >= 1 or T == 0 or B == 0, "source_data must have at least one timestep")
+
+    L = _lib.load()
+    src = source_data.contiguous()
+    st = _times(source_times)
+    tt = _times(target_times)
+    out = torch.empty((B, T, D), dtype=source_data.dtype, device=source_data.device)
+    dev = source_data.device
+    rc = L.rc_resample(src.data_ptr(), st.data_ptr(), tt.data_ptr(), out.data_ptr(), B, S, T, D, code,
+                       dev.index, _stream_ptr(dev))
+    _lib.check(rc, "resample_trajectories")
+    return out
+
+
+def fuse_streams_cuda(datas: Sequence[torch.Tensor], times: Sequence[torch.Tensor],
+                      target_times: torch.Tensor) -> torch.Tensor:
+    """N timestamped streams -> [B,T,sum(D_k)] in one launch (N <= 8)."""
+    n = len(datas)
+    _check(1 <= n <= _lib.RC_MAX_STREAMS and len(times) == n,
+           f"between 1 and {_lib.RC_MAX_STREAMS} streams are supported")
+    for k, d in enumerate(datas, 1):
+        _check(d.is_cuda, f"stream{k}_data must be on CUDA device")
+    for k, d in enumerate(datas, 1):
+        _check(d.dim() == 3, f"stream{k}_data must be 3D [B, S{k}, D{k}]")
+    for k, t in enumerate(times, 1):
+        _check(t.dim() == 2, f"stream{k}_times must be 2D [B, S{k}]")
+    _check(target_times.dim() == 2, "target_times must be 2D [B, T]")
+    B = datas[0].shape[0]
+    for d in datas[1:]:
+        _check(d.shape[0] == B, "Batch size mismatch")
+    for k, (d, t) in enumerate(zip(datas, times), 1):
+        _check(t.shape[1] == d.shape[1], f"stream{k}_times length mismatch")
+        _check(t.shape[0] == B, "Batch size mismatch")
+    _check(target_times.shape[0] == B, "Batch size mismatch")
+    for d in datas[1:]:
+        _check(d.dtype == datas[0].dtype, "Stream dtypes must match")
+    dev = datas[0].device
+    for x in list(datas) + list(times) + [target_times]:
+        _check(x.device == dev, "all tensors must be on the same CUDA device")
+    code = _dtype_code(datas[0].dtype)
+    T = target_times.shape[1]
+    for d in datas:
+        _check(d.shape[1] >= 1 or T == 0 or B == 0, "every stream must have at least one timestep")
+
+    L = _lib.load()
+    datas_c = [d.contiguous() for d in datas]
+    times_c = [_times(t) for t in times]
+    tt = _times(target_times)
+    out = torch.empty((B, T, sum(d.shape[2] for d in datas)), dtype=datas[0].dtype, device=dev)
+    descs = (_lib.StreamDesc * n)()
+    for k in range(n):
+        descs[k].data = datas_c[k].data_ptr()
+        descs[k].times = times_c[k].data_ptr()
+        descs[k].S = datas_c[k].shape[1]
+        descs[k].D = datas_c[k].shape[2]
+    rc = L.rc_fuse(descs, n, tt.data_ptr(), out.data_ptr(), B, T, code, dev.index, _stream_ptr(dev))
+    _lib.check(rc, "fuse_multimodal")
+    return out
+
+
+def fuse_multimodal_cuda(stream1_data, stream1_times, stream2_data, stream2_times, stream3_data,
+                         stream3_times, target_times) -> torch.Tensor:
+    """Three streams -> [B,T,D1+D2+D3]; slices in stream order."""
+    return fuse_streams_cuda([stream1_data, stream2_data, stream3_data],
+                             [stream1_times, stream2_times, stream3_times], target_times)
+
+
+def resample_brackets_cuda(source_times: torch.Tensor, target_times: torch.Tensor):
+    """(left int32, right int32, weight fp32), each [B,T]: the rows and weight the resampler uses."""
+    _check(source_times.is_cuda and target_times.is_cuda, "times must be CUDA tensors")
+    _check(source_times.dim() == 2 and target_times.dim() == 2, "times must be 2D")
+    _check(source_times.shape[0] == target_times.shape[0], "Batch size mismatch")
+    L = _lib.load()
+    st, tt = _times(source_times), _times(target_times)
+    B, S = st.shape
+    T = tt.shape[1]
+    dev = st.device
+    left = torch.empty((B, T), dtype=torch.int32, device=dev)
+    right = torch.empty((B, T), dtype=torch.int32, device=dev)
+    w = torch.empty((B, T), dtype=torch.float32, device=dev)
+    rc = L.rc_resample_brackets(st.data_ptr(), tt.data_ptr(), B, S, T, left.data_ptr(), right.data_ptr(),
+                                w.data_ptr(), dev.index, _stream_ptr(dev))
+    _lib.check(rc, "resample_brackets")
+    return left, right, w
+
+
+def voxelize_pointcloud_cuda(points: torch.Tensor, features: Optional[torch.Tensor], grid_min: Sequence[float],
+                             voxel_size: float, grid_size: Sequence[int], mode: str, *,
+                             normalize: bool = True, warp_aggregate: bool = False,
+                             occupancy_dtype: torch.dtype = torch.int32) -> List[torch.Tensor]:
+    """[N,3] points (+ [N,F] features) -> [grid] or, for mean mode, [grid, counts].
+
+    The grid is a contiguous tensor shaped [gx,gy,gz] (or [gx,gy,gz,F]) whose flat index is
+    vz*gx*gy + vy*gx + vx, as the reference's CUDA kernels lay it out.  ``normalize=False``
+    leaves feature sums in the grid (partial grids of the multi-GPU harness);
+    ``occupancy_dtype=torch.uint8`` selects the compact occupancy plane.
+    """
+    _check(points.is_cuda, "points must be on CUDA device")
+    _check(points.dim() == 2, "points must be 2D [N, 3]")
+    _check(points.shape[1] == 3, "points must have 3 coordinates (x, y, z)")
+    _check(len(grid_min) == 3, "grid_min must have 3 elements [x, y, z]")
+    _check(len(grid_size) == 3, "grid_size must have 3 elements [X, Y, Z]")
+    _check(voxel_size > 0, "voxel_size must be positive")
+    if mode not in _MODES:
+        raise RuntimeError(f"Invalid mode: {mode}. Must be 'count', 'occupancy', 'mean', or 'max'")
+    code = _MODES[mode]
+    N = points.shape[0]
+    gx, gy, gz = (int(v) for v in grid_size)
+    _check(gx >= 0 and gy >= 0 and gz >= 0, "grid_size must be non-negative")
+    dev = points.device
+    F = 0
+    feats = None
+    if mode in ("mean", "max"):
+        # the reference's API layer passes torch.empty(0) when the caller gave no features
+        _check(features is not None and not (features.dim() == 1 and features.numel() == 0),
+               "features required for mean/max modes")
+        _check(features.is_cuda, "features must be on CUDA device")
+        _check(features.dim() == 2, "features must be 2D [N, F]")
+        _check(features.shape[0] == N, "features must match points length")
+        _check(features.device == dev, "all tensors must be on the same CUDA device")
+        F = features.shape[1]
+        feats = features.to(torch.float32).contiguous()
+    pts = points.to(torch.float32).contiguous()
+
+    L = _lib.load()
+    counts = None
+    if mode in ("count", "occupancy"):
+        if mode == "occupancy" and occupancy_dtype == torch.uint8:
+            code = _lib.VOXEL_OCCUPANCY_U8
+            grid = torch.empty((gx, gy, gz), dtype=torch.uint8, device=dev)
+        else:
+            grid = torch.empty((gx, gy, gz), dtype=torch.int32, device=dev)
+    else:
+        grid = torch.empty((gx, gy, gz, F), dtype=torch.float32, device=dev)
+        if mode == "mean":
+            counts = torch.empty((gx, gy, gz), dtype=torch.int32, device=dev)
+    flags = _lib.VOXEL_ZERO_INIT
+    if not normalize:
+        flags |= _lib.VOXEL_NO_NORMALIZE
+    if warp_aggregate:
+        flags |= _lib.VOXEL_WARP_AGGREGATE
+    gmin = (ctypes.c_float * 3)(*[float(v) for v in grid_min])
+    gsz = (ctypes.c_int32 * 3)(gx, gy, gz)
+    rc = L.rc_voxelize(pts.data_ptr(), feats.data_ptr() if feats is not None else None, grid.data_ptr(),
+                       counts.data_ptr() if counts is not None else None, N, F, gmin, float(voxel_size), gsz,
+                       code, flags, dev.index, _stream_ptr(dev))
+    _lib.check(rc, "voxelize_pointcloud")
+    return [grid, counts] if mode == "mean" else [grid]
+
+
+def voxel_normalize_cuda(grid: torch.Tensor, counts: torch.Tensor, voxel_begin: int = 0,
+                         voxel_end: Optional[int] = None) -> None:
+    """In place: grid[v,:] *= 1/counts[v] for occupied voxels v in [voxel_begin, voxel_end)."""
+    _check(grid.is_cuda and counts.is_cuda, "grid and counts must be on CUDA device")
+    _check(grid.dtype == torch.float32 and counts.dtype == torch.int32, "grid must be float32, counts int32")
+    _check(grid.is_contiguous() and counts.is_contiguous(), "grid and counts must be contiguous")
+    V = counts.numel()
+    F = grid.numel() // V if V else 0
+    _check(V * F == grid.numel(), "grid must be [..., F] over the voxels of counts")
+    end = V if voxel_end is None else int(voxel_end)
+    dev = grid.device
+    rc = _lib.load().rc_voxel_normalize(grid.data_ptr(), counts.data_ptr(), int(voxel_begin), end, F, dev.index,
+                                        _stream_ptr(dev))
+    _lib.check(rc, "voxel_normalize")

@@ -1,0 +1,111 @@
+"""Parity of the one-launch multimodal fusion with the CPU oracle (bit-exact values, see
+test_resample_gpu.py for the gates) plus the reference tests' invariants."""
+import pytest
+import torch
+
+import oracle
+import robocache
+from conftest import golden_names, load_golden
+from robogoat_b200 import ops, workloads
+from test_resample_gpu import DEV, assert_exact
+
+pytestmark = pytest.mark.gpu
+
+
+def expected(args):
+    ref = oracle.fuse_multimodal(*args)
+    return oracle.round_to_bf16(ref) if args[0].dtype == torch.bfloat16 else ref
+
+
+def run(args):
+    out = robocache.fuse_multimodal(*[a.to(DEV) for a in args])
+    torch.cuda.synchronize()
+    return out.cpu()
+
+
+@pytest.mark.parametrize("name", golden_names("fusion_"))
+def test_golden_vectors(name, cuda_lib):
+    g = load_golden(name)
+    args = (g["s1"], g["t1"], g["s2"], g["t2"], g["s3"], g["t3"], g["tt"])
+    exp = oracle.round_to_bf16(g["out"]) if g["_bf16"] else g["out"]
+    assert_exact(run(args), exp, name)
+
+
+@pytest.mark.parametrize("B", [1, 4, 37, 256])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_headline_shape(B, dtype, cuda_lib):
+    args = workloads.fusion_inputs(B=B, dtype=dtype, seed=B)
+    out = run(args)
+    assert out.shape == (B, 50, 588)
+    assert_exact(out, expected(args))
+
+
+@pytest.mark.parametrize("streams,T", [
+    (((10, 64), (20, 32), (40, 12)), 15),      # robocache/python/robocache/__init__.py:415-432
+    (((5, 10), (5, 20), (5, 30)), 5),          # robocache/tests/test_all_operations.py:128-150
+    (((7, 3), (1, 5), (2, 1)), 9),             # odd widths, a one-row stream
+    (((30, 512), (100, 64), (200, 12)), 1),
+    (((3, 8), (4, 1000), (90, 2)), 130),
+    (((600, 16), (2, 16), (33, 16)), 64),
+])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_ragged_streams(streams, T, dtype, cuda_lib):
+    args = list(workloads.fusion_inputs(B=3, T=T, dtype=dtype, seed=T, streams=streams))
+    g = torch.Generator().manual_seed(T)
+    args[6] = torch.rand(3, T, generator=g) * 1.2 - 0.1     # unsorted targets, some outside the range
+    assert_exact(run(args), expected(args))
+
+
+def test_concat_order_and_clamp(cuda_lib):
+    g = load_golden("fusion_concat_order")
+    out = run((g["s1"], g["t1"], g["s2"], g["t2"], g["s3"], g["t3"], g["tt"]))
+    assert torch.allclose(out[0, 0, :10], torch.ones(10)) and torch.allclose(out[0, 0, 10:30], torch.ones(20) * 2)
+    assert torch.allclose(out[0, 0, 30:], torch.ones(30) * 3)
+    g = load_golden("fusion_clamp")    # robocache/tests/test_timestamp_alignment.py:292-338
+    out = run((g["s1"], g["t1"], g["s2"], g["t2"], g["s3"], g["t3"], g["tt"]))
+    for t in (0, 25, -1):
+        assert torch.allclose(out[0, t, :8], torch.full((8,), 10.0), atol=0.1)
+        assert torch.allclose(out[0, t, 8:12], torch.full((4,), 20.0), atol=0.1)
+
+
+def test_errors(cuda_lib):
+    a = [x.to(DEV) for x in workloads.fusion_inputs(B=2, dtype=torch.float32)]
+    bad = list(a)
+    bad[2] = bad[2].bfloat16()
+    with pytest.raises(RuntimeError, match="dtypes must match"):      # robocache/tests/test_mixed_precision.py:79
+        robocache.fuse_multimodal(*bad)
+    bad = list(a)
+    bad[0] = bad[0].half(); bad[2] = bad[2].half(); bad[4] = bad[4].half()
+    with pytest.raises(RuntimeError, match="Unsupported dtype"):
+        robocache.fuse_multimodal(*bad)
+    bad = list(a)
+    bad[3] = bad[3][:, :50]
+    with pytest.raises(RuntimeError, match="stream2_times length mismatch"):
+        robocache.fuse_multimodal(*bad)
+    bad = list(a)
+    bad[4] = bad[4][:1]
+    with pytest.raises(RuntimeError, match="Batch size mismatch"):
+        robocache.fuse_multimodal(*bad)
+
+
+def test_determinism_and_n_streams(cuda_lib):
+    a = [x.to(DEV) for x in workloads.fusion_inputs(B=64, dtype=torch.bfloat16, seed=9)]
+    o1, o2 = robocache.fuse_multimodal(*a), robocache.fuse_multimodal(*a)    # robocache/tests/test_determinism.py:24-55
+    assert torch.equal(o1.view(torch.int16), o2.view(torch.int16))
+    # fusion == per-stream resampling concatenated; also exercises 1, 2 and 5 streams in one launch
+    parts = [robocache.resample_trajectories(a[2 * k], a[2 * k + 1], a[6]) for k in range(3)]
+    assert torch.equal(torch.cat(parts, dim=-1).view(torch.int16), o1.view(torch.int16))
+    five = ops.fuse_streams_cuda([a[0], a[2], a[4], a[2], a[0]], [a[1], a[3], a[5], a[3], a[1]], a[6])
+    assert torch.equal(five.view(torch.int16), torch.cat(parts + [parts[1], parts[0]], dim=-1).view(torch.int16))
+
+
+def test_throughput_size_properties(cuda_lib):
+    """B=16384 headline throughput case: a seeded slice against the oracle and equality with per-stream resampling."""
+    a = workloads.fusion_inputs(B=16384, dtype=torch.bfloat16, seed=0, device=DEV)
+    out = robocache.fuse_multimodal(*a)
+    assert out.shape == (16384, 50, 588)
+    for sl in (slice(0, 4), slice(9000, 9004), slice(16380, 16384)):
+        cpu_args = [x[sl].cpu() for x in a]
+        assert_exact(out[sl].cpu(), expected(cpu_args), f"slice {sl}")
+    vis = robocache.resample_trajectories(a[0], a[1], a[6])
+    assert torch.equal(vis.view(torch.int16), out[:, :, :512].contiguous().view(torch.int16))

@@ -1,0 +1,151 @@
+"""Parity of the CUDA resampler (through the C ABI / Python operator) with the CPU oracle.
+Gates: bracket rows exact; fp32 values bit-exact (stronger than rel 1e-6); bf16 values equal to the
+oracle's fp32 result rounded once to bf16 (0 ulp, inside the 1-ulp allowance)."""
+import pytest
+import torch
+
+import oracle
+import robocache
+from conftest import bits, golden_names, load_golden
+from robogoat_b200 import ops, workloads
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def expected(src, st, tt):
+    ref = oracle.resample_trajectories(src, st, tt)
+    return oracle.round_to_bf16(ref) if src.dtype == torch.bfloat16 else ref
+
+
+def run(src, st, tt):
+    out = robocache.resample_trajectories(src.to(DEV), st.to(DEV), tt.to(DEV))
+    torch.cuda.synchronize()
+    return out.cpu()
+
+
+def assert_exact(out, exp, what=""):
+    assert out.shape == exp.shape and out.dtype == exp.dtype
+    same = bits(out) == bits(exp)
+    if not bool(same.all()):
+        # NaN payloads may differ; everything else must match bit for bit
+        both_nan = torch.isnan(out.float()) & torch.isnan(exp.float())
+        bad = ~(same | both_nan)
+        assert not bool(bad.any()), f"{what}: {int(bad.sum())} of {bad.numel()} elements differ, max abs " \
+                                    f"{(out.float() - exp.float())[bad].abs().max().item()}"
+
+
+@pytest.mark.parametrize("name", golden_names("resample_"))
+def test_golden_vectors(name, cuda_lib):
+    g = load_golden(name)
+    out = run(g["src"], g["st"], g["tt"])
+    exp = oracle.round_to_bf16(g["out"]) if g["_bf16"] else g["out"]
+    assert_exact(out, exp, name)
+    left, right, w = ops.resample_brackets_cuda(g["st"].to(DEV), g["tt"].to(DEV))
+    assert torch.equal(left.cpu(), g["left"]) and torch.equal(right.cpu(), g["right"])
+
+
+# shapes of the reference's own CUDA parity test (robocache/tests/test_cuda_correctness.py:17-88)
+@pytest.mark.parametrize("B,S,T,D", [(1, 50, 25, 64), (8, 100, 50, 128), (32, 500, 256, 256), (32, 500, 250, 256)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_reference_test_shapes(B, S, T, D, dtype, cuda_lib):
+    src, st, tt = workloads.resample_inputs(B, S, D, T, dtype=dtype, irregular_targets=True, seed=B + S)
+    assert_exact(run(src, st, tt), expected(src, st, tt))
+
+
+# every access width (16/8/4/2 bytes), ragged rows, short and long rows, S in {1,2,3}, T in {1, 33, ...}
+@pytest.mark.parametrize("B,S,T,D", [
+    (3, 1, 5, 4), (2, 2, 7, 3), (2, 3, 1, 1), (5, 17, 40, 12), (4, 9, 33, 7), (2, 64, 65, 8), (3, 31, 97, 588),
+    (2, 12, 300, 1024), (1, 500, 250, 2), (7, 5, 31, 6), (2, 40, 64, 520), (1, 3, 1000, 16),
+])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_ragged_shapes(B, S, T, D, dtype, cuda_lib):
+    g = torch.Generator().manual_seed(B * 1000 + S * 10 + D)
+    st = workloads.cumsum_times(B, S, g)
+    src = torch.randn(B, S, D, generator=g).to(dtype)
+    tt = torch.rand(B, T, generator=g) * 1.4 - 0.2          # unsorted, partly outside the source range
+    if S > 2 and T > 2:
+        tt[:, 0] = st[:, 1]                                   # exact hits on source timestamps
+        tt[:, 1] = st[:, -1]
+    assert_exact(run(src, st, tt), expected(src, st, tt))
+    left, right, w = ops.resample_brackets_cuda(st.to(DEV), tt.to(DEV))
+    el, er, ew = oracle.brackets(st, tt)
+    assert torch.equal(left.cpu(), el) and torch.equal(right.cpu(), er)
+    assert torch.equal(bits(w), bits(ew))
+
+
+def test_duplicate_timestamps_and_ties(cuda_lib):
+    st = torch.tensor([[0.0, 0.1, 0.1, 0.1, 0.4, 0.4, 0.9, 1.0]]).repeat(3, 1)
+    tt = torch.tensor([[0.1, 0.4, 0.0, 1.0, 0.25, 0.9, 0.95, -1.0, 2.0, 0.1000001]]).repeat(3, 1)
+    src = torch.randn(3, 8, 20)
+    assert_exact(run(src, st, tt), expected(src, st, tt))
+
+
+def test_unaligned_views_take_the_narrow_path(cuda_lib):
+    """Slices that break 16-byte alignment must still be exact (the wrapper makes them contiguous,
+    the C ABI picks a narrower access width for odd base addresses)."""
+    src, st, tt = workloads.resample_inputs(4, 30, 40, 20, dtype=torch.bfloat16, irregular_targets=True, seed=5)
+    s = src[:, :, 1:39]                                      # D=38, non-contiguous
+    assert_exact(run(s, st, tt), expected(s.contiguous(), st, tt))
+    L = cuda_lib
+    # raw C-ABI call on a buffer offset by one element: base pointer only 2-byte aligned
+    flat = torch.empty(4 * 30 * 40 + 1, dtype=torch.bfloat16, device=DEV)
+    flat[1:] = src.flatten().to(DEV)
+    out = torch.empty(4 * 20 * 40 + 1, dtype=torch.bfloat16, device=DEV)
+    std, ttd = st.to(DEV), tt.to(DEV)
+    rc = L.rc_resample(flat.data_ptr() + 2, std.data_ptr(), ttd.data_ptr(), out.data_ptr() + 2, 4, 30, 20, 40, 1, 0,
+                       torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert_exact(out[1:].view(4, 20, 40).cpu(), expected(src, st, tt))
+    # a pointer that is not even element aligned is rejected, not dereferenced
+    assert L.rc_resample(flat.data_ptr() + 1, std.data_ptr(), ttd.data_ptr(), out.data_ptr(), 4, 30, 20, 40, 1, 0,
+                         None) == 4
+
+
+def test_long_rows_search_global_memory(cuda_lib):
+    """S beyond the shared-memory staging limit switches to the global-memory search."""
+    B, S, T, D = 2, 60000, 300, 8
+    src, st, tt = workloads.resample_inputs(B, S, D, T, irregular_targets=True, seed=11)
+    assert_exact(run(src, st, tt), expected(src, st, tt))
+
+
+def test_dtype_and_shape_errors(cuda_lib):
+    src, st, tt = workloads.resample_inputs(2, 10, 8, 5)
+    with pytest.raises(RuntimeError, match="Unsupported dtype"):
+        robocache.resample_trajectories(src.half().to(DEV), st.to(DEV), tt.to(DEV))
+    with pytest.raises(RuntimeError, match="Source length mismatch"):
+        robocache.resample_trajectories(src.to(DEV), st[:, :5].to(DEV), tt.to(DEV))
+    with pytest.raises(RuntimeError, match="Batch size mismatch"):
+        robocache.resample_trajectories(src.to(DEV), st.to(DEV), tt[:1].to(DEV))
+    with pytest.raises(RuntimeError, match="3D"):
+        robocache.resample_trajectories(src[0].to(DEV), st.to(DEV), tt.to(DEV))
+    out = robocache.resample_trajectories(src.to(DEV), st.double().to(DEV), tt.double().to(DEV))   # times in any float dtype
+    assert_exact(out.cpu(), expected(src, st, tt))
+    empty = robocache.resample_trajectories(src.to(DEV), st.to(DEV), tt[:, :0].to(DEV))
+    assert empty.shape == (2, 0, 8)
+
+
+def test_device_argument_and_identity(cuda_lib):
+    src, st, tt = workloads.resample_inputs(4, 50, 16, 50)
+    out = robocache.resample_trajectories(src, st, st, device=DEV)       # CPU tensors moved by device=
+    assert out.is_cuda and (out.cpu() - src).abs().max() < 1e-5         # robocache/tests/test_trajectory.py:40-53
+
+
+def test_full_size_properties(cuda_lib):
+    """Headline size (B=4096, S=500, D=256, T=250, bf16): checked through properties that do not need
+    the oracle on 1.5 GB — a seeded slice against the oracle, exact reproduction of source rows at
+    source timestamps, constant rows staying constant, and run-to-run determinism."""
+    B, S, D, T = 4096, 500, 256, 250
+    src, st, tt = workloads.resample_inputs(B, S, D, T, dtype=torch.bfloat16, irregular_targets=True, seed=0, device=DEV)
+    out = robocache.resample_trajectories(src, st, tt)
+    out2 = robocache.resample_trajectories(src, st, tt)
+    assert torch.equal(out.view(torch.int16), out2.view(torch.int16))
+    for sl in (slice(0, 8), slice(2048, 2056), slice(4088, 4096)):
+        assert_exact(out[sl].cpu(), expected(src[sl].cpu(), st[sl].cpu(), tt[sl].cpu()), f"slice {sl}")
+    # resampling at the source timestamps themselves returns the source rows (weights are 0 or 1 up to
+    # the 1e-8 epsilon, far below bf16 resolution)
+    ident = robocache.resample_trajectories(src[:64], st[:64], st[:64])
+    assert (ident.float() - src[:64].float()).abs().max().item() <= 2 ** -7 * src[:64].float().abs().max().item()
+    const = torch.full((16, S, D), 3.0, dtype=torch.bfloat16, device=DEV)
+    assert torch.equal(robocache.resample_trajectories(const, st[:16], tt[:16]), torch.full((16, T, D), 3.0, dtype=torch.bfloat16, device=DEV))

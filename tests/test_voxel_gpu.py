@@ -1,0 +1,194 @@
+"""Parity of the CUDA voxeliser with the CPU oracle: occupancy and counts bit-exact, feature means
+within |x-y| <= 1e-5*|y| + 1e-6*mean|f| (fp32 sums are order dependent)."""
+import pytest
+import torch
+
+import oracle
+import robocache
+from conftest import golden_names, load_golden
+from robogoat_b200 import ops, workloads
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def dense_from_golden(g):
+    V = int(g["gs"].prod())
+    d = torch.zeros(V, dtype=torch.int32)
+    d[g["nz"]] = g["density"].to(torch.int32)
+    return d.view(*g["gs"].tolist())
+
+
+@pytest.mark.parametrize("name", golden_names("voxel_"))
+def test_golden_vectors(name, cuda_lib):
+    g = load_golden(name)
+    kw = dict(grid_min=g["gmin"].tolist(), voxel_size=float(g["vs"]), grid_size=g["gs"].tolist())
+    exp = dense_from_golden(g)
+    cnt = robocache.voxelize_pointcloud(g["pts"].to(DEV), mode="count", **kw)
+    occ = robocache.voxelize_pointcloud(g["pts"].to(DEV), mode="occupancy", **kw)
+    assert cnt.dtype == torch.int32 and occ.dtype == torch.int32      # robocache/tests/test_voxelize_correctness.py:128
+    assert torch.equal(cnt.cpu(), exp)
+    assert torch.equal(occ.cpu(), (exp > 0).int())
+
+
+# sizes and grids of robocache/tests/test_voxelize_correctness.py:14-97 and test_voxel_optimized_correctness.py
+@pytest.mark.parametrize("N", [0, 1, 3, 100, 127, 128, 129, 1000, 10_000, 500_000])
+@pytest.mark.parametrize("G", [16, 32, 128])
+def test_count_and_occupancy_exact(N, G, cuda_lib):
+    g = torch.Generator().manual_seed(42 + N + G)
+    pts = torch.rand(N, 3, generator=g) * 20 - 10
+    kw = dict(grid_min=[-10.0, -10.0, -10.0], voxel_size=20.0 / G * 0.75, grid_size=[G, G, G])   # part of the cloud falls outside
+    exp = oracle.voxelize_pointcloud(pts, None, mode="count", **kw)
+    for agg in (False, True):
+        cnt = ops.voxelize_pointcloud_cuda(pts.to(DEV), None, kw["grid_min"], kw["voxel_size"], kw["grid_size"], "count",
+                                           warp_aggregate=agg)[0]
+        assert torch.equal(cnt.cpu(), exp), f"agg={agg}"
+    occ = robocache.voxelize_pointcloud(pts.to(DEV), mode="occupancy", **kw)
+    assert torch.equal(occ.cpu(), (exp > 0).int())
+    u8 = ops.voxelize_pointcloud_cuda(pts.to(DEV), None, kw["grid_min"], kw["voxel_size"], kw["grid_size"], "occupancy",
+                                      occupancy_dtype=torch.uint8)[0]
+    assert u8.dtype == torch.uint8 and torch.equal(u8.cpu().int(), (exp > 0).int())
+
+
+def test_headline_occupancy_geometry(cuda_lib):
+    """N=500000 in U[-10,10)^3 against a 128^3 grid of 0.05 m voxels at -10: most points are dropped."""
+    pts = workloads.voxel_uniform_inputs(500_000, seed=0)
+    kw = workloads.VOXEL_OCCUPANCY_GEOMETRY
+    exp = oracle.voxelize_pointcloud(pts, None, mode="occupancy", **kw)
+    occ = robocache.voxelize_pointcloud(pts.to(DEV), mode="occupancy", **kw)
+    assert torch.equal(occ.cpu(), exp)
+    assert 10_000 < int(exp.sum()) < 25_000
+    occ2 = robocache.voxelize_occupancy(pts.to(DEV), torch.tensor(kw["grid_size"]), kw["voxel_size"], torch.tensor(kw["grid_min"]))
+    assert torch.equal(occ2, occ)
+
+
+def test_noncubic_layout_is_z_major(cuda_lib):
+    pts = torch.tensor([[0.05, 0.15, 0.25]])            # voxel (0, 1, 2)
+    out = robocache.voxelize_pointcloud(pts.to(DEV), grid_min=[0.0, 0.0, 0.0], voxel_size=0.1, grid_size=[4, 5, 6], mode="count")
+    assert out.shape == (4, 5, 6)
+    flat = out.flatten().cpu()
+    assert int(flat[2 * 4 * 5 + 1 * 4 + 0]) == 1 and int(flat.sum()) == 1
+
+
+def test_edge_points(cuda_lib):
+    nan, inf = float("nan"), float("inf")
+    pts = torch.tensor([[0.0, 0.0, 0.0], [-0.0, 0.0, 0.0], [-1e-7, 0.0, 0.0], [1.6, 0.0, 0.0], [1.5999999, 0.0, 0.0],
+                        [nan, 0.0, 0.0], [inf, 0.0, 0.0], [-inf, 0.0, 0.0], [0.5, nan, 0.5], [1e30, 1e30, 1e30],
+                        [0.3, 0.6, 0.9], [0.30000001, 0.6, 0.9]])
+    kw = dict(grid_min=[0.0, 0.0, 0.0], voxel_size=0.1, grid_size=[16, 16, 16])
+    exp = oracle.voxelize_pointcloud(pts, None, mode="count", **kw)
+    out = robocache.voxelize_pointcloud(pts.to(DEV), mode="count", **kw)
+    assert torch.equal(out.cpu(), exp)
+
+
+def test_unaligned_points_view(cuda_lib):
+    pts = workloads.voxel_uniform_inputs(1001, seed=1)
+    kw = dict(grid_min=[-10.0, -10.0, -10.0], voxel_size=0.5, grid_size=[40, 40, 40])
+    dev = pts.to(DEV)
+    view = dev[1:]                                       # base pointer 12 bytes past a 16-byte boundary
+    out = robocache.voxelize_pointcloud(view, mode="count", **kw)
+    assert torch.equal(out.cpu(), oracle.voxelize_pointcloud(pts[1:], None, mode="count", **kw))
+
+
+@pytest.mark.parametrize("F", [1, 2, 3, 4, 8, 6])
+@pytest.mark.parametrize("N", [5, 1000, 200_000])
+def test_mean_within_tolerance(F, N, cuda_lib):
+    g = torch.Generator().manual_seed(F * 7 + N)
+    pts = torch.rand(N, 3, generator=g) * 4 - 2
+    feats = torch.randn(N, F, generator=g)
+    kw = dict(grid_min=[-1.5, -1.5, -1.5], voxel_size=0.25, grid_size=[12, 12, 12])
+    exp, ecnt, sabs = oracle.voxelize_pointcloud(pts, feats, mode="mean", return_aux=True, **kw)
+    grid, counts = ops.voxelize_pointcloud_cuda(pts.to(DEV), feats.to(DEV), kw["grid_min"], kw["voxel_size"], kw["grid_size"], "mean")
+    assert torch.equal(counts.cpu(), ecnt)
+    tol = oracle.mean_tolerance(ecnt, sabs, exp)
+    err = (grid.cpu() - exp).abs()
+    assert bool((err <= tol).all()), f"max excess {(err - tol).max().item()}"
+    assert bool((grid.cpu()[ecnt == 0] == 0).all())
+    api = robocache.voxelize_pointcloud(pts.to(DEV), feats.to(DEV), mode="mean", **kw)
+    assert api.shape == (12, 12, 12, F)
+    # sums + separate normalisation over two slabs == fused call (the multi-GPU harness's split)
+    sums, c2 = ops.voxelize_pointcloud_cuda(pts.to(DEV), feats.to(DEV), kw["grid_min"], kw["voxel_size"], kw["grid_size"], "mean", normalize=False)
+    V = c2.numel()
+    ops.voxel_normalize_cuda(sums, c2, 0, 701)
+    ops.voxel_normalize_cuda(sums, c2, 701, V)
+    assert bool(((sums.cpu() - exp).abs() <= tol).all())
+
+
+def test_max_mode(cuda_lib):
+    g = torch.Generator().manual_seed(5)
+    pts = torch.rand(20_000, 3, generator=g) * 4 - 2
+    feats = torch.randn(20_000, 3, generator=g)
+    kw = dict(grid_min=[-1.5, -1.5, -1.5], voxel_size=0.25, grid_size=[12, 12, 12])
+    ids = oracle.voxel_ids(pts, **kw)
+    exp = torch.full((12 * 12 * 12, 3), float("-inf"))
+    keep = ids >= 0
+    exp.scatter_reduce_(0, ids[keep].unsqueeze(-1).expand(-1, 3), feats[keep], reduce="amax", include_self=True)
+    exp = torch.where(torch.isfinite(exp), exp, torch.zeros_like(exp)).view(12, 12, 12, 3)
+    out = robocache.voxelize_pointcloud(pts.to(DEV), feats.to(DEV), mode="max", **kw)
+    assert torch.equal(out.cpu(), exp)
+
+
+def test_errors(cuda_lib):
+    pts = torch.zeros(10, 3, device=DEV)
+    with pytest.raises(RuntimeError, match="Invalid mode"):
+        robocache.voxelize_pointcloud(pts, mode="median")
+    with pytest.raises(RuntimeError, match="features required"):
+        robocache.voxelize_pointcloud(pts, mode="mean")
+    with pytest.raises(RuntimeError, match="3 coordinates"):
+        robocache.voxelize_pointcloud(torch.zeros(10, 4, device=DEV))
+    with pytest.raises(RuntimeError, match="voxel_size must be positive"):
+        robocache.voxelize_pointcloud(pts, voxel_size=0.0)
+    with pytest.raises(RuntimeError, match="features must match"):
+        robocache.voxelize_pointcloud(pts, torch.zeros(9, 2, device=DEV), mode="mean")
+    with pytest.raises(RuntimeError, match="3 elements"):
+        robocache.voxelize_pointcloud(pts, grid_size=[4, 4])
+
+
+def test_guard_bands_and_determinism(cuda_lib):
+    """Writes stay inside the grid (sentinel words either side, as
+    robocache/tests/test_voxel_optimized_correctness.py:144-162) and integer outputs repeat exactly."""
+    import ctypes
+    L = cuda_lib
+    pts = workloads.voxel_uniform_inputs(100_000, seed=3).to(DEV)
+    G = 32
+    V = G * G * G
+    buf = torch.full((V + 512,), 0x5A5A5A5A, dtype=torch.int32, device=DEV)
+    gmin = (ctypes.c_float * 3)(-10.0, -10.0, -10.0)
+    gs = (ctypes.c_int32 * 3)(G, G, G)
+    first = None
+    for _ in range(5):                                   # robocache/tests/test_voxelize_correctness.py:188-230
+        rc = L.rc_voxelize(pts.data_ptr(), None, buf.data_ptr() + 256 * 4, None, pts.shape[0], 0, gmin, 0.3, gs, 0, 1, 0,
+                           torch.cuda.current_stream().cuda_stream)
+        assert rc == 0
+        torch.cuda.synchronize()
+        assert bool((buf[:256] == 0x5A5A5A5A).all()) and bool((buf[-256:] == 0x5A5A5A5A).all())
+        cur = buf[256:-256].clone()
+        first = cur if first is None else first
+        assert torch.equal(cur, first)
+
+
+def test_mixture_properties_at_scale(cuda_lib):
+    """Count + mean on 2^24 mixture points into 512^3 (a quarter of the headline N, same geometry): counts
+    sum to the in-grid points, means recombine to the global feature sums, empty voxels are exactly 0, and
+    a 2^18 seeded prefix is checked voxel by voxel against the oracle on a sub-grid."""
+    N = 1 << 24
+    pts, feats = workloads.voxel_mixture_inputs(N, seed=0, device=DEV)
+    kw = workloads.VOXEL_MIXTURE_GEOMETRY
+    grid, counts = ops.voxelize_pointcloud_cuda(pts, feats, kw["grid_min"], kw["voxel_size"], kw["grid_size"], "mean")
+    q = torch.floor((pts - torch.tensor(kw["grid_min"], device=DEV)) / kw["voxel_size"])
+    inside = ((q >= 0) & (q < 512)).all(dim=1)
+    assert int(counts.sum(dtype=torch.int64)) == int(inside.sum())
+    total = (grid.double() * counts.unsqueeze(-1)).sum(dim=(0, 1, 2))
+    ref_total = feats[inside].double().sum(0)
+    assert torch.allclose(total, ref_total, rtol=1e-4, atol=1.0)
+    assert bool((grid[counts == 0] == 0).all())
+    cnt_only = robocache.voxelize_pointcloud(pts, mode="count", **kw)
+    assert torch.equal(cnt_only, counts)
+    del grid, q
+    n = 1 << 18
+    sub = dict(grid_min=kw["grid_min"], voxel_size=kw["voxel_size"], grid_size=[512, 512, 512])
+    exp_ids = oracle.voxel_ids(pts[:n].cpu(), **sub)
+    cnt_small = robocache.voxelize_pointcloud(pts[:n], mode="count", **kw).flatten()
+    keep = exp_ids[exp_ids >= 0]
+    exp_counts = torch.bincount(keep, minlength=512 ** 3).int()
+    assert torch.equal(cnt_small.cpu(), exp_counts)
