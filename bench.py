@@ -420,6 +420,43 @@ def run_extras(L, dev, local, rank, world, peak):
     return ex
 
 
+def run_profile_case(name: str):
+    """A few launches of one kernel on a case sized for a profiler capture: larger than L2, well under
+    a GB on the device.  Prints one JSON line with the CUDA-event time of the last launch."""
+    from robogoat_b200 import ops, workloads
+    import robocache
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    if name == "resample":
+        src, st, tt = workloads.resample_inputs(B=1024, dtype=torch.bfloat16, irregular_targets=True, seed=0, device=dev,
+                                                S=HEADLINE["S"], D=HEADLINE["D"], T=HEADLINE["T"])
+        fn = lambda: ops.resample_trajectories_cuda(src, st, tt)
+        units = {"B": 1024, "bytes_all_tensors_once": workloads.resample_bytes(1024, 500, 250, 256, 2)}
+    elif name == "fusion":
+        a = workloads.fusion_inputs(B=4096, dtype=torch.bfloat16, seed=0, device=dev)
+        fn = lambda: ops.fuse_multimodal_cuda(*a)
+        units = {"B": 4096, "bytes_all_tensors_once": workloads.fusion_bytes(4096, 50, 2)}
+    elif name in ("voxel_mean", "voxel_count"):
+        N = 1 << 24
+        pts, feats = workloads.voxel_mixture_inputs(N, seed=0, device=dev)
+        kw = workloads.VOXEL_MIXTURE_GEOMETRY
+        mode = name.split("_")[1]
+        fn = lambda: robocache.voxelize_pointcloud(pts, feats if mode == "mean" else None, mode=mode, **kw)
+        units = {"N": N}
+    elif name == "voxel_occupancy":
+        pts = workloads.voxel_uniform_inputs(500_000, seed=0, device=dev)
+        fn = lambda: robocache.voxelize_pointcloud(pts, mode="occupancy", **workloads.VOXEL_OCCUPANCY_GEOMETRY)
+        units = {"N": 500_000}
+    else:
+        raise SystemExit(f"unknown profile case {name}")
+    for _ in range(3):
+        r = fn(); del r
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record(); r = fn(); b.record(); torch.cuda.synchronize()
+    print(json.dumps({"profile_case": name, "last_call_ms": a.elapsed_time(b), **units}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -427,7 +464,12 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extras", action="store_true")
+    ap.add_argument("--profile-case", default=None,
+                    help="run 4 launches of one kernel on a small case (resample, fusion, voxel_mean, voxel_count, voxel_occupancy)")
     args = ap.parse_args()
+    if args.profile_case:
+        run_profile_case(args.profile_case)
+        return
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
         run_reference_arm(args)
