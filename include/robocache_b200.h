@@ -11,7 +11,8 @@
  *   - Tensors are dense row-major.  Timestamps are fp32.
  *   - Every function returns an rc_status (0 = ok).  rc_strerror() names a code;
  *     rc_last_cuda_error() gives the cudaError_t behind RC_ERR_CUDA for this thread.
- *   - The library is re-entrant and keeps no state between calls.
+ *   - The library is re-entrant and keeps no state between calls, except where an entry
+ *     point says otherwise (rc_voxelize_mean_static).
  */
 #ifndef ROBOCACHE_B200_H
 #define ROBOCACHE_B200_H
@@ -122,6 +123,31 @@ RC_API int rc_voxelize(const float* points, const float* features, void* grid, i
  */
 RC_API int rc_voxel_normalize(float* grid, const int32_t* counts, int64_t voxel_begin, int64_t voxel_end,
                        int32_t F, int device, void* stream);
+
+/*
+ * Mean-mode voxelisation that allocates nothing.  No counterpart in the reference: its binding
+ * always allocates the counter plane with torch (robocache/csrc/cpp/voxelize_ops.cpp:91-100).
+ *
+ * For callers that cannot call cudaMalloc: code inside an allocator or memory-pool callback, a
+ * control loop that forbids driver allocations once it is running, or a host that owns only the
+ * input and output buffers it was given.  The per-voxel counters that mean mode needs live in a
+ * fixed array inside the library (RC_STATIC_MAX_VOXELS int32 = 8 MiB, held by every GPU that
+ * loads the library until the process exits), so the caller passes only points, features and the
+ * fp32 output grid [gx*gy*gz*F]; the counters are not returned.
+ *
+ *   - gx*gy*gz above RC_STATIC_MAX_VOXELS is rejected with RC_ERR_TOO_LARGE.
+ *   - The grid and the counters are cleared on `stream` by every call.
+ *   - All calls on a device share the one counter array: two calls that overlap on the GPU
+ *     (different streams, or different threads) race.  Serialise them on one stream.
+ *   - The first call on each device looks up the array's device address; make that call before
+ *     any stream capture begins.
+ *   - No cudaMalloc, cudaFree or other allocating routine is called.
+ * Results equal rc_voxelize(..., RC_VOXEL_MEAN, RC_VOXEL_ZERO_INIT) up to fp32 summation order.
+ */
+#define RC_STATIC_MAX_VOXELS (1 << 21)
+RC_API int rc_voxelize_mean_static(const float* points, const float* features, float* grid, int64_t N,
+                                   int32_t F, const float grid_min_host[3], float voxel_size,
+                                   const int32_t grid_size_host[3], int device, void* stream);
 
 RC_API const char* rc_strerror(int status);
 RC_API int rc_last_cuda_error(void);

@@ -26,10 +26,11 @@ VOXEL_OCCUPANCY_U8 = 4
 VOXEL_ZERO_INIT = 1
 VOXEL_NO_NORMALIZE = 2
 VOXEL_WARP_AGGREGATE = 4
+STATIC_MAX_VOXELS = 1 << 21
 
 # every symbol the header declares; the CPU test-suite checks the built library exports them all
 EXPORTED_SYMBOLS = (
-    "rc_resample", "rc_fuse", "rc_resample_brackets", "rc_voxelize", "rc_voxel_normalize",
+    "rc_resample", "rc_fuse", "rc_resample_brackets", "rc_voxelize", "rc_voxel_normalize", "rc_voxelize_mean_static",
     "rc_strerror", "rc_last_cuda_error", "rc_abi_version",
 )
 
@@ -56,7 +57,8 @@ def _declare(L: ctypes.CDLL) -> None:
     L.rc_voxelize.argtypes = [vp, vp, vp, vp, i64, i32, ctypes.POINTER(f32), f32,
                               ctypes.POINTER(i32), ci, u32, ci, vp]
     L.rc_voxel_normalize.argtypes = [vp, vp, i64, i64, i32, ci, vp]
-    for name in ("rc_resample", "rc_fuse", "rc_resample_brackets", "rc_voxelize", "rc_voxel_normalize",
+    L.rc_voxelize_mean_static.argtypes = [vp, vp, vp, i64, i32, ctypes.POINTER(f32), f32, ctypes.POINTER(i32), ci, vp]
+    for name in ("rc_resample", "rc_fuse", "rc_resample_brackets", "rc_voxelize", "rc_voxel_normalize", "rc_voxelize_mean_static",
                  "rc_last_cuda_error", "rc_abi_version"):
         getattr(L, name).restype = ci
     L.rc_strerror.argtypes = [ci]

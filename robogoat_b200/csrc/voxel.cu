@@ -18,6 +18,8 @@
 // occupied voxels by 1.0f / count (robocache/csrc/cuda/voxelize_kernel.cu:145-163).
 #include "rc_common.cuh"
 
+#include <mutex>
+
 namespace {
 
 constexpr int kThreads = 256;
@@ -216,6 +218,32 @@ void launch_bin(bool agg, unsigned int blocks, cudaStream_t st, const float* pts
     else     voxel_bin_kernel<MODE, false><<<blocks, kThreads, 0, st>>>(pts, feats, grid, counts, N, F, g, aligned);
 }
 
+// ---------------------------------------------------------------- allocation-free mean mode
+//
+// Count plane for rc_voxelize_mean_static.  It lives in the library image: every GPU that
+// loads the library holds these 8 MiB until the process exits, and every call on a device
+// shares them.
+constexpr long long kStaticMaxVoxels = RC_STATIC_MAX_VOXELS;
+static __device__ __align__(256) int g_static_counts[kStaticMaxVoxels];
+
+// Device address of g_static_counts on `device`, which must be current.  In host code the
+// array's name is only a handle for the runtime, never an address a kernel may use, so the
+// address is asked for once per device and remembered.
+int static_counts_address(int device, int** out) {
+    static std::mutex mu;
+    static int* known[64] = {};
+    if (device < 0 || device >= 64) return RC_ERR_BAD_DEVICE;
+    std::lock_guard<std::mutex> lock(mu);
+    if (known[device] == nullptr) {
+        void* p = nullptr;
+        const cudaError_t e = cudaGetSymbolAddress(&p, g_static_counts);
+        if (e != cudaSuccess) return rc::cuda_fail(e);
+        known[device] = static_cast<int*>(p);
+    }
+    *out = known[device];
+    return RC_OK;
+}
+
 }  // namespace
 
 extern "C" {
@@ -328,6 +356,32 @@ int rc_voxelize(const float* points, const float* features, void* grid, int32_t*
         return rc_voxel_normalize(static_cast<float*>(grid), counts, 0, V, F, device, stream);
     }
     return RC_OK;
+}
+
+
+// Mean-mode voxelisation for callers that must not allocate device memory: code running
+// inside a framework's memory-pool callback or under a real-time loop's "no driver
+// allocation after start-up" rule, or a host that was only handed the input and output
+// buffers.  Mean mode needs one int32 counter per voxel next to the output; here that plane
+// is the file-scope array above instead of a caller buffer, so nothing is allocated, by this
+// function or on its behalf.  The grid and the counters are cleared on `stream` first, then
+// the points are binned and the sums normalised exactly as rc_voxelize does.
+int rc_voxelize_mean_static(const float* points, const float* features, float* grid, int64_t N, int32_t F,
+                            const float grid_min_host[3], float voxel_size, const int32_t grid_size_host[3],
+                            int device, void* stream) {
+    if (grid_size_host == nullptr) return RC_ERR_NULL_POINTER;
+    for (int a = 0; a < 3; ++a)
+        if (grid_size_host[a] < 0) return RC_ERR_BAD_SHAPE;
+    const double voxels = static_cast<double>(grid_size_host[0]) * grid_size_host[1] * grid_size_host[2];
+    if (voxels > static_cast<double>(kStaticMaxVoxels)) return RC_ERR_TOO_LARGE;  // the counter plane is fixed size
+    rc::DeviceScope scope(device);
+    if (scope.status() != RC_OK) return scope.status();
+    int* counts = nullptr;
+    const int rc_addr = static_counts_address(device, &counts);
+    if (rc_addr != RC_OK) return rc_addr;
+    // RC_VOXEL_ZERO_INIT clears the grid and the shared counters, which keep the previous call's values
+    return rc_voxelize(points, features, grid, counts, N, F, grid_min_host, voxel_size, grid_size_host,
+                       RC_VOXEL_MEAN, RC_VOXEL_ZERO_INIT, device, stream);
 }
 
 }  // extern "C"
