@@ -149,6 +149,21 @@ RC_API int rc_voxelize_mean_static(const float* points, const float* features, f
                                    int32_t F, const float grid_min_host[3], float voxel_size,
                                    const int32_t grid_size_host[3], int device, void* stream);
 
+/*
+ * Process-wide switches, for tests and profiling.  RC_OPT_BLOCK_KERNEL (default 1): let
+ * rc_resample / rc_fuse use the TMA-staged kernel when the shapes qualify; 0 forces the
+ * row-gather kernel.  Both kernels produce identical bits.  No counterpart in the reference.
+ */
+#define RC_OPT_BLOCK_KERNEL 0
+RC_API int rc_set_option(int option, int value);
+
+/*
+ * Number of CTAs, since the library was loaded on `device`, whose bounded wait for a bulk
+ * (TMA) copy ran out and which fetched their inputs with ordinary loads instead.  Expected
+ * to stay 0; synchronises the device.  No counterpart in the reference.
+ */
+RC_API int rc_bulk_wait_timeouts(int device, unsigned int* count_host);
+
 RC_API const char* rc_strerror(int status);
 RC_API int rc_last_cuda_error(void);
 RC_API int rc_abi_version(void);

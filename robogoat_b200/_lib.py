@@ -31,7 +31,7 @@ STATIC_MAX_VOXELS = 1 << 21
 # every symbol the header declares; the CPU test-suite checks the built library exports them all
 EXPORTED_SYMBOLS = (
     "rc_resample", "rc_fuse", "rc_resample_brackets", "rc_voxelize", "rc_voxel_normalize", "rc_voxelize_mean_static",
-    "rc_strerror", "rc_last_cuda_error", "rc_abi_version",
+    "rc_set_option", "rc_bulk_wait_timeouts", "rc_strerror", "rc_last_cuda_error", "rc_abi_version",
 )
 
 
@@ -61,6 +61,10 @@ def _declare(L: ctypes.CDLL) -> None:
     for name in ("rc_resample", "rc_fuse", "rc_resample_brackets", "rc_voxelize", "rc_voxel_normalize", "rc_voxelize_mean_static",
                  "rc_last_cuda_error", "rc_abi_version"):
         getattr(L, name).restype = ci
+    L.rc_set_option.argtypes = [ci, ci]
+    L.rc_bulk_wait_timeouts.argtypes = [ci, ctypes.POINTER(u32)]
+    L.rc_set_option.restype = ci
+    L.rc_bulk_wait_timeouts.restype = ci
     L.rc_strerror.argtypes = [ci]
     L.rc_strerror.restype = ctypes.c_char_p
 

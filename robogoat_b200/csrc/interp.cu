@@ -20,12 +20,13 @@
 // (robocache/csrc/cuda/multimodal_kernel.cu:57-196).
 #include <cuda_bf16.h>
 
+#include <atomic>
+
 #include "rc_common.cuh"
 
 namespace {
 
 constexpr int kMaxWarps = 8;       // warps per CTA at most
-constexpr int kUnroll = 4;         // row vectors in flight per lane and source row
 constexpr int kMaxStagedBytes = 200 * 1024;
 
 struct StreamArg {
@@ -138,25 +139,27 @@ template <typename V> __device__ __forceinline__ void store_row(unsigned char* p
     __stcs(reinterpret_cast<V*>(p), v);  // the output is written once and never re-read here
 }
 
-// ---------------------------------------------------------------- one stream, one warp chunk
+// ---------------------------------------------------------------- gather kernel: one warp chunk
 
 // Interpolates the rows of `nt` consecutive targets (owned by lanes 0..nt-1, which hold
 // their bracket row `l` and weight `w`) of one stream into its output slice.
-template <int ES, int VEC>
+// UNIFORM: every row is a whole number of warp-wide accesses, so all lanes work on the
+// same target and U targets are kept in flight; otherwise lanes walk the flat
+// (target, vector) space of the chunk.
+template <int ES, int VEC, bool UNIFORM, int U>
 __device__ __forceinline__ void interp_chunk(const StreamArg& s, const unsigned char* src_b,
                                              unsigned char* out_t0, long long out_row_bytes,
                                              int l, float w, int nt, int lane) {
     using V = typename VecOf<VEC>::type;
     const int vecs = s.vecs;
     const int Sm1 = s.S - 1;
-    if ((vecs & 31) == 0) {
-        // rows of whole warps' width: the target index is uniform across the warp
-        for (int j0 = 0; j0 < nt; j0 += kUnroll) {
-            const unsigned char* pl[kUnroll];
-            const unsigned char* pr[kUnroll];
-            float wj[kUnroll];
+    if (UNIFORM || (vecs & 31) == 0) {
+        for (int j0 = 0; j0 < nt; j0 += U) {
+            const unsigned char* pl[U];
+            const unsigned char* pr[U];
+            float wj[U];
 #pragma unroll
-            for (int u = 0; u < kUnroll; ++u) {
+            for (int u = 0; u < U; ++u) {
                 const int j = min(j0 + u, nt - 1);
                 const int lj = __shfl_sync(0xffffffffu, l, j);
                 wj[u] = __shfl_sync(0xffffffffu, w, j);
@@ -164,17 +167,17 @@ __device__ __forceinline__ void interp_chunk(const StreamArg& s, const unsigned 
                 pr[u] = src_b + static_cast<long long>(min(lj + 1, Sm1)) * s.row_bytes;
             }
             for (int c = lane; c < vecs; c += 32) {
-                V a[kUnroll], b[kUnroll];
+                V a[U], b[U];
                 const long long cb = static_cast<long long>(c) * VEC;
 #pragma unroll
-                for (int u = 0; u < kUnroll; ++u) {
+                for (int u = 0; u < U; ++u) {
                     if (j0 + u < nt) {
                         a[u] = load_row<V>(pl[u] + cb);
                         b[u] = load_row<V>(pr[u] + cb);
                     }
                 }
 #pragma unroll
-                for (int u = 0; u < kUnroll; ++u) {
+                for (int u = 0; u < U; ++u) {
                     if (j0 + u < nt) {
                         const V o = lerp_vec<ES, VEC>(a[u], b[u], wj[u], __fsub_rn(1.0f, wj[u]));
                         store_row<V>(out_t0 + static_cast<long long>(j0 + u) * out_row_bytes + s.col_bytes + cb, o);
@@ -183,46 +186,32 @@ __device__ __forceinline__ void interp_chunk(const StreamArg& s, const unsigned 
             }
         }
     } else {
-        // narrow or ragged rows: lanes walk the flat (target, vector) space
         const int total = nt * vecs;
-        for (int v0 = 0; v0 < total; v0 += 32 * kUnroll) {
-            V a[kUnroll], b[kUnroll];
-            float wj[kUnroll];
-            long long ob[kUnroll];
-            bool ok[kUnroll];
-#pragma unroll
-            for (int u = 0; u < kUnroll; ++u) {
-                const int v = v0 + u * 32 + lane;
-                ok[u] = v < total;
-                const int j = ok[u] ? (v / vecs) : 0;
-                const int c = ok[u] ? (v - j * vecs) : 0;
-                const int lj = __shfl_sync(0xffffffffu, l, j);
-                wj[u] = __shfl_sync(0xffffffffu, w, j);
+        for (int v0 = 0; v0 < total; v0 += 32) {   // warp-uniform trip count: every lane reaches the shuffles
+            const int v = v0 + lane;
+            const bool ok = v < total;
+            const int j = ok ? (v / vecs) : 0;
+            const int c = ok ? (v - j * vecs) : 0;
+            const int lj = __shfl_sync(0xffffffffu, l, j);
+            const float wj = __shfl_sync(0xffffffffu, w, j);
+            if (ok) {
                 const long long cb = static_cast<long long>(c) * VEC;
-                ob[u] = static_cast<long long>(j) * out_row_bytes + s.col_bytes + cb;
-                if (ok[u]) {
-                    a[u] = load_row<V>(src_b + static_cast<long long>(lj) * s.row_bytes + cb);
-                    b[u] = load_row<V>(src_b + static_cast<long long>(min(lj + 1, Sm1)) * s.row_bytes + cb);
-                }
-            }
-#pragma unroll
-            for (int u = 0; u < kUnroll; ++u) {
-                if (ok[u]) {
-                    const V o = lerp_vec<ES, VEC>(a[u], b[u], wj[u], __fsub_rn(1.0f, wj[u]));
-                    store_row<V>(out_t0 + ob[u], o);
-                }
+                const V a = load_row<V>(src_b + static_cast<long long>(lj) * s.row_bytes + cb);
+                const V b = load_row<V>(src_b + static_cast<long long>(min(lj + 1, Sm1)) * s.row_bytes + cb);
+                const V o = lerp_vec<ES, VEC>(a, b, wj, __fsub_rn(1.0f, wj));
+                store_row<V>(out_t0 + static_cast<long long>(j) * out_row_bytes + s.col_bytes + cb, o);
             }
         }
     }
 }
 
-// ---------------------------------------------------------------- kernel
+// ---------------------------------------------------------------- gather kernel
 
 // STAGED: timestamp rows live in shared memory; otherwise lanes search global memory
-// (rows too long for shared memory).
-template <int ES, int VEC, bool STAGED>
-__global__ void __launch_bounds__(32 * kMaxWarps)
-interp_kernel(const __grid_constant__ InterpParams p) {
+// (rows too long for shared memory).  Four CTAs of 256 threads per SM (64 registers).
+template <int ES, int VEC, bool STAGED, bool UNIFORM>
+__global__ void __launch_bounds__(32 * kMaxWarps, 4)
+interp_gather_kernel(const __grid_constant__ InterpParams p) {
     extern __shared__ __align__(16) float s_times[];
 
     const int lane = threadIdx.x & 31;
@@ -253,7 +242,8 @@ interp_kernel(const __grid_constant__ InterpParams p) {
         float w;
         bracket(a, s.S, tq, l, r, w);
         (void)r;
-        interp_chunk<ES, VEC>(s, s.data + b * s.S * s.row_bytes, out_t0, p.out_row_bytes, l, w, nt, lane);
+        interp_chunk<ES, VEC, UNIFORM, UNIFORM ? 2 : 1>(s, s.data + b * s.S * s.row_bytes, out_t0,
+                                                        p.out_row_bytes, l, w, nt, lane);
     }
 }
 
@@ -274,23 +264,258 @@ bracket_kernel(const float* __restrict__ st, const float* __restrict__ tt, long 
     }
 }
 
+// ---------------------------------------------------------------- block kernel (TMA-staged inputs)
+//
+// When the inputs of one batch item are small enough to sit in shared memory (the fusion
+// shapes: 48 KB for 30x512 + 100x64 + 200x12 bf16) a CTA fetches them whole with one bulk
+// asynchronous copy (TMA, cp.async.bulk) per stream, completes them on an mbarrier, and
+// computes its output rows out of shared memory.  Global memory then sees only large
+// contiguous reads (every input byte exactly once per CTA) and fully coalesced writes;
+// rows narrower than a warp access (24-byte IMU rows) and output rows that are only
+// 8-byte aligned cost nothing extra.  The unit of work is an 8-byte piece of an output
+// row (4 bf16 or 2 fp32), so every stream width must be a multiple of 8 bytes.
+
+constexpr int kBlockThreads = 256;
+constexpr int kBlockSmemLimit = 100 * 1024;     // keeps at least two CTAs per SM
+constexpr unsigned int kMbarSpinLimit = 1u << 22;
+
+struct BlockStream {
+    const unsigned char* data;
+    const float* times;
+    int S;
+    int row_bytes;
+    int half_off;       // first 8-byte piece of this stream inside an output row
+    int data_off;       // byte offset of the staged data in shared memory
+    int time_off;       // float offset of the staged time row
+    int block_bytes;    // S * row_bytes
+};
+
+struct BlockParams {
+    BlockStream s[RC_MAX_STREAMS];
+    const float* tt;
+    unsigned char* out;
+    long long out_block_bytes;  // T * out_row_bytes
+    int out_row_bytes;
+    int hpr;                    // 8-byte pieces per output row
+    int ns;
+    int T;
+    int tiles_t;
+    int rows_per_tile;
+    int times_base;             // byte offsets of the regions after the staged data
+    int brk_base;
+    unsigned int tx_bytes;      // sum of block_bytes
+};
+
+// how often a CTA gave up waiting for its bulk copies and fetched the data with plain loads
+__device__ unsigned int g_bulk_wait_timeouts = 0;
+
+__device__ __forceinline__ unsigned int smem_u32(const void* p) {
+    return static_cast<unsigned int>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(unsigned long long* bar, unsigned int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(smem_u32(bar)), "r"(count) : "memory");
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned long long* bar, unsigned int bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+// one thread: global -> this CTA's shared memory, completion counted in bytes on `bar`
+// (no multicast: source and destination belong to this GPU and this CTA)
+__device__ __forceinline__ void bulk_load(void* dst_smem, const void* src_gmem, unsigned int bytes,
+                                          unsigned long long* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 :: "r"(smem_u32(dst_smem)), "l"(src_gmem), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+// bounded wait on phase `parity`; false if the limit ran out
+__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned int parity) {
+    const unsigned int addr = smem_u32(bar);
+    for (unsigned int i = 0; i < kMbarSpinLimit; ++i) {
+        unsigned int done;
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+        if (done) return true;
+        if (i > 64) __nanosleep(64);
+    }
+    return false;
+}
+
+template <int ES>
+__global__ void __launch_bounds__(kBlockThreads)
+interp_block_kernel(const __grid_constant__ BlockParams p) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    unsigned long long* bar = reinterpret_cast<unsigned long long*>(smem);
+    float* s_times = reinterpret_cast<float*>(smem + p.times_base);
+    int* s_l = reinterpret_cast<int*>(smem + p.brk_base);
+    float* s_w = reinterpret_cast<float*>(smem + p.brk_base) + p.ns * p.rows_per_tile;
+    __shared__ int s_half_off[RC_MAX_STREAMS], s_data_off[RC_MAX_STREAMS], s_row_bytes[RC_MAX_STREAMS],
+        s_last_row[RC_MAX_STREAMS];
+
+    const int tid = threadIdx.x;
+    const int lane = tid & 31;
+    const int warp = tid >> 5;
+    const long long b = blockIdx.x / p.tiles_t;
+    const int tile = static_cast<int>(blockIdx.x - b * p.tiles_t);
+    const int t_begin = tile * p.rows_per_tile;
+    const int nrows = min(p.rows_per_tile, p.T - t_begin);
+
+    if (tid == 0) {
+        mbar_init(bar, 1);
+        mbar_expect_tx(bar, p.tx_bytes);
+        for (int k = 0; k < p.ns; ++k)
+            bulk_load(smem + p.s[k].data_off, p.s[k].data + b * p.s[k].block_bytes,
+                      static_cast<unsigned int>(p.s[k].block_bytes), bar);
+    }
+    if (tid < p.ns) {
+        s_half_off[tid] = p.s[tid].half_off;
+        s_data_off[tid] = p.s[tid].data_off;
+        s_row_bytes[tid] = p.s[tid].row_bytes;
+        s_last_row[tid] = p.s[tid].S - 1;
+    }
+    for (int k = 0; k < p.ns; ++k) {
+        const float* g = p.s[k].times + b * p.s[k].S;
+        float* d = s_times + p.s[k].time_off;
+        for (int i = tid; i < p.s[k].S; i += kBlockThreads) d[i] = __ldg(g + i);
+    }
+    __syncthreads();  // mbarrier initialised, time rows and stream table visible
+
+    // brackets of this tile's rows, one (stream, row) pair per thread
+    for (int i = tid; i < nrows * p.ns; i += kBlockThreads) {
+        const int k = i / nrows;
+        const int r = i - k * nrows;
+        int l, rr;
+        float w;
+        bracket(s_times + p.s[k].time_off, p.s[k].S, __ldg(p.tt + b * p.T + t_begin + r), l, rr, w);
+        (void)rr;
+        s_l[k * p.rows_per_tile + r] = l;
+        s_w[k * p.rows_per_tile + r] = w;
+    }
+
+    // wait for the staged data; a CTA whose wait runs out records it and fetches the same
+    // bytes with ordinary loads instead (a late bulk copy would only rewrite equal values)
+    const bool arrived = mbar_wait(bar, 0);
+    if (__syncthreads_or(!arrived)) {
+        if (tid == 0) atomicAdd(&g_bulk_wait_timeouts, 1u);
+        for (int k = 0; k < p.ns; ++k) {
+            const uint2* g = reinterpret_cast<const uint2*>(p.s[k].data + b * p.s[k].block_bytes);
+            uint2* d = reinterpret_cast<uint2*>(smem + p.s[k].data_off);
+            for (int i = tid; i < p.s[k].block_bytes / 8; i += kBlockThreads) d[i] = __ldg(g + i);
+        }
+        __syncthreads();
+    }
+
+    unsigned char* out_b = p.out + b * p.out_block_bytes;
+    const int ns = p.ns;
+    for (int r = warp; r < nrows; r += kBlockThreads / 32) {
+        unsigned char* out_row = out_b + static_cast<long long>(t_begin + r) * p.out_row_bytes;
+        for (int c = lane; c < p.hpr; c += 32) {
+            int k = 0;
+            for (int j = 1; j < ns; ++j) k += (c >= s_half_off[j]) ? 1 : 0;
+            const int cc = c - s_half_off[k];
+            const int l = s_l[k * p.rows_per_tile + r];
+            const float w = s_w[k * p.rows_per_tile + r];
+            const unsigned char* base = smem + s_data_off[k] + cc * 8;
+            const uint2 a = *reinterpret_cast<const uint2*>(base + l * s_row_bytes[k]);
+            const uint2 bb = *reinterpret_cast<const uint2*>(base + min(l + 1, s_last_row[k]) * s_row_bytes[k]);
+            const uint2 o = lerp_vec<ES, 8>(a, bb, w, __fsub_rn(1.0f, w));
+            __stcs(reinterpret_cast<uint2*>(out_row + c * 8), o);
+        }
+    }
+}
+
 // ---------------------------------------------------------------- host side
 
 template <int ES, int VEC>
-int launch_interp(const InterpParams& p, long long grid, int threads, size_t smem, bool staged,
+int launch_gather(const InterpParams& p, long long grid, int threads, size_t smem, bool staged, bool uniform,
                   cudaStream_t stream) {
+    const unsigned int g = static_cast<unsigned int>(grid);
     if (staged) {
-        auto* k = interp_kernel<ES, VEC, true>;
+        auto* ku = interp_gather_kernel<ES, VEC, true, true>;
+        auto* km = interp_gather_kernel<ES, VEC, true, false>;
         if (smem > 48 * 1024) {
-            RC_CUDA_TRY(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize,
+            RC_CUDA_TRY(cudaFuncSetAttribute(uniform ? ku : km, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              static_cast<int>(smem)));
         }
-        k<<<static_cast<unsigned int>(grid), threads, smem, stream>>>(p);
+        if (uniform) ku<<<g, threads, smem, stream>>>(p);
+        else         km<<<g, threads, smem, stream>>>(p);
     } else {
-        interp_kernel<ES, VEC, false><<<static_cast<unsigned int>(grid), threads, 0, stream>>>(p);
+        if (uniform) interp_gather_kernel<ES, VEC, false, true><<<g, threads, 0, stream>>>(p);
+        else         interp_gather_kernel<ES, VEC, false, false><<<g, threads, 0, stream>>>(p);
     }
     return rc::check_launch();
 }
+
+struct LiveStream {
+    const unsigned char* data;
+    const float* times;
+    long long S;
+    long long row_bytes;
+};
+
+// The TMA-staged block kernel applies when every stream width is a multiple of 8 bytes, every
+// per-item input block can be bulk-copied (16-byte aligned, multiple of 16 bytes), the inputs
+// of one item fit the shared-memory budget and most of them are actually used.
+bool try_launch_block(const LiveStream* ls, int ns, const float* tt, unsigned char* out, long long B, long long T,
+                      int es, int device, cudaStream_t stream, int* status) {
+    BlockParams p{};
+    long long in_bytes = 0, out_row = 0;
+    int data_off = 16, time_off = 0;
+    for (int k = 0; k < ns; ++k) {
+        const long long blk = ls[k].S * ls[k].row_bytes;
+        if ((ls[k].row_bytes & 7) != 0 || (blk & 15) != 0 || !rc::aligned_to(ls[k].data, 16)) return false;
+        if (blk > kBlockSmemLimit) return false;
+        BlockStream& s = p.s[k];
+        s.data = ls[k].data;
+        s.times = ls[k].times;
+        s.S = static_cast<int>(ls[k].S);
+        s.row_bytes = static_cast<int>(ls[k].row_bytes);
+        s.half_off = static_cast<int>(out_row / 8);
+        s.data_off = data_off;
+        s.time_off = time_off;
+        s.block_bytes = static_cast<int>(blk);
+        data_off += static_cast<int>(blk);
+        time_off += static_cast<int>(ls[k].S);
+        in_bytes += blk;
+        out_row += ls[k].row_bytes;
+        if (data_off > kBlockSmemLimit) return false;
+    }
+    if (!rc::aligned_to(out, 8) || out_row > (1 << 20)) return false;
+    if (in_bytes > 2 * T * out_row) return false;  // mostly unused inputs: gathering rows moves fewer bytes
+    // rows per CTA: whole items when there are plenty of them, slices of an item otherwise
+    const int sms = rc::sm_count(device);
+    long long tiles = 1;
+    if (B < 2ll * sms) {
+        tiles = (2ll * sms + B - 1) / B;
+        const long long max_tiles = (T + 7) / 8;  // at least one row per warp
+        if (tiles > max_tiles) tiles = max_tiles;
+    }
+    const long long rpt = (T + tiles - 1) / tiles;
+    tiles = (T + rpt - 1) / rpt;
+    p.times_base = (data_off + 15) & ~15;
+    p.brk_base = p.times_base + ((time_off * 4 + 15) & ~15);
+    const long long smem = p.brk_base + rpt * ns * 8;
+    if (smem > kBlockSmemLimit || B * tiles >= (1ll << 31)) return false;
+    p.tt = tt;
+    p.out = out;
+    p.out_block_bytes = T * out_row;
+    p.out_row_bytes = static_cast<int>(out_row);
+    p.hpr = static_cast<int>(out_row / 8);
+    p.ns = ns;
+    p.T = static_cast<int>(T);
+    p.tiles_t = static_cast<int>(tiles);
+    p.rows_per_tile = static_cast<int>(rpt);
+    p.tx_bytes = static_cast<unsigned int>(in_bytes);
+    auto* kern = (es == 2) ? interp_block_kernel<2> : interp_block_kernel<4>;
+    if (smem > 48 * 1024) {
+        const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                   static_cast<int>(smem));
+        if (e != cudaSuccess) { *status = rc::cuda_fail(e); return true; }
+    }
+    kern<<<static_cast<unsigned int>(B * tiles), kBlockThreads, static_cast<size_t>(smem), stream>>>(p);
+    *status = rc::check_launch();
+    return true;
+}
+
+std::atomic<int> g_allow_block_kernel{1};
 
 int interp_dispatch(const rc_stream_desc* streams, int ns, const float* tt, void* out, int64_t B,
                     int64_t T, int dtype, int device, void* stream_v) {
@@ -301,12 +526,10 @@ int interp_dispatch(const rc_stream_desc* streams, int ns, const float* tt, void
     const int es = (dtype == RC_DTYPE_BF16) ? 2 : 4;
 
     long long out_d = 0;
-    long long staged_floats = 0;
     for (int k = 0; k < ns; ++k) {
         if (streams[k].S < 0 || streams[k].D < 0) return RC_ERR_BAD_SHAPE;
         if (streams[k].S >= (1ll << 31) || streams[k].D >= (1ll << 31)) return RC_ERR_TOO_LARGE;
         out_d += streams[k].D;
-        staged_floats += streams[k].S;
     }
     if (T >= (1ll << 31)) return RC_ERR_TOO_LARGE;
     if (B == 0 || T == 0 || out_d == 0) return RC_OK;  // nothing to write
@@ -316,42 +539,57 @@ int interp_dispatch(const rc_stream_desc* streams, int ns, const float* tt, void
     if (tt == nullptr || out == nullptr) return RC_ERR_NULL_POINTER;
     if (!rc::aligned_to(tt, 4) || !rc::aligned_to(out, es)) return RC_ERR_BAD_ALIGNMENT;
 
+    // streams with D == 0 own an empty column slice and are dropped here
+    LiveStream ls[RC_MAX_STREAMS];
+    int live = 0;
+    for (int k = 0; k < ns; ++k) {
+        if (streams[k].D == 0) continue;
+        if (streams[k].data == nullptr || streams[k].times == nullptr) return RC_ERR_NULL_POINTER;
+        if (!rc::aligned_to(streams[k].data, es) || !rc::aligned_to(streams[k].times, 4))
+            return RC_ERR_BAD_ALIGNMENT;
+        ls[live++] = LiveStream{static_cast<const unsigned char*>(streams[k].data), streams[k].times,
+                                streams[k].S, streams[k].D * es};
+    }
+
+    rc::DeviceScope scope(device);
+    if (scope.status() != RC_OK) return scope.status();
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+
+    if (g_allow_block_kernel.load(std::memory_order_relaxed)) {
+        int status = RC_OK;
+        if (try_launch_block(ls, live, tt, static_cast<unsigned char*>(out), B, T, es, device, stream, &status))
+            return status;
+    }
+
     InterpParams p{};
-    p.ns = ns;
+    p.ns = live;
     p.tt = tt;
     p.out = static_cast<unsigned char*>(out);
     p.out_row_bytes = out_d * es;
     p.T = static_cast<int>(T);
-
     // widest access every row, slice and pointer allows
     uintptr_t bits = reinterpret_cast<uintptr_t>(out) | static_cast<uintptr_t>(p.out_row_bytes);
     long long col = 0;
     int smem_off = 0;
-    int live = 0;
-    for (int k = 0; k < ns; ++k) {
-        if (streams[k].D == 0) continue;  // an empty slice contributes nothing
-        if (streams[k].data == nullptr || streams[k].times == nullptr) return RC_ERR_NULL_POINTER;
-        if (!rc::aligned_to(streams[k].data, es) || !rc::aligned_to(streams[k].times, 4))
-            return RC_ERR_BAD_ALIGNMENT;
-        StreamArg& s = p.s[live++];
-        s.data = static_cast<const unsigned char*>(streams[k].data);
-        s.times = streams[k].times;
-        s.S = static_cast<int>(streams[k].S);
-        s.row_bytes = streams[k].D * es;
+    for (int k = 0; k < live; ++k) {
+        StreamArg& s = p.s[k];
+        s.data = ls[k].data;
+        s.times = ls[k].times;
+        s.S = static_cast<int>(ls[k].S);
+        s.row_bytes = ls[k].row_bytes;
         s.col_bytes = col;
         s.smem_off = smem_off;
         smem_off += (s.S + 3) & ~3;  // keep every staged row 16-byte aligned
-        bits |= reinterpret_cast<uintptr_t>(s.data) | static_cast<uintptr_t>(s.row_bytes) |
-                static_cast<uintptr_t>(col);
+        bits |= reinterpret_cast<uintptr_t>(s.data) | static_cast<uintptr_t>(s.row_bytes) | static_cast<uintptr_t>(col);
         col += s.row_bytes;
     }
-    p.ns = live;
     int vec = 16;
     while (vec > es && (bits & (vec - 1)) != 0) vec >>= 1;
-    for (int k = 0; k < live; ++k) p.s[k].vecs = static_cast<int>(p.s[k].row_bytes / vec);
-
-    rc::DeviceScope scope(device);
-    if (scope.status() != RC_OK) return scope.status();
+    bool uniform = true;
+    for (int k = 0; k < live; ++k) {
+        p.s[k].vecs = static_cast<int>(p.s[k].row_bytes / vec);
+        uniform = uniform && (p.s[k].vecs % 32 == 0);
+    }
 
     // warps per CTA: enough to cover a target row, fewer when the grid would be too small
     int warps = 1;
@@ -364,22 +602,19 @@ int interp_dispatch(const rc_stream_desc* streams, int ns, const float* tt, void
 
     const size_t smem = static_cast<size_t>(smem_off) * sizeof(float);
     const bool staged = smem <= static_cast<size_t>(kMaxStagedBytes);
-    (void)staged_floats;
-    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
     const int threads = warps * 32;
-
     if (es == 2) {
         switch (vec) {
-            case 16: return launch_interp<2, 16>(p, grid, threads, smem, staged, stream);
-            case 8:  return launch_interp<2, 8>(p, grid, threads, smem, staged, stream);
-            case 4:  return launch_interp<2, 4>(p, grid, threads, smem, staged, stream);
-            default: return launch_interp<2, 2>(p, grid, threads, smem, staged, stream);
+            case 16: return launch_gather<2, 16>(p, grid, threads, smem, staged, uniform, stream);
+            case 8:  return launch_gather<2, 8>(p, grid, threads, smem, staged, uniform, stream);
+            case 4:  return launch_gather<2, 4>(p, grid, threads, smem, staged, uniform, stream);
+            default: return launch_gather<2, 2>(p, grid, threads, smem, staged, uniform, stream);
         }
     }
     switch (vec) {
-        case 16: return launch_interp<4, 16>(p, grid, threads, smem, staged, stream);
-        case 8:  return launch_interp<4, 8>(p, grid, threads, smem, staged, stream);
-        default: return launch_interp<4, 4>(p, grid, threads, smem, staged, stream);
+        case 16: return launch_gather<4, 16>(p, grid, threads, smem, staged, uniform, stream);
+        case 8:  return launch_gather<4, 8>(p, grid, threads, smem, staged, uniform, stream);
+        default: return launch_gather<4, 4>(p, grid, threads, smem, staged, uniform, stream);
     }
 }
 
@@ -418,6 +653,22 @@ int rc_resample_brackets(const float* source_times, const float* target_times, i
     bracket_kernel<<<static_cast<unsigned int>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
         source_times, target_times, B, static_cast<int>(S), static_cast<int>(T), left, right, weight);
     return rc::check_launch();
+}
+
+int rc_set_option(int option, int value) {
+    if (option == RC_OPT_BLOCK_KERNEL) {
+        g_allow_block_kernel.store(value != 0, std::memory_order_relaxed);
+        return RC_OK;
+    }
+    return RC_ERR_BAD_VALUE;
+}
+
+int rc_bulk_wait_timeouts(int device, unsigned int* count_host) {
+    if (count_host == nullptr) return RC_ERR_NULL_POINTER;
+    rc::DeviceScope scope(device);
+    if (scope.status() != RC_OK) return scope.status();
+    RC_CUDA_TRY(cudaMemcpyFromSymbol(count_host, g_bulk_wait_timeouts, sizeof(unsigned int)));
+    return RC_OK;
 }
 
 }  // extern "C"

@@ -58,3 +58,12 @@ def cuda_lib():
     """The built CUDA library; on a GPU box its absence is a failure."""
     from robogoat_b200 import _lib
     return _lib.load()
+
+
+@pytest.fixture(params=["staged-block", "row-gather"])
+def kernel_choice(request, cuda_lib):
+    """Runs a test once with the TMA-staged block kernel allowed (it is used where shapes qualify)
+    and once with the row-gather kernel forced; both must produce the same bits."""
+    cuda_lib.rc_set_option(0, 1 if request.param == "staged-block" else 0)
+    yield request.param
+    cuda_lib.rc_set_option(0, 1)

@@ -9,7 +9,7 @@ from conftest import golden_names, load_golden
 from robogoat_b200 import ops, workloads
 from test_resample_gpu import DEV, assert_exact
 
-pytestmark = pytest.mark.gpu
+pytestmark = [pytest.mark.gpu, pytest.mark.usefixtures("kernel_choice")]
 
 
 def expected(args):
@@ -109,3 +109,11 @@ def test_throughput_size_properties(cuda_lib):
         assert_exact(out[sl].cpu(), expected(cpu_args), f"slice {sl}")
     vis = robocache.resample_trajectories(a[0], a[1], a[6])
     assert torch.equal(vis.view(torch.int16), out[:, :, :512].contiguous().view(torch.int16))
+
+
+def test_no_bulk_copy_wait_ever_ran_out(cuda_lib):
+    """The bounded mbarrier wait of the staged kernel is a safety net; it must not have fired."""
+    import ctypes
+    n = ctypes.c_uint32(12345)
+    assert cuda_lib.rc_bulk_wait_timeouts(0, ctypes.byref(n)) == 0
+    assert n.value == 0

@@ -9,7 +9,7 @@ import robocache
 from conftest import bits, golden_names, load_golden
 from robogoat_b200 import ops, workloads
 
-pytestmark = pytest.mark.gpu
+pytestmark = [pytest.mark.gpu, pytest.mark.usefixtures("kernel_choice")]
 DEV = "cuda:0"
 
 
