@@ -1,0 +1,144 @@
+"""Multi-GPU harness: one process per GPU, ``torch.distributed`` for the plumbing.
+
+* Resampling and fusion shard over independent batch rows: contiguous ceil-div slices of ``B``
+  (the rule of robocache/kernels/cutlass/multi_gpu.cuh:344-367).  No collective is needed to
+  compute a shard; gathering the outputs is optional.
+* Voxelisation shards over points.  Every rank bins its slice into a private full grid, the
+  partial grids are combined with one collective — ``MAX`` for occupancy (as
+  robocache/tests/test_multi_gpu.py:76 does), ``SUM`` for counts and feature sums — and means are
+  normalised after the reduce, each rank on its own slab of voxels when ``slab_normalize`` is set.
+
+The collective helpers only call ``torch.distributed`` and work on any backend (NCCL on GPUs; the
+CPU test-suite drives them with gloo).  The ``*_sharded`` operators call the CUDA kernels.
+"""
+from __future__ import annotations
+
+from typing import Optional, Sequence, Tuple
+
+import torch
+import torch.distributed as dist
+
+
+def world(group=None) -> Tuple[int, int]:
+    """(rank, world_size); (0, 1) when no process group is initialised."""
+    if dist.is_available() and dist.is_initialized():
+        return dist.get_rank(group), dist.get_world_size(group)
+    return 0, 1
+
+
+def shard_bounds(n: int, rank: int, world_size: int) -> Tuple[int, int]:
+    """Contiguous ceil-div slice [begin, end) of ``n`` items owned by ``rank``; trailing ranks may be empty."""
+    if world_size <= 0 or not (0 <= rank < world_size):
+        raise ValueError(f"bad rank {rank} for world size {world_size}")
+    per = (n + world_size - 1) // world_size
+    begin = min(n, rank * per)
+    return begin, min(n, begin + per)
+
+
+def shard_rows(tensors: Sequence[torch.Tensor], rank: int, world_size: int) -> list:
+    """The rank's slice of dimension 0 of every tensor (all must share that dimension)."""
+    n = tensors[0].shape[0]
+    for t in tensors:
+        if t.shape[0] != n:
+            raise RuntimeError("Batch size mismatch")
+    a, b = shard_bounds(n, rank, world_size)
+    return [t[a:b] for t in tensors]
+
+
+def gather_rows(local: torch.Tensor, total_rows: int, group=None) -> torch.Tensor:
+    """All-gather of ceil-div row shards back into a [total_rows, ...] tensor on every rank."""
+    rank, ws = world(group)
+    if ws == 1:
+        return local
+    per = (total_rows + ws - 1) // ws
+    padded = local
+    if local.shape[0] < per:  # trailing shards are shorter: pad so every rank sends the same size
+        pad = torch.zeros((per - local.shape[0],) + tuple(local.shape[1:]), dtype=local.dtype, device=local.device)
+        padded = torch.cat([local, pad], dim=0)
+    out = torch.empty((ws * per,) + tuple(local.shape[1:]), dtype=local.dtype, device=local.device)
+    dist.all_gather_into_tensor(out, padded.contiguous(), group=group)
+    return out[:total_rows]
+
+
+def reduce_partial_grids(grid: torch.Tensor, counts: Optional[torch.Tensor], mode: str, group=None) -> None:
+    """In-place reduce of per-rank partial voxel grids over the group.
+
+    occupancy: element-wise MAX (union); count: SUM of int32 counts (exact); mean: SUM of the fp32
+    feature sums and of the int32 counts (call before normalising); max: element-wise MAX.
+    """
+    _, ws = world(group)
+    if ws == 1:
+        return
+    if mode == "occupancy":
+        dist.all_reduce(grid, op=dist.ReduceOp.MAX, group=group)
+    elif mode == "count":
+        dist.all_reduce(grid, op=dist.ReduceOp.SUM, group=group)
+    elif mode == "mean":
+        if counts is None:
+            raise RuntimeError("mean mode reduces counts together with the feature sums")
+        dist.all_reduce(grid, op=dist.ReduceOp.SUM, group=group)
+        dist.all_reduce(counts, op=dist.ReduceOp.SUM, group=group)
+    elif mode == "max":
+        dist.all_reduce(grid, op=dist.ReduceOp.MAX, group=group)
+    else:
+        raise RuntimeError(f"Invalid mode: {mode}. Must be 'count', 'occupancy', 'mean', or 'max'")
+
+
+# ----------------------------------------------------------------------------- sharded operators (CUDA)
+
+def resample_sharded(source_data, source_times, target_times, gather: bool = False, group=None) -> torch.Tensor:
+    """Each rank resamples its batch slice of the (replicated or host-resident) inputs.
+
+    Returns the rank's [rows, T, D] shard, or the full [B, T, D] on every rank with ``gather=True``.
+    """
+    from . import ops
+    rank, ws = world(group)
+    dev = torch.device("cuda", torch.cuda.current_device())
+    src, st, tt = (t.to(dev, non_blocking=True) for t in shard_rows([source_data, source_times, target_times], rank, ws))
+    out = ops.resample_trajectories_cuda(src, st, tt)
+    return gather_rows(out, source_data.shape[0], group) if gather else out
+
+
+def fuse_sharded(s1, t1, s2, t2, s3, t3, target_times, gather: bool = False, group=None) -> torch.Tensor:
+    """Batch-sharded three-stream fusion; see ``resample_sharded``."""
+    from . import ops
+    rank, ws = world(group)
+    dev = torch.device("cuda", torch.cuda.current_device())
+    parts = [t.to(dev, non_blocking=True) for t in shard_rows([s1, t1, s2, t2, s3, t3, target_times], rank, ws)]
+    out = ops.fuse_multimodal_cuda(*parts)
+    return gather_rows(out, s1.shape[0], group) if gather else out
+
+
+def voxelize_sharded(points_local: torch.Tensor, features_local: Optional[torch.Tensor] = None,
+                     grid_min=(-10.0, -10.0, -10.0), voxel_size: float = 0.1, grid_size=(128, 128, 128),
+                     mode: str = "occupancy", slab_normalize: bool = False, group=None) -> torch.Tensor:
+    """Voxelise a point cloud whose points are spread over the ranks.
+
+    ``points_local`` / ``features_local`` are this rank's points (on its GPU).  Every rank returns the
+    grid of the union cloud: occupancy/count bit-identical to a single-GPU run on all points, means
+    equal up to fp32 summation order.  With ``slab_normalize`` each rank normalises only its own
+    ceil-div slab of voxels and the slabs are all-gathered (less normalisation work per rank).
+    """
+    from . import ops
+    rank, ws = world(group)
+    occupancy_dtype = torch.uint8 if (mode == "occupancy" and ws > 1) else torch.int32  # 4x smaller reduce payload
+    res = ops.voxelize_pointcloud_cuda(points_local, features_local, list(grid_min), float(voxel_size), list(grid_size),
+                                       mode, normalize=(ws == 1), occupancy_dtype=occupancy_dtype)
+    grid = res[0]
+    counts = res[1] if mode == "mean" else None
+    if ws == 1:
+        return grid
+    reduce_partial_grids(grid, counts, mode, group)
+    if mode == "occupancy":
+        return grid.to(torch.int32)
+    if mode == "mean":
+        V = counts.numel()
+        if slab_normalize:
+            a, b = shard_bounds(V, rank, ws)
+            ops.voxel_normalize_cuda(grid, counts, a, b)
+            F = grid.shape[-1]
+            flat = grid.view(V, F)
+            full = gather_rows(flat[a:b], V, group)
+            return full.view(grid.shape)
+        ops.voxel_normalize_cuda(grid, counts, 0, V)
+    return grid

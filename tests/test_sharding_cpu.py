@@ -1,0 +1,128 @@
+"""Host logic of the multi-GPU harness on CPU: shard arithmetic, and the gather / reduce helpers run as
+two gloo ranks.  The per-rank partial results are made with the CPU oracle here (in the product they
+come from the CUDA kernels); what is under test is the partition rule and the collective semantics:
+occupancy MAX, count SUM (exact), feature-sum SUM then normalise, batch-row gather."""
+import datetime
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+import oracle
+from robogoat_b200 import sharding, workloads
+
+
+def test_shard_bounds_partition():
+    for n in (0, 1, 7, 4096, 16385):
+        for ws in (1, 2, 3, 4, 8):
+            spans = [sharding.shard_bounds(n, r, ws) for r in range(ws)]
+            assert spans[0][0] == 0 and spans[-1][1] == n
+            for (a, b), (c, d) in zip(spans, spans[1:]):
+                assert b == c and a <= b
+            per = (n + ws - 1) // ws
+            assert all(b - a <= per for a, b in spans)
+    assert sharding.shard_bounds(4096, 7, 8) == (3584, 4096)
+    assert sharding.shard_bounds(16384, 3, 8) == (6144, 8192)
+    with pytest.raises(ValueError):
+        sharding.shard_bounds(10, 2, 2)
+    assert sharding.world() == (0, 1)
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, ws, port, fn, ret):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=ws, timeout=datetime.timedelta(seconds=60))
+    try:
+        ret[rank] = fn(rank, ws)
+    finally:
+        dist.destroy_process_group()
+
+
+def _run(fn, ws=2):
+    ctx = mp.get_context("spawn")
+    ret = ctx.Manager().dict()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, ws, port, fn, ret)) for r in range(ws)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(120)
+        assert p.exitcode == 0
+    return dict(ret)
+
+
+def _batch_job(rank, ws):
+    B = 7                                                       # odd: the last shard is shorter
+    src, st, tt = workloads.resample_inputs(B=B, S=40, D=12, T=9, irregular_targets=True, seed=3)
+    full = oracle.resample_trajectories(src, st, tt)
+    s, t, q = sharding.shard_rows([src, st, tt], rank, ws)
+    local = oracle.resample_trajectories(s, t, q) if s.shape[0] else torch.empty(0, 9, 12)
+    got = sharding.gather_rows(local, B)
+    return bool(torch.equal(got, full)) and local.shape[0] == (4 if rank == 0 else 3)
+
+
+def _voxel_job(rank, ws):
+    g = torch.Generator().manual_seed(9)
+    pts = torch.rand(20_001, 3, generator=g) * 4 - 2
+    feats = torch.randn(20_001, 4, generator=g)
+    kw = dict(grid_min=[-1.5, -1.5, -1.5], voxel_size=0.25, grid_size=[12, 12, 12])
+    a, b = sharding.shard_bounds(pts.shape[0], rank, ws)
+    ok = True
+    for mode in ("occupancy", "count"):
+        full = oracle.voxelize_pointcloud(pts, None, mode=mode, **kw)
+        part = oracle.voxelize_pointcloud(pts[a:b], None, mode=mode, **kw)
+        sharding.reduce_partial_grids(part, None, mode)
+        ok = ok and bool(torch.equal(part, full))
+    full, fcnt, sabs = oracle.voxelize_pointcloud(pts, feats, mode="mean", return_aux=True, **kw)
+    mean, cnt, _ = oracle.voxelize_pointcloud(pts[a:b], feats[a:b], mode="mean", return_aux=True, **kw)
+    sums = mean * cnt.unsqueeze(-1)                             # partial feature sums of this rank
+    sharding.reduce_partial_grids(sums, cnt, "mean")
+    ok = ok and bool(torch.equal(cnt, fcnt))
+    merged = torch.where(cnt.unsqueeze(-1) > 0, sums * (1.0 / cnt.clamp(min=1)).unsqueeze(-1), torch.zeros_like(sums))
+    tol = oracle.mean_tolerance(fcnt, sabs, full) + 1e-6
+    ok = ok and bool(((merged - full).abs() <= tol).all())
+    try:
+        sharding.reduce_partial_grids(sums, None, "mean")
+        ok = False
+    except RuntimeError:
+        pass
+    return ok
+
+
+def test_batch_shards_gather_to_the_unsharded_result():
+    assert _run(_batch_job) == {0: True, 1: True}
+
+
+def test_partial_grids_reduce_to_the_single_process_grid():
+    assert _run(_voxel_job) == {0: True, 1: True}
+
+
+def _lonely_rank(port, q):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    try:
+        dist.init_process_group("gloo", rank=0, world_size=2, timeout=datetime.timedelta(seconds=3))
+        t = torch.ones(4)
+        dist.all_reduce(t)
+        q.put("completed")
+    except Exception as e:  # the missing peer must surface as an error on the host, not a hang
+        q.put("error:" + type(e).__name__)
+
+
+def test_a_rank_that_never_joins_is_reported_not_waited_for_forever():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    p = ctx.Process(target=_lonely_rank, args=(_free_port(), q))
+    p.start()
+    p.join(60)
+    assert not p.is_alive(), "rendezvous did not time out"
+    assert q.get(timeout=5).startswith("error:")
