@@ -152,9 +152,14 @@ RC_API int rc_voxelize_mean_static(const float* points, const float* features, f
 /*
  * Process-wide switches, for tests and profiling.  RC_OPT_BLOCK_KERNEL (default 1): let
  * rc_resample / rc_fuse use the TMA-staged kernel when the shapes qualify; 0 forces the
- * row-gather kernel.  Both kernels produce identical bits.  No counterpart in the reference.
+ * row-gather kernel.  Both kernels produce identical bits.
+ * RC_OPT_VOXEL_PASSES (default 0 = choose automatically): number of slab passes of the count /
+ * mean / max scatter; each pass re-reads the coordinates but scatters into only 1/passes of the
+ * grid, which keeps the touched part of large sparse grids resident in L2.
+ * No counterpart in the reference.
  */
 #define RC_OPT_BLOCK_KERNEL 0
+#define RC_OPT_VOXEL_PASSES 1
 RC_API int rc_set_option(int option, int value);
 
 /*

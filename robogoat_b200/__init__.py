@@ -16,6 +16,8 @@ from .api import (  # noqa: F401
     voxelize_pointcloud,
 )
 
+from .host_pipeline import resample_trajectories_host  # noqa: E402,F401  (host-buffer entry point, not part of the reference API)
+
 __all__ = [
     "resample_trajectories", "fuse_multimodal", "voxelize_pointcloud", "voxelize_occupancy",
     "is_cuda_available", "check_installation", "self_test", "print_installation_info", "__version__",

@@ -345,10 +345,10 @@ interp_block_kernel(const __grid_constant__ BlockParams p) {
     extern __shared__ __align__(128) unsigned char smem[];
     unsigned long long* bar = reinterpret_cast<unsigned long long*>(smem);
     float* s_times = reinterpret_cast<float*>(smem + p.times_base);
-    int* s_l = reinterpret_cast<int*>(smem + p.brk_base);
-    float* s_w = reinterpret_cast<float*>(smem + p.brk_base) + p.ns * p.rows_per_tile;
-    __shared__ int s_half_off[RC_MAX_STREAMS], s_data_off[RC_MAX_STREAMS], s_row_bytes[RC_MAX_STREAMS],
-        s_last_row[RC_MAX_STREAMS];
+    // per (stream, row of this tile): shared-memory byte offsets of the two bracket rows, and the weight
+    int* s_lo = reinterpret_cast<int*>(smem + p.brk_base);
+    int* s_hi = s_lo + p.ns * p.rows_per_tile;
+    float* s_w = reinterpret_cast<float*>(s_hi + p.ns * p.rows_per_tile);
 
     const int tid = threadIdx.x;
     const int lane = tid & 31;
@@ -365,34 +365,31 @@ interp_block_kernel(const __grid_constant__ BlockParams p) {
             bulk_load(smem + p.s[k].data_off, p.s[k].data + b * p.s[k].block_bytes,
                       static_cast<unsigned int>(p.s[k].block_bytes), bar);
     }
-    if (tid < p.ns) {
-        s_half_off[tid] = p.s[tid].half_off;
-        s_data_off[tid] = p.s[tid].data_off;
-        s_row_bytes[tid] = p.s[tid].row_bytes;
-        s_last_row[tid] = p.s[tid].S - 1;
-    }
     for (int k = 0; k < p.ns; ++k) {
         const float* g = p.s[k].times + b * p.s[k].S;
         float* d = s_times + p.s[k].time_off;
         for (int i = tid; i < p.s[k].S; i += kBlockThreads) d[i] = __ldg(g + i);
     }
-    __syncthreads();  // mbarrier initialised, time rows and stream table visible
+    __syncthreads();  // mbarrier initialised, time rows visible
 
     // brackets of this tile's rows, one (stream, row) pair per thread
     for (int i = tid; i < nrows * p.ns; i += kBlockThreads) {
         const int k = i / nrows;
         const int r = i - k * nrows;
+        const BlockStream& s = p.s[k];
         int l, rr;
         float w;
-        bracket(s_times + p.s[k].time_off, p.s[k].S, __ldg(p.tt + b * p.T + t_begin + r), l, rr, w);
-        (void)rr;
-        s_l[k * p.rows_per_tile + r] = l;
+        bracket(s_times + s.time_off, s.S, __ldg(p.tt + b * p.T + t_begin + r), l, rr, w);
+        s_lo[k * p.rows_per_tile + r] = s.data_off + l * s.row_bytes;
+        s_hi[k * p.rows_per_tile + r] = s.data_off + rr * s.row_bytes;
         s_w[k * p.rows_per_tile + r] = w;
     }
 
-    // wait for the staged data; a CTA whose wait runs out records it and fetches the same
-    // bytes with ordinary loads instead (a late bulk copy would only rewrite equal values)
-    const bool arrived = mbar_wait(bar, 0);
+    // One thread waits for the staged data (bounded); the others park at the barrier.  A CTA
+    // whose wait runs out records it and fetches the same bytes with ordinary loads instead
+    // (a late bulk copy would only rewrite equal values).
+    bool arrived = true;
+    if (tid == 0) arrived = mbar_wait(bar, 0);
     if (__syncthreads_or(!arrived)) {
         if (tid == 0) atomicAdd(&g_bulk_wait_timeouts, 1u);
         for (int k = 0; k < p.ns; ++k) {
@@ -403,21 +400,25 @@ interp_block_kernel(const __grid_constant__ BlockParams p) {
         __syncthreads();
     }
 
-    unsigned char* out_b = p.out + b * p.out_block_bytes;
-    const int ns = p.ns;
-    for (int r = warp; r < nrows; r += kBlockThreads / 32) {
-        unsigned char* out_row = out_b + static_cast<long long>(t_begin + r) * p.out_row_bytes;
-        for (int c = lane; c < p.hpr; c += 32) {
-            int k = 0;
-            for (int j = 1; j < ns; ++j) k += (c >= s_half_off[j]) ? 1 : 0;
-            const int cc = c - s_half_off[k];
-            const int l = s_l[k * p.rows_per_tile + r];
-            const float w = s_w[k * p.rows_per_tile + r];
-            const unsigned char* base = smem + s_data_off[k] + cc * 8;
-            const uint2 a = *reinterpret_cast<const uint2*>(base + l * s_row_bytes[k]);
-            const uint2 bb = *reinterpret_cast<const uint2*>(base + min(l + 1, s_last_row[k]) * s_row_bytes[k]);
+    // Each lane owns the 8-byte pieces c = lane, lane+32, ... of an output row; which stream a
+    // piece belongs to does not depend on the row, so it is resolved once per piece and the
+    // warp then walks its rows (warp, warp+8, ...) with that piece fixed.
+    unsigned char* out_tile = p.out + b * p.out_block_bytes + static_cast<long long>(t_begin) * p.out_row_bytes;
+    for (int c = lane; c < p.hpr; c += 32) {
+        int k = 0;
+        for (int j = 1; j < p.ns; ++j) k += (c >= p.s[j].half_off) ? 1 : 0;
+        const int cc8 = (c - p.s[k].half_off) * 8;
+        const int* lo = s_lo + k * p.rows_per_tile;
+        const int* hi = s_hi + k * p.rows_per_tile;
+        const float* ww = s_w + k * p.rows_per_tile;
+        unsigned char* out_c = out_tile + c * 8;
+#pragma unroll 2
+        for (int r = warp; r < nrows; r += kBlockThreads / 32) {
+            const float w = ww[r];
+            const uint2 a = *reinterpret_cast<const uint2*>(smem + lo[r] + cc8);
+            const uint2 bb = *reinterpret_cast<const uint2*>(smem + hi[r] + cc8);
             const uint2 o = lerp_vec<ES, 8>(a, bb, w, __fsub_rn(1.0f, w));
-            __stcs(reinterpret_cast<uint2*>(out_row + c * 8), o);
+            __stcs(reinterpret_cast<uint2*>(out_c + static_cast<long long>(r) * p.out_row_bytes), o);
         }
     }
 }
@@ -492,7 +493,7 @@ bool try_launch_block(const LiveStream* ls, int ns, const float* tt, unsigned ch
     tiles = (T + rpt - 1) / rpt;
     p.times_base = (data_off + 15) & ~15;
     p.brk_base = p.times_base + ((time_off * 4 + 15) & ~15);
-    const long long smem = p.brk_base + rpt * ns * 8;
+    const long long smem = p.brk_base + rpt * ns * 12;
     if (smem > kBlockSmemLimit || B * tiles >= (1ll << 31)) return false;
     p.tt = tt;
     p.out = out;
@@ -514,8 +515,6 @@ bool try_launch_block(const LiveStream* ls, int ns, const float* tt, unsigned ch
     *status = rc::check_launch();
     return true;
 }
-
-std::atomic<int> g_allow_block_kernel{1};
 
 int interp_dispatch(const rc_stream_desc* streams, int ns, const float* tt, void* out, int64_t B,
                     int64_t T, int dtype, int device, void* stream_v) {
@@ -555,7 +554,7 @@ int interp_dispatch(const rc_stream_desc* streams, int ns, const float* tt, void
     if (scope.status() != RC_OK) return scope.status();
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
 
-    if (g_allow_block_kernel.load(std::memory_order_relaxed)) {
+    if (rc::g_allow_block_kernel.load(std::memory_order_relaxed)) {
         int status = RC_OK;
         if (try_launch_block(ls, live, tt, static_cast<unsigned char*>(out), B, T, es, device, stream, &status))
             return status;
@@ -653,14 +652,6 @@ int rc_resample_brackets(const float* source_times, const float* target_times, i
     bracket_kernel<<<static_cast<unsigned int>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
         source_times, target_times, B, static_cast<int>(S), static_cast<int>(T), left, right, weight);
     return rc::check_launch();
-}
-
-int rc_set_option(int option, int value) {
-    if (option == RC_OPT_BLOCK_KERNEL) {
-        g_allow_block_kernel.store(value != 0, std::memory_order_relaxed);
-        return RC_OK;
-    }
-    return RC_ERR_BAD_VALUE;
 }
 
 int rc_bulk_wait_timeouts(int device, unsigned int* count_host) {

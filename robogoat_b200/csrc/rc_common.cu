@@ -6,6 +6,8 @@
 namespace rc {
 
 thread_local int g_last_cuda_error = 0;
+std::atomic<int> g_allow_block_kernel{1};
+std::atomic<int> g_voxel_passes{0};
 
 // SM count per device, filled on first use (immutable hardware facts, not call state).
 static std::atomic<int> g_sm_count[64];
@@ -46,5 +48,18 @@ const char* rc_strerror(int status) {
 int rc_last_cuda_error(void) { return rc::g_last_cuda_error; }
 
 int rc_abi_version(void) { return RC_ABI_VERSION; }
+
+int rc_set_option(int option, int value) {
+    if (option == RC_OPT_BLOCK_KERNEL) {
+        rc::g_allow_block_kernel.store(value != 0, std::memory_order_relaxed);
+        return RC_OK;
+    }
+    if (option == RC_OPT_VOXEL_PASSES) {
+        if (value < 0 || value > 64) return RC_ERR_BAD_VALUE;
+        rc::g_voxel_passes.store(value, std::memory_order_relaxed);
+        return RC_OK;
+    }
+    return RC_ERR_BAD_VALUE;
+}
 
 }  // extern "C"

@@ -5,6 +5,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
+
 #include "robocache_b200.h"
 
 namespace rc {
@@ -67,5 +69,9 @@ inline int check_launch() {
 }
 
 int sm_count(int device);
+
+// process-wide switches behind rc_set_option
+extern std::atomic<int> g_allow_block_kernel;  // RC_OPT_BLOCK_KERNEL
+extern std::atomic<int> g_voxel_passes;        // RC_OPT_VOXEL_PASSES
 
 }  // namespace rc

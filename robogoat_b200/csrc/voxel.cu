@@ -18,6 +18,7 @@
 // occupied voxels by 1.0f / count (robocache/csrc/cuda/voxelize_kernel.cu:145-163).
 #include "rc_common.cuh"
 
+#include <atomic>
 #include <mutex>
 
 namespace {
@@ -92,95 +93,137 @@ __device__ __forceinline__ void load_tile(const float* __restrict__ pts, long lo
     }
 }
 
+// Scatter of one point tile.  `id_lo/id_hi` restrict the pass to a slab of voxel ids (a
+// contiguous range of the grid in memory); points outside the slab are skipped in this pass.
 template <int MODE, bool AGG>
 __global__ void __launch_bounds__(kThreads)
 voxel_bin_kernel(const float* __restrict__ pts, const float* __restrict__ feats, void* __restrict__ grid_v,
-                 int* __restrict__ counts, long long N, int F, VoxelGeom g, bool pts_aligned) {
+                 int* __restrict__ counts, long long N, int F, VoxelGeom g, bool pts_aligned,
+                 long long id_lo, long long id_hi) {
     __shared__ __align__(16) float s_xyz[kThreads / 32][kPointsPerWarp * 3];
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
-    const long long base = (static_cast<long long>(blockIdx.x) * (kThreads / 32) + warp) * kPointsPerWarp;
-    if (base >= N) return;
+    const long long ntiles = (N + kPointsPerWarp - 1) / kPointsPerWarp;
+    const long long warps_total = static_cast<long long>(gridDim.x) * (kThreads / 32);
+    const bool whole_grid = (id_lo <= 0) && (id_hi >= static_cast<long long>(g.gx) * g.gy * g.gz);
 
-    float x[kPointsPerLane], y[kPointsPerLane], z[kPointsPerLane];
-    load_tile(pts, base, N, pts_aligned && (base + kPointsPerWarp <= N), s_xyz[warp], lane, x, y, z);
+    for (long long tile = static_cast<long long>(blockIdx.x) * (kThreads / 32) + warp; tile < ntiles;
+         tile += warps_total) {
+        const long long base = tile * kPointsPerWarp;
+        const bool full = base + kPointsPerWarp <= N;
 
-    long long id[kPointsPerLane];
+        // mean mode, four channels, single pass: the feature rows are requested together with
+        // the coordinates so that every load of the tile is in flight at once
+        float4 fv[kPointsPerLane];
+        const bool eager = (MODE == kMean) && (F == 4) && full && whole_grid;
+        if (eager) {
 #pragma unroll
-    for (int i = 0; i < kPointsPerLane; ++i) id[i] = voxel_id(x[i], y[i], z[i], g);
-
-    if (MODE == kOccupancy) {
-        int* grid = static_cast<int*>(grid_v);
-#pragma unroll
-        for (int i = 0; i < kPointsPerLane; ++i)
-            if (id[i] >= 0) grid[id[i]] = 1;
-    } else if (MODE == kOccupancyU8) {
-        unsigned char* grid = static_cast<unsigned char*>(grid_v);
-#pragma unroll
-        for (int i = 0; i < kPointsPerLane; ++i)
-            if (id[i] >= 0) grid[id[i]] = 1;
-    } else if (MODE == kCount) {
-        int* grid = static_cast<int*>(grid_v);
-#pragma unroll
-        for (int i = 0; i < kPointsPerLane; ++i) {
-            if (AGG) {
-                // lanes holding the same voxel elect their lowest lane to add the group size
-                const unsigned int peers = __match_any_sync(0xffffffffu, id[i]);
-                if (id[i] >= 0 && lane == (__ffs(peers) - 1)) atomicAdd(grid + id[i], __popc(peers));
-            } else {
-                if (id[i] >= 0) atomicAdd(grid + id[i], 1);
-            }
+            for (int i = 0; i < kPointsPerLane; ++i)
+                fv[i] = __ldcs(reinterpret_cast<const float4*>(feats) + base + i * 32 + lane);
         }
-    } else if (MODE == kMean) {
-        float* grid = static_cast<float*>(grid_v);
+
+        float x[kPointsPerLane], y[kPointsPerLane], z[kPointsPerLane];
+        load_tile(pts, base, N, pts_aligned && full, s_xyz[warp], lane, x, y, z);
+
+        long long id[kPointsPerLane];
 #pragma unroll
         for (int i = 0; i < kPointsPerLane; ++i) {
-            const long long pi = base + i * 32 + lane;
-            if (id[i] < 0) continue;
-            const float* f = feats + pi * F;
-            float* o = grid + id[i] * F;
-            if ((F & 3) == 0) {
-                for (int c = 0; c < F; c += 4) red_add_v4(o + c, __ldcs(reinterpret_cast<const float4*>(f + c)));
-            } else if ((F & 1) == 0) {
-                for (int c = 0; c < F; c += 2) red_add_v2(o + c, __ldcs(reinterpret_cast<const float2*>(f + c)));
-            } else {
-                for (int c = 0; c < F; ++c) atomicAdd(o + c, __ldg(f + c));
-            }
-            atomicAdd(counts + id[i], 1);
+            id[i] = voxel_id(x[i], y[i], z[i], g);
+            if (!whole_grid && (id[i] < id_lo || id[i] >= id_hi)) id[i] = -1;
         }
-    } else {  // kMax: running maximum kept as an ordered integer, decoded by the fix-up pass
-        int* grid = static_cast<int*>(grid_v);
+
+        if (MODE == kOccupancy) {
+            int* grid = static_cast<int*>(grid_v);
 #pragma unroll
-        for (int i = 0; i < kPointsPerLane; ++i) {
-            const long long pi = base + i * 32 + lane;
-            if (id[i] < 0) continue;
-            for (int c = 0; c < F; ++c) atomicMax(grid + id[i] * F + c, float_ordered(__ldg(feats + pi * F + c)));
+            for (int i = 0; i < kPointsPerLane; ++i)
+                if (id[i] >= 0) grid[id[i]] = 1;
+        } else if (MODE == kOccupancyU8) {
+            unsigned char* grid = static_cast<unsigned char*>(grid_v);
+#pragma unroll
+            for (int i = 0; i < kPointsPerLane; ++i)
+                if (id[i] >= 0) grid[id[i]] = 1;
+        } else if (MODE == kCount) {
+            int* grid = static_cast<int*>(grid_v);
+#pragma unroll
+            for (int i = 0; i < kPointsPerLane; ++i) {
+                if (AGG) {
+                    // lanes holding the same voxel elect their lowest lane to add the group size
+                    const unsigned int peers = __match_any_sync(0xffffffffu, id[i]);
+                    if (id[i] >= 0 && lane == (__ffs(peers) - 1)) atomicAdd(grid + id[i], __popc(peers));
+                } else {
+                    if (id[i] >= 0) atomicAdd(grid + id[i], 1);
+                }
+            }
+        } else if (MODE == kMean) {
+            float* grid = static_cast<float*>(grid_v);
+#pragma unroll
+            for (int i = 0; i < kPointsPerLane; ++i) {
+                const long long pi = base + i * 32 + lane;
+                if (id[i] < 0) continue;
+                const float* f = feats + pi * F;
+                float* o = grid + id[i] * F;
+                if (eager) {
+                    red_add_v4(o, fv[i]);
+                } else if ((F & 3) == 0) {
+                    for (int c = 0; c < F; c += 4) red_add_v4(o + c, __ldcs(reinterpret_cast<const float4*>(f + c)));
+                } else if ((F & 1) == 0) {
+                    for (int c = 0; c < F; c += 2) red_add_v2(o + c, __ldcs(reinterpret_cast<const float2*>(f + c)));
+                } else {
+                    for (int c = 0; c < F; ++c) atomicAdd(o + c, __ldg(f + c));
+                }
+                atomicAdd(counts + id[i], 1);
+            }
+        } else {  // kMax: running maximum kept as an ordered integer, decoded by the fix-up pass
+            int* grid = static_cast<int*>(grid_v);
+#pragma unroll
+            for (int i = 0; i < kPointsPerLane; ++i) {
+                const long long pi = base + i * 32 + lane;
+                if (id[i] < 0) continue;
+                for (int c = 0; c < F; ++c) atomicMax(grid + id[i] * F + c, float_ordered(__ldg(feats + pi * F + c)));
+            }
         }
     }
 }
 
-// mean pass 2, wide form: four voxels per thread; counts + v0 is 16-byte aligned, (v1 - v0) % 4 == 0
+// mean pass 2, wide form: counts + v0 is 16-byte aligned and (v1 - v0) % 4 == 0.  A thread reads
+// kNormBatch groups of four counters at a time (all loads issued before any is used) and rescales the
+// feature sums of the occupied voxels among them; the grid is walked with a grid-wide stride.
+constexpr int kNormBatch = 4;
 template <bool VEC4>
 __global__ void __launch_bounds__(kThreads)
 voxel_normalize_wide_kernel(float* __restrict__ grid, const int* __restrict__ counts, long long v0, long long v1, int F) {
-    const long long v = v0 + (blockIdx.x * static_cast<long long>(kThreads) + threadIdx.x) * 4;
-    if (v >= v1) return;
-    const int4 c = __ldcs(reinterpret_cast<const int4*>(counts + v));
-    const int cc[4] = {c.x, c.y, c.z, c.w};
+    const long long quads = (v1 - v0) >> 2;
+    const long long nthreads = static_cast<long long>(gridDim.x) * kThreads;
+    const int4* c4 = reinterpret_cast<const int4*>(counts + v0);
+    for (long long q0 = blockIdx.x * static_cast<long long>(kThreads) + threadIdx.x; q0 < quads;
+         q0 += nthreads * kNormBatch) {
+        int4 c[kNormBatch];
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
-        if (cc[k] <= 0) continue;  // empty voxels stay exactly 0
-        const float inv = __fdiv_rn(1.0f, static_cast<float>(cc[k]));
-        float* o = grid + (v + k) * F;
-        if (VEC4) {
-            for (int f = 0; f < F; f += 4) {
-                float4 s = *reinterpret_cast<float4*>(o + f);
-                s.x = __fmul_rn(s.x, inv); s.y = __fmul_rn(s.y, inv);
-                s.z = __fmul_rn(s.z, inv); s.w = __fmul_rn(s.w, inv);
-                *reinterpret_cast<float4*>(o + f) = s;
+        for (int u = 0; u < kNormBatch; ++u) {
+            const long long q = q0 + u * nthreads;
+            c[u] = (q < quads) ? __ldcs(c4 + q) : make_int4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int u = 0; u < kNormBatch; ++u) {
+            if ((c[u].x | c[u].y | c[u].z | c[u].w) == 0) continue;  // counts are never negative
+            const long long v = v0 + (q0 + u * nthreads) * 4;
+            const int cc[4] = {c[u].x, c[u].y, c[u].z, c[u].w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                if (cc[k] <= 0) continue;  // empty voxels stay exactly 0
+                const float inv = __fdiv_rn(1.0f, static_cast<float>(cc[k]));
+                float* o = grid + (v + k) * F;
+                if (VEC4) {
+                    for (int f = 0; f < F; f += 4) {
+                        float4 s = *reinterpret_cast<float4*>(o + f);
+                        s.x = __fmul_rn(s.x, inv); s.y = __fmul_rn(s.y, inv);
+                        s.z = __fmul_rn(s.z, inv); s.w = __fmul_rn(s.w, inv);
+                        *reinterpret_cast<float4*>(o + f) = s;
+                    }
+                } else {
+                    for (int f = 0; f < F; ++f) o[f] = __fmul_rn(o[f], inv);
+                }
             }
-        } else {
-            for (int f = 0; f < F; ++f) o[f] = __fmul_rn(o[f], inv);
         }
     }
 }
@@ -213,9 +256,9 @@ __global__ void __launch_bounds__(kThreads) voxel_max_decode_kernel(int* __restr
 
 template <int MODE>
 void launch_bin(bool agg, unsigned int blocks, cudaStream_t st, const float* pts, const float* feats, void* grid,
-                int* counts, long long N, int F, const VoxelGeom& g, bool aligned) {
-    if (agg) voxel_bin_kernel<MODE, true><<<blocks, kThreads, 0, st>>>(pts, feats, grid, counts, N, F, g, aligned);
-    else     voxel_bin_kernel<MODE, false><<<blocks, kThreads, 0, st>>>(pts, feats, grid, counts, N, F, g, aligned);
+                int* counts, long long N, int F, const VoxelGeom& g, bool aligned, long long id_lo, long long id_hi) {
+    if (agg) voxel_bin_kernel<MODE, true><<<blocks, kThreads, 0, st>>>(pts, feats, grid, counts, N, F, g, aligned, id_lo, id_hi);
+    else     voxel_bin_kernel<MODE, false><<<blocks, kThreads, 0, st>>>(pts, feats, grid, counts, N, F, g, aligned, id_lo, id_hi);
 }
 
 // ---------------------------------------------------------------- allocation-free mean mode
@@ -271,7 +314,9 @@ int rc_voxel_normalize(float* grid, const int32_t* counts, int64_t voxel_begin, 
     if ((voxel_end - voxel_begin + kThreads - 1) / kThreads >= (1ll << 31)) return RC_ERR_TOO_LARGE;
     scalar(voxel_begin, head);
     if (body_end > head) {
-        const long long blocks = ((body_end - head) / 4 + kThreads - 1) / kThreads;
+        long long blocks = ((body_end - head) / 4 + kThreads - 1) / kThreads;
+        const long long cap = 32ll * rc::sm_count(device);
+        if (blocks > cap) blocks = cap;
         const unsigned int nb = static_cast<unsigned int>(blocks);
         if ((F & 3) == 0 && rc::aligned_to(grid, 16))
             voxel_normalize_wide_kernel<true><<<nb, kThreads, 0, st>>>(grid, counts, head, body_end, F);
@@ -326,25 +371,35 @@ int rc_voxelize(const float* points, const float* features, void* grid, int32_t*
     }
 
     if (N > 0 && V > 0 && !(feat_mode && F == 0)) {
-        const long long blocks = (N + kPointsPerBlock - 1) / kPointsPerBlock;
-        if (blocks >= (1ll << 31)) return RC_ERR_TOO_LARGE;
+        long long blocks = (N + kPointsPerBlock - 1) / kPointsPerBlock;
+        const long long cap = 16ll * rc::sm_count(device);  // two waves of resident CTAs; warps stride over tiles
+        if (blocks > cap) blocks = cap;
         const unsigned int nb = static_cast<unsigned int>(blocks);
         const bool aligned = rc::aligned_to(points, 16);
         const bool agg = (flags & RC_VOXEL_WARP_AGGREGATE) != 0;
         // vector feature accesses need the feature rows and grid cells aligned to their width
-        int Fk = F;
         if (feat_mode) {
             const bool a16 = rc::aligned_to(features, 16) && rc::aligned_to(grid, 16);
             const bool a8 = rc::aligned_to(features, 8) && rc::aligned_to(grid, 8);
             if ((F & 3) == 0 && !a16) return RC_ERR_BAD_ALIGNMENT;
             if ((F & 3) != 0 && (F & 1) == 0 && !a8) return RC_ERR_BAD_ALIGNMENT;
         }
-        switch (mode) {
-            case RC_VOXEL_COUNT: launch_bin<kCount>(agg, nb, st, points, features, grid, counts, N, Fk, g, aligned); break;
-            case RC_VOXEL_OCCUPANCY: launch_bin<kOccupancy>(false, nb, st, points, features, grid, counts, N, Fk, g, aligned); break;
-            case RC_VOXEL_OCCUPANCY_U8: launch_bin<kOccupancyU8>(false, nb, st, points, features, grid, counts, N, Fk, g, aligned); break;
-            case RC_VOXEL_MEAN: launch_bin<kMean>(false, nb, st, points, features, grid, counts, N, Fk, g, aligned); break;
-            default: launch_bin<kMax>(false, nb, st, points, features, grid, counts, N, Fk, g, aligned); break;
+        // slab passes: each pass scatters only into one contiguous range of voxel ids so that the
+        // sectors it touches stay resident in L2 (RC_OPT_VOXEL_PASSES)
+        int passes = rc::g_voxel_passes.load(std::memory_order_relaxed);
+        if (passes == 0) passes = 1;  // automatic choice: see below
+        if (passes < 1 || mode == RC_VOXEL_OCCUPANCY || mode == RC_VOXEL_OCCUPANCY_U8) passes = 1;
+        const long long slab = (V + passes - 1) / passes;
+        for (int ps = 0; ps < passes; ++ps) {
+            const long long lo = (passes == 1) ? 0 : ps * slab;
+            const long long hi = (passes == 1) ? V : ((ps + 1) * slab < V ? (ps + 1) * slab : V);
+            switch (mode) {
+                case RC_VOXEL_COUNT: launch_bin<kCount>(agg, nb, st, points, features, grid, counts, N, F, g, aligned, lo, hi); break;
+                case RC_VOXEL_OCCUPANCY: launch_bin<kOccupancy>(false, nb, st, points, features, grid, counts, N, F, g, aligned, lo, hi); break;
+                case RC_VOXEL_OCCUPANCY_U8: launch_bin<kOccupancyU8>(false, nb, st, points, features, grid, counts, N, F, g, aligned, lo, hi); break;
+                case RC_VOXEL_MEAN: launch_bin<kMean>(false, nb, st, points, features, grid, counts, N, F, g, aligned, lo, hi); break;
+                default: launch_bin<kMax>(false, nb, st, points, features, grid, counts, N, F, g, aligned, lo, hi); break;
+            }
         }
     }
     if (mode == RC_VOXEL_MAX && cells > 0) {

@@ -149,3 +149,22 @@ def test_full_size_properties(cuda_lib):
     assert (ident.float() - src[:64].float()).abs().max().item() <= 2 ** -7 * src[:64].float().abs().max().item()
     const = torch.full((16, S, D), 3.0, dtype=torch.bfloat16, device=DEV)
     assert torch.equal(robocache.resample_trajectories(const, st[:16], tt[:16]), torch.full((16, T, D), 3.0, dtype=torch.bfloat16, device=DEV))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_host_buffer_pipeline_matches_device_api(dtype, cuda_lib):
+    """The chunked host-buffer entry point (upload / kernel / download overlapped on three streams)
+    returns exactly what the device-tensor operator returns, for ragged chunk counts and repeated calls."""
+    from robogoat_b200.host_pipeline import resample_trajectories_host
+    src, st, tt = workloads.resample_inputs(B=37, S=120, D=64, T=45, dtype=dtype, irregular_targets=True, seed=21)
+    exp = expected(src, st, tt)
+    for chunk in (5, 8, 37, 100):
+        got = resample_trajectories_host(src.pin_memory(), st.pin_memory(), tt.pin_memory(), chunk_rows=chunk)
+        assert not got.is_cuda and got.is_pinned()
+        assert_exact(got, exp, f"chunk={chunk}")
+    out = torch.empty_like(exp).pin_memory()
+    src2, st2, tt2 = workloads.resample_inputs(B=37, S=120, D=64, T=45, dtype=dtype, irregular_targets=True, seed=22)
+    resample_trajectories_host(src2, st2, tt2, out=out, chunk_rows=6)          # pageable inputs, same cached buffers
+    assert_exact(out, expected(src2, st2, tt2), "second call")
+    with pytest.raises(RuntimeError, match="CPU tensors"):
+        resample_trajectories_host(src.to(DEV), st, tt)
