@@ -39,6 +39,8 @@ if ROOT not in sys.path:
 HEADLINE = dict(B=4096, S=500, D=256, T=250)
 METRIC = "resample_throughput"
 UNIT = "GB/s"
+WORKLOAD = "resample bf16 B=4096 S=500 D=256 T=250 sorted-uniform targets, per GPU"
+BYTES_CONVENTION = "min(all tensors once, touched rows + times + output)"
 
 
 # ----------------------------------------------------------------------------- helpers
@@ -215,8 +217,8 @@ def run_reference_arm(args):
         "impl": "reference", "metric": METRIC, "value": gbs, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": "resample bf16 B=4096 S=500 D=256 T=250 (timed on a B=256 sample, rate is size independent)",
-                   "bytes_per_step": nbytes},
+        "config": {"workload": WORKLOAD, "sample": "B=256 rows per step (the CPU rate does not depend on B)",
+                   "bytes_per_step": nbytes, "bytes_convention": BYTES_CONVENTION},
         "cpu_baseline": {"value": gbs, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": gbs, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -315,10 +317,10 @@ def run_ours(args):
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic",
-            "config": {"workload": "resample bf16 B=4096 S=500 D=256 T=250 sorted-uniform targets, per GPU",
+            "config": {"workload": WORKLOAD,
                        "global_batch": B * world, "parallelism": f"batch-shard x{world}, no collective",
                        "l2": "inputs (1.06 GB) and output (0.52 GB) exceed the 126 MB L2; no flush needed",
-                       "bytes_per_step_per_gpu": step_bytes, "bytes_convention": "min(all tensors once, touched rows + times + output)"},
+                       "bytes_per_step_per_gpu": step_bytes, "bytes_convention": BYTES_CONVENTION},
             "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e, "gpu_launches": args.steps, "clocks": clocks,
             "extras": extras,
         }
@@ -382,12 +384,16 @@ def run_extras(L, dev, local, rank, world, peak):
     med, mean = time_cold(lambda: ops.fuse_multimodal_cuda(*a4), 200, 20, flush)
     ex["fusion_bf16_B4_latency_us"] = {"median": med * 1e3, "mean": mean * 1e3, "timing": "per-call events, L2 flushed before each call"}
 
-    # voxel occupancy, 500k points, 128^3
+    # voxel occupancy, 500k points, 128^3 (public API: int32 grid; harness format: uint8 grid)
     pts = workloads.voxel_uniform_inputs(500_000, seed=rank, device=dev)
     kw = workloads.VOXEL_OCCUPANCY_GEOMETRY
     med, mean = time_cold(lambda: robocache.voxelize_pointcloud(pts, mode="occupancy", **kw), 200, 20, flush)
     ex["voxel_occupancy_500k_128"] = {"median_us": med * 1e3, "Gpts/s": 500_000 / (med * 1e-3) / 1e9,
                                       "timing": "per-call events incl. grid allocation and zero-fill, L2 flushed before each call"}
+    med, mean = time_cold(lambda: ops.voxelize_pointcloud_cuda(pts, None, kw["grid_min"], kw["voxel_size"], kw["grid_size"],
+                                                               "occupancy", occupancy_dtype=torch.uint8), 200, 20, flush)
+    ex["voxel_occupancy_u8_500k_128"] = {"median_us": med * 1e3, "Gpts/s": 500_000 / (med * 1e-3) / 1e9,
+                                         "timing": "same, uint8 occupancy plane (2 MiB zero-fill instead of 8 MiB)"}
     del pts
 
     # voxel count + mean at scale: N = 2^26 points per GPU, 512^3, F=4
