@@ -40,6 +40,7 @@ HEADLINE = dict(B=4096, S=500, D=256, T=250)
 METRIC = "resample_throughput"
 UNIT = "GB/s"
 WORKLOAD = "resample bf16 B=4096 S=500 D=256 T=250 sorted-uniform targets, per GPU"
+RESAMPLE_DRAM_BYTES_PER_ROW = (169117952 + 88358656) / 1024   # ncu capture, B=1024
 BYTES_CONVENTION = "min(all tensors once, touched rows + times + output)"
 
 
@@ -275,7 +276,7 @@ def run_ours(args):
     peak, peak_kind = measured_peak_gbs()
     achieved = step_bytes / (kernel_ms * 1e-3) / 1e9
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                "traffic": None, "peak_source": f"of {peak_kind}", "kernel": "interp_kernel<bf16,16B,staged>",
+                "traffic": int(RESAMPLE_DRAM_BYTES_PER_ROW * B), "traffic_source": "ncu dram__bytes_read+write of a B=1024 capture (profiles/resample_gather_bf16_B1024.md), scaled by rows", "peak_source": f"of {peak_kind}", "kernel": "interp_gather_kernel<bf16, 16 B, staged, uniform>",
                 "kernel_ms": kernel_ms, "bytes_algorithmic_all_tensors_once": algo_bytes,
                 "bytes_touched_rows": touched_bytes, "achieved_all_tensors_once": algo_bytes / (kernel_ms * 1e-3) / 1e9}
 
