@@ -446,8 +446,8 @@ def run_profile_case(name: str):
         a = workloads.fusion_inputs(B=4096, dtype=torch.bfloat16, seed=0, device=dev)
         fn = lambda: ops.fuse_multimodal_cuda(*a)
         units = {"B": 4096, "bytes_all_tensors_once": workloads.fusion_bytes(4096, 50, 2)}
-    elif name in ("voxel_mean", "voxel_count"):
-        N = 1 << 24
+    elif name in ("voxel_mean", "voxel_count", "voxel_mean_full"):
+        N = (1 << 26) if name.endswith("_full") else (1 << 24)  # the full-size case is for single-pass counter sets only
         pts, feats = workloads.voxel_mixture_inputs(N, seed=0, device=dev)
         kw = workloads.VOXEL_MIXTURE_GEOMETRY
         mode = name.split("_")[1]
@@ -475,7 +475,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extras", action="store_true")
     ap.add_argument("--profile-case", default=None,
-                    help="run 4 launches of one kernel on a small case (resample, fusion, voxel_mean, voxel_count, voxel_occupancy)")
+                    help="run 4 launches of one kernel on a small case (resample, fusion, voxel_mean, voxel_count, voxel_occupancy; voxel_mean_full = headline size)")
     args = ap.parse_args()
     if args.profile_case:
         run_profile_case(args.profile_case)
