@@ -110,6 +110,14 @@ class ClockSampler:
                 "sm_max_mhz": max(smax) if smax else None, "reasons": sorted(reasons), "samples": len(sm)}
 
 
+def host_threads() -> int:
+    """Host cores this process may use (torchrun pins OMP_NUM_THREADS=1, which is not what is wanted here)."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
 def physical_gpu_index(local_rank: int) -> int:
     vis = os.environ.get("CUDA_VISIBLE_DEVICES")
     if vis:
@@ -199,7 +207,7 @@ def run_reference_arm(args):
         return
     import oracle
     from robogoat_b200 import workloads
-    threads = oracle.max_threads()
+    threads = host_threads()
     B_s = 256                                  # bounded sample: 1/16 of the headline batch per step
     src, st, tt = workloads.resample_inputs(B=B_s, dtype=torch.bfloat16, irregular_targets=True, seed=0,
                                             S=HEADLINE["S"], D=HEADLINE["D"], T=HEADLINE["T"])
@@ -337,7 +345,7 @@ def cpu_baseline_leg(world: int):
         return None
     import oracle
     from robogoat_b200 import workloads
-    threads = oracle.max_threads()
+    threads = host_threads()
     B_s = 512
     src, st, tt = workloads.resample_inputs(B=B_s, dtype=torch.bfloat16, irregular_targets=True, seed=0,
                                             S=HEADLINE["S"], D=HEADLINE["D"], T=HEADLINE["T"])

@@ -27,6 +27,7 @@ constexpr int kThreads = 256;
 constexpr int kPointsPerLane = 4;
 constexpr int kPointsPerWarp = 32 * kPointsPerLane;            // 128
 constexpr int kPointsPerBlock = kThreads * kPointsPerLane;     // 1024
+constexpr size_t kSmallGridBytes = 64u << 20;                  // grids up to this size are cleared by voxel_zero_kernel
 
 struct VoxelGeom {
     float minx, miny, minz, vs;
@@ -93,6 +94,26 @@ __device__ __forceinline__ void load_tile(const float* __restrict__ pts, long lo
     }
 }
 
+// Programmatic dependent launch (sm_90+): a kernel launched with the programmatic-serialisation
+// attribute may start while its predecessor in the stream is still running; it must execute
+// grid_dependency_wait() before touching memory the predecessor writes.  Launched normally, the
+// wait returns at once.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_dependency_release() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// Zero-fill for small grids (latency regime): lets the scatter kernel that follows be scheduled
+// right away, so that its point loads and voxel-id arithmetic overlap this fill.
+__global__ void __launch_bounds__(kThreads) voxel_zero_kernel(unsigned char* __restrict__ p, long long bytes) {
+    grid_dependency_release();
+    const long long n16 = bytes >> 4;
+    uint4* p16 = reinterpret_cast<uint4*>(p);
+    const long long stride = static_cast<long long>(gridDim.x) * kThreads;
+    for (long long i = blockIdx.x * static_cast<long long>(kThreads) + threadIdx.x; i < n16; i += stride)
+        p16[i] = make_uint4(0u, 0u, 0u, 0u);
+    if (blockIdx.x == 0)
+        for (long long i = (n16 << 4) + threadIdx.x; i < bytes; i += kThreads) p[i] = 0;
+}
+
 // Scatter of one point tile.  `id_lo/id_hi` restrict the pass to a slab of voxel ids (a
 // contiguous range of the grid in memory); points outside the slab are skipped in this pass.
 template <int MODE, bool AGG>
@@ -131,6 +152,8 @@ voxel_bin_kernel(const float* __restrict__ pts, const float* __restrict__ feats,
             id[i] = voxel_id(x[i], y[i], z[i], g);
             if (!whole_grid && (id[i] < id_lo || id[i] >= id_hi)) id[i] = -1;
         }
+
+        grid_dependency_wait();  // the grid may still be being cleared by the preceding launch
 
         if (MODE == kOccupancy) {
             int* grid = static_cast<int*>(grid_v);
@@ -254,11 +277,35 @@ __global__ void __launch_bounds__(kThreads) voxel_max_decode_kernel(int* __restr
     }
 }
 
+template <int MODE, bool AGG>
+void launch_bin_one(bool overlap_prev, unsigned int blocks, cudaStream_t st, const float* pts, const float* feats,
+                    void* grid, int* counts, long long N, int F, const VoxelGeom& g, bool aligned, long long id_lo,
+                    long long id_hi) {
+    if (overlap_prev) {
+        cudaLaunchConfig_t cfg{};
+        cfg.gridDim = dim3(blocks);
+        cfg.blockDim = dim3(kThreads);
+        cfg.dynamicSmemBytes = 0;
+        cfg.stream = st;
+        cudaLaunchAttribute attr{};
+        attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr.val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = &attr;
+        cfg.numAttrs = 1;
+        if (cudaLaunchKernelEx(&cfg, voxel_bin_kernel<MODE, AGG>, pts, feats, grid, counts, N, F, g, aligned, id_lo,
+                               id_hi) == cudaSuccess)
+            return;
+        cudaGetLastError();  // attribute refused: fall through to an ordinary launch
+    }
+    voxel_bin_kernel<MODE, AGG><<<blocks, kThreads, 0, st>>>(pts, feats, grid, counts, N, F, g, aligned, id_lo, id_hi);
+}
+
 template <int MODE>
-void launch_bin(bool agg, unsigned int blocks, cudaStream_t st, const float* pts, const float* feats, void* grid,
-                int* counts, long long N, int F, const VoxelGeom& g, bool aligned, long long id_lo, long long id_hi) {
-    if (agg) voxel_bin_kernel<MODE, true><<<blocks, kThreads, 0, st>>>(pts, feats, grid, counts, N, F, g, aligned, id_lo, id_hi);
-    else     voxel_bin_kernel<MODE, false><<<blocks, kThreads, 0, st>>>(pts, feats, grid, counts, N, F, g, aligned, id_lo, id_hi);
+void launch_bin(bool agg, bool overlap_prev, unsigned int blocks, cudaStream_t st, const float* pts, const float* feats,
+                void* grid, int* counts, long long N, int F, const VoxelGeom& g, bool aligned, long long id_lo,
+                long long id_hi) {
+    if (agg) launch_bin_one<MODE, true>(overlap_prev, blocks, st, pts, feats, grid, counts, N, F, g, aligned, id_lo, id_hi);
+    else     launch_bin_one<MODE, false>(overlap_prev, blocks, st, pts, feats, grid, counts, N, F, g, aligned, id_lo, id_hi);
 }
 
 // ---------------------------------------------------------------- allocation-free mean mode
@@ -362,9 +409,18 @@ int rc_voxelize(const float* points, const float* features, void* grid, int32_t*
     const unsigned int fill_blocks =
         static_cast<unsigned int>(fill_blocks_ll < 64ll * rc::sm_count(device) ? (fill_blocks_ll > 0 ? fill_blocks_ll : 1)
                                                                            : 64ll * rc::sm_count(device));
+    bool overlap_fill = false;
     if (mode == RC_VOXEL_MAX) {
         // max mode always starts from "empty": the caller's buffer content is never an operand
         if (cells > 0) voxel_max_fill_kernel<<<fill_blocks, kThreads, 0, st>>>(static_cast<int*>(grid), cells);
+    } else if ((flags & RC_VOXEL_ZERO_INIT) && !feat_mode && cells > 0 &&
+               static_cast<size_t>(cells) * cell_bytes <= kSmallGridBytes && rc::aligned_to(grid, 16)) {
+        // small grid: own fill kernel, and the scatter below is allowed to start before it has finished
+        const long long fb = (static_cast<long long>(cells) * cell_bytes / 16 + kThreads - 1) / kThreads;
+        const long long fcap = 8ll * rc::sm_count(device);
+        voxel_zero_kernel<<<static_cast<unsigned int>(fb < 1 ? 1 : (fb > fcap ? fcap : fb)), kThreads, 0, st>>>(
+            static_cast<unsigned char*>(grid), static_cast<long long>(cells) * cell_bytes);
+        overlap_fill = true;
     } else if (flags & RC_VOXEL_ZERO_INIT) {
         if (cells > 0) RC_CUDA_TRY(cudaMemsetAsync(grid, 0, static_cast<size_t>(cells) * cell_bytes, st));
         if (mode == RC_VOXEL_MEAN && V > 0) RC_CUDA_TRY(cudaMemsetAsync(counts, 0, static_cast<size_t>(V) * 4, st));
@@ -394,11 +450,11 @@ int rc_voxelize(const float* points, const float* features, void* grid, int32_t*
             const long long lo = (passes == 1) ? 0 : ps * slab;
             const long long hi = (passes == 1) ? V : ((ps + 1) * slab < V ? (ps + 1) * slab : V);
             switch (mode) {
-                case RC_VOXEL_COUNT: launch_bin<kCount>(agg, nb, st, points, features, grid, counts, N, F, g, aligned, lo, hi); break;
-                case RC_VOXEL_OCCUPANCY: launch_bin<kOccupancy>(false, nb, st, points, features, grid, counts, N, F, g, aligned, lo, hi); break;
-                case RC_VOXEL_OCCUPANCY_U8: launch_bin<kOccupancyU8>(false, nb, st, points, features, grid, counts, N, F, g, aligned, lo, hi); break;
-                case RC_VOXEL_MEAN: launch_bin<kMean>(false, nb, st, points, features, grid, counts, N, F, g, aligned, lo, hi); break;
-                default: launch_bin<kMax>(false, nb, st, points, features, grid, counts, N, F, g, aligned, lo, hi); break;
+                case RC_VOXEL_COUNT: launch_bin<kCount>(agg, overlap_fill && ps == 0, nb, st, points, features, grid, counts, N, F, g, aligned, lo, hi); break;
+                case RC_VOXEL_OCCUPANCY: launch_bin<kOccupancy>(false, overlap_fill && ps == 0, nb, st, points, features, grid, counts, N, F, g, aligned, lo, hi); break;
+                case RC_VOXEL_OCCUPANCY_U8: launch_bin<kOccupancyU8>(false, overlap_fill && ps == 0, nb, st, points, features, grid, counts, N, F, g, aligned, lo, hi); break;
+                case RC_VOXEL_MEAN: launch_bin<kMean>(false, overlap_fill && ps == 0, nb, st, points, features, grid, counts, N, F, g, aligned, lo, hi); break;
+                default: launch_bin<kMax>(false, overlap_fill && ps == 0, nb, st, points, features, grid, counts, N, F, g, aligned, lo, hi); break;
             }
         }
     }
