@@ -116,6 +116,21 @@ RC_API int rc_voxelize(const float* points, const float* features, void* grid, i
                 const int32_t grid_size_host[3], int mode, uint32_t flags, int device, void* stream);
 
 /*
+ * rc_voxelize with an optional device scratch buffer.  Mean mode on grids whose accumulators do not
+ * fit in L2 then runs in two phases (voxel ids written once to the scratch, then several passes that
+ * each scatter into one slab of the grid), which keeps the atomics L2-resident.  Results are the
+ * same as rc_voxelize's (counts exact, sums equal up to fp32 summation order).
+ *   scratch, scratch_bytes : device buffer, 16-byte aligned, at least rc_voxelize_scratch_bytes()
+ *                            (4 bytes per point when the two-phase path applies, else 0); may be NULL.
+ * The scratch is only used during the call's own work on `stream`.  No counterpart in the reference.
+ */
+RC_API uint64_t rc_voxelize_scratch_bytes(int64_t N, int32_t F, const int32_t grid_size_host[3], int mode);
+RC_API int rc_voxelize_ex(const float* points, const float* features, void* grid, int32_t* counts, int64_t N,
+                          int32_t F, const float grid_min_host[3], float voxel_size,
+                          const int32_t grid_size_host[3], int mode, uint32_t flags, void* scratch,
+                          uint64_t scratch_bytes, int device, void* stream);
+
+/*
  * Second pass of mean mode on voxels [voxel_begin, voxel_end): grid[v,:] *= 1.0f / counts[v]
  * where counts[v] > 0.  Replaces normalize_mean_kernel
  * (robocache/csrc/cuda/voxelize_kernel.cu:145-163); the range lets each rank of the

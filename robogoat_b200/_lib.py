@@ -31,7 +31,7 @@ STATIC_MAX_VOXELS = 1 << 21
 # every symbol the header declares; the CPU test-suite checks the built library exports them all
 EXPORTED_SYMBOLS = (
     "rc_resample", "rc_fuse", "rc_resample_brackets", "rc_voxelize", "rc_voxel_normalize", "rc_voxelize_mean_static",
-    "rc_set_option", "rc_bulk_wait_timeouts", "rc_strerror", "rc_last_cuda_error", "rc_abi_version",
+    "rc_voxelize_ex", "rc_voxelize_scratch_bytes", "rc_set_option", "rc_bulk_wait_timeouts", "rc_strerror", "rc_last_cuda_error", "rc_abi_version",
 )
 
 
@@ -57,6 +57,11 @@ def _declare(L: ctypes.CDLL) -> None:
     L.rc_voxelize.argtypes = [vp, vp, vp, vp, i64, i32, ctypes.POINTER(f32), f32,
                               ctypes.POINTER(i32), ci, u32, ci, vp]
     L.rc_voxel_normalize.argtypes = [vp, vp, i64, i64, i32, ci, vp]
+    L.rc_voxelize_ex.argtypes = [vp, vp, vp, vp, i64, i32, ctypes.POINTER(f32), f32, ctypes.POINTER(i32), ci, u32, vp,
+                                 ctypes.c_uint64, ci, vp]
+    L.rc_voxelize_ex.restype = ci
+    L.rc_voxelize_scratch_bytes.argtypes = [i64, i32, ctypes.POINTER(i32), ci]
+    L.rc_voxelize_scratch_bytes.restype = ctypes.c_uint64
     L.rc_voxelize_mean_static.argtypes = [vp, vp, vp, i64, i32, ctypes.POINTER(f32), f32, ctypes.POINTER(i32), ci, vp]
     for name in ("rc_resample", "rc_fuse", "rc_resample_brackets", "rc_voxelize", "rc_voxel_normalize", "rc_voxelize_mean_static",
                  "rc_last_cuda_error", "rc_abi_version"):

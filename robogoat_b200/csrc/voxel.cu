@@ -27,6 +27,8 @@ constexpr int kThreads = 256;
 constexpr int kPointsPerLane = 4;
 constexpr int kPointsPerWarp = 32 * kPointsPerLane;            // 128
 constexpr int kPointsPerBlock = kThreads * kPointsPerLane;     // 1024
+constexpr size_t kResidentBytes = 96u << 20;   // accumulators up to this size are treated as L2-resident (one pass)
+constexpr int kAutoMeanPasses = 6;             // slab passes of the two-phase mean scatter on larger grids
 constexpr size_t kSmallGridBytes = 64u << 20;                  // grids up to this size are cleared by voxel_zero_kernel
 
 struct VoxelGeom {
@@ -208,46 +210,157 @@ voxel_bin_kernel(const float* __restrict__ pts, const float* __restrict__ feats,
     }
 }
 
-// mean pass 2, wide form: counts + v0 is 16-byte aligned and (v1 - v0) % 4 == 0.  A thread reads
-// kNormBatch groups of four counters at a time (all loads issued before any is used) and rescales the
-// feature sums of the occupied voxels among them; the grid is walked with a grid-wide stride.
-constexpr int kNormBatch = 4;
+// ---------------------------------------------------------------- two-phase scatter for large sparse grids
+//
+// When the accumulators of a grid do not fit in L2, an atomic that misses waits for a DRAM
+// sector, and the scatter runs at a fraction of the rate it reaches on an L2-resident grid.
+// Phase 1 writes the voxel id of every point once (4 bytes per point, -1 for dropped points).
+// Phase 2 runs P passes over those ids; pass p scatters only the points whose id falls into the
+// p-th contiguous slab of the grid, so the sectors it touches stay resident.  Re-reading ids costs
+// 4 bytes per point and pass instead of the 12-byte coordinates.
+
+__global__ void __launch_bounds__(kThreads)
+voxel_ids_kernel(const float* __restrict__ pts, long long N, VoxelGeom g, bool pts_aligned, int* __restrict__ ids) {
+    __shared__ __align__(16) float s_xyz[kThreads / 32][kPointsPerWarp * 3];
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    const long long ntiles = (N + kPointsPerWarp - 1) / kPointsPerWarp;
+    const long long warps_total = static_cast<long long>(gridDim.x) * (kThreads / 32);
+    for (long long tile = static_cast<long long>(blockIdx.x) * (kThreads / 32) + warp; tile < ntiles; tile += warps_total) {
+        const long long base = tile * kPointsPerWarp;
+        float x[kPointsPerLane], y[kPointsPerLane], z[kPointsPerLane];
+        load_tile(pts, base, N, pts_aligned && (base + kPointsPerWarp <= N), s_xyz[warp], lane, x, y, z);
+#pragma unroll
+        for (int i = 0; i < kPointsPerLane; ++i) {
+            const long long pi = base + i * 32 + lane;
+            if (pi < N) __stcs(ids + pi, static_cast<int>(voxel_id(x[i], y[i], z[i], g)));
+        }
+    }
+}
+
+template <int MODE>
+__device__ __forceinline__ void scatter_one(int id, long long pi, const float* __restrict__ feats, void* grid_v,
+                                            int* __restrict__ counts, int F) {
+    if (MODE == kCount) {
+        atomicAdd(static_cast<int*>(grid_v) + id, 1);
+    } else {
+        const float* f = feats + pi * F;
+        float* o = static_cast<float*>(grid_v) + static_cast<long long>(id) * F;
+        if ((F & 3) == 0) {
+            for (int c = 0; c < F; c += 4) red_add_v4(o + c, __ldcs(reinterpret_cast<const float4*>(f + c)));
+        } else if ((F & 1) == 0) {
+            for (int c = 0; c < F; c += 2) red_add_v2(o + c, __ldcs(reinterpret_cast<const float2*>(f + c)));
+        } else {
+            for (int c = 0; c < F; ++c) atomicAdd(o + c, __ldg(f + c));
+        }
+        atomicAdd(counts + id, 1);
+    }
+}
+
+// ids is 16-byte aligned.  Per step a warp reads 256 consecutive ids (two 16-byte loads per lane),
+// compacts the points of the current slab into its shared-memory queue with ballots, and then
+// scatters the queue with all lanes busy: a pass costs one cheap scan of the ids plus only its own
+// share of the feature gathers and atomics.
+template <int MODE>
+__global__ void __launch_bounds__(kThreads)
+voxel_scatter_ids_kernel(const int* __restrict__ ids, const float* __restrict__ feats, void* __restrict__ grid_v,
+                         int* __restrict__ counts, long long N, int F, int id_lo, int id_hi) {
+    __shared__ int s_id[kThreads / 32][256];
+    __shared__ int s_pt[kThreads / 32][256];   // point index relative to the warp's step base
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    const unsigned int lt_mask = (1u << lane) - 1u;
+    const long long steps = (N + 255) >> 8;
+    const long long warps_total = static_cast<long long>(gridDim.x) * (kThreads / 32);
+    const unsigned int span = static_cast<unsigned int>(id_hi - id_lo);
+    int* qid = s_id[warp];
+    int* qpt = s_pt[warp];
+    for (long long step = static_cast<long long>(blockIdx.x) * (kThreads / 32) + warp; step < steps; step += warps_total) {
+        const long long base = step << 8;
+        int v[8];
+        if (base + 256 <= N) {
+            const int4 a = __ldcs(reinterpret_cast<const int4*>(ids + base) + lane);
+            const int4 b = __ldcs(reinterpret_cast<const int4*>(ids + base) + 32 + lane);
+            v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+        } else {
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const long long pi = base + (k >> 2) * 128 + lane * 4 + (k & 3);
+                v[k] = (pi < N) ? ids[pi] : -1;
+            }
+        }
+        int n = 0;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {  // one unsigned compare covers id >= lo, id < hi and id == -1
+            const bool in = static_cast<unsigned int>(v[k] - id_lo) < span;
+            const unsigned int m = __ballot_sync(0xffffffffu, in);
+            if (in) {
+                const int slot = n + __popc(m & lt_mask);
+                qid[slot] = v[k];
+                qpt[slot] = (k >> 2) * 128 + lane * 4 + (k & 3);
+            }
+            n += __popc(m);
+        }
+        __syncwarp();
+        for (int j = lane; j < n; j += 32) scatter_one<MODE>(qid[j], base + qpt[j], feats, grid_v, counts, F);
+        __syncwarp();
+    }
+}
+
+// mean pass 2, wide form: counts + v0 is 16-byte aligned and (v1 - v0) % 4 == 0.  Per step a warp reads
+// 256 consecutive counters (two 16-byte loads per lane), queues the occupied voxels among them in
+// shared memory with ballots, and rescales the queued voxels with all lanes busy and independent
+// loads in flight; empty regions of a sparse grid cost one streaming read of the counter plane.
 template <bool VEC4>
 __global__ void __launch_bounds__(kThreads)
 voxel_normalize_wide_kernel(float* __restrict__ grid, const int* __restrict__ counts, long long v0, long long v1, int F) {
-    const long long quads = (v1 - v0) >> 2;
-    const long long nthreads = static_cast<long long>(gridDim.x) * kThreads;
-    const int4* c4 = reinterpret_cast<const int4*>(counts + v0);
-    for (long long q0 = blockIdx.x * static_cast<long long>(kThreads) + threadIdx.x; q0 < quads;
-         q0 += nthreads * kNormBatch) {
-        int4 c[kNormBatch];
+    __shared__ int s_vox[kThreads / 32][256];
+    __shared__ int s_cnt[kThreads / 32][256];
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    const unsigned int lt_mask = (1u << lane) - 1u;
+    const long long nvox = v1 - v0;
+    const long long steps = (nvox + 255) >> 8;
+    const long long warps_total = static_cast<long long>(gridDim.x) * (kThreads / 32);
+    int* qv = s_vox[warp];
+    int* qc = s_cnt[warp];
+    for (long long step = static_cast<long long>(blockIdx.x) * (kThreads / 32) + warp; step < steps; step += warps_total) {
+        const long long base = v0 + (step << 8);
+        const long long left = v1 - base;  // > 0, multiple of 4
+        int c[8];
+        const int4 z = make_int4(0, 0, 0, 0);
+        const int4 a = (lane * 4 < left) ? __ldcs(reinterpret_cast<const int4*>(counts + base) + lane) : z;
+        const int4 b = (128 + lane * 4 < left) ? __ldcs(reinterpret_cast<const int4*>(counts + base) + 32 + lane) : z;
+        c[0] = a.x; c[1] = a.y; c[2] = a.z; c[3] = a.w; c[4] = b.x; c[5] = b.y; c[6] = b.z; c[7] = b.w;
+        int n = 0;
 #pragma unroll
-        for (int u = 0; u < kNormBatch; ++u) {
-            const long long q = q0 + u * nthreads;
-            c[u] = (q < quads) ? __ldcs(c4 + q) : make_int4(0, 0, 0, 0);
+        for (int k = 0; k < 8; ++k) {
+            const bool occ = c[k] > 0;  // empty voxels stay exactly 0
+            const unsigned int m = __ballot_sync(0xffffffffu, occ);
+            if (occ) {
+                const int slot = n + __popc(m & lt_mask);
+                qv[slot] = (k >> 2) * 128 + lane * 4 + (k & 3);
+                qc[slot] = c[k];
+            }
+            n += __popc(m);
         }
-#pragma unroll
-        for (int u = 0; u < kNormBatch; ++u) {
-            if ((c[u].x | c[u].y | c[u].z | c[u].w) == 0) continue;  // counts are never negative
-            const long long v = v0 + (q0 + u * nthreads) * 4;
-            const int cc[4] = {c[u].x, c[u].y, c[u].z, c[u].w};
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                if (cc[k] <= 0) continue;  // empty voxels stay exactly 0
-                const float inv = __fdiv_rn(1.0f, static_cast<float>(cc[k]));
-                float* o = grid + (v + k) * F;
-                if (VEC4) {
-                    for (int f = 0; f < F; f += 4) {
-                        float4 s = *reinterpret_cast<float4*>(o + f);
-                        s.x = __fmul_rn(s.x, inv); s.y = __fmul_rn(s.y, inv);
-                        s.z = __fmul_rn(s.z, inv); s.w = __fmul_rn(s.w, inv);
-                        *reinterpret_cast<float4*>(o + f) = s;
-                    }
-                } else {
-                    for (int f = 0; f < F; ++f) o[f] = __fmul_rn(o[f], inv);
+        __syncwarp();
+#pragma unroll 2
+        for (int j = lane; j < n; j += 32) {
+            const float inv = __fdiv_rn(1.0f, static_cast<float>(qc[j]));
+            float* o = grid + (base + qv[j]) * F;
+            if (VEC4) {
+                for (int f = 0; f < F; f += 4) {
+                    float4 sgl = *reinterpret_cast<float4*>(o + f);
+                    sgl.x = __fmul_rn(sgl.x, inv); sgl.y = __fmul_rn(sgl.y, inv);
+                    sgl.z = __fmul_rn(sgl.z, inv); sgl.w = __fmul_rn(sgl.w, inv);
+                    *reinterpret_cast<float4*>(o + f) = sgl;
                 }
+            } else {
+                for (int f = 0; f < F; ++f) o[f] = __fmul_rn(o[f], inv);
             }
         }
+        __syncwarp();
     }
 }
 
@@ -361,8 +474,8 @@ int rc_voxel_normalize(float* grid, const int32_t* counts, int64_t voxel_begin, 
     if ((voxel_end - voxel_begin + kThreads - 1) / kThreads >= (1ll << 31)) return RC_ERR_TOO_LARGE;
     scalar(voxel_begin, head);
     if (body_end > head) {
-        long long blocks = ((body_end - head) / 4 + kThreads - 1) / kThreads;
-        const long long cap = 32ll * rc::sm_count(device);
+        long long blocks = (((body_end - head) + 255) / 256 + kThreads / 32 - 1) / (kThreads / 32);
+        const long long cap = 16ll * rc::sm_count(device);
         if (blocks > cap) blocks = cap;
         const unsigned int nb = static_cast<unsigned int>(blocks);
         if ((F & 3) == 0 && rc::aligned_to(grid, 16))
@@ -377,6 +490,24 @@ int rc_voxel_normalize(float* grid, const int32_t* counts, int64_t voxel_begin, 
 int rc_voxelize(const float* points, const float* features, void* grid, int32_t* counts, int64_t N,
                 int32_t F, const float grid_min_host[3], float voxel_size,
                 const int32_t grid_size_host[3], int mode, uint32_t flags, int device, void* stream) {
+    return rc_voxelize_ex(points, features, grid, counts, N, F, grid_min_host, voxel_size, grid_size_host, mode, flags,
+                          nullptr, 0, device, stream);
+}
+
+uint64_t rc_voxelize_scratch_bytes(int64_t N, int32_t F, const int32_t grid_size_host[3], int mode) {
+    if (grid_size_host == nullptr || N <= 0) return 0;
+    if (mode != RC_VOXEL_MEAN && mode != RC_VOXEL_COUNT) return 0;
+    const double cells = static_cast<double>(grid_size_host[0]) * grid_size_host[1] * grid_size_host[2];
+    if (cells <= 0 || cells >= 2147483648.0) return 0;
+    const double acc_bytes = cells * 4.0 * (mode == RC_VOXEL_MEAN ? (1 + (F > 0 ? F : 0)) : 1);
+    if (mode == RC_VOXEL_COUNT || acc_bytes <= static_cast<double>(kResidentBytes)) return 0;  // one pass is enough
+    return static_cast<uint64_t>(N) * 4u;
+}
+
+int rc_voxelize_ex(const float* points, const float* features, void* grid, int32_t* counts, int64_t N,
+                   int32_t F, const float grid_min_host[3], float voxel_size,
+                   const int32_t grid_size_host[3], int mode, uint32_t flags, void* scratch, uint64_t scratch_bytes,
+                   int device, void* stream) {
     if (mode < RC_VOXEL_COUNT || mode > RC_VOXEL_OCCUPANCY_U8) return RC_ERR_BAD_MODE;
     if (grid_min_host == nullptr || grid_size_host == nullptr || grid == nullptr) return RC_ERR_NULL_POINTER;
     if (N < 0 || F < 0) return RC_ERR_BAD_SHAPE;
@@ -440,21 +571,45 @@ int rc_voxelize(const float* points, const float* features, void* grid, int32_t*
             if ((F & 3) == 0 && !a16) return RC_ERR_BAD_ALIGNMENT;
             if ((F & 3) != 0 && (F & 1) == 0 && !a8) return RC_ERR_BAD_ALIGNMENT;
         }
-        // slab passes: each pass scatters only into one contiguous range of voxel ids so that the
-        // sectors it touches stay resident in L2 (RC_OPT_VOXEL_PASSES)
-        int passes = rc::g_voxel_passes.load(std::memory_order_relaxed);
-        if (passes == 0) passes = 1;  // automatic choice: see below
-        if (passes < 1 || mode == RC_VOXEL_OCCUPANCY || mode == RC_VOXEL_OCCUPANCY_U8) passes = 1;
+        // Slab passes (RC_OPT_VOXEL_PASSES, 0 = automatic): each pass scatters only into one contiguous
+        // range of voxel ids so that the sectors it touches stay resident in L2.
+        const int forced = rc::g_voxel_passes.load(std::memory_order_relaxed);
+        const bool scatter_mode = (mode == RC_VOXEL_COUNT || mode == RC_VOXEL_MEAN || mode == RC_VOXEL_MAX);
+        const double acc_bytes = static_cast<double>(V) * 4.0 * (mode == RC_VOXEL_MEAN ? (1 + F) : (feat_mode ? F : 1));
+        const bool ids_path = (mode == RC_VOXEL_MEAN) && scratch != nullptr && rc::aligned_to(scratch, 16) &&
+                              scratch_bytes >= static_cast<uint64_t>(N) * 4u && V < (1ll << 31) &&
+                              (forced > 1 || (forced == 0 && acc_bytes > static_cast<double>(kResidentBytes)));
+        int passes = 1;
+        if (scatter_mode) {
+            if (forced > 0) passes = forced;
+            else if (ids_path) passes = kAutoMeanPasses;
+            else if (mode == RC_VOXEL_COUNT && acc_bytes > static_cast<double>(kResidentBytes)) passes = 2;
+        }
+        if (passes > V) passes = static_cast<int>(V);
         const long long slab = (V + passes - 1) / passes;
-        for (int ps = 0; ps < passes; ++ps) {
-            const long long lo = (passes == 1) ? 0 : ps * slab;
-            const long long hi = (passes == 1) ? V : ((ps + 1) * slab < V ? (ps + 1) * slab : V);
-            switch (mode) {
-                case RC_VOXEL_COUNT: launch_bin<kCount>(agg, overlap_fill && ps == 0, nb, st, points, features, grid, counts, N, F, g, aligned, lo, hi); break;
-                case RC_VOXEL_OCCUPANCY: launch_bin<kOccupancy>(false, overlap_fill && ps == 0, nb, st, points, features, grid, counts, N, F, g, aligned, lo, hi); break;
-                case RC_VOXEL_OCCUPANCY_U8: launch_bin<kOccupancyU8>(false, overlap_fill && ps == 0, nb, st, points, features, grid, counts, N, F, g, aligned, lo, hi); break;
-                case RC_VOXEL_MEAN: launch_bin<kMean>(false, overlap_fill && ps == 0, nb, st, points, features, grid, counts, N, F, g, aligned, lo, hi); break;
-                default: launch_bin<kMax>(false, overlap_fill && ps == 0, nb, st, points, features, grid, counts, N, F, g, aligned, lo, hi); break;
+        if (ids_path) {
+            int* ids = static_cast<int*>(scratch);
+            voxel_ids_kernel<<<nb, kThreads, 0, st>>>(points, N, g, aligned, ids);
+            long long sb = (((N + 255) >> 8) + kThreads / 32 - 1) / (kThreads / 32);
+            if (sb > cap) sb = cap;
+            if (sb < 1) sb = 1;
+            for (int ps = 0; ps < passes; ++ps) {
+                const long long lo = ps * slab;
+                const long long hi = (lo + slab < V) ? lo + slab : V;
+                voxel_scatter_ids_kernel<kMean><<<static_cast<unsigned int>(sb), kThreads, 0, st>>>(
+                    ids, features, grid, counts, N, F, static_cast<int>(lo), static_cast<int>(hi));
+            }
+        } else {
+            for (int ps = 0; ps < passes; ++ps) {
+                const long long lo = (passes == 1) ? 0 : ps * slab;
+                const long long hi = (passes == 1) ? V : ((ps + 1) * slab < V ? (ps + 1) * slab : V);
+                switch (mode) {
+                    case RC_VOXEL_COUNT: launch_bin<kCount>(agg, overlap_fill && ps == 0, nb, st, points, features, grid, counts, N, F, g, aligned, lo, hi); break;
+                    case RC_VOXEL_OCCUPANCY: launch_bin<kOccupancy>(false, overlap_fill && ps == 0, nb, st, points, features, grid, counts, N, F, g, aligned, lo, hi); break;
+                    case RC_VOXEL_OCCUPANCY_U8: launch_bin<kOccupancyU8>(false, overlap_fill && ps == 0, nb, st, points, features, grid, counts, N, F, g, aligned, lo, hi); break;
+                    case RC_VOXEL_MEAN: launch_bin<kMean>(false, overlap_fill && ps == 0, nb, st, points, features, grid, counts, N, F, g, aligned, lo, hi); break;
+                    default: launch_bin<kMax>(false, overlap_fill && ps == 0, nb, st, points, features, grid, counts, N, F, g, aligned, lo, hi); break;
+                }
             }
         }
     }

@@ -204,9 +204,13 @@ def voxelize_pointcloud_cuda(points: torch.Tensor, features: Optional[torch.Tens
         flags |= _lib.VOXEL_WARP_AGGREGATE
     gmin = (ctypes.c_float * 3)(*[float(v) for v in grid_min])
     gsz = (ctypes.c_int32 * 3)(gx, gy, gz)
-    rc = L.rc_voxelize(pts.data_ptr(), feats.data_ptr() if feats is not None else None, grid.data_ptr(),
-                       counts.data_ptr() if counts is not None else None, N, F, gmin, float(voxel_size), gsz,
-                       code, flags, dev.index, _stream_ptr(dev))
+    # large sparse grids in mean mode run a two-phase scatter that wants 4 bytes of scratch per point
+    need = int(L.rc_voxelize_scratch_bytes(N, F, gsz, code))
+    scratch = torch.empty(need, dtype=torch.uint8, device=dev) if need > 0 else None
+    rc = L.rc_voxelize_ex(pts.data_ptr(), feats.data_ptr() if feats is not None else None, grid.data_ptr(),
+                          counts.data_ptr() if counts is not None else None, N, F, gmin, float(voxel_size), gsz,
+                          code, flags, scratch.data_ptr() if scratch is not None else None, need, dev.index,
+                          _stream_ptr(dev))
     _lib.check(rc, "voxelize_pointcloud")
     return [grid, counts] if mode == "mean" else [grid]
 
