@@ -83,6 +83,19 @@ RC_API int rc_resample(const void* src, const float* source_times, const float* 
                 int64_t B, int64_t S, int64_t T, int64_t D, int dtype, int device, void* stream);
 
 /*
+ * Resampling of variable-length items without padding.  The source rows of all items are packed
+ * back to back: src_rows [sum S_b, D], source_times [sum S_b], and item b owns rows
+ * [row_offsets[b], row_offsets[b+1]) (row_offsets: B+1 int64 on the device, ascending).  max_len is
+ * an upper bound of the item lengths (host value; it sizes the shared-memory staging).
+ * The result equals padding every item to a common length by repeating its last step — what the
+ * reference's loader does before batching (robocache/python/robocache/datasets/rtx_loader.py:214-221)
+ * — and calling rc_resample, without materialising the padded batch.  Items with no rows yield zeros.
+ */
+RC_API int rc_resample_ragged(const void* src_rows, const float* source_times, const int64_t* row_offsets,
+                              int64_t max_len, const float* target_times, void* out, int64_t B, int64_t T,
+                              int64_t D, int dtype, int device, void* stream);
+
+/*
  * N-stream temporal fusion in one launch: every stream is resampled to target_times and
  * written into its column slice of out [B,T,sum(D_k)] (slice order = stream order).
  * Replaces multimodal_fusion_cuda (robocache/csrc/cuda/multimodal_kernel.cu:201-251) behind

@@ -30,8 +30,9 @@ constexpr int kMaxWarps = 8;       // warps per CTA at most
 constexpr int kMaxStagedBytes = 200 * 1024;
 
 struct StreamArg {
-    const unsigned char* data;  // [B,S,D]
-    const float* times;         // [B,S]
+    const unsigned char* data;  // [B,S,D], or packed rows [sum S_b, D] when row_offsets is set
+    const float* times;         // [B,S], or packed [sum S_b]
+    const long long* row_offsets;  // ragged input: item b owns rows [row_offsets[b], row_offsets[b+1]); else NULL
     long long row_bytes;        // D * element size
     long long col_bytes;        // byte offset of this stream's slice inside an output row
     int S;
@@ -149,10 +150,10 @@ template <typename V> __device__ __forceinline__ void store_row(unsigned char* p
 template <int ES, int VEC, bool UNIFORM, int U>
 __device__ __forceinline__ void interp_chunk(const StreamArg& s, const unsigned char* src_b,
                                              unsigned char* out_t0, long long out_row_bytes,
-                                             int l, float w, int nt, int lane) {
+                                             int S, int l, float w, int nt, int lane) {
     using V = typename VecOf<VEC>::type;
     const int vecs = s.vecs;
-    const int Sm1 = s.S - 1;
+    const int Sm1 = S - 1;
     if (UNIFORM || (vecs & 31) == 0) {
         for (int j0 = 0; j0 < nt; j0 += U) {
             const unsigned char* pl[U];
@@ -220,11 +221,21 @@ interp_gather_kernel(const __grid_constant__ InterpParams p) {
     const long long b = blockIdx.x / p.tiles_per_row;
     const int tile = static_cast<int>(blockIdx.x - b * p.tiles_per_row);
 
+    // item b of stream k: first row and number of rows (dense: b*S and S)
+    auto first_row = [&](int k) -> long long {
+        return p.s[k].row_offsets ? __ldg(p.s[k].row_offsets + b) : b * p.s[k].S;
+    };
+    auto num_rows = [&](int k) -> int {
+        return p.s[k].row_offsets ? static_cast<int>(__ldg(p.s[k].row_offsets + b + 1) - __ldg(p.s[k].row_offsets + b))
+                                  : p.s[k].S;
+    };
+
     if (STAGED) {
         for (int k = 0; k < p.ns; ++k) {
-            const float* g = p.s[k].times + b * p.s[k].S;
+            const float* g = p.s[k].times + first_row(k);
             float* d = s_times + p.s[k].smem_off;
-            for (int i = threadIdx.x; i < p.s[k].S; i += blockDim.x) d[i] = __ldg(g + i);
+            const int n = num_rows(k);
+            for (int i = threadIdx.x; i < n; i += blockDim.x) d[i] = __ldg(g + i);
         }
         __syncthreads();
     }
@@ -237,13 +248,23 @@ interp_gather_kernel(const __grid_constant__ InterpParams p) {
 
     for (int k = 0; k < p.ns; ++k) {
         const StreamArg& s = p.s[k];
-        const float* a = STAGED ? (s_times + s.smem_off) : (s.times + b * s.S);
+        const long long row0 = first_row(k);
+        const int S = num_rows(k);
+        if (S <= 0) {
+            // an item without source rows (ragged input only) yields zeros
+            for (int i = lane; i < nt * static_cast<int>(s.row_bytes); i += 32) {
+                const int j = i / static_cast<int>(s.row_bytes);
+                out_t0[static_cast<long long>(j) * p.out_row_bytes + s.col_bytes + (i - j * static_cast<int>(s.row_bytes))] = 0;
+            }
+            continue;
+        }
+        const float* a = STAGED ? (s_times + s.smem_off) : (s.times + row0);
         int l, r;
         float w;
-        bracket(a, s.S, tq, l, r, w);
+        bracket(a, S, tq, l, r, w);
         (void)r;
-        interp_chunk<ES, VEC, UNIFORM, UNIFORM ? 2 : 1>(s, s.data + b * s.S * s.row_bytes, out_t0,
-                                                        p.out_row_bytes, l, w, nt, lane);
+        interp_chunk<ES, VEC, UNIFORM, UNIFORM ? 2 : 1>(s, s.data + row0 * s.row_bytes, out_t0,
+                                                        p.out_row_bytes, S, l, w, nt, lane);
     }
 }
 
@@ -433,8 +454,10 @@ int launch_gather(const InterpParams& p, long long grid, int threads, size_t sme
         auto* ku = interp_gather_kernel<ES, VEC, true, true>;
         auto* km = interp_gather_kernel<ES, VEC, true, false>;
         if (smem > 48 * 1024) {
-            RC_CUDA_TRY(cudaFuncSetAttribute(uniform ? ku : km, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             static_cast<int>(smem)));
+            int device = 0;
+            RC_CUDA_TRY(cudaGetDevice(&device));
+            const int rc_attr = rc::ensure_dynamic_smem(reinterpret_cast<const void*>(uniform ? ku : km), device, smem);
+            if (rc_attr != RC_OK) return rc_attr;
         }
         if (uniform) ku<<<g, threads, smem, stream>>>(p);
         else         km<<<g, threads, smem, stream>>>(p);
@@ -507,9 +530,8 @@ bool try_launch_block(const LiveStream* ls, int ns, const float* tt, unsigned ch
     p.tx_bytes = static_cast<unsigned int>(in_bytes);
     auto* kern = (es == 2) ? interp_block_kernel<2> : interp_block_kernel<4>;
     if (smem > 48 * 1024) {
-        const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                   static_cast<int>(smem));
-        if (e != cudaSuccess) { *status = rc::cuda_fail(e); return true; }
+        const int rc_attr = rc::ensure_dynamic_smem(reinterpret_cast<const void*>(kern), device, static_cast<size_t>(smem));
+        if (rc_attr != RC_OK) { *status = rc_attr; return true; }
     }
     kern<<<static_cast<unsigned int>(B * tiles), kBlockThreads, static_cast<size_t>(smem), stream>>>(p);
     *status = rc::check_launch();
@@ -617,6 +639,67 @@ int interp_dispatch(const rc_stream_desc* streams, int ns, const float* tt, void
     }
 }
 
+// Ragged resampling: one stream whose items have different lengths, packed back to back.
+int ragged_dispatch(const void* src, const float* times, const long long* row_offsets, long long max_len,
+                    const float* tt, void* out, int64_t B, int64_t T, int64_t D, int dtype, int device, void* stream_v) {
+    if (dtype != RC_DTYPE_F32 && dtype != RC_DTYPE_BF16) return RC_ERR_BAD_DTYPE;
+    if (B < 0 || T < 0 || D < 0 || max_len < 0) return RC_ERR_BAD_SHAPE;
+    if (T >= (1ll << 31) || D >= (1ll << 31) || max_len >= (1ll << 31)) return RC_ERR_TOO_LARGE;
+    if (B == 0 || T == 0 || D == 0) return RC_OK;
+    if (row_offsets == nullptr || tt == nullptr || out == nullptr) return RC_ERR_NULL_POINTER;
+    if (max_len > 0 && (src == nullptr || times == nullptr)) return RC_ERR_NULL_POINTER;
+    const int es = (dtype == RC_DTYPE_BF16) ? 2 : 4;
+    if (!rc::aligned_to(src, es) || !rc::aligned_to(times, 4) || !rc::aligned_to(tt, 4) || !rc::aligned_to(out, es) ||
+        !rc::aligned_to(row_offsets, 8))
+        return RC_ERR_BAD_ALIGNMENT;
+    rc::DeviceScope scope(device);
+    if (scope.status() != RC_OK) return scope.status();
+
+    InterpParams p{};
+    p.ns = 1;
+    p.tt = tt;
+    p.out = static_cast<unsigned char*>(out);
+    p.out_row_bytes = D * es;
+    p.T = static_cast<int>(T);
+    StreamArg& s = p.s[0];
+    s.data = static_cast<const unsigned char*>(src);
+    s.times = times;
+    s.row_offsets = row_offsets;
+    s.S = static_cast<int>(max_len);
+    s.row_bytes = D * es;
+    s.col_bytes = 0;
+    s.smem_off = 0;
+    const uintptr_t bits = reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(src) | static_cast<uintptr_t>(s.row_bytes);
+    int vec = 16;
+    while (vec > es && (bits & (vec - 1)) != 0) vec >>= 1;
+    s.vecs = static_cast<int>(s.row_bytes / vec);
+    const bool uniform = (s.vecs % 32 == 0);
+    int warps = 1;
+    while (warps < kMaxWarps && warps * 32 < T) warps <<= 1;
+    const long long want = 4ll * rc::sm_count(device);
+    while (warps > 1 && B * ((T + 32 * warps - 1) / (32 * warps)) < want) warps >>= 1;
+    p.tiles_per_row = static_cast<int>((T + 32 * warps - 1) / (32 * warps));
+    const long long grid = B * p.tiles_per_row;
+    if (grid >= (1ll << 31)) return RC_ERR_TOO_LARGE;
+    const size_t smem = static_cast<size_t>((max_len + 3) & ~3ll) * sizeof(float);
+    const bool staged = smem <= static_cast<size_t>(kMaxStagedBytes);
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    const int threads = warps * 32;
+    if (es == 2) {
+        switch (vec) {
+            case 16: return launch_gather<2, 16>(p, grid, threads, smem, staged, uniform, stream);
+            case 8:  return launch_gather<2, 8>(p, grid, threads, smem, staged, uniform, stream);
+            case 4:  return launch_gather<2, 4>(p, grid, threads, smem, staged, uniform, stream);
+            default: return launch_gather<2, 2>(p, grid, threads, smem, staged, uniform, stream);
+        }
+    }
+    switch (vec) {
+        case 16: return launch_gather<4, 16>(p, grid, threads, smem, staged, uniform, stream);
+        case 8:  return launch_gather<4, 8>(p, grid, threads, smem, staged, uniform, stream);
+        default: return launch_gather<4, 4>(p, grid, threads, smem, staged, uniform, stream);
+    }
+}
+
 }  // namespace
 
 extern "C" {
@@ -625,6 +708,13 @@ int rc_resample(const void* src, const float* source_times, const float* target_
                 int64_t B, int64_t S, int64_t T, int64_t D, int dtype, int device, void* stream) {
     rc_stream_desc s{src, source_times, S, D};
     return interp_dispatch(&s, 1, target_times, out, B, T, dtype, device, stream);
+}
+
+int rc_resample_ragged(const void* src_rows, const float* source_times, const int64_t* row_offsets, int64_t max_len,
+                       const float* target_times, void* out, int64_t B, int64_t T, int64_t D, int dtype, int device,
+                       void* stream) {
+    return ragged_dispatch(src_rows, source_times, reinterpret_cast<const long long*>(row_offsets), max_len,
+                           target_times, out, B, T, D, dtype, device, stream);
 }
 
 int rc_fuse(const rc_stream_desc* streams, int n_streams, const float* target_times, void* out,

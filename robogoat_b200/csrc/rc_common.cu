@@ -2,6 +2,9 @@
 #include "rc_common.cuh"
 
 #include <atomic>
+#include <map>
+#include <mutex>
+#include <utility>
 
 namespace rc {
 
@@ -23,6 +26,18 @@ int sm_count(int device) {
     }
     g_sm_count[device].store(n, std::memory_order_relaxed);
     return n;
+}
+
+int ensure_dynamic_smem(const void* kernel, int device, size_t bytes) {
+    static std::mutex mu;
+    static std::map<std::pair<const void*, int>, size_t> granted;
+    std::lock_guard<std::mutex> lock(mu);
+    size_t& have = granted[std::make_pair(kernel, device)];
+    if (have >= bytes) return RC_OK;
+    const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes));
+    if (e != cudaSuccess) return cuda_fail(e);
+    have = bytes;
+    return RC_OK;
 }
 
 }  // namespace rc

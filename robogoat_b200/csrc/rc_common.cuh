@@ -70,6 +70,10 @@ inline int check_launch() {
 
 int sm_count(int device);
 
+// Raises a kernel's dynamic shared-memory limit to `bytes` on `device` (current) once; later calls with
+// the same or a smaller size return without touching the runtime, so launches stay capturable.
+int ensure_dynamic_smem(const void* kernel, int device, size_t bytes);
+
 // process-wide switches behind rc_set_option
 extern std::atomic<int> g_allow_block_kernel;  // RC_OPT_BLOCK_KERNEL
 extern std::atomic<int> g_voxel_passes;        // RC_OPT_VOXEL_PASSES

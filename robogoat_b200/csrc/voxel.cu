@@ -63,35 +63,41 @@ __device__ __forceinline__ int float_ordered(float f) {
 
 enum : int { kCount = 0, kOccupancy = 1, kMean = 2, kMax = 3, kOccupancyU8 = 4 };
 
-// Loads the xyz of the warp's 128-point tile starting at `base` into registers:
-// point i of the lane is (base + i*32 + lane).  ALIGNED: the tile is full and 16-byte aligned.
-__device__ __forceinline__ void load_tile(const float* __restrict__ pts, long long base, long long N,
-                                          bool full_aligned, float* s_warp, int lane,
-                                          float (&x)[kPointsPerLane], float (&y)[kPointsPerLane],
-                                          float (&z)[kPointsPerLane]) {
-    if (full_aligned) {
-        const float4* src = reinterpret_cast<const float4*>(pts + base * 3);
-        float4* dst = reinterpret_cast<float4*>(s_warp);
+// The xyz of a warp's 128-point tile: point i of a lane is (base + i*32 + lane).
+// Fast tiles (full, 16-byte aligned) are fetched with three coalesced 16-byte loads per lane
+// (tile_issue), issued one tile ahead of their use, and transposed through the warp's slice of
+// shared memory (tile_unpack); other tiles are read with scalar loads (tile_load_slow).
+__device__ __forceinline__ void tile_issue(const float* __restrict__ pts, long long base, int lane, float4 (&v)[3]) {
+    const float4* src = reinterpret_cast<const float4*>(pts + base * 3);
 #pragma unroll
-        for (int k = 0; k < 3; ++k) dst[k * 32 + lane] = __ldcs(src + k * 32 + lane);
-        __syncwarp();
+    for (int k = 0; k < 3; ++k) v[k] = __ldcs(src + k * 32 + lane);
+}
+__device__ __forceinline__ void tile_unpack(const float4 (&v)[3], float* s_warp, int lane,
+                                            float (&x)[kPointsPerLane], float (&y)[kPointsPerLane],
+                                            float (&z)[kPointsPerLane]) {
+    float4* dst = reinterpret_cast<float4*>(s_warp);
 #pragma unroll
-        for (int i = 0; i < kPointsPerLane; ++i) {
-            const float* q = s_warp + (i * 32 + lane) * 3;
-            x[i] = q[0]; y[i] = q[1]; z[i] = q[2];
-        }
-        __syncwarp();
-    } else {
+    for (int k = 0; k < 3; ++k) dst[k * 32 + lane] = v[k];
+    __syncwarp();
 #pragma unroll
-        for (int i = 0; i < kPointsPerLane; ++i) {
-            const long long pi = base + i * 32 + lane;
-            if (pi < N) {
-                x[i] = __ldg(pts + pi * 3 + 0);
-                y[i] = __ldg(pts + pi * 3 + 1);
-                z[i] = __ldg(pts + pi * 3 + 2);
-            } else {
-                x[i] = y[i] = z[i] = __int_as_float(0x7fc00000);  // NaN: dropped
-            }
+    for (int i = 0; i < kPointsPerLane; ++i) {
+        const float* q = s_warp + (i * 32 + lane) * 3;  // stride of three words: conflict free
+        x[i] = q[0]; y[i] = q[1]; z[i] = q[2];
+    }
+    __syncwarp();
+}
+__device__ __forceinline__ void tile_load_slow(const float* __restrict__ pts, long long base, long long N, int lane,
+                                               float (&x)[kPointsPerLane], float (&y)[kPointsPerLane],
+                                               float (&z)[kPointsPerLane]) {
+#pragma unroll
+    for (int i = 0; i < kPointsPerLane; ++i) {
+        const long long pi = base + i * 32 + lane;
+        if (pi < N) {
+            x[i] = __ldg(pts + pi * 3 + 0);
+            y[i] = __ldg(pts + pi * 3 + 1);
+            z[i] = __ldg(pts + pi * 3 + 2);
+        } else {
+            x[i] = y[i] = z[i] = __int_as_float(0x7fc00000);  // NaN: dropped
         }
     }
 }
@@ -130,8 +136,10 @@ voxel_bin_kernel(const float* __restrict__ pts, const float* __restrict__ feats,
     const long long warps_total = static_cast<long long>(gridDim.x) * (kThreads / 32);
     const bool whole_grid = (id_lo <= 0) && (id_hi >= static_cast<long long>(g.gx) * g.gy * g.gz);
 
-    for (long long tile = static_cast<long long>(blockIdx.x) * (kThreads / 32) + warp; tile < ntiles;
-         tile += warps_total) {
+    const long long tile0 = static_cast<long long>(blockIdx.x) * (kThreads / 32) + warp;
+    float4 ahead[3];  // coordinates of the next fast tile, requested one iteration early
+    if (pts_aligned && tile0 < ntiles && (tile0 + 1) * kPointsPerWarp <= N) tile_issue(pts, tile0 * kPointsPerWarp, lane, ahead);
+    for (long long tile = tile0; tile < ntiles; tile += warps_total) {
         const long long base = tile * kPointsPerWarp;
         const bool full = base + kPointsPerWarp <= N;
 
@@ -146,7 +154,14 @@ voxel_bin_kernel(const float* __restrict__ pts, const float* __restrict__ feats,
         }
 
         float x[kPointsPerLane], y[kPointsPerLane], z[kPointsPerLane];
-        load_tile(pts, base, N, pts_aligned && full, s_xyz[warp], lane, x, y, z);
+        if (pts_aligned && full) {
+            float4 cur[3] = {ahead[0], ahead[1], ahead[2]};
+            const long long next = tile + warps_total;
+            if (next < ntiles && (next + 1) * kPointsPerWarp <= N) tile_issue(pts, next * kPointsPerWarp, lane, ahead);
+            tile_unpack(cur, s_xyz[warp], lane, x, y, z);
+        } else {
+            tile_load_slow(pts, base, N, lane, x, y, z);
+        }
 
         long long id[kPointsPerLane];
 #pragma unroll
@@ -226,10 +241,20 @@ voxel_ids_kernel(const float* __restrict__ pts, long long N, VoxelGeom g, bool p
     const int warp = threadIdx.x >> 5;
     const long long ntiles = (N + kPointsPerWarp - 1) / kPointsPerWarp;
     const long long warps_total = static_cast<long long>(gridDim.x) * (kThreads / 32);
-    for (long long tile = static_cast<long long>(blockIdx.x) * (kThreads / 32) + warp; tile < ntiles; tile += warps_total) {
+    const long long tile0 = static_cast<long long>(blockIdx.x) * (kThreads / 32) + warp;
+    float4 ahead[3];
+    if (pts_aligned && tile0 < ntiles && (tile0 + 1) * kPointsPerWarp <= N) tile_issue(pts, tile0 * kPointsPerWarp, lane, ahead);
+    for (long long tile = tile0; tile < ntiles; tile += warps_total) {
         const long long base = tile * kPointsPerWarp;
         float x[kPointsPerLane], y[kPointsPerLane], z[kPointsPerLane];
-        load_tile(pts, base, N, pts_aligned && (base + kPointsPerWarp <= N), s_xyz[warp], lane, x, y, z);
+        if (pts_aligned && base + kPointsPerWarp <= N) {
+            float4 cur[3] = {ahead[0], ahead[1], ahead[2]};
+            const long long next = tile + warps_total;
+            if (next < ntiles && (next + 1) * kPointsPerWarp <= N) tile_issue(pts, next * kPointsPerWarp, lane, ahead);
+            tile_unpack(cur, s_xyz[warp], lane, x, y, z);
+        } else {
+            tile_load_slow(pts, base, N, lane, x, y, z);
+        }
 #pragma unroll
         for (int i = 0; i < kPointsPerLane; ++i) {
             const long long pi = base + i * 32 + lane;

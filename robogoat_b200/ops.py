@@ -229,3 +229,36 @@ def voxel_normalize_cuda(grid: torch.Tensor, counts: torch.Tensor, voxel_begin: 
     rc = _lib.load().rc_voxel_normalize(grid.data_ptr(), counts.data_ptr(), int(voxel_begin), end, F, dev.index,
                                         _stream_ptr(dev))
     _lib.check(rc, "voxel_normalize")
+
+
+def resample_ragged_cuda(source_rows: torch.Tensor, source_times: torch.Tensor, row_offsets: torch.Tensor,
+                         target_times: torch.Tensor, max_len: Optional[int] = None) -> torch.Tensor:
+    """Resample variable-length items that are packed back to back, without padding them.
+
+    source_rows [sum S_b, D] (bf16/fp32), source_times [sum S_b], row_offsets [B+1] (int64, ascending,
+    row_offsets[0] = 0), target_times [B, T] -> [B, T, D].  Equal to padding every item with its last step
+    (as robocache/python/robocache/datasets/rtx_loader.py:214-221 does) and resampling the padded batch.
+    ``max_len``: an upper bound of the item lengths; computed from the offsets (one host sync) when omitted.
+    """
+    _check(source_rows.is_cuda and source_times.is_cuda and row_offsets.is_cuda and target_times.is_cuda,
+           "all tensors must be CUDA tensors")
+    _check(source_rows.dim() == 2, "source_rows must be 2D [sum S, D]")
+    _check(source_times.dim() == 1 and source_times.shape[0] == source_rows.shape[0],
+           "source_times must be 1D with one entry per source row")
+    _check(target_times.dim() == 2, "target_times must be 2D [B, T]")
+    B, T = target_times.shape
+    _check(row_offsets.dim() == 1 and row_offsets.shape[0] == B + 1, "row_offsets must have B+1 entries")
+    code = _dtype_code(source_rows.dtype)
+    dev = source_rows.device
+    offs = row_offsets.to(torch.int64).contiguous()
+    if max_len is None:
+        max_len = int((offs[1:] - offs[:-1]).max().item()) if B > 0 else 0
+    D = source_rows.shape[1]
+    L = _lib.load()
+    src = source_rows.contiguous()
+    st, tt = _times(source_times), _times(target_times)
+    out = torch.empty((B, T, D), dtype=source_rows.dtype, device=dev)
+    rc = L.rc_resample_ragged(src.data_ptr(), st.data_ptr(), offs.data_ptr(), int(max_len), tt.data_ptr(), out.data_ptr(),
+                              B, T, D, code, dev.index, _stream_ptr(dev))
+    _lib.check(rc, "resample_ragged")
+    return out

@@ -117,3 +117,19 @@ def test_no_bulk_copy_wait_ever_ran_out(cuda_lib):
     n = ctypes.c_uint32(12345)
     assert cuda_lib.rc_bulk_wait_timeouts(0, ctypes.byref(n)) == 0
     assert n.value == 0
+
+
+def test_cuda_graph_replay_matches_direct_calls(cuda_lib):
+    """Small-batch latency path: the operator captured into a CUDA graph and replayed on new inputs returns
+    the same bits as a direct call (robocache/python/robocache/cuda_graph_cache.py:75-148 is the reference's cache)."""
+    from robogoat_b200.graphs import GraphCache
+    cache = GraphCache(capacity=2)
+    for seed in (1, 2, 3):
+        a = [x.to(DEV) for x in workloads.fusion_inputs(B=4, dtype=torch.bfloat16, seed=seed)]
+        got = cache.run(robocache.fuse_multimodal, *a).clone()
+        assert torch.equal(got.view(torch.int16), robocache.fuse_multimodal(*a).view(torch.int16)), seed
+    assert cache.stats() == {"entries": 1, "hits": 2, "misses": 1}
+    src, st, tt = (x.to(DEV) for x in workloads.resample_inputs(B=8, S=100, D=64, T=40, irregular_targets=True, seed=4))
+    got = cache.run(robocache.resample_trajectories, src, st, tt).clone()
+    assert torch.equal(got, robocache.resample_trajectories(src, st, tt))
+    assert cache.stats()["entries"] == 2

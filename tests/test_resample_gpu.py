@@ -168,3 +168,34 @@ def test_host_buffer_pipeline_matches_device_api(dtype, cuda_lib):
     assert_exact(out, expected(src2, st2, tt2), "second call")
     with pytest.raises(RuntimeError, match="CPU tensors"):
         resample_trajectories_host(src.to(DEV), st, tt)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("D", [256, 12])
+def test_ragged_items_equal_per_item_oracle_and_last_step_padding(dtype, D, cuda_lib):
+    """Variable-length items packed back to back: every item must equal the oracle run on that item alone,
+    and the whole batch must equal 'pad with the last step, then resample' (the reference loader's padding,
+    robocache/python/robocache/datasets/rtx_loader.py:214-221)."""
+    g = torch.Generator().manual_seed(31 + D)
+    lens = [1, 2, 3, 17, 500, 64, 0, 129]
+    T = 70
+    rows, times = [], []
+    for n in lens:
+        rows.append(torch.randn(n, D, generator=g).to(dtype))
+        times.append(workloads.cumsum_times(1, n, g)[0] if n > 0 else torch.empty(0))
+    tt = torch.rand(len(lens), T, generator=g) * 1.3 - 0.15
+    offs = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int64)
+    out = ops.resample_ragged_cuda(torch.cat(rows).to(DEV), torch.cat(times).to(DEV), offs.to(DEV), tt.to(DEV)).cpu()
+    for b, n in enumerate(lens):
+        if n == 0:
+            assert bool((out[b].float() == 0).all())
+            continue
+        exp = expected(rows[b].unsqueeze(0), times[b].unsqueeze(0), tt[b:b + 1])
+        assert_exact(out[b:b + 1], exp, f"item {b} (len {n})")
+    # padded batch through the dense operator
+    S = max(lens)
+    keep = [b for b, n in enumerate(lens) if n > 0]
+    pad_rows = torch.stack([torch.cat([rows[b], rows[b][-1:].expand(S - lens[b], -1)]) for b in keep])
+    pad_times = torch.stack([torch.cat([times[b], times[b][-1:].expand(S - lens[b])]) for b in keep])
+    dense = robocache.resample_trajectories(pad_rows.to(DEV), pad_times.to(DEV), tt[keep].to(DEV)).cpu()
+    assert_exact(out[keep], dense, "ragged vs last-step padding")
