@@ -35,6 +35,12 @@ class GraphedOp:
         with torch.cuda.graph(self.graph):
             self.static_output = fn(*self.static_inputs)
 
+    def replay(self) -> torch.Tensor:
+        """Replay on whatever the static input buffers (``static_inputs``) hold now: the zero-copy way to use
+        the graph is to produce the next inputs directly into those buffers."""
+        self.graph.replay()
+        return self.static_output
+
     def __call__(self, *inputs: torch.Tensor) -> torch.Tensor:
         """Replay with new input values (same shapes/dtypes).  The returned tensor is the graph's static
         output buffer: it is overwritten by the next call."""
