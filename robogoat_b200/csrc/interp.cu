@@ -210,7 +210,7 @@ __device__ __forceinline__ void interp_chunk(const StreamArg& s, const unsigned 
 
 // STAGED: timestamp rows live in shared memory; otherwise lanes search global memory
 // (rows too long for shared memory).  Four CTAs of 256 threads per SM (64 registers).
-template <int ES, int VEC, bool STAGED, bool UNIFORM>
+template <int ES, int VEC, bool STAGED, bool UNIFORM, bool RAGGED>
 __global__ void __launch_bounds__(32 * kMaxWarps, 4)
 interp_gather_kernel(const __grid_constant__ InterpParams p) {
     extern __shared__ __align__(16) float s_times[];
@@ -223,11 +223,10 @@ interp_gather_kernel(const __grid_constant__ InterpParams p) {
 
     // item b of stream k: first row and number of rows (dense: b*S and S)
     auto first_row = [&](int k) -> long long {
-        return p.s[k].row_offsets ? __ldg(p.s[k].row_offsets + b) : b * p.s[k].S;
+        return RAGGED ? __ldg(p.s[k].row_offsets + b) : b * p.s[k].S;
     };
     auto num_rows = [&](int k) -> int {
-        return p.s[k].row_offsets ? static_cast<int>(__ldg(p.s[k].row_offsets + b + 1) - __ldg(p.s[k].row_offsets + b))
-                                  : p.s[k].S;
+        return RAGGED ? static_cast<int>(__ldg(p.s[k].row_offsets + b + 1) - __ldg(p.s[k].row_offsets + b)) : p.s[k].S;
     };
 
     if (STAGED) {
@@ -250,8 +249,8 @@ interp_gather_kernel(const __grid_constant__ InterpParams p) {
         const StreamArg& s = p.s[k];
         const long long row0 = first_row(k);
         const int S = num_rows(k);
-        if (S <= 0) {
-            // an item without source rows (ragged input only) yields zeros
+        if (RAGGED && S <= 0) {
+            // an item without source rows yields zeros
             for (int i = lane; i < nt * static_cast<int>(s.row_bytes); i += 32) {
                 const int j = i / static_cast<int>(s.row_bytes);
                 out_t0[static_cast<long long>(j) * p.out_row_bytes + s.col_bytes + (i - j * static_cast<int>(s.row_bytes))] = 0;
@@ -446,26 +445,33 @@ interp_block_kernel(const __grid_constant__ BlockParams p) {
 
 // ---------------------------------------------------------------- host side
 
+template <int ES, int VEC, bool STAGED, bool UNIFORM>
+int launch_gather_one(const InterpParams& p, unsigned int g, int threads, size_t smem, bool ragged, cudaStream_t stream) {
+    if (STAGED && smem > 48 * 1024) {
+        int device = 0;
+        RC_CUDA_TRY(cudaGetDevice(&device));
+        const void* k = ragged ? reinterpret_cast<const void*>(interp_gather_kernel<ES, VEC, STAGED, UNIFORM, true>)
+                               : reinterpret_cast<const void*>(interp_gather_kernel<ES, VEC, STAGED, UNIFORM, false>);
+        const int rc_attr = rc::ensure_dynamic_smem(k, device, smem);
+        if (rc_attr != RC_OK) return rc_attr;
+    }
+    const size_t dyn = STAGED ? smem : 0;
+    if (ragged) interp_gather_kernel<ES, VEC, STAGED, UNIFORM, true><<<g, threads, dyn, stream>>>(p);
+    else        interp_gather_kernel<ES, VEC, STAGED, UNIFORM, false><<<g, threads, dyn, stream>>>(p);
+    return rc::check_launch();
+}
+
 template <int ES, int VEC>
 int launch_gather(const InterpParams& p, long long grid, int threads, size_t smem, bool staged, bool uniform,
                   cudaStream_t stream) {
     const unsigned int g = static_cast<unsigned int>(grid);
+    const bool ragged = p.s[0].row_offsets != nullptr;
     if (staged) {
-        auto* ku = interp_gather_kernel<ES, VEC, true, true>;
-        auto* km = interp_gather_kernel<ES, VEC, true, false>;
-        if (smem > 48 * 1024) {
-            int device = 0;
-            RC_CUDA_TRY(cudaGetDevice(&device));
-            const int rc_attr = rc::ensure_dynamic_smem(reinterpret_cast<const void*>(uniform ? ku : km), device, smem);
-            if (rc_attr != RC_OK) return rc_attr;
-        }
-        if (uniform) ku<<<g, threads, smem, stream>>>(p);
-        else         km<<<g, threads, smem, stream>>>(p);
-    } else {
-        if (uniform) interp_gather_kernel<ES, VEC, false, true><<<g, threads, 0, stream>>>(p);
-        else         interp_gather_kernel<ES, VEC, false, false><<<g, threads, 0, stream>>>(p);
+        return uniform ? launch_gather_one<ES, VEC, true, true>(p, g, threads, smem, ragged, stream)
+                       : launch_gather_one<ES, VEC, true, false>(p, g, threads, smem, ragged, stream);
     }
-    return rc::check_launch();
+    return uniform ? launch_gather_one<ES, VEC, false, true>(p, g, threads, smem, ragged, stream)
+                   : launch_gather_one<ES, VEC, false, false>(p, g, threads, smem, ragged, stream);
 }
 
 struct LiveStream {
