@@ -39,7 +39,7 @@ _ptr = ctypes.c_void_p
 def build(reference_root: Optional[str] = None) -> None:
     """Compile the oracle and, if a reference checkout is reachable, ``oracle/_ref``."""
     subprocess.run(["make", "-C", _HERE, "all"], check=True, capture_output=True)
-    root = reference_root or "/root/reference"
+    root = reference_root or os.environ.get("REFERENCE_ROOT") or os.path.abspath(os.path.join(_HERE, "..", "..", "reference"))
     if os.path.exists(os.path.join(root, "robocache", "validation", "cpu_reference.hpp")):
         subprocess.run(["make", "-C", _HERE, "ref", f"REFERENCE_ROOT={root}"],
                        check=True, capture_output=True)

@@ -28,6 +28,7 @@ constexpr int kPointsPerLane = 4;
 constexpr int kPointsPerWarp = 32 * kPointsPerLane;            // 128
 constexpr int kPointsPerBlock = kThreads * kPointsPerLane;     // 1024
 constexpr size_t kResidentBytes = 96u << 20;   // accumulators up to this size are treated as L2-resident (one pass)
+constexpr long long kProbeMinPoints = 1ll << 20;  // below this the order probe is not worth its launch
 constexpr int kAutoMeanPasses = 6;             // slab passes of the two-phase mean scatter on larger grids
 constexpr size_t kSmallGridBytes = 64u << 20;                  // grids up to this size are cleared by voxel_zero_kernel
 
@@ -128,8 +129,9 @@ template <int MODE, bool AGG>
 __global__ void __launch_bounds__(kThreads)
 voxel_bin_kernel(const float* __restrict__ pts, const float* __restrict__ feats, void* __restrict__ grid_v,
                  int* __restrict__ counts, long long N, int F, VoxelGeom g, bool pts_aligned,
-                 long long id_lo, long long id_hi) {
+                 long long id_lo, long long id_hi, const int* __restrict__ gate, int gate_want) {
     __shared__ __align__(16) float s_xyz[kThreads / 32][kPointsPerWarp * 3];
+    if (gate != nullptr && *gate != gate_want) return;  // this variant was not chosen by the order probe
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
     const long long ntiles = (N + kPointsPerWarp - 1) / kPointsPerWarp;
@@ -235,8 +237,10 @@ voxel_bin_kernel(const float* __restrict__ pts, const float* __restrict__ feats,
 // 4 bytes per point and pass instead of the 12-byte coordinates.
 
 __global__ void __launch_bounds__(kThreads)
-voxel_ids_kernel(const float* __restrict__ pts, long long N, VoxelGeom g, bool pts_aligned, int* __restrict__ ids) {
+voxel_ids_kernel(const float* __restrict__ pts, long long N, VoxelGeom g, bool pts_aligned, int* __restrict__ ids,
+                 const int* __restrict__ gate, int gate_want) {
     __shared__ __align__(16) float s_xyz[kThreads / 32][kPointsPerWarp * 3];
+    if (gate != nullptr && *gate != gate_want) return;
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
     const long long ntiles = (N + kPointsPerWarp - 1) / kPointsPerWarp;
@@ -261,6 +265,42 @@ voxel_ids_kernel(const float* __restrict__ pts, long long N, VoxelGeom g, bool p
             if (pi < N) __stcs(ids + pi, static_cast<int>(voxel_id(x[i], y[i], z[i], g)));
         }
     }
+}
+
+// Order probe.  Whether slab passes pay off depends on the order of the points: a spatially coherent
+// stream (a scan, cluster after cluster) keeps its accumulators in L2 by itself and is fastest in one
+// pass, an iid stream is not.  One CTA looks at kProbeTiles tiles spread over the cloud and counts how
+// often two consecutive points fall into the same 1/64 slab of the grid; *flag = 1 (coherent) if at
+// least 15 % do.  The kernels of both strategies are launched behind it and the ones that were not
+// chosen return at once, so the decision never leaves the device.
+constexpr int kProbeTiles = 256;
+__global__ void __launch_bounds__(1024)
+voxel_order_probe_kernel(const float* __restrict__ pts, long long N, VoxelGeom g, long long V, int* __restrict__ flag) {
+    __shared__ int s_same, s_pairs;
+    if (threadIdx.x == 0) { s_same = 0; s_pairs = 0; }
+    __syncthreads();
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    const long long ntiles = N / kPointsPerWarp;  // full tiles only
+    const long long step = ntiles > kProbeTiles ? ntiles / kProbeTiles : 1;
+    int same = 0, pairs = 0;
+    for (long long t = warp; t < kProbeTiles && t * step < ntiles; t += 32) {
+        const long long base = t * step * kPointsPerWarp;
+        float x[kPointsPerLane], y[kPointsPerLane], z[kPointsPerLane];
+        tile_load_slow(pts, base, N, lane, x, y, z);
+#pragma unroll
+        for (int i = 0; i < kPointsPerLane; ++i) {
+            const long long id = voxel_id(x[i], y[i], z[i], g);
+            const int slab = (id < 0) ? -1 : static_cast<int>(id * 64 / V);
+            const int next = __shfl_down_sync(0xffffffffu, slab, 1);
+            const bool ok = lane < 31 && slab >= 0 && next >= 0;
+            pairs += __popc(__ballot_sync(0xffffffffu, ok));
+            same += __popc(__ballot_sync(0xffffffffu, ok && slab == next));
+        }
+    }
+    if (lane == 0) { atomicAdd(&s_same, same); atomicAdd(&s_pairs, pairs); }
+    __syncthreads();
+    if (threadIdx.x == 0) *flag = (s_pairs > 0 && 100ll * s_same >= 15ll * s_pairs) ? 1 : 0;
 }
 
 template <int MODE>
@@ -289,8 +329,10 @@ __device__ __forceinline__ void scatter_one(int id, long long pi, const float* _
 template <int MODE>
 __global__ void __launch_bounds__(kThreads)
 voxel_scatter_ids_kernel(const int* __restrict__ ids, const float* __restrict__ feats, void* __restrict__ grid_v,
-                         int* __restrict__ counts, long long N, int F, int id_lo, int id_hi) {
+                         int* __restrict__ counts, long long N, int F, int id_lo, int id_hi,
+                         const int* __restrict__ gate, int gate_want) {
     __shared__ int s_id[kThreads / 32][256];
+    if (gate != nullptr && *gate != gate_want) return;
     __shared__ int s_pt[kThreads / 32][256];   // point index relative to the warp's step base
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
@@ -418,7 +460,7 @@ __global__ void __launch_bounds__(kThreads) voxel_max_decode_kernel(int* __restr
 template <int MODE, bool AGG>
 void launch_bin_one(bool overlap_prev, unsigned int blocks, cudaStream_t st, const float* pts, const float* feats,
                     void* grid, int* counts, long long N, int F, const VoxelGeom& g, bool aligned, long long id_lo,
-                    long long id_hi) {
+                    long long id_hi, const int* gate, int gate_want) {
     if (overlap_prev) {
         cudaLaunchConfig_t cfg{};
         cfg.gridDim = dim3(blocks);
@@ -431,19 +473,20 @@ void launch_bin_one(bool overlap_prev, unsigned int blocks, cudaStream_t st, con
         cfg.attrs = &attr;
         cfg.numAttrs = 1;
         if (cudaLaunchKernelEx(&cfg, voxel_bin_kernel<MODE, AGG>, pts, feats, grid, counts, N, F, g, aligned, id_lo,
-                               id_hi) == cudaSuccess)
+                               id_hi, gate, gate_want) == cudaSuccess)
             return;
         cudaGetLastError();  // attribute refused: fall through to an ordinary launch
     }
-    voxel_bin_kernel<MODE, AGG><<<blocks, kThreads, 0, st>>>(pts, feats, grid, counts, N, F, g, aligned, id_lo, id_hi);
+    voxel_bin_kernel<MODE, AGG><<<blocks, kThreads, 0, st>>>(pts, feats, grid, counts, N, F, g, aligned, id_lo, id_hi,
+                                                             gate, gate_want);
 }
 
 template <int MODE>
 void launch_bin(bool agg, bool overlap_prev, unsigned int blocks, cudaStream_t st, const float* pts, const float* feats,
                 void* grid, int* counts, long long N, int F, const VoxelGeom& g, bool aligned, long long id_lo,
-                long long id_hi) {
-    if (agg) launch_bin_one<MODE, true>(overlap_prev, blocks, st, pts, feats, grid, counts, N, F, g, aligned, id_lo, id_hi);
-    else     launch_bin_one<MODE, false>(overlap_prev, blocks, st, pts, feats, grid, counts, N, F, g, aligned, id_lo, id_hi);
+                long long id_hi, const int* gate = nullptr, int gate_want = 0) {
+    if (agg) launch_bin_one<MODE, true>(overlap_prev, blocks, st, pts, feats, grid, counts, N, F, g, aligned, id_lo, id_hi, gate, gate_want);
+    else     launch_bin_one<MODE, false>(overlap_prev, blocks, st, pts, feats, grid, counts, N, F, g, aligned, id_lo, id_hi, gate, gate_want);
 }
 
 // ---------------------------------------------------------------- allocation-free mean mode
@@ -525,8 +568,9 @@ uint64_t rc_voxelize_scratch_bytes(int64_t N, int32_t F, const int32_t grid_size
     const double cells = static_cast<double>(grid_size_host[0]) * grid_size_host[1] * grid_size_host[2];
     if (cells <= 0 || cells >= 2147483648.0) return 0;
     const double acc_bytes = cells * 4.0 * (mode == RC_VOXEL_MEAN ? (1 + (F > 0 ? F : 0)) : 1);
-    if (mode == RC_VOXEL_COUNT || acc_bytes <= static_cast<double>(kResidentBytes)) return 0;  // one pass is enough
-    return static_cast<uint64_t>(N) * 4u;
+    if (acc_bytes <= static_cast<double>(kResidentBytes)) return 0;  // L2-resident accumulators: one pass
+    if (mode == RC_VOXEL_COUNT) return (N >= kProbeMinPoints) ? 16 : 0;     // the order probe's flag
+    return ((static_cast<uint64_t>(N) * 4u + 15u) & ~static_cast<uint64_t>(15)) + 16u;  // ids + flag
 }
 
 int rc_voxelize_ex(const float* points, const float* features, void* grid, int32_t* counts, int64_t N,
@@ -601,20 +645,35 @@ int rc_voxelize_ex(const float* points, const float* features, void* grid, int32
         const int forced = rc::g_voxel_passes.load(std::memory_order_relaxed);
         const bool scatter_mode = (mode == RC_VOXEL_COUNT || mode == RC_VOXEL_MEAN || mode == RC_VOXEL_MAX);
         const double acc_bytes = static_cast<double>(V) * 4.0 * (mode == RC_VOXEL_MEAN ? (1 + F) : (feat_mode ? F : 1));
-        const bool ids_path = (mode == RC_VOXEL_MEAN) && scratch != nullptr && rc::aligned_to(scratch, 16) &&
-                              scratch_bytes >= static_cast<uint64_t>(N) * 4u && V < (1ll << 31) &&
-                              (forced > 1 || (forced == 0 && acc_bytes > static_cast<double>(kResidentBytes)));
+        const bool big = acc_bytes > static_cast<double>(kResidentBytes);
+        const uint64_t ids_bytes = (static_cast<uint64_t>(N) * 4u + 15u) & ~static_cast<uint64_t>(15);
+        const bool ids_room = scratch != nullptr && rc::aligned_to(scratch, 16) && scratch_bytes >= ids_bytes && V < (1ll << 31);
+        const bool ids_path = (mode == RC_VOXEL_MEAN) && ids_room && (forced > 1 || (forced == 0 && big));
+        // automatic choice on large grids: let the order probe pick between one pass and slab passes
+        int* flag = nullptr;
+        if (forced == 0 && big && N >= kProbeMinPoints && scratch != nullptr && rc::aligned_to(scratch, 16)) {
+            if (mode == RC_VOXEL_MEAN && ids_room && scratch_bytes >= ids_bytes + 16)
+                flag = reinterpret_cast<int*>(static_cast<unsigned char*>(scratch) + ids_bytes);
+            else if (mode == RC_VOXEL_COUNT && scratch_bytes >= 16)
+                flag = static_cast<int*>(scratch);
+        }
+        if (flag != nullptr) voxel_order_probe_kernel<<<1, 1024, 0, st>>>(points, N, g, V, flag);
         int passes = 1;
         if (scatter_mode) {
             if (forced > 0) passes = forced;
             else if (ids_path) passes = kAutoMeanPasses;
-            else if (mode == RC_VOXEL_COUNT && acc_bytes > static_cast<double>(kResidentBytes)) passes = 2;
+            else if (mode == RC_VOXEL_COUNT && big) passes = 2;
         }
         if (passes > V) passes = static_cast<int>(V);
         const long long slab = (V + passes - 1) / passes;
+        if (flag != nullptr) {
+            // coherent order (flag 1): one pass over the whole grid
+            if (mode == RC_VOXEL_MEAN) launch_bin<kMean>(false, false, nb, st, points, features, grid, counts, N, F, g, aligned, 0, V, flag, 1);
+            else launch_bin<kCount>(agg, false, nb, st, points, features, grid, counts, N, F, g, aligned, 0, V, flag, 1);
+        }
         if (ids_path) {
             int* ids = static_cast<int*>(scratch);
-            voxel_ids_kernel<<<nb, kThreads, 0, st>>>(points, N, g, aligned, ids);
+            voxel_ids_kernel<<<nb, kThreads, 0, st>>>(points, N, g, aligned, ids, flag, 0);
             long long sb = (((N + 255) >> 8) + kThreads / 32 - 1) / (kThreads / 32);
             if (sb > cap) sb = cap;
             if (sb < 1) sb = 1;
@@ -622,14 +681,14 @@ int rc_voxelize_ex(const float* points, const float* features, void* grid, int32
                 const long long lo = ps * slab;
                 const long long hi = (lo + slab < V) ? lo + slab : V;
                 voxel_scatter_ids_kernel<kMean><<<static_cast<unsigned int>(sb), kThreads, 0, st>>>(
-                    ids, features, grid, counts, N, F, static_cast<int>(lo), static_cast<int>(hi));
+                    ids, features, grid, counts, N, F, static_cast<int>(lo), static_cast<int>(hi), flag, 0);
             }
         } else {
             for (int ps = 0; ps < passes; ++ps) {
                 const long long lo = (passes == 1) ? 0 : ps * slab;
                 const long long hi = (passes == 1) ? V : ((ps + 1) * slab < V ? (ps + 1) * slab : V);
                 switch (mode) {
-                    case RC_VOXEL_COUNT: launch_bin<kCount>(agg, overlap_fill && ps == 0, nb, st, points, features, grid, counts, N, F, g, aligned, lo, hi); break;
+                    case RC_VOXEL_COUNT: launch_bin<kCount>(agg, overlap_fill && ps == 0, nb, st, points, features, grid, counts, N, F, g, aligned, lo, hi, flag, 0); break;
                     case RC_VOXEL_OCCUPANCY: launch_bin<kOccupancy>(false, overlap_fill && ps == 0, nb, st, points, features, grid, counts, N, F, g, aligned, lo, hi); break;
                     case RC_VOXEL_OCCUPANCY_U8: launch_bin<kOccupancyU8>(false, overlap_fill && ps == 0, nb, st, points, features, grid, counts, N, F, g, aligned, lo, hi); break;
                     case RC_VOXEL_MEAN: launch_bin<kMean>(false, overlap_fill && ps == 0, nb, st, points, features, grid, counts, N, F, g, aligned, lo, hi); break;

@@ -64,9 +64,11 @@ def voxel_uniform_inputs(N=500_000, seed=0, device="cpu") -> torch.Tensor:
 
 
 def voxel_mixture_inputs(N=1 << 26, F=4, clusters=256, sigma=0.5, seed=0, device="cpu",
-                         chunk=1 << 24) -> Tuple[torch.Tensor, torch.Tensor]:
-    """Mixture of ``clusters`` isotropic Gaussians (centres U[-25,25)^3), iid order, F-channel N(0,1)
-    features.  Generated in chunks so the peak temporary stays small."""
+                         chunk=1 << 24, cluster_sorted=False) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Mixture of ``clusters`` isotropic Gaussians (centres U[-25,25)^3), F-channel N(0,1) features.
+    Points come in iid order (the worst case for locality) unless ``cluster_sorted``, which emits the
+    clusters one after another (a spatially coherent scan).  Generated in chunks so the peak temporary
+    stays small."""
     g = _gen(seed, device)
     centres = torch.rand(clusters, 3, generator=g, device=device) * 50.0 - 25.0
     pts = torch.empty(N, 3, device=device)
@@ -74,6 +76,8 @@ def voxel_mixture_inputs(N=1 << 26, F=4, clusters=256, sigma=0.5, seed=0, device
     for a in range(0, N, chunk):
         b = min(N, a + chunk)
         k = torch.randint(0, clusters, (b - a,), generator=g, device=device)
+        if cluster_sorted:  # coherent within each generated chunk
+            k = torch.sort(k).values
         pts[a:b] = centres[k] + sigma * torch.randn(b - a, 3, generator=g, device=device)
         feats[a:b] = torch.randn(b - a, F, generator=g, device=device)
     return pts, feats

@@ -155,7 +155,7 @@ def voxel_cases(g):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference-root", default="/root/reference")
+    ap.add_argument("--reference-root", default=os.path.abspath(os.path.join(ROOT, "..", "reference")))
     args = ap.parse_args()
     sys.path.insert(0, os.path.join(args.reference_root, "robocache", "python"))
     sys.path.insert(0, ROOT)

@@ -168,17 +168,17 @@ def test_guard_bands_and_determinism(cuda_lib):
 
 
 def test_mixture_properties_at_scale(cuda_lib):
-    """Count + mean on 2^24 mixture points into 512^3 (a quarter of the headline N, same geometry): counts
+    """Count + mean on the headline cloud (2^26 mixture points, F=4, 512^3): counts
     sum to the in-grid points, means recombine to the global feature sums, empty voxels are exactly 0, and
     a 2^18 seeded prefix is checked voxel by voxel against the oracle on a sub-grid."""
-    N = 1 << 24
+    N = 1 << 26
     pts, feats = workloads.voxel_mixture_inputs(N, seed=0, device=DEV)
     kw = workloads.VOXEL_MIXTURE_GEOMETRY
     grid, counts = ops.voxelize_pointcloud_cuda(pts, feats, kw["grid_min"], kw["voxel_size"], kw["grid_size"], "mean")
-    q = torch.floor((pts - torch.tensor(kw["grid_min"], device=DEV)) / kw["voxel_size"])
+    q = torch.floor((pts - torch.tensor(kw["grid_min"], device=DEV)) / torch.tensor(kw["voxel_size"], device=DEV))
     inside = ((q >= 0) & (q < 512)).all(dim=1)
     assert int(counts.sum(dtype=torch.int64)) == int(inside.sum())
-    total = (grid.double() * counts.unsqueeze(-1)).sum(dim=(0, 1, 2))
+    total = torch.stack([(grid[..., c].double() * counts).sum() for c in range(4)])
     ref_total = feats[inside].double().sum(0)
     assert torch.allclose(total, ref_total, rtol=1e-4, atol=1.0)
     assert bool((grid[counts == 0] == 0).all())
@@ -192,3 +192,28 @@ def test_mixture_properties_at_scale(cuda_lib):
     keep = exp_ids[exp_ids >= 0]
     exp_counts = torch.bincount(keep, minlength=512 ** 3).int()
     assert torch.equal(cnt_small.cpu(), exp_counts)
+
+
+@pytest.mark.parametrize("cluster_sorted", [False, True])
+def test_automatic_strategy_equals_single_pass(cluster_sorted, cuda_lib):
+    """On grids larger than L2 the library probes the point order on the device and runs either one pass
+    (coherent order) or slab passes / the two-phase id path (iid order).  Whatever it picks, counts must be
+    identical to the forced single pass and means must agree within the summation-order tolerance."""
+    N = 1 << 22
+    pts, feats = workloads.voxel_mixture_inputs(N, seed=5, device=DEV, cluster_sorted=cluster_sorted)
+    kw = workloads.VOXEL_MIXTURE_GEOMETRY
+    args = (kw["grid_min"], kw["voxel_size"], kw["grid_size"])
+    try:
+        cuda_lib.rc_set_option(1, 1)
+        ref_cnt = ops.voxelize_pointcloud_cuda(pts, None, *args, "count")[0]
+        ref_mean, ref_c = ops.voxelize_pointcloud_cuda(pts, feats, *args, "mean")
+        sabs, _ = ops.voxelize_pointcloud_cuda(pts, feats.abs(), *args, "mean", normalize=False)
+        for forced in (0, 2, 5):
+            cuda_lib.rc_set_option(1, forced)
+            assert torch.equal(ops.voxelize_pointcloud_cuda(pts, None, *args, "count")[0], ref_cnt), forced
+            mean, c = ops.voxelize_pointcloud_cuda(pts, feats, *args, "mean")
+            assert torch.equal(c, ref_c), forced
+            tol = 1e-5 * ref_mean.abs() + 1e-6 * sabs / ref_c.clamp(min=1).unsqueeze(-1)
+            assert bool(((mean - ref_mean).abs() <= tol).all()), forced
+    finally:
+        cuda_lib.rc_set_option(1, 0)
