@@ -79,31 +79,44 @@ def fuse_streams_cuda(datas: Sequence[torch.Tensor], times: Sequence[torch.Tenso
                       target_times: torch.Tensor) -> torch.Tensor:
     """N timestamped streams -> [B,T,sum(D_k)] in one launch (N <= 8)."""
     n = len(datas)
-    _check(1 <= n <= _lib.RC_MAX_STREAMS and len(times) == n,
-           f"between 1 and {_lib.RC_MAX_STREAMS} streams are supported")
+    if not (1 <= n <= _lib.RC_MAX_STREAMS and len(times) == n):
+        raise RuntimeError(f"between 1 and {_lib.RC_MAX_STREAMS} streams are supported")
+    # the checks of the reference binding, in its order; messages are only built on failure
     for k, d in enumerate(datas, 1):
-        _check(d.is_cuda, f"stream{k}_data must be on CUDA device")
+        if not d.is_cuda:
+            raise RuntimeError(f"stream{k}_data must be on CUDA device")
     for k, d in enumerate(datas, 1):
-        _check(d.dim() == 3, f"stream{k}_data must be 3D [B, S{k}, D{k}]")
+        if d.dim() != 3:
+            raise RuntimeError(f"stream{k}_data must be 3D [B, S{k}, D{k}]")
     for k, t in enumerate(times, 1):
-        _check(t.dim() == 2, f"stream{k}_times must be 2D [B, S{k}]")
-    _check(target_times.dim() == 2, "target_times must be 2D [B, T]")
+        if t.dim() != 2:
+            raise RuntimeError(f"stream{k}_times must be 2D [B, S{k}]")
+    if target_times.dim() != 2:
+        raise RuntimeError("target_times must be 2D [B, T]")
     B = datas[0].shape[0]
-    for d in datas[1:]:
-        _check(d.shape[0] == B, "Batch size mismatch")
-    for k, (d, t) in enumerate(zip(datas, times), 1):
-        _check(t.shape[1] == d.shape[1], f"stream{k}_times length mismatch")
-        _check(t.shape[0] == B, "Batch size mismatch")
-    _check(target_times.shape[0] == B, "Batch size mismatch")
-    for d in datas[1:]:
-        _check(d.dtype == datas[0].dtype, "Stream dtypes must match")
+    dtype0 = datas[0].dtype
     dev = datas[0].device
-    for x in list(datas) + list(times) + [target_times]:
-        _check(x.device == dev, "all tensors must be on the same CUDA device")
-    code = _dtype_code(datas[0].dtype)
     T = target_times.shape[1]
     for d in datas:
-        _check(d.shape[1] >= 1 or T == 0 or B == 0, "every stream must have at least one timestep")
+        if d.shape[0] != B:
+            raise RuntimeError("Batch size mismatch")
+    for k, (d, t) in enumerate(zip(datas, times), 1):
+        if t.shape[1] != d.shape[1]:
+            raise RuntimeError(f"stream{k}_times length mismatch")
+        if t.shape[0] != B:
+            raise RuntimeError("Batch size mismatch")
+    if target_times.shape[0] != B:
+        raise RuntimeError("Batch size mismatch")
+    for d in datas:
+        if d.dtype != dtype0:
+            raise RuntimeError("Stream dtypes must match")
+    for x in (*datas, *times, target_times):
+        if x.device != dev:
+            raise RuntimeError("all tensors must be on the same CUDA device")
+    code = _dtype_code(dtype0)
+    for d in datas:
+        if d.shape[1] < 1 and T != 0 and B != 0:
+            raise RuntimeError("every stream must have at least one timestep")
 
     L = _lib.load()
     datas_c = [d.contiguous() for d in datas]

@@ -217,3 +217,23 @@ def test_automatic_strategy_equals_single_pass(cluster_sorted, cuda_lib):
             assert bool(((mean - ref_mean).abs() <= tol).all()), forced
     finally:
         cuda_lib.rc_set_option(1, 0)
+
+
+def test_batched_float_grids_match_reference_header(cuda_lib):
+    """[B,N,3] -> [B,D,H,W] float occupancy / density against the reference's own C++ header, item by item
+    (skipped where that header was not compiled); also against the oracle, which is always available."""
+    from robogoat_b200.batched import voxelize_density_batched, voxelize_occupancy_batched
+    g = torch.Generator().manual_seed(17)
+    B, N = 3, 5000
+    pts = torch.rand(B, N, 3, generator=g) * 6 - 3
+    origin, vs, dhw = [-2.0, -2.5, -1.0], 0.125, [20, 36, 28]          # depth(z), height(y), width(x)
+    dens = voxelize_density_batched(pts.to(DEV), dhw, vs, origin).cpu()
+    occ = voxelize_occupancy_batched(pts.to(DEV), torch.tensor(dhw), vs, torch.tensor(origin)).cpu()
+    assert dens.shape == (B, 20, 36, 28) and dens.dtype == torch.float32
+    for b in range(B):
+        exp = oracle.voxelize_pointcloud(pts[b], None, origin, vs, [28, 36, 20], mode="count").flatten().float()
+        assert torch.equal(dens[b].flatten(), exp)
+        assert torch.equal(occ[b].flatten(), (exp > 0).float())
+        ref = oracle.ref_header_voxelize(pts[b], origin, vs, [28, 36, 20], density=True)
+        if ref is not None:
+            assert torch.equal(dens[b].flatten(), ref)
