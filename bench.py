@@ -21,7 +21,6 @@ all host threads) on a bounded sample of the same workload and prints the same l
 from __future__ import annotations
 
 import argparse
-import ctypes
 import json
 import os
 import statistics

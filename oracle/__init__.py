@@ -20,7 +20,6 @@ import os
 import subprocess
 from typing import Optional, Sequence, Tuple
 
-import numpy as np
 import torch
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
