@@ -133,3 +133,17 @@ def test_cuda_graph_replay_matches_direct_calls(cuda_lib):
     got = cache.run(robocache.resample_trajectories, src, st, tt).clone()
     assert torch.equal(got, robocache.resample_trajectories(src, st, tt))
     assert cache.stats()["entries"] == 2
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("streams,T,B", [
+    (((30, 512), (100, 64), (200, 12)), 50, 1500),      # headline widths, several CTAs per SM
+    (((7, 16), (3, 8), (5, 4)), 9, 2500),               # tiny rows, odd lengths
+    (((40, 36), (600, 4), (2, 20)), 33, 1300),          # a long time row
+])
+def test_many_items(streams, T, B, dtype, cuda_lib):
+    """Batches of a few thousand items (several waves of CTAs per SM) against the oracle."""
+    args = list(workloads.fusion_inputs(B=B, T=T, dtype=dtype, seed=B + T, streams=streams))
+    g = torch.Generator().manual_seed(B)
+    args[6] = torch.rand(B, T, generator=g) * 1.2 - 0.1
+    assert_exact(run(args), expected(args))
