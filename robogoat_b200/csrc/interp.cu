@@ -295,7 +295,7 @@ bracket_kernel(const float* __restrict__ st, const float* __restrict__ tt, long 
 // 8-byte aligned cost nothing extra.  The unit of work is an 8-byte piece of an output
 // row (4 bf16 or 2 fp32), so every stream width must be a multiple of 8 bytes.
 
-constexpr int kBlockThreads = 256;
+constexpr int kBlockThreads = 512;  // 4 CTAs x 16 warps per SM at the fusion headline shape (measured best of 256/512/1024)
 constexpr int kBlockSmemLimit = 100 * 1024;     // keeps at least two CTAs per SM
 constexpr unsigned int kMbarSpinLimit = 1u << 22;
 
@@ -323,6 +323,7 @@ struct BlockParams {
     int rows_per_tile;
     int times_base;             // byte offsets of the regions after the staged data
     int brk_base;
+    int vec_base;               // table of output-vector descriptors (16-byte path)
     unsigned int tx_bytes;      // sum of block_bytes
 };
 
@@ -331,6 +332,22 @@ __device__ unsigned int g_bulk_wait_timeouts = 0;
 
 __device__ __forceinline__ unsigned int smem_u32(const void* p) {
     return static_cast<unsigned int>(__cvta_generic_to_shared(p));
+}
+// shared-memory loads through 32-bit window addresses (results of smem_u32)
+__device__ __forceinline__ unsigned int lds_u32(unsigned int addr) {
+    unsigned int v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ float lds_f32(unsigned int addr) {
+    float v;
+    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint2 lds_v2(unsigned int addr) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+    return v;
 }
 __device__ __forceinline__ void mbar_init(unsigned long long* bar, unsigned int count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(smem_u32(bar)), "r"(count) : "memory");
@@ -359,20 +376,133 @@ __device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned int 
     return false;
 }
 
-template <int ES>
+// pieces of the block kernel ---------------------------------------------------------------
+
+// brackets of rows [t_begin, t_begin + nrows) of item b, one (stream, row) pair per thread, stored as
+// byte offsets (from the stage origin) of the two bracket rows, plus the weight
+__device__ __forceinline__ void block_brackets(const BlockParams& p, const float* s_times, int* s_lo, int* s_hi,
+                                               float* s_w, long long b, int t_begin, int nrows, int tid, int nthreads) {
+    for (int i = tid; i < nrows * p.ns; i += nthreads) {
+        const int k = i / nrows;
+        const int r = i - k * nrows;
+        const BlockStream& s = p.s[k];
+        int l, rr;
+        float w;
+        bracket(s_times + s.time_off, s.S, __ldg(p.tt + b * p.T + t_begin + r), l, rr, w);
+        s_lo[k * p.rows_per_tile + r] = s.data_off + l * s.row_bytes;
+        s_hi[k * p.rows_per_tile + r] = s.data_off + rr * s.row_bytes;
+        s_w[k * p.rows_per_tile + r] = w;
+    }
+}
+
+// the same bytes a bulk copy would have delivered, fetched with ordinary loads (a wait timed out)
+__device__ __forceinline__ void block_fetch_plain(const BlockParams& p, unsigned char* stage, long long b, int tid,
+                                                  int nthreads) {
+    for (int k = 0; k < p.ns; ++k) {
+        const uint2* g = reinterpret_cast<const uint2*>(p.s[k].data + b * p.s[k].block_bytes);
+        uint2* d = reinterpret_cast<uint2*>(stage + p.s[k].data_off);
+        for (int i = tid; i < p.s[k].block_bytes / 8; i += nthreads) d[i] = __ldg(g + i);
+    }
+}
+
+// Descriptor table (offsets relative to the stage origin).  16-byte path: for each vector of a row
+// group and each of its two 8-byte halves, the offset of its piece inside a staged row (x, y) and the
+// offset of its bracket entry for group 0 (z, w).  8-byte path: the same for each piece of a row (x, z).
+template <bool V16>
+__device__ __forceinline__ void block_unit_table(const BlockParams& p, uint4* s_vec, int tid, int nthreads) {
+    const int G = (V16 && (p.hpr & 1)) ? 2 : 1;
+    const int units = V16 ? ((G * p.hpr) >> 1) : p.hpr;
+    for (int m = tid; m < units; m += nthreads) {
+        unsigned int e[4] = {0u, 0u, 0u, 0u};
+#pragma unroll
+        for (int h = 0; h < (V16 ? 2 : 1); ++h) {
+            const int q = V16 ? (2 * m + h) : m;
+            const int dr = (q >= p.hpr) ? 1 : 0;
+            const int c = q - dr * p.hpr;
+            int k = 0;
+            for (int j = 1; j < p.ns; ++j) k += (c >= p.s[j].half_off) ? 1 : 0;
+            e[h] = static_cast<unsigned int>((c - p.s[k].half_off) * 8);
+            e[2 + h] = static_cast<unsigned int>(p.brk_base) + static_cast<unsigned int>(k * p.rows_per_tile + dr) * 4u;
+        }
+        s_vec[m] = make_uint4(e[0], e[1], e[2], e[3]);
+    }
+}
+
+// Interpolates `nrows` rows of one item out of a stage into out_tile.
+// V16: output written as 16-byte vectors.  Output rows are a multiple of 8 bytes, so rows (or, when a
+// row is an odd number of 8-byte pieces, pairs of rows) start 16-byte aligned; a group of G = 1 or 2
+// rows is then a whole number of vectors, and which (row of the group, piece) each half of vector m
+// covers is the same for every group: it is read from the descriptor table, and the threads walk the
+// flat (group, vector) space of the tile, so the work is spread evenly whatever the row width.
+// Otherwise the unit is an 8-byte piece of a row, walked the same way over the flat (row, piece) space.
+template <int ES, bool V16>
+__device__ __forceinline__ void block_compute(const BlockParams& p, const unsigned char* stage, const uint4* s_vec,
+                                              unsigned char* out_tile, int nrows, int tid, int nthreads) {
+    const int* s_lo = reinterpret_cast<const int*>(stage + p.brk_base);
+    const int* s_hi = s_lo + p.ns * p.rows_per_tile;
+    const float* s_w = reinterpret_cast<const float*>(s_hi + p.ns * p.rows_per_tile);
+    if (V16) {
+        const int G = (p.hpr & 1) ? 2 : 1;
+        const int vpg = (G * p.hpr) >> 1;             // vectors per group
+        const int ngroups = nrows / G;                // the host guarantees nrows % G == 0
+        const unsigned int sb = smem_u32(stage);
+        const unsigned int plane = static_cast<unsigned int>(p.ns * p.rows_per_tile) * 4u;  // lo -> hi -> w arrays
+        const int total = ngroups * vpg;
+        const int dm = nthreads % vpg, dg = nthreads / vpg;
+        int m = tid % vpg, g = tid / vpg;
+        const unsigned int gstep = static_cast<unsigned int>(G) * 4u;
+        for (int v = tid; v < total; v += nthreads) {
+            const uint4 e = s_vec[m];
+            const unsigned int b0 = sb + e.z + static_cast<unsigned int>(g) * gstep;
+            const unsigned int b1 = sb + e.w + static_cast<unsigned int>(g) * gstep;
+            const unsigned int la = lds_u32(b0), ha = lds_u32(b0 + plane);
+            const float wa = lds_f32(b0 + 2u * plane);
+            unsigned int lb = la, hb = ha;
+            float wb = wa;
+            if (b1 != b0) {  // the halves lie in different rows or streams
+                lb = lds_u32(b1); hb = lds_u32(b1 + plane); wb = lds_f32(b1 + 2u * plane);
+            }
+            const uint2 o0 = lerp_vec<ES, 8>(lds_v2(sb + e.x + la), lds_v2(sb + e.x + ha), wa, __fsub_rn(1.0f, wa));
+            const uint2 o1 = lerp_vec<ES, 8>(lds_v2(sb + e.y + lb), lds_v2(sb + e.y + hb), wb, __fsub_rn(1.0f, wb));
+            __stcs(reinterpret_cast<uint4*>(out_tile + static_cast<long long>(g) * (G * p.out_row_bytes) + m * 16),
+                   make_uint4(o0.x, o0.y, o1.x, o1.y));
+            m += dm; g += dg;
+            if (m >= vpg) { m -= vpg; ++g; }
+        }
+    } else {
+        const unsigned int sb = smem_u32(stage);
+        const unsigned int plane = static_cast<unsigned int>(p.ns * p.rows_per_tile) * 4u;
+        const int total = nrows * p.hpr;
+        const int dm = nthreads % p.hpr, dg = nthreads / p.hpr;
+        int m = tid % p.hpr, r = tid / p.hpr;
+        for (int v = tid; v < total; v += nthreads) {
+            const uint4 e = s_vec[m];
+            const unsigned int b0 = sb + e.z + static_cast<unsigned int>(r) * 4u;
+            const unsigned int la = lds_u32(b0), ha = lds_u32(b0 + plane);
+            const float w = lds_f32(b0 + 2u * plane);
+            const uint2 o = lerp_vec<ES, 8>(lds_v2(sb + e.x + la), lds_v2(sb + e.x + ha), w, __fsub_rn(1.0f, w));
+            __stcs(reinterpret_cast<uint2*>(out_tile + static_cast<long long>(r) * p.out_row_bytes + m * 8), o);
+            m += dm; r += dg;
+            if (m >= p.hpr) { m -= p.hpr; ++r; }
+        }
+    }
+}
+
+// One CTA per (item, row tile).  With few items an item's rows spread over several CTAs (each stages
+// the whole item; L2 serves the repeats).
+template <int ES, bool V16>
 __global__ void __launch_bounds__(kBlockThreads)
 interp_block_kernel(const __grid_constant__ BlockParams p) {
     extern __shared__ __align__(128) unsigned char smem[];
     unsigned long long* bar = reinterpret_cast<unsigned long long*>(smem);
     float* s_times = reinterpret_cast<float*>(smem + p.times_base);
-    // per (stream, row of this tile): shared-memory byte offsets of the two bracket rows, and the weight
     int* s_lo = reinterpret_cast<int*>(smem + p.brk_base);
     int* s_hi = s_lo + p.ns * p.rows_per_tile;
     float* s_w = reinterpret_cast<float*>(s_hi + p.ns * p.rows_per_tile);
+    uint4* s_vec = reinterpret_cast<uint4*>(smem + p.vec_base);
 
     const int tid = threadIdx.x;
-    const int lane = tid & 31;
-    const int warp = tid >> 5;
+    const int nthreads = blockDim.x;  // 512 for throughput, 256 when an item is split over several CTAs
     const long long b = blockIdx.x / p.tiles_t;
     const int tile = static_cast<int>(blockIdx.x - b * p.tiles_t);
     const int t_begin = tile * p.rows_per_tile;
@@ -388,22 +518,11 @@ interp_block_kernel(const __grid_constant__ BlockParams p) {
     for (int k = 0; k < p.ns; ++k) {
         const float* g = p.s[k].times + b * p.s[k].S;
         float* d = s_times + p.s[k].time_off;
-        for (int i = tid; i < p.s[k].S; i += kBlockThreads) d[i] = __ldg(g + i);
+        for (int i = tid; i < p.s[k].S; i += nthreads) d[i] = __ldg(g + i);
     }
+    block_unit_table<V16>(p, s_vec, tid, nthreads);
     __syncthreads();  // mbarrier initialised, time rows visible
-
-    // brackets of this tile's rows, one (stream, row) pair per thread
-    for (int i = tid; i < nrows * p.ns; i += kBlockThreads) {
-        const int k = i / nrows;
-        const int r = i - k * nrows;
-        const BlockStream& s = p.s[k];
-        int l, rr;
-        float w;
-        bracket(s_times + s.time_off, s.S, __ldg(p.tt + b * p.T + t_begin + r), l, rr, w);
-        s_lo[k * p.rows_per_tile + r] = s.data_off + l * s.row_bytes;
-        s_hi[k * p.rows_per_tile + r] = s.data_off + rr * s.row_bytes;
-        s_w[k * p.rows_per_tile + r] = w;
-    }
+    block_brackets(p, s_times, s_lo, s_hi, s_w, b, t_begin, nrows, tid, nthreads);
 
     // One thread waits for the staged data (bounded); the others park at the barrier.  A CTA
     // whose wait runs out records it and fetches the same bytes with ordinary loads instead
@@ -412,35 +531,11 @@ interp_block_kernel(const __grid_constant__ BlockParams p) {
     if (tid == 0) arrived = mbar_wait(bar, 0);
     if (__syncthreads_or(!arrived)) {
         if (tid == 0) atomicAdd(&g_bulk_wait_timeouts, 1u);
-        for (int k = 0; k < p.ns; ++k) {
-            const uint2* g = reinterpret_cast<const uint2*>(p.s[k].data + b * p.s[k].block_bytes);
-            uint2* d = reinterpret_cast<uint2*>(smem + p.s[k].data_off);
-            for (int i = tid; i < p.s[k].block_bytes / 8; i += kBlockThreads) d[i] = __ldg(g + i);
-        }
+        block_fetch_plain(p, smem, b, tid, nthreads);
         __syncthreads();
     }
-
-    // Each lane owns the 8-byte pieces c = lane, lane+32, ... of an output row; which stream a
-    // piece belongs to does not depend on the row, so it is resolved once per piece and the
-    // warp then walks its rows (warp, warp+8, ...) with that piece fixed.
     unsigned char* out_tile = p.out + b * p.out_block_bytes + static_cast<long long>(t_begin) * p.out_row_bytes;
-    for (int c = lane; c < p.hpr; c += 32) {
-        int k = 0;
-        for (int j = 1; j < p.ns; ++j) k += (c >= p.s[j].half_off) ? 1 : 0;
-        const int cc8 = (c - p.s[k].half_off) * 8;
-        const int* lo = s_lo + k * p.rows_per_tile;
-        const int* hi = s_hi + k * p.rows_per_tile;
-        const float* ww = s_w + k * p.rows_per_tile;
-        unsigned char* out_c = out_tile + c * 8;
-#pragma unroll 2
-        for (int r = warp; r < nrows; r += kBlockThreads / 32) {
-            const float w = ww[r];
-            const uint2 a = *reinterpret_cast<const uint2*>(smem + lo[r] + cc8);
-            const uint2 bb = *reinterpret_cast<const uint2*>(smem + hi[r] + cc8);
-            const uint2 o = lerp_vec<ES, 8>(a, bb, w, __fsub_rn(1.0f, w));
-            __stcs(reinterpret_cast<uint2*>(out_c + static_cast<long long>(r) * p.out_row_bytes), o);
-        }
-    }
+    block_compute<ES, V16>(p, smem, s_vec, out_tile, nrows, tid, nthreads);
 }
 
 // ---------------------------------------------------------------- host side
@@ -518,11 +613,17 @@ bool try_launch_block(const LiveStream* ls, int ns, const float* tt, unsigned ch
         const long long max_tiles = (T + 7) / 8;  // at least one row per warp
         if (tiles > max_tiles) tiles = max_tiles;
     }
-    const long long rpt = (T + tiles - 1) / tiles;
+    long long rpt = (T + tiles - 1) / tiles;
+    // 16-byte output vectors: rows (or pairs of rows, when a row is an odd number of 8-byte pieces) must
+    // start 16-byte aligned in every tile of every item
+    const long long G = ((out_row / 8) & 1) ? 2 : 1;
+    const bool v16 = rc::aligned_to(out, 16) && (T % G == 0);
+    if (v16 && (rpt % G) != 0) ++rpt;
     tiles = (T + rpt - 1) / rpt;
     p.times_base = (data_off + 15) & ~15;
     p.brk_base = p.times_base + ((time_off * 4 + 15) & ~15);
-    const long long smem = p.brk_base + rpt * ns * 12;
+    p.vec_base = static_cast<int>((p.brk_base + rpt * ns * 12 + 15) & ~15ll);
+    const long long smem = p.vec_base + (v16 ? (G * (out_row / 8) / 2) : (out_row / 8)) * 16;
     if (smem > kBlockSmemLimit || B * tiles >= (1ll << 31)) return false;
     p.tt = tt;
     p.out = out;
@@ -534,12 +635,14 @@ bool try_launch_block(const LiveStream* ls, int ns, const float* tt, unsigned ch
     p.tiles_t = static_cast<int>(tiles);
     p.rows_per_tile = static_cast<int>(rpt);
     p.tx_bytes = static_cast<unsigned int>(in_bytes);
-    auto* kern = (es == 2) ? interp_block_kernel<2> : interp_block_kernel<4>;
+    auto* kern = (es == 2) ? (v16 ? interp_block_kernel<2, true> : interp_block_kernel<2, false>)
+                           : (v16 ? interp_block_kernel<4, true> : interp_block_kernel<4, false>);
     if (smem > 48 * 1024) {
         const int rc_attr = rc::ensure_dynamic_smem(reinterpret_cast<const void*>(kern), device, static_cast<size_t>(smem));
         if (rc_attr != RC_OK) { *status = rc_attr; return true; }
     }
-    kern<<<static_cast<unsigned int>(B * tiles), kBlockThreads, static_cast<size_t>(smem), stream>>>(p);
+    const int threads = (tiles > 1) ? 256 : kBlockThreads;  // split items are latency bound: smaller CTAs start sooner
+    kern<<<static_cast<unsigned int>(B * tiles), threads, static_cast<size_t>(smem), stream>>>(p);
     *status = rc::check_launch();
     return true;
 }
