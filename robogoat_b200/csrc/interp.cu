@@ -1,6 +1,12 @@
 // Timestamp-aligned resampling and N-stream temporal fusion for sm_100a.
 //
-// One kernel serves both operators.  A CTA owns one batch row b and a tile of 32*W
+// Two kernels serve both operators; the host picks per call (interp_dispatch):
+//   * the row-gather kernel below, for any shape (the resampling headline: rows of a long source
+//     are fetched straight from global memory, only the rows that are used);
+//   * the block kernel further down, when all inputs of one batch item fit in shared memory (the
+//     fusion shapes): the item is staged whole with bulk asynchronous copies (TMA).
+//
+// Row-gather kernel.  A CTA owns one batch row b and a tile of 32*W
 // target times (W warps).  The source timestamp rows of every stream of b are staged in
 // shared memory once per CTA.  Each LANE then searches the bracket of its own target in
 // shared memory (a branch-free lower bound, the same number of probes in every lane) and
@@ -292,8 +298,9 @@ bracket_kernel(const float* __restrict__ st, const float* __restrict__ tt, long 
 // computes its output rows out of shared memory.  Global memory then sees only large
 // contiguous reads (every input byte exactly once per CTA) and fully coalesced writes;
 // rows narrower than a warp access (24-byte IMU rows) and output rows that are only
-// 8-byte aligned cost nothing extra.  The unit of work is an 8-byte piece of an output
-// row (4 bf16 or 2 fp32), so every stream width must be a multiple of 8 bytes.
+// 8-byte aligned cost nothing extra.  Work is cut into 8-byte pieces of output rows (4 bf16
+// or 2 fp32), written two at a time as 16-byte vectors where the row geometry allows, so
+// every stream width must be a multiple of 8 bytes.
 
 constexpr int kBlockThreads = 512;  // 4 CTAs x 16 warps per SM at the fusion headline shape (measured best of 256/512/1024)
 constexpr int kBlockSmemLimit = 100 * 1024;     // keeps at least two CTAs per SM
