@@ -231,7 +231,61 @@ def run_reference_arm(args):
         "e2e": {"value": gbs, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
+    ref_gpu = reference_cuda_leg()
+    if ref_gpu is not None:
+        line["reference_cuda_kernels_on_this_gpu"] = ref_gpu
     print(json.dumps(line), flush=True)
+
+
+def reference_cuda_leg():
+    """Context for the reference arm: the reference's own CUDA kernels (compiled unmodified for sm_100a into
+    oracle/_ref with its flags) timed with CUDA events on the same workloads.  None where the library or a GPU
+    is missing.  Their outputs differ from the parity target outside the source time range (they extrapolate)."""
+    try:
+        import oracle
+        from robogoat_b200 import workloads
+        if oracle.ref_cuda_lib() is None or not torch.cuda.is_available():
+            return None
+        dev = torch.device("cuda", 0)
+        torch.cuda.set_device(0)
+
+        def timed(fn, n):
+            for _ in range(3):
+                fn()
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(n):
+                fn()
+            b.record(); torch.cuda.synchronize()
+            return a.elapsed_time(b) / n
+
+        out = {}
+        B, S, D, T = HEADLINE["B"], HEADLINE["S"], HEADLINE["D"], HEADLINE["T"]
+        src, st, tt = workloads.resample_inputs(B=B, S=S, D=D, T=T, dtype=torch.bfloat16, irregular_targets=True, seed=0, device=dev)
+        o = torch.empty((B, T, D), dtype=torch.bfloat16, device=dev)
+        ms = timed(lambda: oracle.ref_cuda_resample(src, st, tt, out=o), 10)
+        out["resample_bf16_B4096"] = {"ms": ms, "GB/s_all_tensors_once": workloads.resample_bytes(B, S, T, D, 2) / (ms * 1e-3) / 1e9}
+        del src, o
+        a = workloads.fusion_inputs(B=16384, dtype=torch.bfloat16, seed=0, device=dev)
+        o = torch.empty((16384, 50, 588), dtype=torch.bfloat16, device=dev)
+        ms = timed(lambda: oracle.ref_cuda_fuse(*a, out=o), 10)
+        out["fusion_bf16_B16384"] = {"ms": ms, "GB/s": workloads.fusion_bytes(16384, 50, 2) / (ms * 1e-3) / 1e9}
+        del a, o
+        pts = workloads.voxel_uniform_inputs(500_000, seed=0, device=dev)
+        kw = workloads.VOXEL_OCCUPANCY_GEOMETRY
+        ms = timed(lambda: oracle.ref_cuda_voxelize(pts, None, kw["grid_min"], kw["voxel_size"], kw["grid_size"], "occupancy"), 50)
+        out["voxel_occupancy_500k_128"] = {"us": ms * 1e3, "Gpts/s": 500_000 / (ms * 1e-3) / 1e9, "note": "warm L2, zero-fill by torch included"}
+        N = 1 << 26
+        pts, feats = workloads.voxel_mixture_inputs(N, seed=0, device=dev)
+        kw = workloads.VOXEL_MIXTURE_GEOMETRY
+        for mode in ("count", "mean"):
+            ms = timed(lambda: oracle.ref_cuda_voxelize(pts, feats if mode == "mean" else None, kw["grid_min"], kw["voxel_size"],
+                                                        kw["grid_size"], mode), 5)
+            out[f"voxel_{mode}_64M_512"] = {"ms": ms, "Gpts/s": N / (ms * 1e-3) / 1e9}
+        return out
+    except Exception as e:  # a comparator must never break the arm
+        return {"error": repr(e)}
 
 
 # ----------------------------------------------------------------------------- our arm

@@ -17,6 +17,7 @@ from __future__ import annotations
 
 import ctypes
 import os
+import shutil
 import subprocess
 from typing import Optional, Sequence, Tuple
 
@@ -26,8 +27,11 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 _LIB_PATH = os.path.join(_HERE, "_build", "librobocache_oracle.so")
 _REF_PATH = os.path.join(_HERE, "_ref", "librobocache_ref_cpu.so")
 
+_REF_CUDA_PATH = os.path.join(_HERE, "_ref", "librobocache_ref_cuda.so")
+
 _lib = None
 _ref = None
+_ref_cuda = None
 
 _i64 = ctypes.c_int64
 _i32 = ctypes.c_int32
@@ -41,6 +45,9 @@ def build(reference_root: Optional[str] = None) -> None:
     root = reference_root or os.environ.get("REFERENCE_ROOT") or os.path.abspath(os.path.join(_HERE, "..", "..", "reference"))
     if os.path.exists(os.path.join(root, "robocache", "validation", "cpu_reference.hpp")):
         subprocess.run(["make", "-C", _HERE, "ref", f"REFERENCE_ROOT={root}"],
+                       check=True, capture_output=True)
+    if os.path.exists(os.path.join(root, "robocache", "csrc", "cuda", "resample_kernel.cu")) and shutil.which("nvcc"):
+        subprocess.run(["make", "-C", _HERE, "refcuda", f"REFERENCE_ROOT={root}"],
                        check=True, capture_output=True)
 
 
@@ -81,6 +88,22 @@ def ref_lib() -> Optional[ctypes.CDLL]:
             getattr(R, f).restype = None
         _ref = R
     return _ref
+
+
+def ref_cuda_lib() -> Optional[ctypes.CDLL]:
+    """The reference's own CUDA launchers compiled for sm_100a behind a C shim (comparator only), or None."""
+    global _ref_cuda
+    if _ref_cuda is None and os.path.exists(_REF_CUDA_PATH):
+        R = ctypes.CDLL(_REF_CUDA_PATH)
+        ci = ctypes.c_int
+        R.launch_resample_bf16.argtypes = [_ptr, _ptr, _ptr, _ptr, ci, ci, ci, ci, _ptr]
+        R.launch_resample_fp32.argtypes = [_ptr, _ptr, _ptr, _ptr, ci, ci, ci, ci, _ptr]
+        R.refcuda_fuse.argtypes = [_ptr] * 8 + [ci] * 9 + [_ptr]
+        R.refcuda_voxelize.argtypes = [_ptr, _ptr, _ptr, _ptr, ci, ci, _f32, _f32, _f32, _f32, ci, ci, ci, ci, _ptr]
+        for f in ("launch_resample_bf16", "launch_resample_fp32", "refcuda_fuse", "refcuda_voxelize"):
+            getattr(R, f).restype = None
+        _ref_cuda = R
+    return _ref_cuda
 
 
 def max_threads() -> int:
@@ -221,3 +244,59 @@ def ref_header_voxelize(points, grid_min, voxel_size, grid_size, density: bool) 
     # header argument order: depth (z), height (y), width (x)
     fn(_p(pts), _p(grid), 1, pts.shape[0], gz, gy, gx, float(voxel_size), _farr(grid_min))
     return grid
+
+
+# ----------------------------------------------------------------------------- reference CUDA kernels (comparator)
+
+def ref_cuda_resample(source_data: torch.Tensor, source_times: torch.Tensor, target_times: torch.Tensor,
+                      out: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+    """The reference's resample kernel (robocache/csrc/cuda/resample_kernel.cu) on CUDA tensors, or None."""
+    R = ref_cuda_lib()
+    if R is None:
+        return None
+    B, S, D = source_data.shape
+    T = target_times.shape[1]
+    if out is None:
+        out = torch.empty((B, T, D), dtype=source_data.dtype, device=source_data.device)
+    fn = R.launch_resample_bf16 if source_data.dtype == torch.bfloat16 else R.launch_resample_fp32
+    fn(_p(source_data), _p(source_times), _p(target_times), _p(out), B, S, T, D,
+       torch.cuda.current_stream(source_data.device).cuda_stream)
+    return out
+
+
+def ref_cuda_fuse(s1, t1, s2, t2, s3, t3, target_times, out: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+    """The reference's fusion kernel (robocache/csrc/cuda/multimodal_kernel.cu) on CUDA tensors, or None."""
+    R = ref_cuda_lib()
+    if R is None:
+        return None
+    B, T = target_times.shape
+    if out is None:
+        out = torch.empty((B, T, s1.shape[2] + s2.shape[2] + s3.shape[2]), dtype=s1.dtype, device=s1.device)
+    R.refcuda_fuse(_p(s1), _p(t1), _p(s2), _p(t2), _p(s3), _p(t3), _p(target_times), _p(out), B, s1.shape[1], s1.shape[2],
+                   s2.shape[1], s2.shape[2], s3.shape[1], s3.shape[2], T, 1 if s1.dtype == torch.bfloat16 else 0,
+                   torch.cuda.current_stream(s1.device).cuda_stream)
+    return out
+
+
+def ref_cuda_voxelize(points, features, grid_min, voxel_size, grid_size, mode: str):
+    """The reference's voxel kernels (robocache/csrc/cuda/voxelize_kernel.cu): returns (grid, counts or None), or None.
+    Grids are zero-filled with torch first, as the reference binding does."""
+    R = ref_cuda_lib()
+    if R is None:
+        return None
+    code = {"count": 0, "occupancy": 1, "mean": 2}[mode]
+    gx, gy, gz = [int(v) for v in grid_size]
+    dev = points.device
+    counts = None
+    if mode == "mean":
+        F = features.shape[1]
+        grid = torch.zeros((gx, gy, gz, F), dtype=torch.float32, device=dev)
+        counts = torch.zeros((gx, gy, gz), dtype=torch.int32, device=dev)
+    else:
+        F = 0
+        grid = torch.zeros((gx, gy, gz), dtype=torch.int32, device=dev)
+    R.refcuda_voxelize(_p(points), _p(features) if features is not None else None, _p(grid),
+                       _p(counts) if counts is not None else None, points.shape[0], F, float(grid_min[0]),
+                       float(grid_min[1]), float(grid_min[2]), float(voxel_size), gx, gy, gz, code,
+                       torch.cuda.current_stream(dev).cuda_stream)
+    return grid, counts
