@@ -515,7 +515,18 @@ def run_extras(L, dev, local, rank, world, peak):
         e1.record(); torch.cuda.synchronize()
         ms = max_over_ranks(e0.elapsed_time(e1) / 5, world, dev)
         ex["voxel_mean_sharded_with_grid_reduce"] = {"ms": ms, "Gpts/s_total": N * world / (ms * 1e-3) / 1e9,
-                                                     "note": "point shards + NCCL sum of partial grids + slab normalise"}
+                                                     "note": "point shards + NCCL all-reduce of the 2.68 GB partial grids + normalise; every rank holds the full grid"}
+        fn = lambda: sharding.voxelize_sharded_slab(pts, feats, mode="mean", **kw)
+        for _ in range(2):
+            r = fn(); del r
+        barrier(world)
+        e0.record()
+        for _ in range(5):
+            r = fn(); del r
+        e1.record(); torch.cuda.synchronize()
+        ms = max_over_ranks(e0.elapsed_time(e1) / 5, world, dev)
+        ex["voxel_mean_sharded_slab_output"] = {"ms": ms, "Gpts/s_total": N * world / (ms * 1e-3) / 1e9,
+                                                "note": "point shards + NCCL reduce-scatter; each rank keeps the reduced, normalised 1/N slab of z-planes"}
     return ex
 
 

@@ -109,6 +109,49 @@ def fuse_sharded(s1, t1, s2, t2, s3, t3, target_times, gather: bool = False, gro
     return gather_rows(out, s1.shape[0], group) if gather else out
 
 
+def reduce_scatter_partial_grids(grid: torch.Tensor, counts: Optional[torch.Tensor], mode: str, group=None):
+    """Reduce per-rank partial grids so that every rank ends up with the reduced values of its own slab only
+    (voxel ids [rank*V/R, (rank+1)*V/R)): half the traffic of an all-reduce, and the dense grid never has to
+    exist reduced on one GPU.  Returns (grid_slab [V/R, ...], counts_slab or None).  V must divide by the group size."""
+    rank, ws = world(group)
+    V = counts.numel() if counts is not None else (grid.numel() if grid.dim() == 3 else grid.numel() // grid.shape[-1])
+    if V % ws != 0:
+        raise RuntimeError(f"the grid's {V} voxels do not divide over {ws} ranks")
+    flat = grid.reshape(V, -1) if grid.dim() == 4 else grid.reshape(V)
+    op = dist.ReduceOp.MAX if mode in ("occupancy", "max") else dist.ReduceOp.SUM
+    out = torch.empty((V // ws,) + tuple(flat.shape[1:]), dtype=flat.dtype, device=flat.device)
+    dist.reduce_scatter_tensor(out, flat.contiguous(), op=op, group=group)
+    cout = None
+    if mode == "mean":
+        if counts is None:
+            raise RuntimeError("mean mode reduces counts together with the feature sums")
+        cout = torch.empty(V // ws, dtype=counts.dtype, device=counts.device)
+        dist.reduce_scatter_tensor(cout, counts.reshape(V).contiguous(), op=dist.ReduceOp.SUM, group=group)
+    return out, cout
+
+
+def voxelize_sharded_slab(points_local: torch.Tensor, features_local: Optional[torch.Tensor] = None,
+                          grid_min=(-10.0, -10.0, -10.0), voxel_size: float = 0.1, grid_size=(128, 128, 128),
+                          mode: str = "occupancy", group=None) -> torch.Tensor:
+    """Like ``voxelize_sharded`` but the result stays sharded: each rank returns the voxels
+    [rank*V/R, (rank+1)*V/R) of the union cloud's grid (for a z-major grid: its block of z-planes), shaped
+    [V/R] or [V/R, F].  The partial grids are combined with one reduce-scatter and means are normalised on the
+    slab only."""
+    from . import ops
+    rank, ws = world(group)
+    res = ops.voxelize_pointcloud_cuda(points_local, features_local, list(grid_min), float(voxel_size), list(grid_size),
+                                       mode, normalize=(ws == 1))
+    grid = res[0]
+    counts = res[1] if mode == "mean" else None
+    V = int(grid_size[0]) * int(grid_size[1]) * int(grid_size[2])
+    if ws == 1:
+        return grid.reshape(V, -1) if grid.dim() == 4 else grid.reshape(V)
+    slab, cslab = reduce_scatter_partial_grids(grid, counts, mode, group)
+    if mode == "mean":
+        ops.voxel_normalize_cuda(slab, cslab, 0, cslab.numel())
+    return slab
+
+
 def voxelize_sharded(points_local: torch.Tensor, features_local: Optional[torch.Tensor] = None,
                      grid_min=(-10.0, -10.0, -10.0), voxel_size: float = 0.1, grid_size=(128, 128, 128),
                      mode: str = "occupancy", slab_normalize: bool = False, group=None) -> torch.Tensor:

@@ -43,6 +43,14 @@ tol = 1e-5 * full.abs() + 1e-6 * sabs / cnt.clamp(min=1).unsqueeze(-1)
 for slab in (False, True):
     got = sharding.voxelize_sharded(pts[lo:hi], feats[lo:hi], mode="mean", slab_normalize=slab, **kw)
     assert bool(((got - full).abs() <= tol).all()), f"mean slab={slab}"
+V = 24 ** 3
+for mode in ("count", "mean"):
+    slab = sharding.voxelize_sharded_slab(pts[lo:hi], feats[lo:hi] if mode == "mean" else None, mode=mode, **kw)
+    a, b = rank * V // ws, (rank + 1) * V // ws
+    if mode == "count":
+        assert torch.equal(slab, robocache.voxelize_pointcloud(pts, mode="count", **kw).reshape(V)[a:b]), "slab count"
+    else:
+        assert bool(((slab - full.reshape(V, 4)[a:b]).abs() <= tol.reshape(V, 4)[a:b]).all()), "slab mean"
 torch.cuda.synchronize()
 dist.barrier()
 dist.destroy_process_group()
