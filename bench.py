@@ -490,19 +490,6 @@ def run_extras(L, dev, local, rank, world, peak):
         ms = max_over_ranks(e0.elapsed_time(e1) / iters, world, dev)
         ex[f"voxel_{mode}_64M_512"] = {"ms": ms, "Gpts/s_per_gpu": N / (ms * 1e-3) / 1e9,
                                        "timing": "10 back-to-back calls incl. zero-fill (and normalise for mean); working set > L2"}
-    del pts, feats
-    pts, feats = workloads.voxel_mixture_inputs(N, seed=rank, device=dev, cluster_sorted=True)
-    fn = lambda: robocache.voxelize_pointcloud(pts, feats, mode="mean", **kw)
-    for _ in range(3):
-        r = fn(); del r
-    barrier(world)
-    e0.record()
-    for _ in range(10):
-        r = fn(); del r
-    e1.record(); torch.cuda.synchronize()
-    ms = max_over_ranks(e0.elapsed_time(e1) / 10, world, dev)
-    ex["voxel_mean_64M_512_cluster_sorted"] = {"ms": ms, "Gpts/s_per_gpu": N / (ms * 1e-3) / 1e9,
-                                               "timing": "same cloud emitted cluster after cluster (spatially coherent order)"}
     if world > 1:
         from robogoat_b200 import sharding
         fn = lambda: sharding.voxelize_sharded(pts, feats, mode="mean", **kw)
@@ -527,6 +514,19 @@ def run_extras(L, dev, local, rank, world, peak):
         ms = max_over_ranks(e0.elapsed_time(e1) / 5, world, dev)
         ex["voxel_mean_sharded_slab_output"] = {"ms": ms, "Gpts/s_total": N * world / (ms * 1e-3) / 1e9,
                                                 "note": "point shards + NCCL reduce-scatter; each rank keeps the reduced, normalised 1/N slab of z-planes"}
+    del pts, feats
+    pts, feats = workloads.voxel_mixture_inputs(N, seed=rank, device=dev, cluster_sorted=True)
+    fn = lambda: robocache.voxelize_pointcloud(pts, feats, mode="mean", **kw)
+    for _ in range(3):
+        r = fn(); del r
+    barrier(world)
+    e0.record()
+    for _ in range(10):
+        r = fn(); del r
+    e1.record(); torch.cuda.synchronize()
+    ms = max_over_ranks(e0.elapsed_time(e1) / 10, world, dev)
+    ex["voxel_mean_64M_512_cluster_sorted"] = {"ms": ms, "Gpts/s_per_gpu": N / (ms * 1e-3) / 1e9,
+                                               "timing": "same cloud emitted cluster after cluster (spatially coherent order)"}
     return ex
 
 
