@@ -378,6 +378,7 @@ def run_ours(args):
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "arithmetic": "bf16 rows widened to f32, every product and sum rounded separately, one round-to-nearest back to bf16",
             "data": "synthetic",
             "config": {"workload": WORKLOAD,
                        "global_batch": B * world, "parallelism": f"batch-shard x{world}, no collective",

@@ -7,12 +7,14 @@
  * Conventions
  *   - All data pointers are DEVICE pointers on `device`, unless a name ends in _host.
  *   - `stream` is a cudaStream_t passed as void* (NULL = the legacy default stream).
- *     Calls only enqueue work; they never synchronise and never allocate.
+ *     The operators only enqueue work; they never synchronise and never allocate device memory.
+ *     (rc_bulk_wait_timeouts, a diagnostic, copies a counter back and therefore synchronises.)
  *   - Tensors are dense row-major.  Timestamps are fp32.
  *   - Every function returns an rc_status (0 = ok).  rc_strerror() names a code;
  *     rc_last_cuda_error() gives the cudaError_t behind RC_ERR_CUDA for this thread.
- *   - The library is re-entrant and keeps no state between calls, except where an entry
- *     point says otherwise (rc_voxelize_mean_static).
+ *   - The library is re-entrant.  State kept between calls: the switches of rc_set_option, a
+ *     per-device record of shared-memory limits already raised, and the counter array of
+ *     rc_voxelize_mean_static (see there).
  */
 #ifndef ROBOCACHE_B200_H
 #define ROBOCACHE_B200_H
