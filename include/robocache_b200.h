@@ -107,6 +107,20 @@ RC_API int rc_fuse(const rc_stream_desc* streams, int n_streams, const float* ta
             int64_t B, int64_t T, int dtype, int device, void* stream);
 
 /*
+ * rc_resample / rc_fuse with explicit row strides for the timestamp tensors, in floats: the distance
+ * between the time rows of consecutive batch items.  0 means one row shared by the whole batch — what
+ * `linspace(...).expand(B, -1)` is in the reference's examples and tests — so such views need no
+ * materialised copy; otherwise the stride must be at least the row length.  Feature data and the output
+ * stay dense.  No counterpart in the reference (its bindings copy, or misread, expanded time tensors).
+ */
+RC_API int rc_resample_strided(const void* src, const float* source_times, int64_t source_time_stride,
+                               const float* target_times, int64_t target_time_stride, void* out, int64_t B,
+                               int64_t S, int64_t T, int64_t D, int dtype, int device, void* stream);
+RC_API int rc_fuse_strided(const rc_stream_desc* streams, const int64_t* time_strides, int n_streams,
+                           const float* target_times, int64_t target_time_stride, void* out, int64_t B,
+                           int64_t T, int dtype, int device, void* stream);
+
+/*
  * Bracket rows and weights only (no feature traffic): left/right int32 [B,T], weight fp32 [B,T].
  * Plays the role of compute_all_indices
  * (robocache/kernels/cutlass/trajectory_resample_bulk.cu:37-95); used for the bit-exact

@@ -30,7 +30,7 @@ STATIC_MAX_VOXELS = 1 << 21
 
 # every symbol the header declares; the CPU test-suite checks the built library exports them all
 EXPORTED_SYMBOLS = (
-    "rc_resample", "rc_resample_ragged", "rc_fuse", "rc_resample_brackets", "rc_voxelize", "rc_voxel_normalize", "rc_voxelize_mean_static",
+    "rc_resample", "rc_resample_strided", "rc_resample_ragged", "rc_fuse", "rc_fuse_strided", "rc_resample_brackets", "rc_voxelize", "rc_voxel_normalize", "rc_voxelize_mean_static",
     "rc_voxelize_ex", "rc_voxelize_scratch_bytes", "rc_set_option", "rc_bulk_wait_timeouts", "rc_strerror", "rc_last_cuda_error", "rc_abi_version",
 )
 
@@ -52,6 +52,10 @@ def _declare(L: ctypes.CDLL) -> None:
     vp, i64, i32, ci, f32, u32 = (ctypes.c_void_p, ctypes.c_int64, ctypes.c_int32, ctypes.c_int,
                                   ctypes.c_float, ctypes.c_uint32)
     L.rc_resample.argtypes = [vp, vp, vp, vp, i64, i64, i64, i64, ci, ci, vp]
+    L.rc_resample_strided.argtypes = [vp, vp, i64, vp, i64, vp, i64, i64, i64, i64, ci, ci, vp]
+    L.rc_resample_strided.restype = ci
+    L.rc_fuse_strided.argtypes = [ctypes.POINTER(StreamDesc), ctypes.POINTER(i64), ci, vp, i64, vp, i64, i64, ci, ci, vp]
+    L.rc_fuse_strided.restype = ci
     L.rc_resample_ragged.argtypes = [vp, vp, vp, i64, vp, vp, i64, i64, i64, ci, ci, vp]
     L.rc_resample_ragged.restype = ci
     L.rc_fuse.argtypes = [ctypes.POINTER(StreamDesc), ci, vp, vp, i64, i64, ci, ci, vp]
@@ -65,7 +69,7 @@ def _declare(L: ctypes.CDLL) -> None:
     L.rc_voxelize_scratch_bytes.argtypes = [i64, i32, ctypes.POINTER(i32), ci]
     L.rc_voxelize_scratch_bytes.restype = ctypes.c_uint64
     L.rc_voxelize_mean_static.argtypes = [vp, vp, vp, i64, i32, ctypes.POINTER(f32), f32, ctypes.POINTER(i32), ci, vp]
-    for name in ("rc_resample", "rc_resample_ragged", "rc_fuse", "rc_resample_brackets", "rc_voxelize", "rc_voxel_normalize", "rc_voxelize_mean_static",
+    for name in ("rc_resample", "rc_resample_strided", "rc_resample_ragged", "rc_fuse", "rc_fuse_strided", "rc_resample_brackets", "rc_voxelize", "rc_voxel_normalize", "rc_voxelize_mean_static",
                  "rc_last_cuda_error", "rc_abi_version"):
         getattr(L, name).restype = ci
     L.rc_set_option.argtypes = [ci, ci]
@@ -94,7 +98,7 @@ def load() -> ctypes.CDLL:
 
 
 def is_built() -> bool:
-    return os.path.exists(LIB_PATH)
+    return _lib is not None or os.path.exists(LIB_PATH)
 
 
 def check(status: int, what: str) -> None:

@@ -58,11 +58,13 @@ def resample_trajectories(source_data: torch.Tensor, source_times: torch.Tensor,
         range take the first / last row.
     """
     _resolve_backend(backend)
-    if device is None:
-        device = source_data.device
-    source_data = source_data.to(device)
-    source_times = source_times.to(device)
-    target_times = target_times.to(device)
+    if device is not None:
+        source_data = source_data.to(device)
+        source_times = source_times.to(device)
+        target_times = target_times.to(device)
+    elif source_times.device != source_data.device or target_times.device != source_data.device:
+        source_times = source_times.to(source_data.device)   # default: everything follows source_data
+        target_times = target_times.to(source_data.device)
     _require_cuda(source_data)
     return ops.resample_trajectories_cuda(source_data, source_times, target_times)
 

@@ -39,6 +39,7 @@ struct StreamArg {
     const unsigned char* data;  // [B,S,D], or packed rows [sum S_b, D] when row_offsets is set
     const float* times;         // [B,S], or packed [sum S_b]
     const long long* row_offsets;  // ragged input: item b owns rows [row_offsets[b], row_offsets[b+1]); else NULL
+    long long time_stride;      // floats between the time rows of consecutive items (0: one row shared by all)
     long long row_bytes;        // D * element size
     long long col_bytes;        // byte offset of this stream's slice inside an output row
     int S;
@@ -50,6 +51,7 @@ struct StreamArg {
 struct InterpParams {
     StreamArg s[RC_MAX_STREAMS];
     const float* tt;            // [B,T]
+    long long tt_stride;        // floats between target rows of consecutive items (0: shared row)
     unsigned char* out;         // [B,T,sum D]
     long long out_row_bytes;
     int ns;
@@ -237,7 +239,7 @@ interp_gather_kernel(const __grid_constant__ InterpParams p) {
 
     if (STAGED) {
         for (int k = 0; k < p.ns; ++k) {
-            const float* g = p.s[k].times + first_row(k);
+            const float* g = p.s[k].times + (RAGGED ? first_row(k) : b * p.s[k].time_stride);
             float* d = s_times + p.s[k].smem_off;
             const int n = num_rows(k);
             for (int i = threadIdx.x; i < n; i += blockDim.x) d[i] = __ldg(g + i);
@@ -248,7 +250,7 @@ interp_gather_kernel(const __grid_constant__ InterpParams p) {
     const int t0 = (tile * nwarps + warp) * 32;
     if (t0 >= p.T) return;
     const int nt = min(32, p.T - t0);
-    const float tq = (lane < nt) ? __ldg(p.tt + b * p.T + t0 + lane) : 0.0f;
+    const float tq = (lane < nt) ? __ldg(p.tt + b * p.tt_stride + t0 + lane) : 0.0f;
     unsigned char* out_t0 = p.out + (b * p.T + t0) * p.out_row_bytes;
 
     for (int k = 0; k < p.ns; ++k) {
@@ -263,7 +265,7 @@ interp_gather_kernel(const __grid_constant__ InterpParams p) {
             }
             continue;
         }
-        const float* a = STAGED ? (s_times + s.smem_off) : (s.times + row0);
+        const float* a = STAGED ? (s_times + s.smem_off) : (s.times + (RAGGED ? row0 : b * s.time_stride));
         int l, r;
         float w;
         bracket(a, S, tq, l, r, w);
@@ -315,11 +317,13 @@ struct BlockStream {
     int data_off;       // byte offset of the staged data in shared memory
     int time_off;       // float offset of the staged time row
     int block_bytes;    // S * row_bytes
+    long long time_stride;  // floats between the time rows of consecutive items (0: shared row)
 };
 
 struct BlockParams {
     BlockStream s[RC_MAX_STREAMS];
     const float* tt;
+    long long tt_stride;        // floats between target rows of consecutive items (0: shared row)
     unsigned char* out;
     long long out_block_bytes;  // T * out_row_bytes
     int out_row_bytes;
@@ -395,7 +399,7 @@ __device__ __forceinline__ void block_brackets(const BlockParams& p, const float
         const BlockStream& s = p.s[k];
         int l, rr;
         float w;
-        bracket(s_times + s.time_off, s.S, __ldg(p.tt + b * p.T + t_begin + r), l, rr, w);
+        bracket(s_times + s.time_off, s.S, __ldg(p.tt + b * p.tt_stride + t_begin + r), l, rr, w);
         s_lo[k * p.rows_per_tile + r] = s.data_off + l * s.row_bytes;
         s_hi[k * p.rows_per_tile + r] = s.data_off + rr * s.row_bytes;
         s_w[k * p.rows_per_tile + r] = w;
@@ -523,7 +527,7 @@ interp_block_kernel(const __grid_constant__ BlockParams p) {
                       static_cast<unsigned int>(p.s[k].block_bytes), bar);
     }
     for (int k = 0; k < p.ns; ++k) {
-        const float* g = p.s[k].times + b * p.s[k].S;
+        const float* g = p.s[k].times + b * p.s[k].time_stride;
         float* d = s_times + p.s[k].time_off;
         for (int i = tid; i < p.s[k].S; i += nthreads) d[i] = __ldg(g + i);
     }
@@ -581,13 +585,14 @@ struct LiveStream {
     const float* times;
     long long S;
     long long row_bytes;
+    long long time_stride;
 };
 
 // The TMA-staged block kernel applies when every stream width is a multiple of 8 bytes, every
 // per-item input block can be bulk-copied (16-byte aligned, multiple of 16 bytes), the inputs
 // of one item fit the shared-memory budget and most of them are actually used.
-bool try_launch_block(const LiveStream* ls, int ns, const float* tt, unsigned char* out, long long B, long long T,
-                      int es, int device, cudaStream_t stream, int* status) {
+bool try_launch_block(const LiveStream* ls, int ns, const float* tt, long long tt_stride, unsigned char* out, long long B,
+                      long long T, int es, int device, cudaStream_t stream, int* status) {
     BlockParams p{};
     long long in_bytes = 0, out_row = 0;
     int data_off = 16, time_off = 0;
@@ -598,6 +603,7 @@ bool try_launch_block(const LiveStream* ls, int ns, const float* tt, unsigned ch
         BlockStream& s = p.s[k];
         s.data = ls[k].data;
         s.times = ls[k].times;
+        s.time_stride = ls[k].time_stride;
         s.S = static_cast<int>(ls[k].S);
         s.row_bytes = static_cast<int>(ls[k].row_bytes);
         s.half_off = static_cast<int>(out_row / 8);
@@ -633,6 +639,7 @@ bool try_launch_block(const LiveStream* ls, int ns, const float* tt, unsigned ch
     const long long smem = p.vec_base + (v16 ? (G * (out_row / 8) / 2) : (out_row / 8)) * 16;
     if (smem > kBlockSmemLimit || B * tiles >= (1ll << 31)) return false;
     p.tt = tt;
+    p.tt_stride = tt_stride;
     p.out = out;
     p.out_block_bytes = T * out_row;
     p.out_row_bytes = static_cast<int>(out_row);
@@ -654,8 +661,10 @@ bool try_launch_block(const LiveStream* ls, int ns, const float* tt, unsigned ch
     return true;
 }
 
-int interp_dispatch(const rc_stream_desc* streams, int ns, const float* tt, void* out, int64_t B,
-                    int64_t T, int dtype, int device, void* stream_v) {
+// time_strides: per stream, floats between the time rows of consecutive items (NULL: dense, = S); tt_stride: the
+// same for the target rows (< 0: dense, = T).  A stride of 0 means one row shared by the whole batch.
+int interp_dispatch(const rc_stream_desc* streams, int ns, const int64_t* time_strides, const float* tt,
+                    int64_t tt_stride_in, void* out, int64_t B, int64_t T, int dtype, int device, void* stream_v) {
     if (dtype != RC_DTYPE_F32 && dtype != RC_DTYPE_BF16) return RC_ERR_BAD_DTYPE;
     if (ns < 1 || ns > RC_MAX_STREAMS) return RC_ERR_BAD_SHAPE;
     if (streams == nullptr) return RC_ERR_NULL_POINTER;
@@ -684,9 +693,14 @@ int interp_dispatch(const rc_stream_desc* streams, int ns, const float* tt, void
         if (streams[k].data == nullptr || streams[k].times == nullptr) return RC_ERR_NULL_POINTER;
         if (!rc::aligned_to(streams[k].data, es) || !rc::aligned_to(streams[k].times, 4))
             return RC_ERR_BAD_ALIGNMENT;
+        const long long ts = time_strides ? time_strides[k] : streams[k].S;
+        if (ts != 0 && ts < streams[k].S) return RC_ERR_BAD_SHAPE;
         ls[live++] = LiveStream{static_cast<const unsigned char*>(streams[k].data), streams[k].times,
-                                streams[k].S, streams[k].D * es};
+                                streams[k].S, streams[k].D * es, ts};
     }
+
+    const long long tt_stride = (tt_stride_in < 0) ? T : tt_stride_in;
+    if (tt_stride != 0 && tt_stride < T) return RC_ERR_BAD_SHAPE;
 
     rc::DeviceScope scope(device);
     if (scope.status() != RC_OK) return scope.status();
@@ -694,13 +708,14 @@ int interp_dispatch(const rc_stream_desc* streams, int ns, const float* tt, void
 
     if (rc::g_allow_block_kernel.load(std::memory_order_relaxed)) {
         int status = RC_OK;
-        if (try_launch_block(ls, live, tt, static_cast<unsigned char*>(out), B, T, es, device, stream, &status))
+        if (try_launch_block(ls, live, tt, tt_stride, static_cast<unsigned char*>(out), B, T, es, device, stream, &status))
             return status;
     }
 
     InterpParams p{};
     p.ns = live;
     p.tt = tt;
+    p.tt_stride = tt_stride;
     p.out = static_cast<unsigned char*>(out);
     p.out_row_bytes = out_d * es;
     p.T = static_cast<int>(T);
@@ -712,6 +727,7 @@ int interp_dispatch(const rc_stream_desc* streams, int ns, const float* tt, void
         StreamArg& s = p.s[k];
         s.data = ls[k].data;
         s.times = ls[k].times;
+        s.time_stride = ls[k].time_stride;
         s.S = static_cast<int>(ls[k].S);
         s.row_bytes = ls[k].row_bytes;
         s.col_bytes = col;
@@ -774,6 +790,7 @@ int ragged_dispatch(const void* src, const float* times, const long long* row_of
     InterpParams p{};
     p.ns = 1;
     p.tt = tt;
+    p.tt_stride = T;
     p.out = static_cast<unsigned char*>(out);
     p.out_row_bytes = D * es;
     p.T = static_cast<int>(T);
@@ -823,7 +840,15 @@ extern "C" {
 int rc_resample(const void* src, const float* source_times, const float* target_times, void* out,
                 int64_t B, int64_t S, int64_t T, int64_t D, int dtype, int device, void* stream) {
     rc_stream_desc s{src, source_times, S, D};
-    return interp_dispatch(&s, 1, target_times, out, B, T, dtype, device, stream);
+    return interp_dispatch(&s, 1, nullptr, target_times, -1, out, B, T, dtype, device, stream);
+}
+
+int rc_resample_strided(const void* src, const float* source_times, int64_t source_time_stride,
+                        const float* target_times, int64_t target_time_stride, void* out, int64_t B, int64_t S, int64_t T,
+                        int64_t D, int dtype, int device, void* stream) {
+    rc_stream_desc s{src, source_times, S, D};
+    if (target_time_stride < 0) return RC_ERR_BAD_SHAPE;
+    return interp_dispatch(&s, 1, &source_time_stride, target_times, target_time_stride, out, B, T, dtype, device, stream);
 }
 
 int rc_resample_ragged(const void* src_rows, const float* source_times, const int64_t* row_offsets, int64_t max_len,
@@ -835,7 +860,15 @@ int rc_resample_ragged(const void* src_rows, const float* source_times, const in
 
 int rc_fuse(const rc_stream_desc* streams, int n_streams, const float* target_times, void* out,
             int64_t B, int64_t T, int dtype, int device, void* stream) {
-    return interp_dispatch(streams, n_streams, target_times, out, B, T, dtype, device, stream);
+    return interp_dispatch(streams, n_streams, nullptr, target_times, -1, out, B, T, dtype, device, stream);
+}
+
+int rc_fuse_strided(const rc_stream_desc* streams, const int64_t* time_strides, int n_streams, const float* target_times,
+                    int64_t target_time_stride, void* out, int64_t B, int64_t T, int dtype, int device, void* stream) {
+    if (time_strides == nullptr) return RC_ERR_NULL_POINTER;
+    if (target_time_stride < 0) return RC_ERR_BAD_SHAPE;
+    return interp_dispatch(streams, n_streams, time_strides, target_times, target_time_stride, out, B, T, dtype, device,
+                           stream);
 }
 
 int rc_resample_brackets(const float* source_times, const float* target_times, int64_t B, int64_t S,

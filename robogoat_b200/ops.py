@@ -44,6 +44,17 @@ def _times(t: torch.Tensor) -> torch.Tensor:
     return t.to(torch.float32).contiguous()
 
 
+def _time_rows(t: torch.Tensor):
+    """(tensor to keep alive, row stride in floats) of a [B, n] timestamp tensor.  fp32 rows with unit inner
+    stride are used in place — in particular ``linspace(...).expand(B, -1)`` (row stride 0) is not copied."""
+    if t.dtype == torch.float32 and (t.shape[1] <= 1 or t.stride(1) == 1):
+        s0 = t.stride(0) if t.shape[0] > 1 else t.shape[1]
+        if s0 == 0 or s0 >= t.shape[1]:
+            return t, s0
+    c = t.to(torch.float32).contiguous()
+    return c, c.shape[1]
+
+
 def resample_trajectories_cuda(source_data: torch.Tensor, source_times: torch.Tensor,
                                target_times: torch.Tensor) -> torch.Tensor:
     """[B,S,D] x [B,S] x [B,T] -> [B,T,D], dtype of ``source_data`` (fp32 or bf16)."""
@@ -65,12 +76,12 @@ def resample_trajectories_cuda(source_data: torch.Tensor, source_times: torch.Te
 
     L = _lib.load()
     src = source_data.contiguous()
-    st = _times(source_times)
-    tt = _times(target_times)
+    st, st_stride = _time_rows(source_times)
+    tt, tt_stride = _time_rows(target_times)
     out = torch.empty((B, T, D), dtype=source_data.dtype, device=source_data.device)
     dev = source_data.device
-    rc = L.rc_resample(src.data_ptr(), st.data_ptr(), tt.data_ptr(), out.data_ptr(), B, S, T, D, code,
-                       dev.index, _stream_ptr(dev))
+    rc = L.rc_resample_strided(src.data_ptr(), st.data_ptr(), st_stride, tt.data_ptr(), tt_stride, out.data_ptr(),
+                               B, S, T, D, code, dev.index, _stream_ptr(dev))
     _lib.check(rc, "resample_trajectories")
     return out
 
@@ -120,16 +131,19 @@ def fuse_streams_cuda(datas: Sequence[torch.Tensor], times: Sequence[torch.Tenso
 
     L = _lib.load()
     datas_c = [d.contiguous() for d in datas]
-    times_c = [_times(t) for t in times]
-    tt = _times(target_times)
+    times_c = [_time_rows(t) for t in times]
+    tt, tt_stride = _time_rows(target_times)
     out = torch.empty((B, T, sum(d.shape[2] for d in datas)), dtype=datas[0].dtype, device=dev)
     descs = (_lib.StreamDesc * n)()
+    strides = (ctypes.c_int64 * n)()
     for k in range(n):
         descs[k].data = datas_c[k].data_ptr()
-        descs[k].times = times_c[k].data_ptr()
+        descs[k].times = times_c[k][0].data_ptr()
         descs[k].S = datas_c[k].shape[1]
         descs[k].D = datas_c[k].shape[2]
-    rc = L.rc_fuse(descs, n, tt.data_ptr(), out.data_ptr(), B, T, code, dev.index, _stream_ptr(dev))
+        strides[k] = times_c[k][1]
+    rc = L.rc_fuse_strided(descs, strides, n, tt.data_ptr(), tt_stride, out.data_ptr(), B, T, code, dev.index,
+                           _stream_ptr(dev))
     _lib.check(rc, "fuse_multimodal")
     return out
 

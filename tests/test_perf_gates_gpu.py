@@ -1,0 +1,43 @@
+"""The reference's own latency gates for the resampler (robocache/tests/perf/test_trajectory_perf.py:48-98),
+measured the way its perf guard measures (robocache/tests/perf/perf_guard.py:31-75): host wall clock around one
+call of the public API followed by a device synchronise, median of 100 calls after 10 warm-ups, bf16, source and
+target times given as expanded (stride-0) linspace rows.  Thresholds are the reference's P50 limits; as in the
+reference (perf_guard.py:91-93) they are enforced when PERF_GUARD_ENFORCE=1, otherwise the test records the
+figures and only requires them to stay within 4x of the gate (host-side jitter on a shared box moves a ~40 us
+wall-clock median by more than the gate's margin).  Measured on a B200: 41.5 / 48.3 / 70.0 us against gates of
+50 / 200 / 1000 us."""
+import os
+import statistics
+import time
+
+import pytest
+import torch
+
+import robocache
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def p50_ms(fn, warmup=10, iters=100):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(iters):
+        t0 = time.perf_counter()
+        fn()
+        torch.cuda.synchronize()
+        ts.append((time.perf_counter() - t0) * 1e3)
+    return statistics.median(ts)
+
+
+@pytest.mark.parametrize("B,S,T,D,limit_ms", [(8, 250, 128, 128, 0.05), (32, 500, 256, 256, 0.20), (64, 1000, 512, 512, 1.0)])
+def test_reference_p50_gates(B, S, T, D, limit_ms, cuda_lib):
+    src = torch.randn(B, S, D, device=DEV, dtype=torch.bfloat16)
+    st = torch.linspace(0, 5, S, device=DEV).unsqueeze(0).expand(B, -1)
+    tt = torch.linspace(0, 5, T, device=DEV).unsqueeze(0).expand(B, -1)
+    p50 = p50_ms(lambda: robocache.resample_trajectories(src, st, tt))
+    print(f"resample {B}x{S}x{D}->{T}: P50 {p50 * 1e3:.1f} us (gate {limit_ms * 1e3:.0f} us)")
+    slack = 1.0 if os.environ.get("PERF_GUARD_ENFORCE") == "1" else 4.0
+    assert p50 < limit_ms * slack

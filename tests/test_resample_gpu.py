@@ -199,3 +199,23 @@ def test_ragged_items_equal_per_item_oracle_and_last_step_padding(dtype, D, cuda
     pad_times = torch.stack([torch.cat([times[b], times[b][-1:].expand(S - lens[b])]) for b in keep])
     dense = robocache.resample_trajectories(pad_rows.to(DEV), pad_times.to(DEV), tt[keep].to(DEV)).cpu()
     assert_exact(out[keep], dense, "ragged vs last-step padding")
+
+
+def test_expanded_and_strided_time_rows_are_used_in_place(cuda_lib):
+    """Timestamps given as stride-0 expanded rows (the reference's usual linspace(...).expand(B, -1)) or as
+    row-strided views give the same bits as their materialised copies."""
+    B, S, T, D = 6, 40, 25, 32
+    g = torch.Generator().manual_seed(77)
+    src = torch.randn(B, S, D, generator=g).to(DEV)
+    st_row = torch.sort(torch.rand(S, generator=g)).values.to(DEV)
+    tt_row = (torch.rand(T, generator=g) * 1.2 - 0.1).to(DEV)
+    st_e, tt_e = st_row.unsqueeze(0).expand(B, -1), tt_row.unsqueeze(0).expand(B, -1)
+    ref = robocache.resample_trajectories(src, st_e.contiguous(), tt_e.contiguous())
+    assert torch.equal(robocache.resample_trajectories(src, st_e, tt_e), ref)
+    assert torch.equal(robocache.resample_trajectories(src, st_e, tt_e.contiguous()), ref)
+    wide_st = torch.zeros(B, S + 7, device=DEV); wide_st[:, :S] = st_e
+    wide_tt = torch.zeros(B, T + 3, device=DEV); wide_tt[:, :T] = tt_e
+    assert torch.equal(robocache.resample_trajectories(src, wide_st[:, :S], wide_tt[:, :T]), ref)   # row stride > row length
+    fa = [x.to(DEV) for x in workloads.fusion_inputs(B=B, dtype=torch.float32, seed=3)]
+    lin = torch.linspace(0, 1, 50, device=DEV).unsqueeze(0).expand(B, -1)
+    assert torch.equal(robocache.fuse_multimodal(*fa[:6], lin), robocache.fuse_multimodal(*fa[:6], lin.contiguous()))
