@@ -41,3 +41,35 @@ def test_reference_p50_gates(B, S, T, D, limit_ms, cuda_lib):
     print(f"resample {B}x{S}x{D}->{T}: P50 {p50 * 1e3:.1f} us (gate {limit_ms * 1e3:.0f} us)")
     slack = 1.0 if os.environ.get("PERF_GUARD_ENFORCE") == "1" else 4.0
     assert p50 < limit_ms * slack
+
+
+def _gate(p50, limit_ms, what):
+    print(f"{what}: P50 {p50 * 1e3:.1f} us (gate {limit_ms * 1e3:.0f} us)")
+    slack = 1.0 if os.environ.get("PERF_GUARD_ENFORCE") == "1" else 4.0
+    assert p50 < limit_ms * slack
+
+
+# robocache/tests/perf/test_multimodal_perf.py:33-135 (bf16; the force stream is 6 wide: 12-byte rows)
+@pytest.mark.parametrize("B,shapes,T,limit_ms", [
+    (8, ((30, 256), (100, 16), (333, 6)), 50, 0.10),
+    (32, ((30, 256), (100, 16), (333, 6)), 50, 0.30),
+    (16, ((100, 128), (200, 16), (500, 6)), 1000, 2.0),
+])
+def test_reference_fusion_gates(B, shapes, T, limit_ms, cuda_lib):
+    args = []
+    for n, d in shapes:
+        args += [torch.randn(B, n, d, device=DEV, dtype=torch.bfloat16),
+                 torch.linspace(0, 1, n, device=DEV).unsqueeze(0).expand(B, -1)]
+    args.append(torch.linspace(0, 1, T, device=DEV).unsqueeze(0).expand(B, -1))
+    _gate(p50_ms(lambda: robocache.fuse_multimodal(*args)), limit_ms, f"fusion B={B} T={T}")
+
+
+# robocache/tests/perf/test_voxelize_perf.py:33-128 (occupancy through the compatibility wrapper)
+@pytest.mark.parametrize("n_points,extent,grid,limit_ms", [
+    (10_000, 3.0, 32, 0.50), (100_000, 6.0, 64, 5.0), (1_000_000, 12.0, 128, 50.0), (500_000, 25.0, 256, 100.0),
+])
+def test_reference_voxel_gates(n_points, extent, grid, limit_ms, cuda_lib):
+    points = torch.rand(n_points, 3, device=DEV) * extent
+    origin = torch.zeros(3)
+    fn = lambda: robocache.voxelize_occupancy(points, [grid, grid, grid], 0.1, origin)
+    _gate(p50_ms(fn), limit_ms, f"voxel occupancy N={n_points} grid={grid}^3")
