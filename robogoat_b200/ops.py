@@ -28,7 +28,13 @@ def _check(cond: bool, msg: str) -> None:
         raise RuntimeError(msg)
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream_ptr(device: torch.device) -> int:
+    """cudaStream_t of torch's current stream on ``device`` (the raw accessor skips building a Stream object)."""
+    if _raw_stream is not None:
+        return _raw_stream(device.index)
     return torch.cuda.current_stream(device).cuda_stream
 
 
