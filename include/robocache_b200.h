@@ -169,7 +169,40 @@ RC_API int rc_voxel_normalize(float* grid, const int32_t* counts, int64_t voxel_
                        int32_t F, int device, void* stream);
 
 /*
- * Mean-mode voxelisation that allocates nothing.  No counterpart in the reference: its binding
+ * Point exchange for multi-GPU voxelisation: instead of reducing dense partial grids, every rank
+ * buckets its points by the rank that owns their voxel, the buckets are exchanged (all-to-all by
+ * the caller), and each owner scatters what it received into its own slab of the grid.  The grid
+ * is cut into n_parts contiguous ranges of voxel ids of ceil(V / n_parts) voxels each (blocks of
+ * z-planes when gz divides).  No counterpart in the reference, whose multi-GPU test all-reduces
+ * dense grids (robocache/tests/test_multi_gpu.py:76).
+ *
+ * rc_voxel_partition: stable partition of the in-grid points by owning part; dropped points vanish.
+ *   ids_out      : int32 [N]      voxel ids (global, z-major), part 0's points first, input order kept
+ *   features_out : fp32  [N, F]   the same points' feature rows (NULL with F == 0 or features == NULL)
+ *   part_counts  : int64 [n_parts] on the device: points per part; only the first sum(part_counts)
+ *                  entries of ids_out / features_out are written
+ *   scratch      : device buffer of rc_voxel_partition_scratch_bytes() bytes, 16-byte aligned
+ * Limits: n_parts in [1, 64]; N and gx*gy*gz below 2^31.  Everything runs on `stream`; the counts
+ * are ready when the stream reaches the end of the call's work.
+ *
+ * rc_voxel_scatter_ids: accumulates points given as (voxel id, feature row) into the slab of
+ * voxels [id_begin, id_end); ids outside the range (and -1) are ignored.
+ *   grid   : first cell of voxel id_begin: int32 [id_end-id_begin] (count, occupancy) or
+ *            fp32 [id_end-id_begin, F] (mean);  counts : int32 [id_end-id_begin], mean mode only
+ *   mode   : RC_VOXEL_COUNT, RC_VOXEL_OCCUPANCY or RC_VOXEL_MEAN;  flags as rc_voxelize
+ *   ids must be 16-byte aligned.
+ */
+RC_API uint64_t rc_voxel_partition_scratch_bytes(int64_t N, int32_t n_parts, int device);
+RC_API int rc_voxel_partition(const float* points, const float* features, int64_t N, int32_t F,
+                              const float grid_min_host[3], float voxel_size, const int32_t grid_size_host[3],
+                              int32_t n_parts, int32_t* ids_out, float* features_out, int64_t* part_counts,
+                              void* scratch, uint64_t scratch_bytes, int device, void* stream);
+RC_API int rc_voxel_scatter_ids(const int32_t* ids, const float* features, void* grid, int32_t* counts,
+                                int64_t M, int32_t F, int64_t id_begin, int64_t id_end, int mode,
+                                uint32_t flags, int device, void* stream);
+
+/*
+ * Mean-mode voxelisation that allocates nothing. No counterpart in the reference: its binding
  * always allocates the counter plane with torch (robocache/csrc/cpp/voxelize_ops.cpp:91-100).
  *
  * For callers that cannot call cudaMalloc: code inside an allocator or memory-pool callback, a

@@ -31,7 +31,8 @@ STATIC_MAX_VOXELS = 1 << 21
 # every symbol the header declares; the CPU test-suite checks the built library exports them all
 EXPORTED_SYMBOLS = (
     "rc_resample", "rc_resample_strided", "rc_resample_ragged", "rc_fuse", "rc_fuse_strided", "rc_resample_brackets", "rc_voxelize", "rc_voxel_normalize", "rc_voxelize_mean_static",
-    "rc_voxelize_ex", "rc_voxelize_scratch_bytes", "rc_set_option", "rc_bulk_wait_timeouts", "rc_strerror", "rc_last_cuda_error", "rc_abi_version",
+    "rc_voxelize_ex", "rc_voxelize_scratch_bytes", "rc_voxel_partition", "rc_voxel_partition_scratch_bytes", "rc_voxel_scatter_ids",
+    "rc_set_option", "rc_bulk_wait_timeouts", "rc_strerror", "rc_last_cuda_error", "rc_abi_version",
 )
 
 
@@ -68,6 +69,13 @@ def _declare(L: ctypes.CDLL) -> None:
     L.rc_voxelize_ex.restype = ci
     L.rc_voxelize_scratch_bytes.argtypes = [i64, i32, ctypes.POINTER(i32), ci]
     L.rc_voxelize_scratch_bytes.restype = ctypes.c_uint64
+    L.rc_voxel_partition_scratch_bytes.argtypes = [i64, i32, ci]
+    L.rc_voxel_partition_scratch_bytes.restype = ctypes.c_uint64
+    L.rc_voxel_partition.argtypes = [vp, vp, i64, i32, ctypes.POINTER(f32), f32, ctypes.POINTER(i32), i32, vp, vp, vp, vp,
+                                     ctypes.c_uint64, ci, vp]
+    L.rc_voxel_partition.restype = ci
+    L.rc_voxel_scatter_ids.argtypes = [vp, vp, vp, vp, i64, i32, i64, i64, ci, u32, ci, vp]
+    L.rc_voxel_scatter_ids.restype = ci
     L.rc_voxelize_mean_static.argtypes = [vp, vp, vp, i64, i32, ctypes.POINTER(f32), f32, ctypes.POINTER(i32), ci, vp]
     for name in ("rc_resample", "rc_resample_strided", "rc_resample_ragged", "rc_fuse", "rc_fuse_strided", "rc_resample_brackets", "rc_voxelize", "rc_voxel_normalize", "rc_voxelize_mean_static",
                  "rc_last_cuda_error", "rc_abi_version"):

@@ -30,6 +30,7 @@ constexpr int kPointsPerBlock = kThreads * kPointsPerLane;     // 1024
 constexpr size_t kResidentBytes = 96u << 20;   // accumulators up to this size are treated as L2-resident (one pass)
 constexpr long long kProbeMinPoints = 1ll << 20;  // below this the order probe is not worth its launch
 constexpr int kAutoMeanPasses = 6;             // slab passes of the two-phase mean scatter on larger grids
+constexpr double kSlabPassBytes = 448.0 * 1048576.0;          // accumulator bytes per slab pass of rc_voxel_scatter_ids
 constexpr size_t kSmallGridBytes = 64u << 20;                  // grids up to this size are cleared by voxel_zero_kernel
 
 struct VoxelGeom {
@@ -308,6 +309,8 @@ __device__ __forceinline__ void scatter_one(int id, long long pi, const float* _
                                             int* __restrict__ counts, int F) {
     if (MODE == kCount) {
         atomicAdd(static_cast<int*>(grid_v) + id, 1);
+    } else if (MODE == kOccupancy) {
+        static_cast<int*>(grid_v)[id] = 1;
     } else {
         const float* f = feats + pi * F;
         float* o = static_cast<float*>(grid_v) + static_cast<long long>(id) * F;
@@ -487,6 +490,128 @@ void launch_bin(bool agg, bool overlap_prev, unsigned int blocks, cudaStream_t s
                 long long id_hi, const int* gate = nullptr, int gate_want = 0) {
     if (agg) launch_bin_one<MODE, true>(overlap_prev, blocks, st, pts, feats, grid, counts, N, F, g, aligned, id_lo, id_hi, gate, gate_want);
     else     launch_bin_one<MODE, false>(overlap_prev, blocks, st, pts, feats, grid, counts, N, F, g, aligned, id_lo, id_hi, gate, gate_want);
+}
+
+// ---------------------------------------------------------------- partition by owning part (point exchange)
+//
+// A stable counting partition in three launches.  Every warp owns a contiguous run of 128-point
+// tiles.  Launch 1 (MOVE = false) counts, per warp and part, the in-grid points; launch 2 turns each
+// part's column of that table into exclusive prefixes (one CTA per part); launch 3 (MOVE = true)
+// walks the same tiles again, recomputes the voxel ids (cheaper than keeping them: 12 bytes re-read
+// against 4 written + 4 read) and writes every point at part start + warp prefix + rank in the warp.
+// Ranks come from __match_any_sync, so input order is kept inside a part and the result does not
+// depend on scheduling.
+constexpr int kMaxParts = 64;
+
+template <bool MOVE>
+__global__ void __launch_bounds__(kThreads)
+voxel_part_kernel(const float* __restrict__ pts, const float* __restrict__ feats, long long N, int F, VoxelGeom g,
+                  bool pts_aligned, bool vec4, unsigned int slab, int P, long long tiles_per_warp,
+                  int* __restrict__ table, const long long* __restrict__ part_counts, int* __restrict__ ids_out,
+                  float* __restrict__ feats_out) {
+    __shared__ __align__(16) float s_xyz[kThreads / 32][kPointsPerWarp * 3];
+    __shared__ int s_cur[kThreads / 32][kMaxParts];
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    const unsigned int lt_mask = (1u << lane) - 1u;
+    const long long gw = static_cast<long long>(blockIdx.x) * (kThreads / 32) + warp;
+    int* cur = s_cur[warp];
+    for (int p = lane; p < P; p += 32) {
+        int start = 0;
+        if (MOVE) {
+            long long before = 0;
+            for (int q = 0; q < p; ++q) before += part_counts[q];
+            start = static_cast<int>(before) + table[gw * P + p];
+        }
+        cur[p] = start;
+    }
+    __syncwarp();
+    const long long ntiles = (N + kPointsPerWarp - 1) / kPointsPerWarp;
+    const long long t0 = gw * tiles_per_warp;
+    const long long t1 = (t0 + tiles_per_warp < ntiles) ? t0 + tiles_per_warp : ntiles;
+    float4 ahead[3];
+    if (pts_aligned && t0 < t1 && (t0 + 1) * kPointsPerWarp <= N) tile_issue(pts, t0 * kPointsPerWarp, lane, ahead);
+    for (long long tile = t0; tile < t1; ++tile) {
+        const long long base = tile * kPointsPerWarp;
+        float x[kPointsPerLane], y[kPointsPerLane], z[kPointsPerLane];
+        if (pts_aligned && base + kPointsPerWarp <= N) {
+            float4 now[3] = {ahead[0], ahead[1], ahead[2]};
+            if (tile + 1 < t1 && (tile + 2) * kPointsPerWarp <= N) tile_issue(pts, (tile + 1) * kPointsPerWarp, lane, ahead);
+            tile_unpack(now, s_xyz[warp], lane, x, y, z);
+        } else {
+            tile_load_slow(pts, base, N, lane, x, y, z);
+        }
+        float4 f4[kPointsPerLane];
+        int id[kPointsPerLane];
+#pragma unroll
+        for (int i = 0; i < kPointsPerLane; ++i) {
+            const long long pi = base + i * 32 + lane;
+            id[i] = (pi < N) ? static_cast<int>(voxel_id(x[i], y[i], z[i], g)) : -1;
+            if (MOVE && vec4 && id[i] >= 0) f4[i] = __ldcs(reinterpret_cast<const float4*>(feats + pi * 4));
+        }
+#pragma unroll
+        for (int i = 0; i < kPointsPerLane; ++i) {
+            const int part = (id[i] < 0) ? -1 : static_cast<int>(static_cast<unsigned int>(id[i]) / slab);
+            const unsigned int same = __match_any_sync(0xffffffffu, part);
+            int pos = 0;
+            if (MOVE && part >= 0) pos = cur[part] + __popc(same & lt_mask);
+            __syncwarp();
+            if (part >= 0 && (same & lt_mask) == 0u) cur[part] += __popc(same);   // lowest lane of the group
+            __syncwarp();
+            if (MOVE && part >= 0) {
+                ids_out[pos] = id[i];
+                if (vec4) {
+                    reinterpret_cast<float4*>(feats_out)[pos] = f4[i];
+                } else if (feats_out != nullptr) {
+                    const long long pi = base + i * 32 + lane;
+                    for (int c = 0; c < F; ++c) feats_out[static_cast<long long>(pos) * F + c] = __ldg(feats + pi * F + c);
+                }
+            }
+        }
+    }
+    if (!MOVE) {
+        __syncwarp();
+        for (int p = lane; p < P; p += 32) table[gw * P + p] = cur[p];
+    }
+}
+
+// CTA p: exclusive prefix over the warps of column p of the table, total into part_counts[p]
+__global__ void __launch_bounds__(1024)
+voxel_part_scan_kernel(int* __restrict__ table, long long W, int P, long long* __restrict__ part_counts) {
+    __shared__ long long s_sum[1024];
+    const int p = blockIdx.x;
+    const long long per = (W + 1023) / 1024;
+    const long long a = threadIdx.x * per;
+    const long long b = (a + per < W) ? a + per : W;
+    long long mine = 0;
+    for (long long w = a; w < b; ++w) mine += table[w * P + p];
+    s_sum[threadIdx.x] = mine;
+    __syncthreads();
+    for (int off = 1; off < 1024; off <<= 1) {   // inclusive scan of the per-thread sums
+        const long long add = (threadIdx.x >= off) ? s_sum[threadIdx.x - off] : 0;
+        __syncthreads();
+        s_sum[threadIdx.x] += add;
+        __syncthreads();
+    }
+    long long run = s_sum[threadIdx.x] - mine;
+    for (long long w = a; w < b; ++w) {
+        const int c = table[w * P + p];
+        table[w * P + p] = static_cast<int>(run);
+        run += c;
+    }
+    if (threadIdx.x == 1023) part_counts[p] = s_sum[1023];
+}
+
+// warps (and blocks) that share the tiles of a cloud of N points
+void partition_plan(long long N, int device, long long* blocks, long long* tiles_per_warp) {
+    const long long ntiles = (N + kPointsPerWarp - 1) / kPointsPerWarp;
+    long long nb = (ntiles + kThreads / 32 - 1) / (kThreads / 32);
+    const long long cap = 16ll * rc::sm_count(device);
+    if (nb > cap) nb = cap;
+    if (nb < 1) nb = 1;
+    const long long W = nb * (kThreads / 32);
+    *blocks = nb;
+    *tiles_per_warp = (ntiles + W - 1) / W;
 }
 
 // ---------------------------------------------------------------- allocation-free mean mode
@@ -708,6 +833,126 @@ int rc_voxelize_ex(const float* points, const float* features, void* grid, int32
     return RC_OK;
 }
 
+uint64_t rc_voxel_partition_scratch_bytes(int64_t N, int32_t n_parts, int device) {
+    if (N <= 0 || n_parts < 1 || n_parts > kMaxParts) return 0;
+    long long blocks = 0, tpw = 0;
+    partition_plan(N, device, &blocks, &tpw);
+    return static_cast<uint64_t>(blocks) * (kThreads / 32) * static_cast<uint64_t>(n_parts) * 4u;
+}
+
+int rc_voxel_partition(const float* points, const float* features, int64_t N, int32_t F,
+                       const float grid_min_host[3], float voxel_size, const int32_t grid_size_host[3],
+                       int32_t n_parts, int32_t* ids_out, float* features_out, int64_t* part_counts,
+                       void* scratch, uint64_t scratch_bytes, int device, void* stream) {
+    if (grid_min_host == nullptr || grid_size_host == nullptr || part_counts == nullptr) return RC_ERR_NULL_POINTER;
+    if (N < 0 || F < 0 || n_parts < 1) return RC_ERR_BAD_SHAPE;
+    if (n_parts > kMaxParts || N >= (1ll << 31)) return RC_ERR_TOO_LARGE;
+    if (!(voxel_size > 0.0f) || !(voxel_size <= 3.0e38f)) return RC_ERR_BAD_VALUE;
+    VoxelGeom g;
+    g.minx = grid_min_host[0]; g.miny = grid_min_host[1]; g.minz = grid_min_host[2];
+    g.vs = voxel_size;
+    g.gx = grid_size_host[0]; g.gy = grid_size_host[1]; g.gz = grid_size_host[2];
+    if (g.gx < 0 || g.gy < 0 || g.gz < 0) return RC_ERR_BAD_SHAPE;
+    if (g.gx >= (1 << 24) || g.gy >= (1 << 24) || g.gz >= (1 << 24)) return RC_ERR_TOO_LARGE;
+    if (static_cast<double>(g.gx) * g.gy * g.gz >= 2147483648.0) return RC_ERR_TOO_LARGE;
+    g.fgx = static_cast<float>(g.gx); g.fgy = static_cast<float>(g.gy); g.fgz = static_cast<float>(g.gz);
+    const long long V = static_cast<long long>(g.gx) * g.gy * g.gz;
+    const bool move_feats = features != nullptr && features_out != nullptr && F > 0;
+    if (N > 0 && (points == nullptr || ids_out == nullptr)) return RC_ERR_NULL_POINTER;
+    if (!rc::aligned_to(points, 4) || !rc::aligned_to(features, 4) || !rc::aligned_to(features_out, 4) ||
+        !rc::aligned_to(ids_out, 4) || !rc::aligned_to(part_counts, 8))
+        return RC_ERR_BAD_ALIGNMENT;
+    rc::DeviceScope scope(device);
+    if (scope.status() != RC_OK) return scope.status();
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (N == 0 || V == 0) {
+        RC_CUDA_TRY(cudaMemsetAsync(part_counts, 0, static_cast<size_t>(n_parts) * 8, st));
+        return RC_OK;
+    }
+    long long blocks = 0, tpw = 0;
+    partition_plan(N, device, &blocks, &tpw);
+    const long long W = blocks * (kThreads / 32);
+    if (scratch == nullptr) return RC_ERR_NULL_POINTER;
+    if (!rc::aligned_to(scratch, 16)) return RC_ERR_BAD_ALIGNMENT;
+    if (scratch_bytes < static_cast<uint64_t>(W) * n_parts * 4u) return RC_ERR_BAD_SHAPE;
+    int* table = static_cast<int*>(scratch);
+    const unsigned int slab = static_cast<unsigned int>((V + n_parts - 1) / n_parts);
+    const bool aligned = rc::aligned_to(points, 16);
+    const bool vec4 = move_feats && F == 4 && rc::aligned_to(features, 16) && rc::aligned_to(features_out, 16);
+    const unsigned int nb = static_cast<unsigned int>(blocks);
+    voxel_part_kernel<false><<<nb, kThreads, 0, st>>>(points, nullptr, N, F, g, aligned, false, slab, n_parts, tpw, table,
+                                                      nullptr, nullptr, nullptr);
+    voxel_part_scan_kernel<<<n_parts, 1024, 0, st>>>(table, W, n_parts, reinterpret_cast<long long*>(part_counts));
+    voxel_part_kernel<true><<<nb, kThreads, 0, st>>>(points, move_feats ? features : nullptr, N, F, g, aligned, vec4, slab,
+                                                     n_parts, tpw, table, reinterpret_cast<const long long*>(part_counts),
+                                                     ids_out, move_feats ? features_out : nullptr);
+    return rc::check_launch();
+}
+
+int rc_voxel_scatter_ids(const int32_t* ids, const float* features, void* grid, int32_t* counts, int64_t M,
+                         int32_t F, int64_t id_begin, int64_t id_end, int mode, uint32_t flags, int device,
+                         void* stream) {
+    if (mode != RC_VOXEL_COUNT && mode != RC_VOXEL_OCCUPANCY && mode != RC_VOXEL_MEAN) return RC_ERR_BAD_MODE;
+    if (M < 0 || F < 0 || id_begin < 0 || id_end < id_begin) return RC_ERR_BAD_SHAPE;
+    if (id_end >= (1ll << 31)) return RC_ERR_TOO_LARGE;
+    const long long nvox = id_end - id_begin;
+    const bool mean = (mode == RC_VOXEL_MEAN);
+    if (nvox > 0 && (!mean || F > 0) && grid == nullptr) return RC_ERR_NULL_POINTER;
+    if (mean && nvox > 0 && counts == nullptr) return RC_ERR_NULL_POINTER;
+    if (M > 0 && ids == nullptr) return RC_ERR_NULL_POINTER;
+    if (mean && M > 0 && F > 0 && features == nullptr) return RC_ERR_BAD_MODE;
+    if (!rc::aligned_to(ids, 16) || !rc::aligned_to(grid, 4) || !rc::aligned_to(counts, 4) || !rc::aligned_to(features, 4))
+        return RC_ERR_BAD_ALIGNMENT;
+    if (mean) {
+        const bool a16 = rc::aligned_to(features, 16) && rc::aligned_to(grid, 16);
+        const bool a8 = rc::aligned_to(features, 8) && rc::aligned_to(grid, 8);
+        if ((F & 3) == 0 && !a16) return RC_ERR_BAD_ALIGNMENT;
+        if ((F & 3) != 0 && (F & 1) == 0 && !a8) return RC_ERR_BAD_ALIGNMENT;
+    }
+    rc::DeviceScope scope(device);
+    if (scope.status() != RC_OK) return scope.status();
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const long long cells = mean ? nvox * F : nvox;
+    if (flags & RC_VOXEL_ZERO_INIT) {
+        if (cells > 0) RC_CUDA_TRY(cudaMemsetAsync(grid, 0, static_cast<size_t>(cells) * 4, st));
+        if (mean && nvox > 0) RC_CUDA_TRY(cudaMemsetAsync(counts, 0, static_cast<size_t>(nvox) * 4, st));
+    }
+    if (M > 0 && nvox > 0 && !(mean && F == 0)) {
+        // the kernel indexes with the global id: hand it the address voxel 0 would have
+        const uintptr_t cell = mean ? static_cast<uintptr_t>(F) * 4u : 4u;
+        void* grid0 = reinterpret_cast<void*>(reinterpret_cast<uintptr_t>(grid) - static_cast<uintptr_t>(id_begin) * cell);
+        int* counts0 = mean ? reinterpret_cast<int*>(reinterpret_cast<uintptr_t>(counts) - static_cast<uintptr_t>(id_begin) * 4u)
+                            : nullptr;
+        const int forced = rc::g_voxel_passes.load(std::memory_order_relaxed);
+        const double acc_bytes = static_cast<double>(nvox) * 4.0 * (mean ? (1 + F) : 1);
+        int passes = 1;
+        if (forced > 0) passes = forced;
+        else if (mode != RC_VOXEL_OCCUPANCY && acc_bytes > static_cast<double>(kResidentBytes))
+            passes = static_cast<int>((acc_bytes + kSlabPassBytes - 1) / kSlabPassBytes);
+        if (passes > 64) passes = 64;
+        if (passes > nvox) passes = static_cast<int>(nvox);
+        const long long span = (nvox + passes - 1) / passes;
+        long long sb = (((M + 255) >> 8) + kThreads / 32 - 1) / (kThreads / 32);
+        const long long cap = 16ll * rc::sm_count(device);
+        if (sb > cap) sb = cap;
+        const unsigned int nb = static_cast<unsigned int>(sb < 1 ? 1 : sb);
+        for (int ps = 0; ps < passes; ++ps) {
+            const int lo = static_cast<int>(id_begin + ps * span);
+            const int hi = static_cast<int>((id_begin + (ps + 1) * span < id_end) ? id_begin + (ps + 1) * span : id_end);
+            if (mode == RC_VOXEL_MEAN)
+                voxel_scatter_ids_kernel<kMean><<<nb, kThreads, 0, st>>>(ids, features, grid0, counts0, M, F, lo, hi, nullptr, 0);
+            else if (mode == RC_VOXEL_COUNT)
+                voxel_scatter_ids_kernel<kCount><<<nb, kThreads, 0, st>>>(ids, features, grid0, counts0, M, F, lo, hi, nullptr, 0);
+            else
+                voxel_scatter_ids_kernel<kOccupancy><<<nb, kThreads, 0, st>>>(ids, features, grid0, counts0, M, F, lo, hi, nullptr, 0);
+        }
+    }
+    const int rc_launch = rc::check_launch();
+    if (rc_launch != RC_OK) return rc_launch;
+    if (mean && !(flags & RC_VOXEL_NO_NORMALIZE) && nvox > 0 && F > 0)
+        return rc_voxel_normalize(static_cast<float*>(grid), counts, 0, nvox, F, device, stream);
+    return RC_OK;
+}
 
 // Mean-mode voxelisation for callers that must not allocate device memory: code running
 // inside a framework's memory-pool callback or under a real-time loop's "no driver

@@ -264,6 +264,82 @@ def voxel_normalize_cuda(grid: torch.Tensor, counts: torch.Tensor, voxel_begin: 
     _lib.check(rc, "voxel_normalize")
 
 
+def voxel_partition_cuda(points: torch.Tensor, features: Optional[torch.Tensor], grid_min: Sequence[float],
+                         voxel_size: float, grid_size: Sequence[int], n_parts: int):
+    """Stable partition of a cloud's in-grid points by the part that owns their voxel.
+
+    The grid's voxel ids are cut into ``n_parts`` contiguous ranges of ceil(V / n_parts).  Returns
+    ``(ids [N] int32, features [N,F] or None, part_counts [n_parts] int64)``, all on the device: the first
+    ``part_counts.sum()`` entries hold part 0's points, then part 1's, ... in input order; the rest is
+    unwritten.  Reading ``part_counts`` on the host is the caller's synchronisation point.
+    """
+    _check(points.is_cuda and points.dim() == 2 and points.shape[1] == 3, "points must be a CUDA tensor [N, 3]")
+    _check(1 <= int(n_parts) <= 64, "n_parts must be in [1, 64]")
+    dev = points.device
+    N = points.shape[0]
+    pts = points.to(torch.float32).contiguous()
+    feats = None
+    F = 0
+    if features is not None:
+        _check(features.is_cuda and features.dim() == 2 and features.shape[0] == N, "features must be a CUDA tensor [N, F]")
+        _check(features.device == dev, "all tensors must be on the same CUDA device")
+        feats = features.to(torch.float32).contiguous()
+        F = feats.shape[1]
+    L = _lib.load()
+    ids = torch.empty(N, dtype=torch.int32, device=dev)
+    feats_out = torch.empty((N, F), dtype=torch.float32, device=dev) if feats is not None else None
+    part_counts = torch.empty(int(n_parts), dtype=torch.int64, device=dev)
+    need = int(L.rc_voxel_partition_scratch_bytes(N, int(n_parts), dev.index))
+    scratch = torch.empty(max(need, 16), dtype=torch.uint8, device=dev)
+    gmin = (ctypes.c_float * 3)(*[float(v) for v in grid_min])
+    gsz = (ctypes.c_int32 * 3)(*[int(v) for v in grid_size])
+    rc = L.rc_voxel_partition(pts.data_ptr(), feats.data_ptr() if feats is not None else None, N, F, gmin,
+                              float(voxel_size), gsz, int(n_parts), ids.data_ptr(),
+                              feats_out.data_ptr() if feats_out is not None else None, part_counts.data_ptr(),
+                              scratch.data_ptr(), need, dev.index, _stream_ptr(dev))
+    _lib.check(rc, "voxel_partition")
+    return ids, feats_out, part_counts
+
+
+def voxel_scatter_ids_cuda(ids: torch.Tensor, features: Optional[torch.Tensor], id_begin: int, id_end: int,
+                           mode: str, *, feature_width: int = 0, normalize: bool = True) -> List[torch.Tensor]:
+    """Accumulate points given as (voxel id, feature row) into the slab of voxels [id_begin, id_end).
+
+    Returns ``[grid]`` (int32 [id_end-id_begin] for count / occupancy) or ``[grid, counts]`` (fp32
+    [id_end-id_begin, F] and int32 counts for mean).  Ids outside the range are ignored.
+    """
+    _check(ids.is_cuda and ids.dtype == torch.int32 and ids.dim() == 1 and ids.is_contiguous(),
+           "ids must be a contiguous int32 CUDA vector")
+    if mode not in ("count", "occupancy", "mean"):
+        raise RuntimeError(f"Invalid mode: {mode}. The id scatter supports 'count', 'occupancy' and 'mean'")
+    dev = ids.device
+    M = ids.numel()
+    nvox = int(id_end) - int(id_begin)
+    _check(nvox >= 0 and id_begin >= 0, "bad voxel range")
+    F = 0
+    feats = None
+    counts = None
+    if mode == "mean":
+        _check(features is not None or M == 0, "features required for mean mode")
+        if features is not None:
+            _check(features.is_cuda and features.dim() == 2 and features.shape[0] == M, "features must be [M, F] on CUDA")
+            feats = features.to(torch.float32).contiguous()
+            F = feats.shape[1]
+        else:
+            F = int(feature_width)
+        grid = torch.empty((nvox, F), dtype=torch.float32, device=dev)
+        counts = torch.empty(nvox, dtype=torch.int32, device=dev)
+    else:
+        grid = torch.empty(nvox, dtype=torch.int32, device=dev)
+    flags = _lib.VOXEL_ZERO_INIT | (0 if normalize else _lib.VOXEL_NO_NORMALIZE)
+    rc = _lib.load().rc_voxel_scatter_ids(ids.data_ptr() if M else None, feats.data_ptr() if feats is not None else None,
+                                          grid.data_ptr() if grid.numel() else None,
+                                          counts.data_ptr() if counts is not None and nvox else None, M, F,
+                                          int(id_begin), int(id_end), _MODES[mode], flags, dev.index, _stream_ptr(dev))
+    _lib.check(rc, "voxel_scatter_ids")
+    return [grid, counts] if mode == "mean" else [grid]
+
+
 def resample_ragged_cuda(source_rows: torch.Tensor, source_times: torch.Tensor, row_offsets: torch.Tensor,
                          target_times: torch.Tensor, max_len: Optional[int] = None) -> torch.Tensor:
     """Resample variable-length items that are packed back to back, without padding them.

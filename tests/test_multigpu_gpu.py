@@ -51,6 +51,13 @@ for mode in ("count", "mean"):
         assert torch.equal(slab, robocache.voxelize_pointcloud(pts, mode="count", **kw).reshape(V)[a:b]), "slab count"
     else:
         assert bool(((slab - full.reshape(V, 4)[a:b]).abs() <= tol.reshape(V, 4)[a:b]).all()), "slab mean"
+for mode in ("occupancy", "count", "mean"):                       # point exchange: the owner's slab, no dense grid
+    slab = sharding.voxelize_sharded_exchange(pts[lo:hi], feats[lo:hi] if mode == "mean" else None, mode=mode, **kw)
+    a, b = sharding.slab_bounds(V, rank, ws)
+    if mode == "mean":
+        assert bool(((slab - full.reshape(V, 4)[a:b]).abs() <= tol.reshape(V, 4)[a:b]).all()), "exchange mean"
+    else:
+        assert torch.equal(slab, robocache.voxelize_pointcloud(pts, mode=mode, **kw).reshape(V)[a:b]), "exchange " + mode
 torch.cuda.synchronize()
 dist.barrier()
 dist.destroy_process_group()

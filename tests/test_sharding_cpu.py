@@ -106,6 +106,47 @@ def test_partial_grids_reduce_to_the_single_process_grid():
     assert _run(_voxel_job) == {0: True, 1: True}
 
 
+def _exchange_job(rank, ws):
+    """Point exchange on CPU: the oracle's voxel ids bucketed with a stable sort stand in for the partition
+    kernel; what is checked is the all-to-all bookkeeping and that the owner's slab comes out right."""
+    g = torch.Generator().manual_seed(21)
+    pts = torch.rand(9_001, 3, generator=g) * 4 - 2
+    feats = torch.randn(9_001, 4, generator=g)
+    kw = dict(grid_min=[-1.5, -1.5, -1.5], voxel_size=0.25, grid_size=[12, 12, 11])    # V = 1584, slabs of 792
+    V = 12 * 12 * 11
+    a, b = sharding.shard_bounds(pts.shape[0], rank, ws)
+    ids = oracle.voxel_ids(pts[a:b], **kw)
+    keep = ids >= 0
+    ids_k, f_k = ids[keep].to(torch.int32), feats[a:b][keep]
+    per = (V + ws - 1) // ws
+    owner = ids_k.long() // per
+    order = torch.sort(owner, stable=True).indices
+    send = torch.bincount(owner, minlength=ws).tolist()
+    (ids_in, f_in), recv = sharding.exchange_buckets([ids_k[order], f_k[order]], send)
+    lo, hi = sharding.slab_bounds(V, rank, ws)
+    ok = len(recv) == ws and ids_in.shape[0] == sum(recv) and bool(((ids_in >= lo) & (ids_in < hi)).all())
+    cnt = torch.bincount((ids_in - lo).long(), minlength=hi - lo)
+    full = oracle.voxelize_pointcloud(pts, None, mode="count", **kw).reshape(-1)
+    ok = ok and bool(torch.equal(cnt.int(), full[lo:hi]))
+    sums = torch.zeros(hi - lo, 4, dtype=torch.float64).index_add_(0, (ids_in - lo).long(), f_in.double())
+    all_ids = oracle.voxel_ids(pts, **kw)
+    exp_sums = torch.zeros(V, 4, dtype=torch.float64).index_add_(0, all_ids[all_ids >= 0].long(), feats[all_ids >= 0].double())
+    ok = ok and bool(torch.allclose(sums, exp_sums[lo:hi], rtol=1e-12, atol=1e-12))
+    try:
+        sharding.exchange_buckets([ids_k], send[:-1])
+        ok = False
+    except RuntimeError:
+        pass
+    return ok
+
+
+def test_point_exchange_delivers_every_point_to_the_owner_of_its_voxel():
+    assert _run(_exchange_job) == {0: True, 1: True}
+    assert sharding.slab_bounds(1584, 1, 2) == (792, 1584)
+    one, counts = sharding.exchange_buckets([torch.arange(10)], [7])        # no process group: identity on the prefix
+    assert torch.equal(one[0], torch.arange(7)) and counts == [7]
+
+
 def _lonely_rank(port, q):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)

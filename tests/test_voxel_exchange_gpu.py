@@ -1,0 +1,110 @@
+"""The two kernels of the multi-GPU point exchange, checked on one GPU: the stable partition of a cloud by
+owning slab against a stable sort of the oracle's voxel ids, and the id scatter of every bucket into its slab
+against the single-call grid."""
+import pytest
+import torch
+
+import oracle
+from robogoat_b200 import ops, sharding
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _cloud(N, seed, F=4):
+    g = torch.Generator().manual_seed(seed)
+    pts = torch.rand(N, 3, generator=g) * 5 - 2.5            # part of it falls outside the grid
+    if N > 10:
+        pts[3] = float("nan")
+        pts[7, 1] = float("inf")
+    return pts, torch.randn(N, F, generator=g)
+
+
+@pytest.mark.parametrize("N", [0, 1, 127, 128, 1000, 33_333, 300_001])
+@pytest.mark.parametrize("parts", [1, 2, 3, 8, 64])
+def test_partition_is_the_stable_sort_by_owner(N, parts, cuda_lib):
+    kw = dict(grid_min=[-2.0, -2.0, -2.0], voxel_size=0.25, grid_size=[16, 15, 13])
+    V = 16 * 15 * 13
+    pts, feats = _cloud(N, 100 + parts)
+    ids, fb, pc = ops.voxel_partition_cuda(pts.to(DEV), feats.to(DEV), kw["grid_min"], kw["voxel_size"], kw["grid_size"], parts)
+    exp_ids = oracle.voxel_ids(pts, **kw) if N else torch.empty(0, dtype=torch.int64)
+    keep = exp_ids >= 0
+    per = (V + parts - 1) // parts
+    owner = exp_ids[keep] // per
+    order = torch.sort(owner, stable=True).indices
+    n = int(keep.sum())
+    assert pc.cpu().tolist() == torch.bincount(owner, minlength=parts).tolist()
+    assert torch.equal(ids[:n].cpu().long(), exp_ids[keep][order])
+    assert torch.equal(fb[:n].cpu(), feats[keep][order])
+
+
+@pytest.mark.parametrize("F", [1, 2, 3, 4, 8])
+def test_partition_moves_feature_rows_of_any_width(F, cuda_lib):
+    kw = dict(grid_min=[-2.0, -2.0, -2.0], voxel_size=0.5, grid_size=[8, 8, 8])
+    pts, feats = _cloud(5000, F, F=F)
+    ids, fb, pc = ops.voxel_partition_cuda(pts.to(DEV), feats.to(DEV), kw["grid_min"], kw["voxel_size"], kw["grid_size"], 4)
+    exp_ids = oracle.voxel_ids(pts, **kw)
+    keep = exp_ids >= 0
+    order = torch.sort(exp_ids[keep] // 128, stable=True).indices
+    n = int(keep.sum())
+    assert int(pc.sum()) == n and torch.equal(fb[:n].cpu(), feats[keep][order])
+    ids2, none, pc2 = ops.voxel_partition_cuda(pts.to(DEV), None, kw["grid_min"], kw["voxel_size"], kw["grid_size"], 4)
+    assert none is None and torch.equal(ids2[:n], ids[:n]) and torch.equal(pc, pc2)
+
+
+@pytest.mark.parametrize("parts", [1, 2, 5, 8])
+def test_buckets_scattered_into_their_slabs_rebuild_the_grid(parts, cuda_lib):
+    import robocache
+    kw = dict(grid_min=[-2.0, -2.0, -2.0], voxel_size=0.125, grid_size=[32, 31, 30])
+    V = 32 * 31 * 30
+    pts, feats = _cloud(200_000, 7)
+    p, f = pts.to(DEV), feats.to(DEV)
+    ids, fb, pc = ops.voxel_partition_cuda(p, f, kw["grid_min"], kw["voxel_size"], kw["grid_size"], parts)
+    starts = [0]
+    for c in pc.tolist():
+        starts.append(starts[-1] + c)
+    full_cnt = robocache.voxelize_pointcloud(p, mode="count", **kw).reshape(V)
+    full_occ = robocache.voxelize_pointcloud(p, mode="occupancy", **kw).reshape(V)
+    exp, ecnt, sabs = oracle.voxelize_pointcloud(pts, feats, mode="mean", return_aux=True, **kw)
+    tol = oracle.mean_tolerance(ecnt, sabs, exp).reshape(V, 4)
+    for r in range(parts):
+        a, b = sharding.slab_bounds(V, r, parts)
+        # every rank sees all buckets here; ids outside its slab must be ignored, so hand it the whole list too
+        for lo, hi in ((starts[r], starts[r + 1]), (0, starts[-1])):
+            if lo % 4:                                   # the id list must start on a 16-byte boundary
+                my_ids, my_f = ids[lo:hi].clone(), fb[lo:hi].clone()
+            else:
+                my_ids, my_f = ids[lo:hi], fb[lo:hi]
+            assert torch.equal(ops.voxel_scatter_ids_cuda(my_ids, None, a, b, "count")[0], full_cnt[a:b])
+            assert torch.equal(ops.voxel_scatter_ids_cuda(my_ids, None, a, b, "occupancy")[0], full_occ[a:b])
+            grid, cnt = ops.voxel_scatter_ids_cuda(my_ids, my_f, a, b, "mean")
+            assert torch.equal(cnt, full_cnt[a:b])
+            assert bool(((grid.cpu() - exp.reshape(V, 4)[a:b]).abs() <= tol[a:b]).all())
+
+
+def test_scatter_ids_slab_passes_agree(cuda_lib):
+    """Forcing several slab passes must not change counts, and leaves means within the summation-order tolerance."""
+    from robogoat_b200 import _lib
+    kw = dict(grid_min=[-2.0, -2.0, -2.0], voxel_size=0.125, grid_size=[32, 32, 32])
+    pts, feats = _cloud(100_000, 11)
+    ids, fb, pc = ops.voxel_partition_cuda(pts.to(DEV), feats.to(DEV), kw["grid_min"], kw["voxel_size"], kw["grid_size"], 1)
+    n = int(pc.sum())
+    one = ops.voxel_scatter_ids_cuda(ids[:n], fb[:n], 0, 32 ** 3, "mean")
+    L = _lib.load()
+    try:
+        assert L.rc_set_option(1, 5) == 0
+        five = ops.voxel_scatter_ids_cuda(ids[:n], fb[:n], 0, 32 ** 3, "mean")
+    finally:
+        L.rc_set_option(1, 0)
+    assert torch.equal(one[1], five[1])
+    assert torch.allclose(one[0], five[0], rtol=1e-5, atol=1e-6)
+
+
+def test_exchange_entry_points_reject_bad_arguments(cuda_lib):
+    pts = torch.zeros(10, 3, device=DEV)
+    with pytest.raises(RuntimeError):
+        ops.voxel_partition_cuda(pts, None, [0, 0, 0], 0.1, [4, 4, 4], 65)
+    with pytest.raises(RuntimeError):
+        ops.voxel_scatter_ids_cuda(torch.zeros(4, dtype=torch.int32, device=DEV), None, 0, 8, "max")
+    with pytest.raises(RuntimeError):
+        ops.voxel_scatter_ids_cuda(torch.zeros(8, dtype=torch.int32, device=DEV)[1:5], None, 0, 8, "count")  # misaligned ids
