@@ -515,6 +515,92 @@ def run_extras(L, dev, local, rank, world, peak):
         ms = max_over_ranks(e0.elapsed_time(e1) / 5, world, dev)
         ex["voxel_mean_sharded_slab_output"] = {"ms": ms, "Gpts/s_total": N * world / (ms * 1e-3) / 1e9,
                                                 "note": "point shards + NCCL reduce-scatter; each rank keeps the reduced, normalised 1/N slab of z-planes"}
+        # point exchange: bucket by owner slab, all-to-all of (id, features) records, scatter into the own slab
+        fn = lambda: sharding.voxelize_sharded_exchange(pts, feats, mode="mean", **kw)
+        for _ in range(2):
+            r = fn(); del r
+        barrier(world)
+        e0.record()
+        for _ in range(5):
+            r = fn(); del r
+        e1.record(); torch.cuda.synchronize()
+        ms = max_over_ranks(e0.elapsed_time(e1) / 5, world, dev)
+        K = sharding.sub_parts(512 ** 3, 4, world, "mean")
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+        barrier(world)
+        ev[0].record()
+        ids, fbk, pc = ops.voxel_partition_cuda(pts, feats, kw["grid_min"], kw["voxel_size"], kw["grid_size"], world, K)
+        ev[1].record()
+        plan = sharding.exchange_plan(sharding._gather_counts(pc), rank, K)
+        (ids_in, f_in), _ = sharding.exchange_buckets([ids, fbk], plan["send_counts"], recv_counts=plan["recv_counts"])
+        ev[2].record()
+        lo_v, hi_v = sharding.slab_bounds(512 ** 3, rank, world)
+        r = ops.voxel_scatter_runs_cuda(ids_in.data_ptr(), f_in.data_ptr(), dev, 4, lo_v, hi_v, plan["runs"], K, "mean")
+        ev[3].record(); torch.cuda.synchronize()
+        stages = [max_over_ranks(ev[i].elapsed_time(ev[i + 1]), world, dev) for i in range(3)]
+        received = int(ids_in.numel())
+        del r, ids, fbk, ids_in, f_in
+        ex["voxel_mean_sharded_point_exchange"] = {
+            "ms": ms, "Gpts/s_total": N * world / (ms * 1e-3) / 1e9, "sub_ranges_per_slab": K,
+            "stage_ms": {"partition": stages[0], "counts_and_all_to_all": stages[1], "scatter_normalise": stages[2]},
+            "points_received_rank0": received,
+            "note": "stable partition by owner slab and sub-range + NCCL all-to-all of 20-byte (id, features) records + scatter "
+                    "into the rank's own 1/N slab, one L2-sized sub-range per pass; no rank holds a dense grid"}
+        # direct form: the partition kernel stores into the owners' buffers over NVLink
+        px = sharding.PointExchange(capacity=int(1.25 * N), feature_width=4)
+        fn = lambda: sharding.voxelize_sharded_exchange(pts, feats, mode="mean", direct=px, **kw)
+        for _ in range(2):
+            r = fn(); del r
+        barrier(world)
+        e0.record()
+        for _ in range(5):
+            r = fn(); del r
+        e1.record(); torch.cuda.synchronize()
+        ms = max_over_ranks(e0.elapsed_time(e1) / 5, world, dev)
+        barrier(world)
+        ev[0].record()
+        pc, scratch = ops.voxel_partition_count_cuda(pts, kw["grid_min"], kw["voxel_size"], kw["grid_size"], world, K)
+        plan = sharding.exchange_plan(sharding._gather_counts(pc), rank, K)
+        ev[1].record()
+        fits = max(plan["totals"]) <= px.capacity
+        if fits:
+            ops.voxel_partition_move_cuda(pts, feats, kw["grid_min"], kw["voxel_size"], kw["grid_size"], world, K,
+                                          [px.ids.peers[p // K] for p in range(world * K)],
+                                          [px.features.peers[p // K] for p in range(world * K)], plan["dest_start"], scratch)
+            px.stream_barrier()
+        ev[2].record()
+        if fits:
+            r = ops.voxel_scatter_runs_cuda(px.ids.ptr, px.features.ptr, dev, 4, lo_v, hi_v, plan["runs"], K, "mean")
+            del r
+        ev[3].record(); torch.cuda.synchronize()
+        stages = [max_over_ranks(ev[i].elapsed_time(ev[i + 1]), world, dev) for i in range(3)]
+        sent_remote = sum(c for d, c in enumerate(plan["send_counts"]) if d != rank) * 20
+        ex["voxel_mean_sharded_point_exchange_direct"] = {
+            "ms": ms, "Gpts/s_total": N * world / (ms * 1e-3) / 1e9, "fits_receive_buffers": fits,
+            "stage_ms": {"count_and_count_matrix": stages[0], "move_over_nvlink_and_barrier": stages[1], "scatter_normalise": stages[2]},
+            "nvlink_GB/s_out_per_gpu_during_move": sent_remote / (stages[1] * 1e-3) / 1e9 if fits else None,
+            "note": "same, but the partition kernel stores its sorted chunks straight into the owners' receive buffers "
+                    "(peer memory over NVLink); collectives left: the count matrix and one barrier"}
+        px.close()
+    else:
+        # the two kernels of the point exchange on one GPU: partition for 8 owners, then one owner's bucket into its slab
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+        for it in range(3):
+            ev[0].record()
+            ids, fbk, pc = ops.voxel_partition_cuda(pts, feats, kw["grid_min"], kw["voxel_size"], kw["grid_size"], 8, 4)
+            ev[1].record()
+            cnts = pc.tolist()                  # host read of the counts: synchronises
+            n0 = sum(cnts[:4])
+            runs = [(sum(cnts[:k]), cnts[k], k) for k in range(4)]
+            ev[2].record()
+            r = ops.voxel_scatter_runs_cuda(ids.data_ptr(), fbk.data_ptr(), dev, 4, 0, 512 ** 3 // 8, runs, 4, "mean")
+            ev[3].record(); torch.cuda.synchronize()
+            part_ms, scat_ms = ev[0].elapsed_time(ev[1]), ev[2].elapsed_time(ev[3])
+            del r, ids, fbk
+        ex["voxel_point_exchange_kernels_64M_512"] = {
+            "partition_8x4_parts_ms": part_ms, "partition_Gpts/s": N / (part_ms * 1e-3) / 1e9,
+            "scatter_one_owner_ms": scat_ms, "bucket_points": n0, "scatter_Gpts/s": n0 / (scat_ms * 1e-3) / 1e9,
+            "note": "building blocks of the multi-GPU point exchange, timed alone on one GPU"}
     del pts, feats
     pts, feats = workloads.voxel_mixture_inputs(N, seed=rank, device=dev, cluster_sorted=True)
     fn = lambda: robocache.voxelize_pointcloud(pts, feats, mode="mean", **kw)
@@ -554,6 +640,12 @@ def run_profile_case(name: str):
         mode = name.split("_")[1]
         fn = lambda: robocache.voxelize_pointcloud(pts, feats if mode == "mean" else None, mode=mode, **kw)
         units = {"N": N}
+    elif name == "voxel_partition":
+        N = 1 << 24
+        pts, feats = workloads.voxel_mixture_inputs(N, seed=0, device=dev)
+        kw = workloads.VOXEL_MIXTURE_GEOMETRY
+        fn = lambda: ops.voxel_partition_cuda(pts, feats, kw["grid_min"], kw["voxel_size"], kw["grid_size"], 8, 4)
+        units = {"N": N, "parts": 32}
     elif name == "voxel_occupancy":
         pts = workloads.voxel_uniform_inputs(500_000, seed=0, device=dev)
         fn = lambda: robocache.voxelize_pointcloud(pts, mode="occupancy", **workloads.VOXEL_OCCUPANCY_GEOMETRY)
@@ -576,7 +668,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extras", action="store_true")
     ap.add_argument("--profile-case", default=None,
-                    help="run 4 launches of one kernel on a small case (resample, fusion, voxel_mean, voxel_count, voxel_occupancy; voxel_mean_full = headline size)")
+                    help="run 4 launches of one kernel on a small case (resample, fusion, voxel_mean, voxel_count, voxel_occupancy, voxel_partition; voxel_mean_full = headline size)")
     args = ap.parse_args()
     if args.profile_case:
         run_profile_case(args.profile_case)

@@ -7,7 +7,8 @@
  * Conventions
  *   - All data pointers are DEVICE pointers on `device`, unless a name ends in _host.
  *   - `stream` is a cudaStream_t passed as void* (NULL = the legacy default stream).
- *     The operators only enqueue work; they never synchronise and never allocate device memory.
+ *     The operators only enqueue work; they never synchronise and never allocate device memory
+ *     (rc_peer_alloc / rc_peer_open are set-up calls, not operators).
  *     (rc_bulk_wait_timeouts, a diagnostic, copies a counter back and therefore synchronises.)
  *   - Tensors are dense row-major.  Timestamps are fp32.
  *   - Every function returns an rc_status (0 = ok).  rc_strerror() names a code;
@@ -170,20 +171,31 @@ RC_API int rc_voxel_normalize(float* grid, const int32_t* counts, int64_t voxel_
 
 /*
  * Point exchange for multi-GPU voxelisation: instead of reducing dense partial grids, every rank
- * buckets its points by the rank that owns their voxel, the buckets are exchanged (all-to-all by
- * the caller), and each owner scatters what it received into its own slab of the grid.  The grid
- * is cut into n_parts contiguous ranges of voxel ids of ceil(V / n_parts) voxels each (blocks of
- * z-planes when gz divides).  No counterpart in the reference, whose multi-GPU test all-reduces
- * dense grids (robocache/tests/test_multi_gpu.py:76).
+ * buckets its points by the rank that owns their voxel, the buckets travel to their owners (an
+ * all-to-all by the caller, or written by the partition kernel straight into the owners' memory),
+ * and each owner accumulates what it received into its own slab of the grid.  No counterpart in the
+ * reference, whose multi-GPU test all-reduces dense grids (robocache/tests/test_multi_gpu.py:76).
  *
- * rc_voxel_partition: stable partition of the in-grid points by owning part; dropped points vanish.
- *   ids_out      : int32 [N]      voxel ids (global, z-major), part 0's points first, input order kept
- *   features_out : fp32  [N, F]   the same points' feature rows (NULL with F == 0 or features == NULL)
- *   part_counts  : int64 [n_parts] on the device: points per part; only the first sum(part_counts)
- *                  entries of ids_out / features_out are written
- *   scratch      : device buffer of rc_voxel_partition_scratch_bytes() bytes, 16-byte aligned
- * Limits: n_parts in [1, 64]; N and gx*gy*gz below 2^31.  Everything runs on `stream`; the counts
- * are ready when the stream reaches the end of the call's work.
+ * Parts.  The voxel ids [0, V) are cut into n_groups contiguous ranges of ceil(V / n_groups) ids (one per
+ * owner; blocks of z-planes when gz divides), and each range into parts_per_group sub-ranges of
+ * ceil(range / parts_per_group) ids.  part = group * parts_per_group + sub; n_groups * parts_per_group <= 64.
+ * Sub-ranges let the owner accumulate one L2-sized piece of its slab at a time.
+ *
+ * rc_voxel_partition_count: points per part.
+ *   part_counts : int64 [n_groups * parts_per_group] on the device
+ *   scratch     : device buffer of rc_voxel_partition_scratch_bytes(N, n_parts, device) bytes, 16-byte
+ *                 aligned; it carries the per-block offsets from the count to the move and must stay
+ *                 untouched in between
+ * rc_voxel_partition_move: stable partition (input order kept inside a part; dropped points vanish).
+ *   Part p's points are written as voxel ids (global, z-major; int32) to dest_ids[p] and as feature rows
+ *   (fp32 [., F]) to dest_features[p], from slot dest_start[p] on.  The destinations are device pointers
+ *   given in HOST arrays of n_parts entries and may be buffers of other GPUs mapped with rc_peer_open;
+ *   the caller guarantees room for the counted points.  With dest_start == NULL the parts are packed
+ *   back to back in part order using part_counts_device (then all destinations are normally the same
+ *   buffer).  dest_features may be NULL (ids only).
+ * rc_voxel_partition: count + move into local buffers ids_out [N] / features_out [N, F], parts back to
+ *   back; only the first sum(part_counts) entries are written.
+ * Limits: N and gx*gy*gz below 2^31.  Everything runs on `stream`.
  *
  * rc_voxel_scatter_ids: accumulates points given as (voxel id, feature row) into the slab of
  * voxels [id_begin, id_end); ids outside the range (and -1) are ignored.
@@ -191,15 +203,44 @@ RC_API int rc_voxel_normalize(float* grid, const int32_t* counts, int64_t voxel_
  *            fp32 [id_end-id_begin, F] (mean);  counts : int32 [id_end-id_begin], mean mode only
  *   mode   : RC_VOXEL_COUNT, RC_VOXEL_OCCUPANCY or RC_VOXEL_MEAN;  flags as rc_voxelize
  *   ids must be 16-byte aligned.
+ * rc_voxel_scatter_runs: the same for records that arrive as runs (host arrays run_begin / run_count, in
+ *   records; run_pass[r] in [0, n_passes)): the runs of pass 0 are accumulated first, then pass 1, ...
+ *   Give every sub-range of the slab its own pass and the atomics of a pass stay within that sub-range.
  */
 RC_API uint64_t rc_voxel_partition_scratch_bytes(int64_t N, int32_t n_parts, int device);
+RC_API int rc_voxel_partition_count(const float* points, int64_t N, const float grid_min_host[3], float voxel_size,
+                                    const int32_t grid_size_host[3], int32_t n_groups, int32_t parts_per_group,
+                                    int64_t* part_counts, void* scratch, uint64_t scratch_bytes, int device,
+                                    void* stream);
+RC_API int rc_voxel_partition_move(const float* points, const float* features, int64_t N, int32_t F,
+                                   const float grid_min_host[3], float voxel_size, const int32_t grid_size_host[3],
+                                   int32_t n_groups, int32_t parts_per_group, void* const* dest_ids,
+                                   void* const* dest_features, const int64_t* dest_start,
+                                   const int64_t* part_counts_device, const void* scratch, uint64_t scratch_bytes,
+                                   int device, void* stream);
 RC_API int rc_voxel_partition(const float* points, const float* features, int64_t N, int32_t F,
                               const float grid_min_host[3], float voxel_size, const int32_t grid_size_host[3],
-                              int32_t n_parts, int32_t* ids_out, float* features_out, int64_t* part_counts,
-                              void* scratch, uint64_t scratch_bytes, int device, void* stream);
+                              int32_t n_groups, int32_t parts_per_group, int32_t* ids_out, float* features_out,
+                              int64_t* part_counts, void* scratch, uint64_t scratch_bytes, int device, void* stream);
 RC_API int rc_voxel_scatter_ids(const int32_t* ids, const float* features, void* grid, int32_t* counts,
                                 int64_t M, int32_t F, int64_t id_begin, int64_t id_end, int mode,
                                 uint32_t flags, int device, void* stream);
+RC_API int rc_voxel_scatter_runs(const int32_t* ids, const float* features, void* grid, int32_t* counts, int32_t F,
+                                 int64_t id_begin, int64_t id_end, const int64_t* run_begin,
+                                 const int64_t* run_count, const int32_t* run_pass, int32_t n_runs,
+                                 int32_t n_passes, int mode, uint32_t flags, int device, void* stream);
+
+/*
+ * Device buffers that the other processes of a node can map, for rc_voxel_partition_move's remote
+ * destinations.  rc_peer_alloc allocates `bytes` on `device` (cudaMalloc) and fills the 64-byte CUDA IPC
+ * handle to hand to the other processes; rc_peer_open maps such a handle into this process on `device`
+ * with peer access enabled; rc_peer_close unmaps, rc_peer_free releases (close every mapping first).
+ * These are set-up calls: none of them belongs on a hot path.  No counterpart in the reference.
+ */
+RC_API int rc_peer_alloc(uint64_t bytes, int device, void** ptr, unsigned char handle[64]);
+RC_API int rc_peer_open(const unsigned char handle[64], int device, void** ptr);
+RC_API int rc_peer_close(void* ptr, int device);
+RC_API int rc_peer_free(void* ptr, int device);
 
 /*
  * Mean-mode voxelisation that allocates nothing. No counterpart in the reference: its binding

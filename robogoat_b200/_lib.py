@@ -31,7 +31,8 @@ STATIC_MAX_VOXELS = 1 << 21
 # every symbol the header declares; the CPU test-suite checks the built library exports them all
 EXPORTED_SYMBOLS = (
     "rc_resample", "rc_resample_strided", "rc_resample_ragged", "rc_fuse", "rc_fuse_strided", "rc_resample_brackets", "rc_voxelize", "rc_voxel_normalize", "rc_voxelize_mean_static",
-    "rc_voxelize_ex", "rc_voxelize_scratch_bytes", "rc_voxel_partition", "rc_voxel_partition_scratch_bytes", "rc_voxel_scatter_ids",
+    "rc_voxelize_ex", "rc_voxelize_scratch_bytes", "rc_voxel_partition", "rc_voxel_partition_count", "rc_voxel_partition_move", "rc_voxel_partition_scratch_bytes",
+    "rc_voxel_scatter_ids", "rc_voxel_scatter_runs", "rc_peer_alloc", "rc_peer_open", "rc_peer_close", "rc_peer_free",
     "rc_set_option", "rc_bulk_wait_timeouts", "rc_strerror", "rc_last_cuda_error", "rc_abi_version",
 )
 
@@ -71,9 +72,23 @@ def _declare(L: ctypes.CDLL) -> None:
     L.rc_voxelize_scratch_bytes.restype = ctypes.c_uint64
     L.rc_voxel_partition_scratch_bytes.argtypes = [i64, i32, ci]
     L.rc_voxel_partition_scratch_bytes.restype = ctypes.c_uint64
-    L.rc_voxel_partition.argtypes = [vp, vp, i64, i32, ctypes.POINTER(f32), f32, ctypes.POINTER(i32), i32, vp, vp, vp, vp,
-                                     ctypes.c_uint64, ci, vp]
+    fp, ip = ctypes.POINTER(f32), ctypes.POINTER(i32)
+    L.rc_voxel_partition.argtypes = [vp, vp, i64, i32, fp, f32, ip, i32, i32, vp, vp, vp, vp, ctypes.c_uint64, ci, vp]
     L.rc_voxel_partition.restype = ci
+    L.rc_voxel_partition_count.argtypes = [vp, i64, fp, f32, ip, i32, i32, vp, vp, ctypes.c_uint64, ci, vp]
+    L.rc_voxel_partition_count.restype = ci
+    L.rc_voxel_partition_move.argtypes = [vp, vp, i64, i32, fp, f32, ip, i32, i32, ctypes.POINTER(vp), ctypes.POINTER(vp),
+                                          ctypes.POINTER(i64), vp, vp, ctypes.c_uint64, ci, vp]
+    L.rc_voxel_partition_move.restype = ci
+    L.rc_voxel_scatter_runs.argtypes = [vp, vp, vp, vp, i32, i64, i64, ctypes.POINTER(i64), ctypes.POINTER(i64), ip, i32, i32,
+                                        ci, u32, ci, vp]
+    L.rc_voxel_scatter_runs.restype = ci
+    L.rc_peer_alloc.argtypes = [ctypes.c_uint64, ci, ctypes.POINTER(vp), ctypes.c_char_p]
+    L.rc_peer_open.argtypes = [ctypes.c_char_p, ci, ctypes.POINTER(vp)]
+    L.rc_peer_close.argtypes = [vp, ci]
+    L.rc_peer_free.argtypes = [vp, ci]
+    for name in ("rc_peer_alloc", "rc_peer_open", "rc_peer_close", "rc_peer_free"):
+        getattr(L, name).restype = ci
     L.rc_voxel_scatter_ids.argtypes = [vp, vp, vp, vp, i64, i32, i64, i64, ci, u32, ci, vp]
     L.rc_voxel_scatter_ids.restype = ci
     L.rc_voxelize_mean_static.argtypes = [vp, vp, vp, i64, i32, ctypes.POINTER(f32), f32, ctypes.POINTER(i32), ci, vp]

@@ -494,88 +494,204 @@ void launch_bin(bool agg, bool overlap_prev, unsigned int blocks, cudaStream_t s
 
 // ---------------------------------------------------------------- partition by owning part (point exchange)
 //
-// A stable counting partition in three launches.  Every warp owns a contiguous run of 128-point
-// tiles.  Launch 1 (MOVE = false) counts, per warp and part, the in-grid points; launch 2 turns each
-// part's column of that table into exclusive prefixes (one CTA per part); launch 3 (MOVE = true)
-// walks the same tiles again, recomputes the voxel ids (cheaper than keeping them: 12 bytes re-read
-// against 4 written + 4 read) and writes every point at part start + warp prefix + rank in the warp.
-// Ranks come from __match_any_sync, so input order is kept inside a part and the result does not
-// depend on scheduling.
+// A stable counting partition in three launches.  Every CTA owns a contiguous run of 1024-point
+// chunks.  Launch 1 (MOVE = false) counts the in-grid points per CTA and part; launch 2 turns each
+// part's column of that table into exclusive prefixes over the CTAs (one CTA per part); launch 3
+// (MOVE = true) walks the same chunks again, recomputes the voxel ids (cheaper than keeping them:
+// 12 bytes re-read against 4 written + 4 read), sorts each chunk by part in shared memory and writes
+// the sorted chunk out, so that every part receives runs of consecutive records: full-width stores
+// whether the destination is local memory or a peer's.  Ranks inside a warp come from
+// __match_any_sync and warps are prefixed in order, so input order is kept inside a part and the
+// result does not depend on scheduling.
+//
+// Parts are two-level: n_groups owners (ranks) with ceil(V / n_groups) voxel ids each, every owner's
+// range cut into parts_per_group sub-ranges of ceil(range / parts_per_group) ids; part = group *
+// parts_per_group + sub.  Sub-ranges let the owner accumulate one L2-sized piece of its slab at a time.
 constexpr int kMaxParts = 64;
+constexpr int kChunk = kPointsPerBlock;   // 1024 points: one 128-point tile per warp
+
+struct PartRule {
+    unsigned int slab, sub;       // ids per group, ids per part inside a group
+    float inv_slab, inv_sub;
+    int per_group, P;
+};
+
+struct PartDest {                 // where the points of each part go (move pass)
+    int* ids[kMaxParts];
+    float* feats[kMaxParts];
+    long long start[kMaxParts];   // first slot of this call's points in that buffer
+};
+
+// n / d for quotients up to a few hundred: float estimate, then one correction step either way
+__device__ __forceinline__ unsigned int small_quotient(unsigned int n, unsigned int d, float inv) {
+    unsigned int q = static_cast<unsigned int>(__uint2float_rz(n) * inv);
+    if (static_cast<unsigned long long>(q) * d > n) --q;
+    else if (static_cast<unsigned long long>(q + 1) * d <= n) ++q;
+    return q;
+}
+__device__ __forceinline__ int part_of(int id, const PartRule& r) {
+    const unsigned int u = static_cast<unsigned int>(id);
+    const unsigned int grp = small_quotient(u, r.slab, r.inv_slab);
+    const unsigned int k = small_quotient(u - grp * r.slab, r.sub, r.inv_sub);
+    return static_cast<int>(grp) * r.per_group + static_cast<int>(k);
+}
 
 template <bool MOVE>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, 4)
 voxel_part_kernel(const float* __restrict__ pts, const float* __restrict__ feats, long long N, int F, VoxelGeom g,
-                  bool pts_aligned, bool vec4, unsigned int slab, int P, long long tiles_per_warp,
-                  int* __restrict__ table, const long long* __restrict__ part_counts, int* __restrict__ ids_out,
-                  float* __restrict__ feats_out) {
+                  bool pts_aligned, bool vec4, PartRule rule, long long chunks_per_cta, int* __restrict__ table,
+                  const long long* __restrict__ part_counts, const __grid_constant__ PartDest dest) {
     __shared__ __align__(16) float s_xyz[kThreads / 32][kPointsPerWarp * 3];
-    __shared__ int s_cur[kThreads / 32][kMaxParts];
+    __shared__ int s_wcnt[kThreads / 32][kMaxParts];   // count: per-warp totals; move: this chunk's per-warp counts, then prefixes
+    __shared__ long long s_cur[kMaxParts];             // move: next slot of each part in its destination
+    __shared__ int* s_dst_ids[kMaxParts];
+    __shared__ float* s_dst_feats[kMaxParts];
+    __shared__ int s_lstart[kMaxParts + 1];            // move: start of each part's run in the sorted chunk
+    __shared__ int s_sid[MOVE ? kChunk : 1];
+    __shared__ unsigned short s_ssrc[MOVE ? kChunk : 1];
+    __shared__ unsigned char s_spart[MOVE ? kChunk : 1];
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
     const unsigned int lt_mask = (1u << lane) - 1u;
-    const long long gw = static_cast<long long>(blockIdx.x) * (kThreads / 32) + warp;
-    int* cur = s_cur[warp];
-    for (int p = lane; p < P; p += 32) {
-        int start = 0;
-        if (MOVE) {
-            long long before = 0;
-            for (int q = 0; q < p; ++q) before += part_counts[q];
-            start = static_cast<int>(before) + table[gw * P + p];
+    const int P = rule.P;
+    int* wcnt = s_wcnt[warp];
+    for (int p = lane; p < P; p += 32) wcnt[p] = 0;
+    if (MOVE) {
+        for (int p = threadIdx.x; p < P; p += kThreads) {
+            long long start;
+            if (part_counts != nullptr) {          // local destination: parts packed back to back
+                start = 0;
+                for (int q = 0; q < p; ++q) start += part_counts[q];
+            } else {
+                start = dest.start[p];
+            }
+            s_cur[p] = start + table[static_cast<long long>(blockIdx.x) * P + p];
+            s_dst_ids[p] = dest.ids[p];
+            s_dst_feats[p] = dest.feats[p];
         }
-        cur[p] = start;
     }
-    __syncwarp();
-    const long long ntiles = (N + kPointsPerWarp - 1) / kPointsPerWarp;
-    const long long t0 = gw * tiles_per_warp;
-    const long long t1 = (t0 + tiles_per_warp < ntiles) ? t0 + tiles_per_warp : ntiles;
+    __syncthreads();
+    const long long nchunks = (N + kChunk - 1) / kChunk;
+    const long long c0 = static_cast<long long>(blockIdx.x) * chunks_per_cta;
+    const long long c1 = (c0 + chunks_per_cta < nchunks) ? c0 + chunks_per_cta : nchunks;
     float4 ahead[3];
-    if (pts_aligned && t0 < t1 && (t0 + 1) * kPointsPerWarp <= N) tile_issue(pts, t0 * kPointsPerWarp, lane, ahead);
-    for (long long tile = t0; tile < t1; ++tile) {
-        const long long base = tile * kPointsPerWarp;
+    {
+        const long long tbase = c0 * kChunk + warp * kPointsPerWarp;
+        if (pts_aligned && c0 < c1 && tbase + kPointsPerWarp <= N) tile_issue(pts, tbase, lane, ahead);
+    }
+    for (long long chunk = c0; chunk < c1; ++chunk) {
+        const long long cbase = chunk * kChunk;
+        const long long base = cbase + warp * kPointsPerWarp;
         float x[kPointsPerLane], y[kPointsPerLane], z[kPointsPerLane];
         if (pts_aligned && base + kPointsPerWarp <= N) {
             float4 now[3] = {ahead[0], ahead[1], ahead[2]};
-            if (tile + 1 < t1 && (tile + 2) * kPointsPerWarp <= N) tile_issue(pts, (tile + 1) * kPointsPerWarp, lane, ahead);
+            const long long nbase = base + kChunk;
+            if (chunk + 1 < c1 && nbase + kPointsPerWarp <= N) tile_issue(pts, nbase, lane, ahead);
             tile_unpack(now, s_xyz[warp], lane, x, y, z);
         } else {
             tile_load_slow(pts, base, N, lane, x, y, z);
         }
-        float4 f4[kPointsPerLane];
-        int id[kPointsPerLane];
+        int id[kPointsPerLane], part[kPointsPerLane], rank[kPointsPerLane];
 #pragma unroll
         for (int i = 0; i < kPointsPerLane; ++i) {
             const long long pi = base + i * 32 + lane;
             id[i] = (pi < N) ? static_cast<int>(voxel_id(x[i], y[i], z[i], g)) : -1;
-            if (MOVE && vec4 && id[i] >= 0) f4[i] = __ldcs(reinterpret_cast<const float4*>(feats + pi * 4));
+            part[i] = (id[i] < 0) ? -1 : part_of(id[i], rule);
         }
 #pragma unroll
         for (int i = 0; i < kPointsPerLane; ++i) {
-            const int part = (id[i] < 0) ? -1 : static_cast<int>(static_cast<unsigned int>(id[i]) / slab);
-            const unsigned int same = __match_any_sync(0xffffffffu, part);
-            int pos = 0;
-            if (MOVE && part >= 0) pos = cur[part] + __popc(same & lt_mask);
+            const unsigned int same = __match_any_sync(0xffffffffu, part[i]);
+            rank[i] = 0;
+            if (MOVE && part[i] >= 0) rank[i] = wcnt[part[i]] + __popc(same & lt_mask);
             __syncwarp();
-            if (part >= 0 && (same & lt_mask) == 0u) cur[part] += __popc(same);   // lowest lane of the group
+            if (part[i] >= 0 && (same & lt_mask) == 0u) wcnt[part[i]] += __popc(same);   // lowest lane of the group
             __syncwarp();
-            if (MOVE && part >= 0) {
-                ids_out[pos] = id[i];
-                if (vec4) {
-                    reinterpret_cast<float4*>(feats_out)[pos] = f4[i];
-                } else if (feats_out != nullptr) {
-                    const long long pi = base + i * 32 + lane;
-                    for (int c = 0; c < F; ++c) feats_out[static_cast<long long>(pos) * F + c] = __ldg(feats + pi * F + c);
+        }
+        if (!MOVE) continue;                         // the count pass only accumulates wcnt
+        __syncthreads();
+        if (warp == 0) {
+            // per part: exclusive prefix over the warps, then exclusive prefix of the chunk totals over the parts
+            int tot[2] = {0, 0};
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const int p = lane + 32 * h;
+                if (p < P) {
+                    int c = 0;
+                    for (int w = 0; w < kThreads / 32; ++w) { const int t = s_wcnt[w][p]; s_wcnt[w][p] = c; c += t; }
+                    tot[h] = c;
+                }
+            }
+            int inc0 = tot[0], inc1 = tot[1];
+#pragma unroll
+            for (int off = 1; off < 32; off <<= 1) {
+                const int a = __shfl_up_sync(0xffffffffu, inc0, off);
+                const int b = __shfl_up_sync(0xffffffffu, inc1, off);
+                if (lane >= off) { inc0 += a; inc1 += b; }
+            }
+            const int sum0 = __shfl_sync(0xffffffffu, inc0, 31);
+            if (lane < P) s_lstart[lane] = inc0 - tot[0];
+            if (lane + 32 < P) s_lstart[lane + 32] = sum0 + inc1 - tot[1];
+            if (lane == 31) s_lstart[P] = sum0 + inc1;       // inc1 of lane 31 covers all upper parts (zeros beyond P)
+        }
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < kPointsPerLane; ++i) {
+            if (part[i] >= 0) {
+                const int slot = s_lstart[part[i]] + wcnt[part[i]] + rank[i];
+                s_sid[slot] = id[i];
+                s_ssrc[slot] = static_cast<unsigned short>(warp * kPointsPerWarp + i * 32 + lane);
+                s_spart[slot] = static_cast<unsigned char>(part[i]);
+            }
+        }
+        __syncthreads();
+        const int n = s_lstart[P];
+        if (vec4) {
+            float4 f4[kPointsPerLane];
+            int pj[kPointsPerLane];
+#pragma unroll
+            for (int m = 0; m < kPointsPerLane; ++m) {
+                const int j = threadIdx.x + m * kThreads;
+                pj[m] = (j < n) ? s_spart[j] : -1;
+                if (j < n) f4[m] = __ldcs(reinterpret_cast<const float4*>(feats) + cbase + s_ssrc[j]);
+            }
+#pragma unroll
+            for (int m = 0; m < kPointsPerLane; ++m) {
+                const int j = threadIdx.x + m * kThreads;
+                if (pj[m] >= 0) {
+                    const long long slot = s_cur[pj[m]] + (j - s_lstart[pj[m]]);
+                    s_dst_ids[pj[m]][slot] = s_sid[j];
+                    reinterpret_cast<float4*>(s_dst_feats[pj[m]])[slot] = f4[m];
+                }
+            }
+        } else {
+            for (int j = threadIdx.x; j < n; j += kThreads) {
+                const int p = s_spart[j];
+                const long long slot = s_cur[p] + (j - s_lstart[p]);
+                s_dst_ids[p][slot] = s_sid[j];
+                float* fo = s_dst_feats[p];
+                if (fo != nullptr) {
+                    const float* fi = feats + (cbase + s_ssrc[j]) * F;
+                    for (int c = 0; c < F; ++c) fo[slot * F + c] = __ldg(fi + c);
                 }
             }
         }
+        __syncthreads();
+        for (int p = threadIdx.x; p < P; p += kThreads) s_cur[p] += s_lstart[p + 1] - s_lstart[p];
+        for (int p = lane; p < P; p += 32) wcnt[p] = 0;
+        __syncwarp();
+        // the next chunk's first block-wide barrier orders these updates before their next use
     }
     if (!MOVE) {
-        __syncwarp();
-        for (int p = lane; p < P; p += 32) table[gw * P + p] = cur[p];
+        __syncthreads();
+        for (int p = threadIdx.x; p < P; p += kThreads) {
+            int c = 0;
+            for (int w = 0; w < kThreads / 32; ++w) c += s_wcnt[w][p];
+            table[static_cast<long long>(blockIdx.x) * P + p] = c;
+        }
     }
 }
 
-// CTA p: exclusive prefix over the warps of column p of the table, total into part_counts[p]
+// CTA p: exclusive prefix over the CTAs of column p of the table, total into part_counts[p]
 __global__ void __launch_bounds__(1024)
 voxel_part_scan_kernel(int* __restrict__ table, long long W, int P, long long* __restrict__ part_counts) {
     __shared__ long long s_sum[1024];
@@ -602,16 +718,92 @@ voxel_part_scan_kernel(int* __restrict__ table, long long W, int P, long long* _
     if (threadIdx.x == 1023) part_counts[p] = s_sum[1023];
 }
 
-// warps (and blocks) that share the tiles of a cloud of N points
-void partition_plan(long long N, int device, long long* blocks, long long* tiles_per_warp) {
-    const long long ntiles = (N + kPointsPerWarp - 1) / kPointsPerWarp;
-    long long nb = (ntiles + kThreads / 32 - 1) / (kThreads / 32);
+// CTAs that share the chunks of a cloud of N points
+void partition_plan(long long N, int device, long long* blocks, long long* chunks_per_cta) {
+    const long long nchunks = (N + kChunk - 1) / kChunk;
+    long long nb = nchunks;
     const long long cap = 16ll * rc::sm_count(device);
     if (nb > cap) nb = cap;
     if (nb < 1) nb = 1;
-    const long long W = nb * (kThreads / 32);
+    *chunks_per_cta = (nchunks + nb - 1) / nb;
     *blocks = nb;
-    *tiles_per_warp = (ntiles + W - 1) / W;
+}
+
+int partition_geometry(const float grid_min_host[3], float voxel_size, const int32_t grid_size_host[3], int32_t n_groups,
+                       int32_t parts_per_group, VoxelGeom* g, PartRule* rule, long long* V_out) {
+    if (grid_min_host == nullptr || grid_size_host == nullptr) return RC_ERR_NULL_POINTER;
+    if (n_groups < 1 || parts_per_group < 1) return RC_ERR_BAD_SHAPE;
+    if (static_cast<long long>(n_groups) * parts_per_group > kMaxParts) return RC_ERR_TOO_LARGE;
+    if (!(voxel_size > 0.0f) || !(voxel_size <= 3.0e38f)) return RC_ERR_BAD_VALUE;
+    g->minx = grid_min_host[0]; g->miny = grid_min_host[1]; g->minz = grid_min_host[2];
+    g->vs = voxel_size;
+    g->gx = grid_size_host[0]; g->gy = grid_size_host[1]; g->gz = grid_size_host[2];
+    if (g->gx < 0 || g->gy < 0 || g->gz < 0) return RC_ERR_BAD_SHAPE;
+    if (g->gx >= (1 << 24) || g->gy >= (1 << 24) || g->gz >= (1 << 24)) return RC_ERR_TOO_LARGE;
+    if (static_cast<double>(g->gx) * g->gy * g->gz >= 2147483648.0) return RC_ERR_TOO_LARGE;
+    g->fgx = static_cast<float>(g->gx); g->fgy = static_cast<float>(g->gy); g->fgz = static_cast<float>(g->gz);
+    const long long V = static_cast<long long>(g->gx) * g->gy * g->gz;
+    *V_out = V;
+    const long long slab = (V + n_groups - 1) / n_groups;
+    const long long sub = (slab + parts_per_group - 1) / parts_per_group;
+    rule->slab = static_cast<unsigned int>(slab > 0 ? slab : 1);
+    rule->sub = static_cast<unsigned int>(sub > 0 ? sub : 1);
+    rule->inv_slab = 1.0f / static_cast<float>(rule->slab);
+    rule->inv_sub = 1.0f / static_cast<float>(rule->sub);
+    rule->per_group = parts_per_group;
+    rule->P = n_groups * parts_per_group;
+    return RC_OK;
+}
+
+// ---------------------------------------------------------------- scatter of pre-sorted runs
+//
+// The owner's side of the point exchange.  What arrives is a list of runs, each holding the points
+// of one sub-range of the slab; the runs of one sub-range are accumulated by one launch, so its
+// atomics work on an L2-sized piece of the slab and the records stream in sequentially.
+struct RunTable {
+    long long begin[kMaxParts];
+    long long count[kMaxParts];
+    long long first_block[kMaxParts + 1];   // in blocks of kChunk points
+    int n;
+};
+
+template <int MODE>
+__global__ void __launch_bounds__(kThreads)
+voxel_scatter_runs_kernel(const int* __restrict__ ids, const float* __restrict__ feats, void* __restrict__ grid_v,
+                          int* __restrict__ counts, int F, bool vec4, const __grid_constant__ RunTable rt, int id_lo,
+                          unsigned int span) {
+    const long long total = rt.first_block[rt.n];
+    for (long long b = blockIdx.x; b < total; b += gridDim.x) {
+        int r = 0;
+        while (r + 1 < rt.n && rt.first_block[r + 1] <= b) ++r;
+        const long long off = (b - rt.first_block[r]) * kChunk;
+        const long long cnt = rt.count[r];
+        const long long p0 = rt.begin[r];
+        int id[kPointsPerLane];
+        float4 f4[kPointsPerLane];
+#pragma unroll
+        for (int m = 0; m < kPointsPerLane; ++m) {
+            const long long j = off + m * kThreads + threadIdx.x;
+            id[m] = (j < cnt) ? __ldcs(ids + p0 + j) : -1;
+            if (MODE == kMean && vec4 && j < cnt) f4[m] = __ldcs(reinterpret_cast<const float4*>(feats) + p0 + j);
+        }
+#pragma unroll
+        for (int m = 0; m < kPointsPerLane; ++m) {
+            if (static_cast<unsigned int>(id[m] - id_lo) >= span) continue;   // also drops -1 and foreign ids
+            if (MODE == kMean && vec4) {
+                red_add_v4(static_cast<float*>(grid_v) + static_cast<long long>(id[m]) * 4, f4[m]);
+                atomicAdd(counts + id[m], 1);
+            } else {
+                scatter_one<MODE>(id[m], p0 + off + m * kThreads + threadIdx.x, feats, grid_v, counts, F);
+            }
+        }
+    }
+}
+
+template <int MODE>
+void launch_scatter_runs(unsigned int nb, cudaStream_t st, const int* ids, const float* feats, void* grid0, int* counts0,
+                         int F, bool vec4, const RunTable& rt, int id_lo, unsigned int span) {
+    voxel_scatter_runs_kernel<MODE><<<nb, kThreads, 0, st>>>(ids, feats, grid0, counts0, F, vec4, rt, id_lo, span);
 }
 
 // ---------------------------------------------------------------- allocation-free mean mode
@@ -835,58 +1027,99 @@ int rc_voxelize_ex(const float* points, const float* features, void* grid, int32
 
 uint64_t rc_voxel_partition_scratch_bytes(int64_t N, int32_t n_parts, int device) {
     if (N <= 0 || n_parts < 1 || n_parts > kMaxParts) return 0;
-    long long blocks = 0, tpw = 0;
-    partition_plan(N, device, &blocks, &tpw);
-    return static_cast<uint64_t>(blocks) * (kThreads / 32) * static_cast<uint64_t>(n_parts) * 4u;
+    long long blocks = 0, per = 0;
+    partition_plan(N, device, &blocks, &per);
+    return static_cast<uint64_t>(blocks) * static_cast<uint64_t>(n_parts) * 4u;
 }
 
-int rc_voxel_partition(const float* points, const float* features, int64_t N, int32_t F,
-                       const float grid_min_host[3], float voxel_size, const int32_t grid_size_host[3],
-                       int32_t n_parts, int32_t* ids_out, float* features_out, int64_t* part_counts,
-                       void* scratch, uint64_t scratch_bytes, int device, void* stream) {
-    if (grid_min_host == nullptr || grid_size_host == nullptr || part_counts == nullptr) return RC_ERR_NULL_POINTER;
-    if (N < 0 || F < 0 || n_parts < 1) return RC_ERR_BAD_SHAPE;
-    if (n_parts > kMaxParts || N >= (1ll << 31)) return RC_ERR_TOO_LARGE;
-    if (!(voxel_size > 0.0f) || !(voxel_size <= 3.0e38f)) return RC_ERR_BAD_VALUE;
+int rc_voxel_partition_count(const float* points, int64_t N, const float grid_min_host[3], float voxel_size,
+                             const int32_t grid_size_host[3], int32_t n_groups, int32_t parts_per_group,
+                             int64_t* part_counts, void* scratch, uint64_t scratch_bytes, int device, void* stream) {
     VoxelGeom g;
-    g.minx = grid_min_host[0]; g.miny = grid_min_host[1]; g.minz = grid_min_host[2];
-    g.vs = voxel_size;
-    g.gx = grid_size_host[0]; g.gy = grid_size_host[1]; g.gz = grid_size_host[2];
-    if (g.gx < 0 || g.gy < 0 || g.gz < 0) return RC_ERR_BAD_SHAPE;
-    if (g.gx >= (1 << 24) || g.gy >= (1 << 24) || g.gz >= (1 << 24)) return RC_ERR_TOO_LARGE;
-    if (static_cast<double>(g.gx) * g.gy * g.gz >= 2147483648.0) return RC_ERR_TOO_LARGE;
-    g.fgx = static_cast<float>(g.gx); g.fgy = static_cast<float>(g.gy); g.fgz = static_cast<float>(g.gz);
-    const long long V = static_cast<long long>(g.gx) * g.gy * g.gz;
-    const bool move_feats = features != nullptr && features_out != nullptr && F > 0;
-    if (N > 0 && (points == nullptr || ids_out == nullptr)) return RC_ERR_NULL_POINTER;
-    if (!rc::aligned_to(points, 4) || !rc::aligned_to(features, 4) || !rc::aligned_to(features_out, 4) ||
-        !rc::aligned_to(ids_out, 4) || !rc::aligned_to(part_counts, 8))
-        return RC_ERR_BAD_ALIGNMENT;
+    PartRule rule;
+    long long V = 0;
+    const int rc_geom = partition_geometry(grid_min_host, voxel_size, grid_size_host, n_groups, parts_per_group, &g, &rule, &V);
+    if (rc_geom != RC_OK) return rc_geom;
+    if (part_counts == nullptr) return RC_ERR_NULL_POINTER;
+    if (N < 0) return RC_ERR_BAD_SHAPE;
+    if (N >= (1ll << 31)) return RC_ERR_TOO_LARGE;
+    if (N > 0 && points == nullptr) return RC_ERR_NULL_POINTER;
+    if (!rc::aligned_to(points, 4) || !rc::aligned_to(part_counts, 8)) return RC_ERR_BAD_ALIGNMENT;
     rc::DeviceScope scope(device);
     if (scope.status() != RC_OK) return scope.status();
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (N == 0 || V == 0) {
-        RC_CUDA_TRY(cudaMemsetAsync(part_counts, 0, static_cast<size_t>(n_parts) * 8, st));
+        RC_CUDA_TRY(cudaMemsetAsync(part_counts, 0, static_cast<size_t>(rule.P) * 8, st));
         return RC_OK;
     }
-    long long blocks = 0, tpw = 0;
-    partition_plan(N, device, &blocks, &tpw);
-    const long long W = blocks * (kThreads / 32);
+    long long blocks = 0, per = 0;
+    partition_plan(N, device, &blocks, &per);
     if (scratch == nullptr) return RC_ERR_NULL_POINTER;
     if (!rc::aligned_to(scratch, 16)) return RC_ERR_BAD_ALIGNMENT;
-    if (scratch_bytes < static_cast<uint64_t>(W) * n_parts * 4u) return RC_ERR_BAD_SHAPE;
+    if (scratch_bytes < static_cast<uint64_t>(blocks) * rule.P * 4u) return RC_ERR_BAD_SHAPE;
     int* table = static_cast<int*>(scratch);
-    const unsigned int slab = static_cast<unsigned int>((V + n_parts - 1) / n_parts);
-    const bool aligned = rc::aligned_to(points, 16);
-    const bool vec4 = move_feats && F == 4 && rc::aligned_to(features, 16) && rc::aligned_to(features_out, 16);
-    const unsigned int nb = static_cast<unsigned int>(blocks);
-    voxel_part_kernel<false><<<nb, kThreads, 0, st>>>(points, nullptr, N, F, g, aligned, false, slab, n_parts, tpw, table,
-                                                      nullptr, nullptr, nullptr);
-    voxel_part_scan_kernel<<<n_parts, 1024, 0, st>>>(table, W, n_parts, reinterpret_cast<long long*>(part_counts));
-    voxel_part_kernel<true><<<nb, kThreads, 0, st>>>(points, move_feats ? features : nullptr, N, F, g, aligned, vec4, slab,
-                                                     n_parts, tpw, table, reinterpret_cast<const long long*>(part_counts),
-                                                     ids_out, move_feats ? features_out : nullptr);
+    PartDest none{};
+    voxel_part_kernel<false><<<static_cast<unsigned int>(blocks), kThreads, 0, st>>>(
+        points, nullptr, N, 0, g, rc::aligned_to(points, 16), false, rule, per, table, nullptr, none);
+    voxel_part_scan_kernel<<<rule.P, 1024, 0, st>>>(table, blocks, rule.P, reinterpret_cast<long long*>(part_counts));
     return rc::check_launch();
+}
+
+int rc_voxel_partition_move(const float* points, const float* features, int64_t N, int32_t F,
+                            const float grid_min_host[3], float voxel_size, const int32_t grid_size_host[3],
+                            int32_t n_groups, int32_t parts_per_group, void* const* dest_ids, void* const* dest_features,
+                            const int64_t* dest_start, const int64_t* part_counts_device, const void* scratch,
+                            uint64_t scratch_bytes, int device, void* stream) {
+    VoxelGeom g;
+    PartRule rule;
+    long long V = 0;
+    const int rc_geom = partition_geometry(grid_min_host, voxel_size, grid_size_host, n_groups, parts_per_group, &g, &rule, &V);
+    if (rc_geom != RC_OK) return rc_geom;
+    if (N < 0 || F < 0) return RC_ERR_BAD_SHAPE;
+    if (N >= (1ll << 31)) return RC_ERR_TOO_LARGE;
+    if (N == 0 || V == 0) return RC_OK;
+    if (points == nullptr || dest_ids == nullptr || scratch == nullptr) return RC_ERR_NULL_POINTER;
+    if (dest_start == nullptr && part_counts_device == nullptr) return RC_ERR_NULL_POINTER;
+    const bool move_feats = features != nullptr && dest_features != nullptr && F > 0;
+    PartDest dest{};
+    bool all16 = rc::aligned_to(features, 16);
+    for (int p = 0; p < rule.P; ++p) {
+        dest.ids[p] = static_cast<int*>(dest_ids[p]);
+        dest.feats[p] = move_feats ? static_cast<float*>(dest_features[p]) : nullptr;
+        dest.start[p] = dest_start != nullptr ? dest_start[p] : 0;
+        if (dest.ids[p] == nullptr || (move_feats && dest.feats[p] == nullptr)) return RC_ERR_NULL_POINTER;
+        if (dest.start[p] < 0) return RC_ERR_BAD_SHAPE;
+        if (!rc::aligned_to(dest.ids[p], 4) || !rc::aligned_to(dest.feats[p], 4)) return RC_ERR_BAD_ALIGNMENT;
+        all16 = all16 && rc::aligned_to(dest.feats[p], 16);
+    }
+    if (!rc::aligned_to(points, 4) || !rc::aligned_to(features, 4) || !rc::aligned_to(scratch, 16)) return RC_ERR_BAD_ALIGNMENT;
+    rc::DeviceScope scope(device);
+    if (scope.status() != RC_OK) return scope.status();
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    long long blocks = 0, per = 0;
+    partition_plan(N, device, &blocks, &per);
+    if (scratch_bytes < static_cast<uint64_t>(blocks) * rule.P * 4u) return RC_ERR_BAD_SHAPE;
+    const bool vec4 = move_feats && F == 4 && all16;
+    voxel_part_kernel<true><<<static_cast<unsigned int>(blocks), kThreads, 0, st>>>(
+        points, move_feats ? features : nullptr, N, F, g, rc::aligned_to(points, 16), vec4, rule, per,
+        const_cast<int*>(static_cast<const int*>(scratch)), reinterpret_cast<const long long*>(part_counts_device), dest);
+    return rc::check_launch();
+}
+
+int rc_voxel_partition(const float* points, const float* features, int64_t N, int32_t F,
+                       const float grid_min_host[3], float voxel_size, const int32_t grid_size_host[3],
+                       int32_t n_groups, int32_t parts_per_group, int32_t* ids_out, float* features_out,
+                       int64_t* part_counts, void* scratch, uint64_t scratch_bytes, int device, void* stream) {
+    const int rc_count = rc_voxel_partition_count(points, N, grid_min_host, voxel_size, grid_size_host, n_groups,
+                                                  parts_per_group, part_counts, scratch, scratch_bytes, device, stream);
+    if (rc_count != RC_OK) return rc_count;
+    if (N > 0 && ids_out == nullptr) return RC_ERR_NULL_POINTER;
+    void* ids_of[kMaxParts];
+    void* feats_of[kMaxParts];
+    for (int p = 0; p < kMaxParts; ++p) { ids_of[p] = ids_out; feats_of[p] = features_out; }
+    return rc_voxel_partition_move(points, features, N, F, grid_min_host, voxel_size, grid_size_host, n_groups,
+                                   parts_per_group, ids_of, features_out != nullptr ? feats_of : nullptr, nullptr,
+                                   part_counts, scratch, scratch_bytes, device, stream);
 }
 
 int rc_voxel_scatter_ids(const int32_t* ids, const float* features, void* grid, int32_t* counts, int64_t M,
@@ -945,6 +1178,79 @@ int rc_voxel_scatter_ids(const int32_t* ids, const float* features, void* grid, 
                 voxel_scatter_ids_kernel<kCount><<<nb, kThreads, 0, st>>>(ids, features, grid0, counts0, M, F, lo, hi, nullptr, 0);
             else
                 voxel_scatter_ids_kernel<kOccupancy><<<nb, kThreads, 0, st>>>(ids, features, grid0, counts0, M, F, lo, hi, nullptr, 0);
+        }
+    }
+    const int rc_launch = rc::check_launch();
+    if (rc_launch != RC_OK) return rc_launch;
+    if (mean && !(flags & RC_VOXEL_NO_NORMALIZE) && nvox > 0 && F > 0)
+        return rc_voxel_normalize(static_cast<float*>(grid), counts, 0, nvox, F, device, stream);
+    return RC_OK;
+}
+
+int rc_voxel_scatter_runs(const int32_t* ids, const float* features, void* grid, int32_t* counts, int32_t F,
+                          int64_t id_begin, int64_t id_end, const int64_t* run_begin, const int64_t* run_count,
+                          const int32_t* run_pass, int32_t n_runs, int32_t n_passes, int mode, uint32_t flags,
+                          int device, void* stream) {
+    if (mode != RC_VOXEL_COUNT && mode != RC_VOXEL_OCCUPANCY && mode != RC_VOXEL_MEAN) return RC_ERR_BAD_MODE;
+    if (F < 0 || id_begin < 0 || id_end < id_begin || n_runs < 0 || n_passes < 0) return RC_ERR_BAD_SHAPE;
+    if (id_end >= (1ll << 31)) return RC_ERR_TOO_LARGE;
+    if (n_runs > 0 && (run_begin == nullptr || run_count == nullptr || run_pass == nullptr)) return RC_ERR_NULL_POINTER;
+    const long long nvox = id_end - id_begin;
+    const bool mean = (mode == RC_VOXEL_MEAN);
+    long long total = 0;
+    for (int r = 0; r < n_runs; ++r) {
+        if (run_begin[r] < 0 || run_count[r] < 0 || run_pass[r] < 0 || run_pass[r] >= n_passes) return RC_ERR_BAD_SHAPE;
+        total += run_count[r];
+    }
+    if (nvox > 0 && (!mean || F > 0) && grid == nullptr) return RC_ERR_NULL_POINTER;
+    if (mean && nvox > 0 && counts == nullptr) return RC_ERR_NULL_POINTER;
+    if (total > 0 && ids == nullptr) return RC_ERR_NULL_POINTER;
+    if (mean && total > 0 && F > 0 && features == nullptr) return RC_ERR_BAD_MODE;
+    if (!rc::aligned_to(ids, 4) || !rc::aligned_to(grid, 4) || !rc::aligned_to(counts, 4) || !rc::aligned_to(features, 4))
+        return RC_ERR_BAD_ALIGNMENT;
+    if (mean) {
+        const bool a16 = rc::aligned_to(features, 16) && rc::aligned_to(grid, 16);
+        const bool a8 = rc::aligned_to(features, 8) && rc::aligned_to(grid, 8);
+        if ((F & 3) == 0 && !a16) return RC_ERR_BAD_ALIGNMENT;
+        if ((F & 3) != 0 && (F & 1) == 0 && !a8) return RC_ERR_BAD_ALIGNMENT;
+    }
+    rc::DeviceScope scope(device);
+    if (scope.status() != RC_OK) return scope.status();
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const long long cells = mean ? nvox * F : nvox;
+    if (flags & RC_VOXEL_ZERO_INIT) {
+        if (cells > 0) RC_CUDA_TRY(cudaMemsetAsync(grid, 0, static_cast<size_t>(cells) * 4, st));
+        if (mean && nvox > 0) RC_CUDA_TRY(cudaMemsetAsync(counts, 0, static_cast<size_t>(nvox) * 4, st));
+    }
+    if (total > 0 && nvox > 0 && !(mean && F == 0)) {
+        const uintptr_t cell = mean ? static_cast<uintptr_t>(F) * 4u : 4u;
+        void* grid0 = reinterpret_cast<void*>(reinterpret_cast<uintptr_t>(grid) - static_cast<uintptr_t>(id_begin) * cell);
+        int* counts0 = mean ? reinterpret_cast<int*>(reinterpret_cast<uintptr_t>(counts) - static_cast<uintptr_t>(id_begin) * 4u)
+                            : nullptr;
+        const bool vec4 = mean && F == 4;
+        const long long cap = 16ll * rc::sm_count(device);
+        for (int ps = 0; ps < n_passes; ++ps) {
+            RunTable rt{};
+            auto flush = [&]() {
+                if (rt.n == 0) return;
+                long long nb = rt.first_block[rt.n];
+                if (nb > cap) nb = cap;
+                const unsigned int blocks = static_cast<unsigned int>(nb);
+                const int lo = static_cast<int>(id_begin);
+                const unsigned int span = static_cast<unsigned int>(nvox);
+                if (mode == RC_VOXEL_MEAN) launch_scatter_runs<kMean>(blocks, st, ids, features, grid0, counts0, F, vec4, rt, lo, span);
+                else if (mode == RC_VOXEL_COUNT) launch_scatter_runs<kCount>(blocks, st, ids, features, grid0, counts0, F, false, rt, lo, span);
+                else launch_scatter_runs<kOccupancy>(blocks, st, ids, features, grid0, counts0, F, false, rt, lo, span);
+                rt = RunTable{};
+            };
+            for (int r = 0; r < n_runs; ++r) {
+                if (run_pass[r] != ps || run_count[r] == 0) continue;
+                rt.begin[rt.n] = run_begin[r];
+                rt.count[rt.n] = run_count[r];
+                rt.first_block[rt.n + 1] = rt.first_block[rt.n] + (run_count[r] + kChunk - 1) / kChunk;
+                if (++rt.n == kMaxParts) flush();
+            }
+            flush();
         }
     }
     const int rc_launch = rc::check_launch();

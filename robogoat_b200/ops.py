@@ -13,7 +13,7 @@ kernels run on torch's current stream of the tensors' device.  There is no CPU p
 from __future__ import annotations
 
 import ctypes
-from typing import List, Optional, Sequence
+from typing import List, Optional, Sequence, Tuple
 
 import torch
 
@@ -264,41 +264,131 @@ def voxel_normalize_cuda(grid: torch.Tensor, counts: torch.Tensor, voxel_begin: 
     _lib.check(rc, "voxel_normalize")
 
 
-def voxel_partition_cuda(points: torch.Tensor, features: Optional[torch.Tensor], grid_min: Sequence[float],
-                         voxel_size: float, grid_size: Sequence[int], n_parts: int):
-    """Stable partition of a cloud's in-grid points by the part that owns their voxel.
-
-    The grid's voxel ids are cut into ``n_parts`` contiguous ranges of ceil(V / n_parts).  Returns
-    ``(ids [N] int32, features [N,F] or None, part_counts [n_parts] int64)``, all on the device: the first
-    ``part_counts.sum()`` entries hold part 0's points, then part 1's, ... in input order; the rest is
-    unwritten.  Reading ``part_counts`` on the host is the caller's synchronisation point.
-    """
+def _partition_inputs(points, features):
     _check(points.is_cuda and points.dim() == 2 and points.shape[1] == 3, "points must be a CUDA tensor [N, 3]")
-    _check(1 <= int(n_parts) <= 64, "n_parts must be in [1, 64]")
     dev = points.device
     N = points.shape[0]
     pts = points.to(torch.float32).contiguous()
     feats = None
-    F = 0
     if features is not None:
         _check(features.is_cuda and features.dim() == 2 and features.shape[0] == N, "features must be a CUDA tensor [N, F]")
         _check(features.device == dev, "all tensors must be on the same CUDA device")
         feats = features.to(torch.float32).contiguous()
-        F = feats.shape[1]
+    return pts, feats
+
+
+def _check_parts(n_groups: int, parts_per_group: int) -> int:
+    _check(n_groups >= 1 and parts_per_group >= 1 and n_groups * parts_per_group <= 64,
+           "n_groups * parts_per_group must be in [1, 64]")
+    return n_groups * parts_per_group
+
+
+def voxel_partition_cuda(points: torch.Tensor, features: Optional[torch.Tensor], grid_min: Sequence[float],
+                         voxel_size: float, grid_size: Sequence[int], n_groups: int, parts_per_group: int = 1):
+    """Stable partition of a cloud's in-grid points by the part that owns their voxel.
+
+    The voxel ids are cut into ``n_groups`` contiguous ranges of ceil(V / n_groups), each into
+    ``parts_per_group`` sub-ranges; part = group * parts_per_group + sub.  Returns
+    ``(ids [N] int32, features [N,F] or None, part_counts [parts] int64)``, all on the device: the first
+    ``part_counts.sum()`` entries hold part 0's points, then part 1's, ... in input order; the rest is
+    unwritten.  Reading ``part_counts`` on the host is the caller's synchronisation point.
+    """
+    P = _check_parts(int(n_groups), int(parts_per_group))
+    pts, feats = _partition_inputs(points, features)
+    dev, N = pts.device, pts.shape[0]
+    F = feats.shape[1] if feats is not None else 0
     L = _lib.load()
     ids = torch.empty(N, dtype=torch.int32, device=dev)
     feats_out = torch.empty((N, F), dtype=torch.float32, device=dev) if feats is not None else None
-    part_counts = torch.empty(int(n_parts), dtype=torch.int64, device=dev)
-    need = int(L.rc_voxel_partition_scratch_bytes(N, int(n_parts), dev.index))
+    part_counts = torch.empty(P, dtype=torch.int64, device=dev)
+    need = int(L.rc_voxel_partition_scratch_bytes(N, P, dev.index))
     scratch = torch.empty(max(need, 16), dtype=torch.uint8, device=dev)
     gmin = (ctypes.c_float * 3)(*[float(v) for v in grid_min])
     gsz = (ctypes.c_int32 * 3)(*[int(v) for v in grid_size])
     rc = L.rc_voxel_partition(pts.data_ptr(), feats.data_ptr() if feats is not None else None, N, F, gmin,
-                              float(voxel_size), gsz, int(n_parts), ids.data_ptr(),
+                              float(voxel_size), gsz, int(n_groups), int(parts_per_group), ids.data_ptr(),
                               feats_out.data_ptr() if feats_out is not None else None, part_counts.data_ptr(),
                               scratch.data_ptr(), need, dev.index, _stream_ptr(dev))
     _lib.check(rc, "voxel_partition")
     return ids, feats_out, part_counts
+
+
+def voxel_partition_count_cuda(points: torch.Tensor, grid_min: Sequence[float], voxel_size: float,
+                               grid_size: Sequence[int], n_groups: int, parts_per_group: int = 1):
+    """First half of the partition: ``(part_counts [parts] int64 on the device, scratch)``.  Hand ``scratch``
+    unchanged to ``voxel_partition_move_cuda`` for the same points."""
+    P = _check_parts(int(n_groups), int(parts_per_group))
+    pts, _ = _partition_inputs(points, None)
+    dev, N = pts.device, pts.shape[0]
+    L = _lib.load()
+    part_counts = torch.empty(P, dtype=torch.int64, device=dev)
+    need = int(L.rc_voxel_partition_scratch_bytes(N, P, dev.index))
+    scratch = torch.empty(max(need, 16), dtype=torch.uint8, device=dev)
+    gmin = (ctypes.c_float * 3)(*[float(v) for v in grid_min])
+    gsz = (ctypes.c_int32 * 3)(*[int(v) for v in grid_size])
+    rc = L.rc_voxel_partition_count(pts.data_ptr(), N, gmin, float(voxel_size), gsz, int(n_groups), int(parts_per_group),
+                                    part_counts.data_ptr(), scratch.data_ptr(), need, dev.index, _stream_ptr(dev))
+    _lib.check(rc, "voxel_partition_count")
+    return part_counts, scratch
+
+
+def voxel_partition_move_cuda(points: torch.Tensor, features: Optional[torch.Tensor], grid_min: Sequence[float],
+                              voxel_size: float, grid_size: Sequence[int], n_groups: int, parts_per_group: int,
+                              dest_ids: Sequence[int], dest_features: Optional[Sequence[int]], dest_start: Sequence[int],
+                              scratch: torch.Tensor) -> None:
+    """Second half: writes part p's voxel ids to the device address ``dest_ids[p]`` (and feature rows to
+    ``dest_features[p]``) from slot ``dest_start[p]`` on.  The addresses may belong to peer GPUs' buffers
+    (``PeerBuffer``); the caller guarantees room for the counted points."""
+    P = _check_parts(int(n_groups), int(parts_per_group))
+    _check(len(dest_ids) == P and len(dest_start) == P, "one destination and start slot per part")
+    pts, feats = _partition_inputs(points, features if dest_features is not None else None)
+    dev, N = pts.device, pts.shape[0]
+    F = feats.shape[1] if feats is not None else 0
+    L = _lib.load()
+    VP = ctypes.c_void_p * P
+    ids_arr = VP(*[int(a) for a in dest_ids])
+    feats_arr = VP(*[int(a) for a in dest_features]) if feats is not None else None
+    start_arr = (ctypes.c_int64 * P)(*[int(v) for v in dest_start])
+    gmin = (ctypes.c_float * 3)(*[float(v) for v in grid_min])
+    gsz = (ctypes.c_int32 * 3)(*[int(v) for v in grid_size])
+    rc = L.rc_voxel_partition_move(pts.data_ptr(), feats.data_ptr() if feats is not None else None, N, F, gmin,
+                                   float(voxel_size), gsz, int(n_groups), int(parts_per_group), ids_arr, feats_arr,
+                                   start_arr, None, scratch.data_ptr(), scratch.numel(), dev.index, _stream_ptr(dev))
+    _lib.check(rc, "voxel_partition_move")
+
+
+def voxel_scatter_runs_cuda(ids_ptr: int, features_ptr: Optional[int], device: torch.device, feature_width: int,
+                            id_begin: int, id_end: int, runs: Sequence[Tuple[int, int, int]], n_passes: int, mode: str,
+                            *, normalize: bool = True) -> List[torch.Tensor]:
+    """Accumulate records that arrive as runs into the slab of voxels [id_begin, id_end).
+
+    ``ids_ptr`` / ``features_ptr`` are device addresses of the int32 id list and the fp32 [., F] feature rows
+    (a torch tensor's ``data_ptr()`` or a ``PeerBuffer``); ``runs`` lists ``(first record, records, pass)``.
+    The runs of pass 0 are accumulated first, then pass 1, ...  Returns ``[grid]`` or ``[grid, counts]`` as
+    ``voxel_scatter_ids_cuda``.
+    """
+    if mode not in ("count", "occupancy", "mean"):
+        raise RuntimeError(f"Invalid mode: {mode}. The run scatter supports 'count', 'occupancy' and 'mean'")
+    nvox = int(id_end) - int(id_begin)
+    _check(nvox >= 0 and id_begin >= 0, "bad voxel range")
+    F = int(feature_width) if mode == "mean" else 0
+    counts = None
+    if mode == "mean":
+        grid = torch.empty((nvox, F), dtype=torch.float32, device=device)
+        counts = torch.empty(nvox, dtype=torch.int32, device=device)
+    else:
+        grid = torch.empty(nvox, dtype=torch.int32, device=device)
+    n = len(runs)
+    rb = (ctypes.c_int64 * max(n, 1))(*[int(r[0]) for r in runs])
+    rcnt = (ctypes.c_int64 * max(n, 1))(*[int(r[1]) for r in runs])
+    rp = (ctypes.c_int32 * max(n, 1))(*[int(r[2]) for r in runs])
+    flags = _lib.VOXEL_ZERO_INIT | (0 if normalize else _lib.VOXEL_NO_NORMALIZE)
+    rc = _lib.load().rc_voxel_scatter_runs(ids_ptr or None, features_ptr or None, grid.data_ptr() if grid.numel() else None,
+                                           counts.data_ptr() if counts is not None and nvox else None, F, int(id_begin),
+                                           int(id_end), rb, rcnt, rp, n, int(n_passes), _MODES[mode], flags, device.index,
+                                           _stream_ptr(device))
+    _lib.check(rc, "voxel_scatter_runs")
+    return [grid, counts] if mode == "mean" else [grid]
 
 
 def voxel_scatter_ids_cuda(ids: torch.Tensor, features: Optional[torch.Tensor], id_begin: int, id_end: int,

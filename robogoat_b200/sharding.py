@@ -189,12 +189,14 @@ def voxelize_sharded(points_local: torch.Tensor, features_local: Optional[torch.
 
 # ----------------------------------------------------------------------------- point exchange (all-to-all)
 
-def exchange_buckets(buckets: Sequence[torch.Tensor], send_counts: Sequence[int], group=None):
+def exchange_buckets(buckets: Sequence[torch.Tensor], send_counts: Sequence[int], group=None,
+                     recv_counts: Optional[Sequence[int]] = None):
     """All-to-all of per-destination buckets.
 
     Every tensor in ``buckets`` holds, along dimension 0, ``send_counts[0]`` rows for rank 0, then
     ``send_counts[1]`` rows for rank 1, ...  Returns ``(received, recv_counts)``: for each input tensor the
-    rows this rank received (grouped by source rank), and how many came from each rank.
+    rows this rank received (grouped by source rank), and how many came from each rank.  ``recv_counts`` may be
+    passed when the caller already knows them (it saves the small all-to-all that asks).
     """
     rank, ws = world(group)
     send_counts = [int(c) for c in send_counts]
@@ -202,11 +204,13 @@ def exchange_buckets(buckets: Sequence[torch.Tensor], send_counts: Sequence[int]
         raise RuntimeError(f"{len(send_counts)} send counts for a group of {ws} ranks")
     if ws == 1:
         return [b[:send_counts[0]] for b in buckets], send_counts
-    dev = buckets[0].device
-    sc = torch.tensor(send_counts, dtype=torch.int64, device=dev)
-    rc = torch.empty_like(sc)
-    dist.all_to_all_single(rc, sc, group=group)
-    recv_counts = [int(c) for c in rc.tolist()]
+    if recv_counts is None:                                 # not known yet: ask the senders
+        dev = buckets[0].device
+        sc = torch.tensor(send_counts, dtype=torch.int64, device=dev)
+        rc = torch.empty_like(sc)
+        dist.all_to_all_single(rc, sc, group=group)
+        recv_counts = rc.tolist()
+    recv_counts = [int(c) for c in recv_counts]
     total_in, total_out = sum(recv_counts), sum(send_counts)
     received = []
     for b in buckets:
@@ -221,17 +225,101 @@ def slab_bounds(n_voxels: int, rank: int, world_size: int) -> Tuple[int, int]:
     return shard_bounds(n_voxels, rank, world_size)
 
 
+_RESIDENT_BYTES = 96 << 20      # accumulators of one scatter pass should stay L2-resident
+
+
+def sub_parts(n_voxels: int, feature_width: int, world_size: int, mode: str) -> int:
+    """How many sub-ranges each rank's slab is cut into so that one sub-range's accumulators fit in L2."""
+    if mode == "occupancy":
+        return 1
+    slab = (n_voxels + world_size - 1) // world_size
+    acc = slab * 4 * (1 + feature_width if mode == "mean" else 1)
+    return max(1, min(64 // world_size, (acc + _RESIDENT_BYTES - 1) // _RESIDENT_BYTES))
+
+
+def exchange_plan(counts: Sequence[Sequence[int]], rank: int, per_group: int) -> dict:
+    """Bookkeeping of the point exchange from the count matrix ``counts[s][p]`` = points rank ``s`` holds for
+    part ``p`` (part = owner * per_group + sub-range).  Returns for ``rank``:
+
+    ``send_counts[d]`` / ``recv_counts[s]``  records sent to rank d / received from rank s;
+    ``runs``         (first record, records, sub-range) of every run in this rank's receive buffer, which is
+                     laid out source rank by source rank, sub-ranges in order inside;
+    ``dest_start[p]`` first slot of this rank's part-p records in the owner's receive buffer;
+    ``totals[d]``    records rank d receives in all.
+    """
+    R, K = len(counts), int(per_group)
+    to_owner = [[sum(counts[s][d * K:(d + 1) * K]) for d in range(R)] for s in range(R)]
+    runs, off = [], 0
+    for s in range(R):
+        for k in range(K):
+            c = int(counts[s][rank * K + k])
+            runs.append((off, c, k))
+            off += c
+    dest_start = []
+    for d in range(R):
+        slot = sum(to_owner[s][d] for s in range(rank))
+        for k in range(K):
+            dest_start.append(slot)
+            slot += int(counts[rank][d * K + k])
+    return {"send_counts": to_owner[rank], "recv_counts": [to_owner[s][rank] for s in range(R)], "runs": runs,
+            "dest_start": dest_start, "totals": [sum(to_owner[s][d] for s in range(R)) for d in range(R)]}
+
+
+def _gather_counts(part_counts: torch.Tensor, group=None):
+    """Every rank's per-part counts as nested lists (the host synchronisation point of the exchange)."""
+    _, ws = world(group)
+    if ws == 1:
+        return [part_counts.tolist()]
+    allc = torch.empty((ws, part_counts.numel()), dtype=part_counts.dtype, device=part_counts.device)
+    dist.all_gather_into_tensor(allc, part_counts.contiguous(), group=group)
+    return allc.tolist()
+
+
+class PointExchange:
+    """Receive buffers for the direct form of the point exchange: every rank's partition kernel stores its
+    records straight into the owners' buffers over NVLink (no staging copy, no separate all-to-all).
+
+    ``capacity`` is the number of records this rank can receive per call; a call whose count matrix shows that
+    some rank would receive more falls back to the all-to-all form on every rank.  Construction and ``close``
+    are collective.
+    """
+
+    def __init__(self, capacity: int, feature_width: int, group=None):
+        from .peer import PeerBuffer
+        self.capacity = int(capacity)
+        self.feature_width = int(feature_width)
+        self.group = group
+        self.ids = PeerBuffer(max(16, 4 * self.capacity))
+        self.features = PeerBuffer(max(16, 4 * self.capacity * max(1, self.feature_width)))
+        self.ids.connect(group)
+        self.features.connect(group)
+        self._token = torch.zeros(1, dtype=torch.int32, device=self.ids.device)
+
+    def stream_barrier(self) -> None:
+        """Orders, on the current stream, everything the other ranks enqueued before their call of this
+        method before everything this rank enqueues after it."""
+        dist.all_reduce(self._token, group=self.group)
+
+    def close(self) -> None:
+        self.ids.close()
+        self.features.close()
+
+
 def voxelize_sharded_exchange(points_local: torch.Tensor, features_local: Optional[torch.Tensor] = None,
                               grid_min=(-10.0, -10.0, -10.0), voxel_size: float = 0.1, grid_size=(128, 128, 128),
-                              mode: str = "occupancy", group=None) -> torch.Tensor:
+                              mode: str = "occupancy", group=None, direct: Optional[PointExchange] = None) -> torch.Tensor:
     """Slab-sharded voxelisation by exchanging points instead of reducing grids.
 
-    Every rank buckets its points by the rank that owns their voxel (``slab_bounds``), the buckets travel in
-    one all-to-all of 4-byte voxel ids (+ 4·F bytes of features in mean mode), and each rank accumulates what
-    it received into its own slab only.  Returns the rank's slab, shaped [voxels] or [voxels, F] — the same
-    values ``voxelize_sharded_slab`` returns when the voxel count divides by the group size — without any rank
-    ever holding the dense grid.  Traffic per rank is (R-1)/R · N · (4 + 4F) bytes instead of (R-1)/R of the
-    dense grid, and the local accumulators are R times smaller.
+    Every rank buckets its points by the rank that owns their voxel (``slab_bounds``) and, inside an owner, by
+    L2-sized sub-range of its slab; the buckets travel as 4-byte voxel ids (+ 4*F bytes of features in mean mode)
+    and each rank accumulates what it received into its own slab, one sub-range at a time.  Returns the rank's
+    slab, shaped [voxels] or [voxels, F] - the same values ``voxelize_sharded_slab`` returns when the voxel count
+    divides by the group size - without any rank ever holding the dense grid.  Traffic per rank is
+    (R-1)/R * N * (4 + 4F) bytes instead of (R-1)/R of the dense grid.
+
+    Transport: one NCCL all-to-all per tensor by default; with ``direct`` (a ``PointExchange``) the partition
+    kernel stores into the owners' receive buffers itself and only two small collectives remain (the count
+    matrix, and a barrier between the stores and the owners' reads).
     """
     from . import ops
     rank, ws = world(group)
@@ -241,13 +329,26 @@ def voxelize_sharded_exchange(points_local: torch.Tensor, features_local: Option
     feats = features_local if mode == "mean" else None
     if mode == "mean" and feats is None:
         raise RuntimeError("features required for mean/max modes")
-    ids, fb, part_counts = ops.voxel_partition_cuda(points_local, feats, list(grid_min), float(voxel_size),
-                                                   list(grid_size), ws)
-    send_counts = part_counts.tolist()                       # the one host synchronisation of the path
-    buckets = [ids] if fb is None else [ids, fb]
-    received, _ = exchange_buckets(buckets, send_counts, group)
+    F = feats.shape[1] if feats is not None else 0
+    K = sub_parts(V, F, ws, mode)
+    geom = (list(grid_min), float(voxel_size), list(grid_size))
     a, b = slab_bounds(V, rank, ws)
-    width = fb.shape[1] if fb is not None else 0
-    res = ops.voxel_scatter_ids_cuda(received[0], received[1] if fb is not None else None, a, b, mode,
-                                     feature_width=width)
+    dev = points_local.device
+    if direct is not None and ws > 1 and (feats is None or F == direct.feature_width):
+        part_counts, scratch = ops.voxel_partition_count_cuda(points_local, *geom, ws, K)
+        plan = exchange_plan(_gather_counts(part_counts, group), rank, K)       # host sync; also orders this call
+        if max(plan["totals"]) <= direct.capacity:                               # after the owners' previous reads
+            dest_ids = [direct.ids.peers[p // K] for p in range(ws * K)]
+            dest_f = [direct.features.peers[p // K] for p in range(ws * K)] if feats is not None else None
+            ops.voxel_partition_move_cuda(points_local, feats, *geom, ws, K, dest_ids, dest_f, plan["dest_start"], scratch)
+            direct.stream_barrier()
+            res = ops.voxel_scatter_runs_cuda(direct.ids.ptr, direct.features.ptr if feats is not None else None, dev, F,
+                                              a, b, plan["runs"], K, mode)
+            return res[0]
+    ids, fb, part_counts = ops.voxel_partition_cuda(points_local, feats, *geom, ws, K)
+    plan = exchange_plan(_gather_counts(part_counts, group), rank, K)            # the host synchronisation of the path
+    buckets = [ids] if fb is None else [ids, fb]
+    received, _ = exchange_buckets(buckets, plan["send_counts"], group, recv_counts=plan["recv_counts"])
+    res = ops.voxel_scatter_runs_cuda(received[0].data_ptr(), received[1].data_ptr() if fb is not None else None, dev, F,
+                                      a, b, plan["runs"], K, mode)
     return res[0]

@@ -58,6 +58,23 @@ for mode in ("occupancy", "count", "mean"):                       # point exchan
         assert bool(((slab - full.reshape(V, 4)[a:b]).abs() <= tol.reshape(V, 4)[a:b]).all()), "exchange mean"
     else:
         assert torch.equal(slab, robocache.voxelize_pointcloud(pts, mode=mode, **kw).reshape(V)[a:b]), "exchange " + mode
+# direct form: the partition kernel stores into the owners' receive buffers (peer memory) itself; twice in a row, so
+# that the second call's stores meet buffers the owners have just read, then with a buffer that is too small (falls back)
+px = sharding.PointExchange(capacity=pts.shape[0], feature_width=4)
+for rep in range(2):
+    for mode in ("occupancy", "count", "mean"):
+        slab = sharding.voxelize_sharded_exchange(pts[lo:hi], feats[lo:hi] if mode == "mean" else None, mode=mode, direct=px, **kw)
+        a, b = sharding.slab_bounds(V, rank, ws)
+        if mode == "mean":
+            assert bool(((slab - full.reshape(V, 4)[a:b]).abs() <= tol.reshape(V, 4)[a:b]).all()), "direct mean"
+        else:
+            assert torch.equal(slab, robocache.voxelize_pointcloud(pts, mode=mode, **kw).reshape(V)[a:b]), "direct " + mode
+px.close()
+small = sharding.PointExchange(capacity=10, feature_width=4)
+slab = sharding.voxelize_sharded_exchange(pts[lo:hi], None, mode="count", direct=small, **kw)
+a, b = sharding.slab_bounds(V, rank, ws)
+assert torch.equal(slab, robocache.voxelize_pointcloud(pts, mode="count", **kw).reshape(V)[a:b]), "fallback"
+small.close()
 torch.cuda.synchronize()
 dist.barrier()
 dist.destroy_process_group()

@@ -147,6 +147,32 @@ def test_point_exchange_delivers_every_point_to_the_owner_of_its_voxel():
     assert torch.equal(one[0], torch.arange(7)) and counts == [7]
 
 
+def test_exchange_plan_bookkeeping():
+    """Count matrix -> send/receive sizes, the layout of the receive buffer and every sender's first slot in it."""
+    R, K = 3, 2
+    g = torch.Generator().manual_seed(4)
+    C = torch.randint(0, 50, (R, R * K), generator=g).tolist()
+    plans = [sharding.exchange_plan(C, r, K) for r in range(R)]
+    for d in range(R):
+        assert plans[d]["recv_counts"] == [plans[s]["send_counts"][d] for s in range(R)]
+        assert sum(c for _, c, _ in plans[d]["runs"]) == plans[d]["totals"][d] == sum(plans[d]["recv_counts"])
+        # replay the writes of every sender into owner d's buffer: every slot is hit exactly once, by the run the owner expects
+        slots = [None] * plans[d]["totals"][d]
+        for s in range(R):
+            for k in range(K):
+                first = plans[s]["dest_start"][d * K + k]
+                for j in range(C[s][d * K + k]):
+                    assert slots[first + j] is None
+                    slots[first + j] = (s, k)
+        assert all(x is not None for x in slots)
+        for (off, cnt, k), (s, kk) in zip(plans[d]["runs"], [(s, k) for s in range(R) for k in range(K)]):
+            assert k == kk and all(slots[off + j] == (s, k) for j in range(cnt))
+    assert all(p["totals"] == plans[0]["totals"] for p in plans)
+    assert sharding.sub_parts(512 ** 3, 4, 8, "mean") == 4 and sharding.sub_parts(512 ** 3, 4, 2, "mean") == 14
+    assert sharding.sub_parts(128 ** 3, 0, 2, "count") == 1 and sharding.sub_parts(512 ** 3, 0, 64, "count") == 1
+    assert sharding.sub_parts(10 ** 9, 16, 2, "mean") == 32 and sharding.sub_parts(512 ** 3, 4, 8, "occupancy") == 1
+
+
 def _lonely_rank(port, q):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)

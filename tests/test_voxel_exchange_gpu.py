@@ -38,6 +38,78 @@ def test_partition_is_the_stable_sort_by_owner(N, parts, cuda_lib):
     assert torch.equal(fb[:n].cpu(), feats[keep][order])
 
 
+def _owner(ids, V, groups, per_group):
+    slab = (V + groups - 1) // groups
+    sub = (slab + per_group - 1) // per_group
+    grp = ids // slab
+    return grp * per_group + (ids - grp * slab) // sub
+
+
+@pytest.mark.parametrize("groups,per_group", [(1, 7), (2, 3), (3, 5), (8, 4), (2, 32), (8, 8)])
+@pytest.mark.parametrize("N", [1000, 70_001])
+def test_two_level_partition_and_run_scatter(groups, per_group, N, cuda_lib):
+    """Sub-ranges inside every owner's slab: the partition is still the stable sort by part, and scattering the
+    runs of every owner, one pass per sub-range, rebuilds that owner's slab."""
+    import robocache
+    kw = dict(grid_min=[-2.0, -2.0, -2.0], voxel_size=0.25, grid_size=[16, 15, 13])
+    V = 16 * 15 * 13
+    pts, feats = _cloud(N, 31 * groups + per_group)
+    p, f = pts.to(DEV), feats.to(DEV)
+    ids, fb, pc = ops.voxel_partition_cuda(p, f, kw["grid_min"], kw["voxel_size"], kw["grid_size"], groups, per_group)
+    exp_ids = oracle.voxel_ids(pts, **kw)
+    keep = exp_ids >= 0
+    owner = _owner(exp_ids[keep], V, groups, per_group)
+    order = torch.sort(owner, stable=True).indices
+    n = int(keep.sum())
+    counts = pc.cpu().tolist()
+    assert counts == torch.bincount(owner, minlength=groups * per_group).tolist()
+    assert torch.equal(ids[:n].cpu().long(), exp_ids[keep][order])
+    assert torch.equal(fb[:n].cpu(), feats[keep][order])
+    starts = [0]
+    for c in counts:
+        starts.append(starts[-1] + c)
+    full_cnt = robocache.voxelize_pointcloud(p, mode="count", **kw).reshape(V)
+    exp, ecnt, sabs = oracle.voxelize_pointcloud(pts, feats, mode="mean", return_aux=True, **kw)
+    tol = oracle.mean_tolerance(ecnt, sabs, exp).reshape(V, 4)
+    for g in range(groups):
+        a, b = sharding.slab_bounds(V, g, groups)
+        runs = [(starts[g * per_group + k], counts[g * per_group + k], k) for k in range(per_group)]
+        got = ops.voxel_scatter_runs_cuda(ids.data_ptr(), None, p.device, 0, a, b, runs, per_group, "count")[0]
+        assert torch.equal(got, full_cnt[a:b])
+        got = ops.voxel_scatter_runs_cuda(ids.data_ptr(), None, p.device, 0, a, b, runs, per_group, "occupancy")[0]
+        assert torch.equal(got, (full_cnt[a:b] > 0).int())
+        grid, cnt = ops.voxel_scatter_runs_cuda(ids.data_ptr(), fb.data_ptr(), p.device, 4, a, b, runs, per_group, "mean")
+        assert torch.equal(cnt, full_cnt[a:b])
+        assert bool(((grid.cpu() - exp.reshape(V, 4)[a:b]).abs() <= tol[a:b]).all())
+
+
+def test_split_count_and_move_into_separate_destinations(cuda_lib):
+    """The two halves called separately, every part into a buffer of its own at a chosen slot - the form the
+    direct exchange uses with peer buffers."""
+    kw = dict(grid_min=[-2.0, -2.0, -2.0], voxel_size=0.25, grid_size=[16, 16, 16])
+    V = 16 ** 3
+    pts, feats = _cloud(50_000, 5)
+    p, f = pts.to(DEV), feats.to(DEV)
+    groups, per_group = 2, 3
+    pc, scratch = ops.voxel_partition_count_cuda(p, kw["grid_min"], kw["voxel_size"], kw["grid_size"], groups, per_group)
+    counts = pc.tolist()
+    exp_ids = oracle.voxel_ids(pts, **kw)
+    keep = exp_ids >= 0
+    owner = _owner(exp_ids[keep], V, groups, per_group)
+    assert counts == torch.bincount(owner, minlength=6).tolist()
+    pad = 5
+    bufs_i = [torch.full((c + 2 * pad,), -7, dtype=torch.int32, device=DEV) for c in counts]
+    bufs_f = [torch.full((c + 2 * pad, 4), -7.0, device=DEV) for c in counts]
+    ops.voxel_partition_move_cuda(p, f, kw["grid_min"], kw["voxel_size"], kw["grid_size"], groups, per_group,
+                                  [t.data_ptr() for t in bufs_i], [t.data_ptr() for t in bufs_f], [pad] * 6, scratch)
+    for part in range(6):
+        sel = owner == part
+        assert torch.equal(bufs_i[part][pad:pad + counts[part]].cpu().long(), exp_ids[keep][sel])
+        assert torch.equal(bufs_f[part][pad:pad + counts[part]].cpu(), feats[keep][sel])
+        assert bool((bufs_i[part][:pad] == -7).all()) and bool((bufs_i[part][pad + counts[part]:] == -7).all())   # guard bands
+        assert bool((bufs_f[part][:pad] == -7).all()) and bool((bufs_f[part][pad + counts[part]:] == -7).all())
+
+
 @pytest.mark.parametrize("F", [1, 2, 3, 4, 8])
 def test_partition_moves_feature_rows_of_any_width(F, cuda_lib):
     kw = dict(grid_min=[-2.0, -2.0, -2.0], voxel_size=0.5, grid_size=[8, 8, 8])
