@@ -547,41 +547,46 @@ def run_extras(L, dev, local, rank, world, peak):
             "note": "stable partition by owner slab and sub-range + NCCL all-to-all of 20-byte (id, features) records + scatter "
                     "into the rank's own 1/N slab, one L2-sized sub-range per pass; no rank holds a dense grid"}
         # direct form: the partition kernel stores into the owners' buffers over NVLink
-        px = sharding.PointExchange(capacity=int(1.25 * N), feature_width=4)
-        fn = lambda: sharding.voxelize_sharded_exchange(pts, feats, mode="mean", direct=px, **kw)
-        for _ in range(2):
-            r = fn(); del r
-        barrier(world)
-        e0.record()
-        for _ in range(5):
-            r = fn(); del r
-        e1.record(); torch.cuda.synchronize()
-        ms = max_over_ranks(e0.elapsed_time(e1) / 5, world, dev)
-        barrier(world)
-        ev[0].record()
-        pc, scratch = ops.voxel_partition_count_cuda(pts, kw["grid_min"], kw["voxel_size"], kw["grid_size"], world, K)
-        plan = sharding.exchange_plan(sharding._gather_counts(pc), rank, K)
-        ev[1].record()
-        fits = max(plan["totals"]) <= px.capacity
-        if fits:
-            ops.voxel_partition_move_cuda(pts, feats, kw["grid_min"], kw["voxel_size"], kw["grid_size"], world, K,
-                                          [px.ids.peers[p // K] for p in range(world * K)],
-                                          [px.features.peers[p // K] for p in range(world * K)], plan["dest_start"], scratch)
-            px.stream_barrier()
-        ev[2].record()
-        if fits:
-            r = ops.voxel_scatter_runs_cuda(px.ids.ptr, px.features.ptr, dev, 4, lo_v, hi_v, plan["runs"], K, "mean")
-            del r
-        ev[3].record(); torch.cuda.synchronize()
-        stages = [max_over_ranks(ev[i].elapsed_time(ev[i + 1]), world, dev) for i in range(3)]
-        sent_remote = sum(c for d, c in enumerate(plan["send_counts"]) if d != rank) * 20
-        ex["voxel_mean_sharded_point_exchange_direct"] = {
-            "ms": ms, "Gpts/s_total": N * world / (ms * 1e-3) / 1e9, "fits_receive_buffers": fits,
-            "stage_ms": {"count_and_count_matrix": stages[0], "move_over_nvlink_and_barrier": stages[1], "scatter_normalise": stages[2]},
-            "nvlink_GB/s_out_per_gpu_during_move": sent_remote / (stages[1] * 1e-3) / 1e9 if fits else None,
-            "note": "same, but the partition kernel stores its sorted chunks straight into the owners' receive buffers "
-                    "(peer memory over NVLink); collectives left: the count matrix and one barrier"}
-        px.close()
+        try:
+            px = sharding.PointExchange(capacity=int(1.25 * N), feature_width=4)
+        except RuntimeError as e:       # raised on every rank alike
+            px = None
+            ex["voxel_mean_sharded_point_exchange_direct"] = {"unavailable": str(e)[:200]}
+        if px is not None:
+            fn = lambda: sharding.voxelize_sharded_exchange(pts, feats, mode="mean", direct=px, **kw)
+            for _ in range(2):
+                r = fn(); del r
+            barrier(world)
+            e0.record()
+            for _ in range(5):
+                r = fn(); del r
+            e1.record(); torch.cuda.synchronize()
+            ms = max_over_ranks(e0.elapsed_time(e1) / 5, world, dev)
+            barrier(world)
+            ev[0].record()
+            pc, scratch = ops.voxel_partition_count_cuda(pts, kw["grid_min"], kw["voxel_size"], kw["grid_size"], world, K)
+            plan = sharding.exchange_plan(sharding._gather_counts(pc), rank, K)
+            ev[1].record()
+            fits = max(plan["totals"]) <= px.capacity
+            if fits:
+                ops.voxel_partition_move_cuda(pts, feats, kw["grid_min"], kw["voxel_size"], kw["grid_size"], world, K,
+                                              [px.ids.peers[p // K] for p in range(world * K)],
+                                              [px.features.peers[p // K] for p in range(world * K)], plan["dest_start"], scratch)
+                px.stream_barrier()
+            ev[2].record()
+            if fits:
+                r = ops.voxel_scatter_runs_cuda(px.ids.ptr, px.features.ptr, dev, 4, lo_v, hi_v, plan["runs"], K, "mean")
+                del r
+            ev[3].record(); torch.cuda.synchronize()
+            stages = [max_over_ranks(ev[i].elapsed_time(ev[i + 1]), world, dev) for i in range(3)]
+            sent_remote = sum(c for d, c in enumerate(plan["send_counts"]) if d != rank) * 20
+            ex["voxel_mean_sharded_point_exchange_direct"] = {
+                "ms": ms, "Gpts/s_total": N * world / (ms * 1e-3) / 1e9, "fits_receive_buffers": fits,
+                "stage_ms": {"count_and_count_matrix": stages[0], "move_over_nvlink_and_barrier": stages[1], "scatter_normalise": stages[2]},
+                "nvlink_GB/s_out_per_gpu_during_move": sent_remote / (stages[1] * 1e-3) / 1e9 if fits else None,
+                "note": "same, but the partition kernel stores its sorted chunks straight into the owners' receive buffers "
+                        "(peer memory over NVLink); collectives left: the count matrix and one barrier"}
+            px.close()
     else:
         # the two kernels of the point exchange on one GPU: partition for 8 owners, then one owner's bucket into its slab
         ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]

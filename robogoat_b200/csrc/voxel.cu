@@ -497,8 +497,8 @@ void launch_bin(bool agg, bool overlap_prev, unsigned int blocks, cudaStream_t s
 // A stable counting partition in three launches.  Every CTA owns a contiguous run of 1024-point
 // chunks.  Launch 1 (MOVE = false) counts the in-grid points per CTA and part; launch 2 turns each
 // part's column of that table into exclusive prefixes over the CTAs (one CTA per part); launch 3
-// (MOVE = true) walks the same chunks again, recomputes the voxel ids (cheaper than keeping them:
-// 12 bytes re-read against 4 written + 4 read), sorts each chunk by part in shared memory and writes
+// (MOVE = true) walks the same chunks again - the count pass leaves every point's voxel id in the
+// scratch, so the coordinates are not read twice -, sorts each chunk by part in shared memory and writes
 // the sorted chunk out, so that every part receives runs of consecutive records: full-width stores
 // whether the destination is local memory or a peer's.  Ranks inside a warp come from
 // __match_any_sync and warps are prefixed in order, so input order is kept inside a part and the
@@ -522,34 +522,49 @@ struct PartDest {                 // where the points of each part go (move pass
     long long start[kMaxParts];   // first slot of this call's points in that buffer
 };
 
-// n / d for quotients up to a few hundred: float estimate, then one correction step either way
-__device__ __forceinline__ unsigned int small_quotient(unsigned int n, unsigned int d, float inv) {
+// n / d and n % d for quotients up to a few hundred and n < 2^31: float estimate of the quotient, then
+// one correction step either way on the 32-bit remainder
+__device__ __forceinline__ unsigned int small_divmod(unsigned int n, unsigned int d, float inv, unsigned int* rem) {
     unsigned int q = static_cast<unsigned int>(__uint2float_rz(n) * inv);
-    if (static_cast<unsigned long long>(q) * d > n) --q;
-    else if (static_cast<unsigned long long>(q + 1) * d <= n) ++q;
+    int r = static_cast<int>(n - q * d);
+    if (r < 0) { --q; r += static_cast<int>(d); }
+    else if (r >= static_cast<int>(d)) { ++q; r -= static_cast<int>(d); }
+    *rem = static_cast<unsigned int>(r);
     return q;
 }
 __device__ __forceinline__ int part_of(int id, const PartRule& r) {
-    const unsigned int u = static_cast<unsigned int>(id);
-    const unsigned int grp = small_quotient(u, r.slab, r.inv_slab);
-    const unsigned int k = small_quotient(u - grp * r.slab, r.sub, r.inv_sub);
+    unsigned int rem, rem2;
+    const unsigned int grp = small_divmod(static_cast<unsigned int>(id), r.slab, r.inv_slab, &rem);
+    const unsigned int k = small_divmod(rem, r.sub, r.inv_sub, &rem2);
     return static_cast<int>(grp) * r.per_group + static_cast<int>(k);
 }
 
+// voxel_id for grids of fewer than 2^31 voxels: the same float arithmetic, 32-bit index arithmetic
+__device__ __forceinline__ int voxel_id32(float x, float y, float z, const VoxelGeom& g) {
+    const float fx = floorf(__fdiv_rn(__fsub_rn(x, g.minx), g.vs));
+    const float fy = floorf(__fdiv_rn(__fsub_rn(y, g.miny), g.vs));
+    const float fz = floorf(__fdiv_rn(__fsub_rn(z, g.minz), g.vs));
+    const bool in = (fx >= 0.0f) && (fx < g.fgx) && (fy >= 0.0f) && (fy < g.fgy) && (fz >= 0.0f) && (fz < g.fgz);
+    if (!in) return -1;
+    return (static_cast<int>(fz) * g.gy + static_cast<int>(fy)) * g.gx + static_cast<int>(fx);
+}
+
 template <bool MOVE>
-__global__ void __launch_bounds__(kThreads, 4)
+__global__ void __launch_bounds__(kThreads, 5)
 voxel_part_kernel(const float* __restrict__ pts, const float* __restrict__ feats, long long N, int F, VoxelGeom g,
                   bool pts_aligned, bool vec4, PartRule rule, long long chunks_per_cta, int* __restrict__ table,
-                  const long long* __restrict__ part_counts, const __grid_constant__ PartDest dest) {
-    __shared__ __align__(16) float s_xyz[kThreads / 32][kPointsPerWarp * 3];
-    __shared__ int s_wcnt[kThreads / 32][kMaxParts];   // count: per-warp totals; move: this chunk's per-warp counts, then prefixes
-    __shared__ long long s_cur[kMaxParts];             // move: next slot of each part in its destination
-    __shared__ int* s_dst_ids[kMaxParts];
-    __shared__ float* s_dst_feats[kMaxParts];
-    __shared__ int s_lstart[kMaxParts + 1];            // move: start of each part's run in the sorted chunk
-    __shared__ int s_sid[MOVE ? kChunk : 1];
-    __shared__ unsigned short s_ssrc[MOVE ? kChunk : 1];
-    __shared__ unsigned char s_spart[MOVE ? kChunk : 1];
+                  int* __restrict__ ids_tmp, const long long* __restrict__ part_counts,
+                  const __grid_constant__ PartDest dest) {
+    __shared__ __align__(16) float s_xyz[MOVE ? 1 : kThreads / 32][MOVE ? 4 : kPointsPerWarp * 3];
+    // count pass: per-warp totals.  move pass: this chunk's per-warp counts, turned by warp 0 into the
+    // first slot of every (warp, part) in the sorted chunk
+    __shared__ int s_wcnt[kThreads / 32][kMaxParts];
+    __shared__ long long s_cur[MOVE ? kMaxParts : 1];        // next slot of each part in its destination
+    __shared__ int* s_adj_ids[MOVE ? kMaxParts : 1];         // destination of sorted slot j of part p is s_adj_*[p] + j
+    __shared__ float* s_adj_feats[MOVE ? kMaxParts : 1];
+    __shared__ int s_total;
+    __shared__ int s_sid[MOVE ? kChunk : 1];                 // the chunk's voxel ids, sorted by part
+    __shared__ unsigned short s_meta[MOVE ? kChunk : 1];     // (index in chunk << 6) | part
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
     const unsigned int lt_mask = (1u << lane) - 1u;
@@ -566,8 +581,6 @@ voxel_part_kernel(const float* __restrict__ pts, const float* __restrict__ feats
                 start = dest.start[p];
             }
             s_cur[p] = start + table[static_cast<long long>(blockIdx.x) * P + p];
-            s_dst_ids[p] = dest.ids[p];
-            s_dst_feats[p] = dest.feats[p];
         }
     }
     __syncthreads();
@@ -575,111 +588,167 @@ voxel_part_kernel(const float* __restrict__ pts, const float* __restrict__ feats
     const long long c0 = static_cast<long long>(blockIdx.x) * chunks_per_cta;
     const long long c1 = (c0 + chunks_per_cta < nchunks) ? c0 + chunks_per_cta : nchunks;
     float4 ahead[3];
+    int ids_ahead[kPointsPerLane];
     {
         const long long tbase = c0 * kChunk + warp * kPointsPerWarp;
-        if (pts_aligned && c0 < c1 && tbase + kPointsPerWarp <= N) tile_issue(pts, tbase, lane, ahead);
+        if (MOVE) {
+#pragma unroll
+            for (int i = 0; i < kPointsPerLane; ++i) {
+                const long long pi = tbase + i * 32 + lane;
+                ids_ahead[i] = (c0 < c1 && pi < N) ? __ldcs(ids_tmp + pi) : -1;
+            }
+        } else if (pts_aligned && c0 < c1 && tbase + kPointsPerWarp <= N) {
+            tile_issue(pts, tbase, lane, ahead);
+        }
     }
     for (long long chunk = c0; chunk < c1; ++chunk) {
         const long long cbase = chunk * kChunk;
         const long long base = cbase + warp * kPointsPerWarp;
-        float x[kPointsPerLane], y[kPointsPerLane], z[kPointsPerLane];
-        if (pts_aligned && base + kPointsPerWarp <= N) {
-            float4 now[3] = {ahead[0], ahead[1], ahead[2]};
-            const long long nbase = base + kChunk;
-            if (chunk + 1 < c1 && nbase + kPointsPerWarp <= N) tile_issue(pts, nbase, lane, ahead);
-            tile_unpack(now, s_xyz[warp], lane, x, y, z);
-        } else {
-            tile_load_slow(pts, base, N, lane, x, y, z);
-        }
         int id[kPointsPerLane], part[kPointsPerLane], rank[kPointsPerLane];
+        if (MOVE) {
+            // the voxel ids were left behind by the count pass; fetch the next chunk's while this one is sorted
 #pragma unroll
-        for (int i = 0; i < kPointsPerLane; ++i) {
-            const long long pi = base + i * 32 + lane;
-            id[i] = (pi < N) ? static_cast<int>(voxel_id(x[i], y[i], z[i], g)) : -1;
-            part[i] = (id[i] < 0) ? -1 : part_of(id[i], rule);
+            for (int i = 0; i < kPointsPerLane; ++i) {
+                id[i] = ids_ahead[i];
+                const long long pn = base + kChunk + i * 32 + lane;
+                ids_ahead[i] = (chunk + 1 < c1 && pn < N) ? __ldcs(ids_tmp + pn) : -1;
+            }
+        } else {
+            float x[kPointsPerLane], y[kPointsPerLane], z[kPointsPerLane];
+            if (pts_aligned && base + kPointsPerWarp <= N) {
+                float4 now[3] = {ahead[0], ahead[1], ahead[2]};
+                const long long nbase = base + kChunk;
+                if (chunk + 1 < c1 && nbase + kPointsPerWarp <= N) tile_issue(pts, nbase, lane, ahead);
+                tile_unpack(now, s_xyz[warp], lane, x, y, z);
+            } else {
+                tile_load_slow(pts, base, N, lane, x, y, z);
+            }
+#pragma unroll
+            for (int i = 0; i < kPointsPerLane; ++i) {
+                const long long pi = base + i * 32 + lane;
+                id[i] = (pi < N) ? voxel_id32(x[i], y[i], z[i], g) : -1;
+                if (pi < N) __stcs(ids_tmp + pi, id[i]);
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < kPointsPerLane; ++i) part[i] = (id[i] < 0) ? -1 : part_of(id[i], rule);
+        if (!MOVE) {
+            // counting needs no order: shared-memory atomics on the warp's own row
+#pragma unroll
+            for (int i = 0; i < kPointsPerLane; ++i)
+                if (part[i] >= 0) atomicAdd(&wcnt[part[i]], 1);
+            continue;
         }
 #pragma unroll
         for (int i = 0; i < kPointsPerLane; ++i) {
-            const unsigned int same = __match_any_sync(0xffffffffu, part[i]);
+            // lanes holding the same part: intersect the ballots of the part's six bits (cheaper than
+            // __match_any_sync when a row holds many different parts)
+            unsigned int same = __ballot_sync(0xffffffffu, part[i] >= 0);
+#pragma unroll
+            for (int bit = 0; bit < 6; ++bit) {
+                const bool on = (part[i] >> bit) & 1;
+                const unsigned int b = __ballot_sync(0xffffffffu, on);
+                same &= on ? b : ~b;
+            }
             rank[i] = 0;
-            if (MOVE && part[i] >= 0) rank[i] = wcnt[part[i]] + __popc(same & lt_mask);
+            if (part[i] >= 0) rank[i] = wcnt[part[i]] + __popc(same & lt_mask);
             __syncwarp();
             if (part[i] >= 0 && (same & lt_mask) == 0u) wcnt[part[i]] += __popc(same);   // lowest lane of the group
             __syncwarp();
         }
-        if (!MOVE) continue;                         // the count pass only accumulates wcnt
-        __syncthreads();
-        if (warp == 0) {
-            // per part: exclusive prefix over the warps, then exclusive prefix of the chunk totals over the parts
-            int tot[2] = {0, 0};
+        __syncthreads();   // every warp's counts are in; the previous chunk's sorted arrays are no longer read
+        // Every warp works out the layout of the sorted chunk by itself (no second barrier, no serial phase):
+        // lane p, and p + 32 when there are more than 32 parts, sums part p over the warps, the totals are
+        // prefixed over the parts with shuffles, and the lane keeps the first sorted slot of this warp's
+        // points of its part(s) in registers.
+        const bool wide = P > 32;                                   // uniform: the upper half is skipped for <= 32 parts
+        int tot[2] = {0, 0}, mine[2] = {0, 0};
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int p = lane + 32 * h;
+            if ((h == 0 || wide) && p < P) {
+#pragma unroll
+                for (int w = 0; w < kThreads / 32; ++w) {
+                    const int t = s_wcnt[w][p];
+                    if (w < warp) mine[h] += t;
+                    tot[h] += t;
+                }
+            }
+        }
+        int inc0 = tot[0], inc1 = tot[1];
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) {
+            const int a = __shfl_up_sync(0xffffffffu, inc0, off);
+            if (lane >= off) inc0 += a;
+        }
+        if (wide) {
+#pragma unroll
+            for (int off = 1; off < 32; off <<= 1) {
+                const int b = __shfl_up_sync(0xffffffffu, inc1, off);
+                if (lane >= off) inc1 += b;
+            }
+        }
+        const int sum0 = __shfl_sync(0xffffffffu, inc0, 31);
+        const int lstart[2] = {inc0 - tot[0], sum0 + inc1 - tot[1]};
+        const int first0 = lstart[0] + mine[0], first1 = lstart[1] + mine[1];
+        if (warp == 0) {   // destinations of the sorted slots, advanced by this chunk
+            if (lane == 31) s_total = sum0 + inc1;
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
                 const int p = lane + 32 * h;
                 if (p < P) {
-                    int c = 0;
-                    for (int w = 0; w < kThreads / 32; ++w) { const int t = s_wcnt[w][p]; s_wcnt[w][p] = c; c += t; }
-                    tot[h] = c;
+                    const long long first = s_cur[p] - lstart[h];
+                    s_adj_ids[p] = dest.ids[p] + first;
+                    s_adj_feats[p] = (dest.feats[p] != nullptr) ? dest.feats[p] + first * F : nullptr;
+                    s_cur[p] += tot[h];
                 }
             }
-            int inc0 = tot[0], inc1 = tot[1];
-#pragma unroll
-            for (int off = 1; off < 32; off <<= 1) {
-                const int a = __shfl_up_sync(0xffffffffu, inc0, off);
-                const int b = __shfl_up_sync(0xffffffffu, inc1, off);
-                if (lane >= off) { inc0 += a; inc1 += b; }
-            }
-            const int sum0 = __shfl_sync(0xffffffffu, inc0, 31);
-            if (lane < P) s_lstart[lane] = inc0 - tot[0];
-            if (lane + 32 < P) s_lstart[lane + 32] = sum0 + inc1 - tot[1];
-            if (lane == 31) s_lstart[P] = sum0 + inc1;       // inc1 of lane 31 covers all upper parts (zeros beyond P)
         }
-        __syncthreads();
 #pragma unroll
         for (int i = 0; i < kPointsPerLane; ++i) {
+            const int src_lane = part[i] & 31;                      // all lanes take part in the shuffles
+            const int f0 = __shfl_sync(0xffffffffu, first0, src_lane);
+            const int f1 = wide ? __shfl_sync(0xffffffffu, first1, src_lane) : 0;
             if (part[i] >= 0) {
-                const int slot = s_lstart[part[i]] + wcnt[part[i]] + rank[i];
+                const int slot = ((part[i] < 32) ? f0 : f1) + rank[i];
                 s_sid[slot] = id[i];
-                s_ssrc[slot] = static_cast<unsigned short>(warp * kPointsPerWarp + i * 32 + lane);
-                s_spart[slot] = static_cast<unsigned char>(part[i]);
+                s_meta[slot] = static_cast<unsigned short>(((warp * kPointsPerWarp + i * 32 + lane) << 6) | part[i]);
             }
         }
         __syncthreads();
-        const int n = s_lstart[P];
+        for (int p = lane; p < P; p += 32) wcnt[p] = 0;      // own row, for the next chunk; every warp has read it
+        const int n = s_total;
         if (vec4) {
             float4 f4[kPointsPerLane];
-            int pj[kPointsPerLane];
+            int meta[kPointsPerLane];
 #pragma unroll
             for (int m = 0; m < kPointsPerLane; ++m) {
                 const int j = threadIdx.x + m * kThreads;
-                pj[m] = (j < n) ? s_spart[j] : -1;
-                if (j < n) f4[m] = __ldcs(reinterpret_cast<const float4*>(feats) + cbase + s_ssrc[j]);
+                meta[m] = (j < n) ? s_meta[j] : -1;
+                if (j < n) f4[m] = __ldcs(reinterpret_cast<const float4*>(feats) + cbase + (meta[m] >> 6));
             }
 #pragma unroll
             for (int m = 0; m < kPointsPerLane; ++m) {
                 const int j = threadIdx.x + m * kThreads;
-                if (pj[m] >= 0) {
-                    const long long slot = s_cur[pj[m]] + (j - s_lstart[pj[m]]);
-                    s_dst_ids[pj[m]][slot] = s_sid[j];
-                    reinterpret_cast<float4*>(s_dst_feats[pj[m]])[slot] = f4[m];
+                if (meta[m] >= 0) {
+                    const int p = meta[m] & 63;
+                    s_adj_ids[p][j] = s_sid[j];
+                    reinterpret_cast<float4*>(s_adj_feats[p])[j] = f4[m];
                 }
             }
         } else {
             for (int j = threadIdx.x; j < n; j += kThreads) {
-                const int p = s_spart[j];
-                const long long slot = s_cur[p] + (j - s_lstart[p]);
-                s_dst_ids[p][slot] = s_sid[j];
-                float* fo = s_dst_feats[p];
+                const int meta = s_meta[j];
+                const int p = meta & 63;
+                s_adj_ids[p][j] = s_sid[j];
+                float* fo = s_adj_feats[p];
                 if (fo != nullptr) {
-                    const float* fi = feats + (cbase + s_ssrc[j]) * F;
-                    for (int c = 0; c < F; ++c) fo[slot * F + c] = __ldg(fi + c);
+                    const float* fi = feats + (cbase + (meta >> 6)) * F;
+                    for (int c = 0; c < F; ++c) fo[static_cast<long long>(j) * F + c] = __ldg(fi + c);
                 }
             }
         }
-        __syncthreads();
-        for (int p = threadIdx.x; p < P; p += kThreads) s_cur[p] += s_lstart[p + 1] - s_lstart[p];
-        for (int p = lane; p < P; p += 32) wcnt[p] = 0;
-        __syncwarp();
-        // the next chunk's first block-wide barrier orders these updates before their next use
+        // no barrier here: the next chunk's first barrier comes before anything above is overwritten
     }
     if (!MOVE) {
         __syncthreads();
@@ -727,6 +796,11 @@ void partition_plan(long long N, int device, long long* blocks, long long* chunk
     if (nb < 1) nb = 1;
     *chunks_per_cta = (nchunks + nb - 1) / nb;
     *blocks = nb;
+}
+
+// scratch layout of the partition: per-block offsets [blocks][P] int32, then the voxel id of every point
+uint64_t partition_table_bytes(long long blocks, int P) {
+    return (static_cast<uint64_t>(blocks) * static_cast<uint64_t>(P) * 4u + 15u) & ~static_cast<uint64_t>(15);
 }
 
 int partition_geometry(const float grid_min_host[3], float voxel_size, const int32_t grid_size_host[3], int32_t n_groups,
@@ -1029,7 +1103,7 @@ uint64_t rc_voxel_partition_scratch_bytes(int64_t N, int32_t n_parts, int device
     if (N <= 0 || n_parts < 1 || n_parts > kMaxParts) return 0;
     long long blocks = 0, per = 0;
     partition_plan(N, device, &blocks, &per);
-    return static_cast<uint64_t>(blocks) * static_cast<uint64_t>(n_parts) * 4u;
+    return partition_table_bytes(blocks, n_parts) + static_cast<uint64_t>(N) * 4u;
 }
 
 int rc_voxel_partition_count(const float* points, int64_t N, const float grid_min_host[3], float voxel_size,
@@ -1056,11 +1130,12 @@ int rc_voxel_partition_count(const float* points, int64_t N, const float grid_mi
     partition_plan(N, device, &blocks, &per);
     if (scratch == nullptr) return RC_ERR_NULL_POINTER;
     if (!rc::aligned_to(scratch, 16)) return RC_ERR_BAD_ALIGNMENT;
-    if (scratch_bytes < static_cast<uint64_t>(blocks) * rule.P * 4u) return RC_ERR_BAD_SHAPE;
+    if (scratch_bytes < partition_table_bytes(blocks, rule.P) + static_cast<uint64_t>(N) * 4u) return RC_ERR_BAD_SHAPE;
     int* table = static_cast<int*>(scratch);
+    int* ids_tmp = reinterpret_cast<int*>(static_cast<unsigned char*>(scratch) + partition_table_bytes(blocks, rule.P));
     PartDest none{};
     voxel_part_kernel<false><<<static_cast<unsigned int>(blocks), kThreads, 0, st>>>(
-        points, nullptr, N, 0, g, rc::aligned_to(points, 16), false, rule, per, table, nullptr, none);
+        points, nullptr, N, 0, g, rc::aligned_to(points, 16), false, rule, per, table, ids_tmp, nullptr, none);
     voxel_part_scan_kernel<<<rule.P, 1024, 0, st>>>(table, blocks, rule.P, reinterpret_cast<long long*>(part_counts));
     return rc::check_launch();
 }
@@ -1098,11 +1173,14 @@ int rc_voxel_partition_move(const float* points, const float* features, int64_t 
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     long long blocks = 0, per = 0;
     partition_plan(N, device, &blocks, &per);
-    if (scratch_bytes < static_cast<uint64_t>(blocks) * rule.P * 4u) return RC_ERR_BAD_SHAPE;
+    if (scratch_bytes < partition_table_bytes(blocks, rule.P) + static_cast<uint64_t>(N) * 4u) return RC_ERR_BAD_SHAPE;
     const bool vec4 = move_feats && F == 4 && all16;
+    int* table = const_cast<int*>(static_cast<const int*>(scratch));
+    int* ids_tmp = reinterpret_cast<int*>(const_cast<unsigned char*>(static_cast<const unsigned char*>(scratch)) +
+                                          partition_table_bytes(blocks, rule.P));
     voxel_part_kernel<true><<<static_cast<unsigned int>(blocks), kThreads, 0, st>>>(
-        points, move_feats ? features : nullptr, N, F, g, rc::aligned_to(points, 16), vec4, rule, per,
-        const_cast<int*>(static_cast<const int*>(scratch)), reinterpret_cast<const long long*>(part_counts_device), dest);
+        points, move_feats ? features : nullptr, N, F, g, rc::aligned_to(points, 16), vec4, rule, per, table, ids_tmp,
+        reinterpret_cast<const long long*>(part_counts_device), dest);
     return rc::check_launch();
 }
 

@@ -29,10 +29,12 @@ class PeerBuffer:
         self.peers: List[int] = []          # address of every rank's buffer as seen from this process
         self._opened: List[int] = []
         self._group = None
+        self._connect_called = False
 
     def connect(self, group=None) -> None:
         """Collective: exchange the handles and map every other rank's buffer."""
         self._group = group
+        self._connect_called = True
         rank, ws = dist.get_rank(group), dist.get_world_size(group)
         handles: List[Optional[bytes]] = [None] * ws
         dist.all_gather_object(handles, self.handle, group=group)
@@ -54,8 +56,9 @@ class PeerBuffer:
         for p in self._opened:
             L.rc_peer_close(p, self.device.index)
         self._opened = []
-        if self.peers and dist.is_initialized():
+        if self._connect_called and dist.is_initialized():   # every rank that connected takes part, mapped or not
             dist.barrier(group=self._group)
+        self._connect_called = False
         self.peers = []
         if self.ptr:
             L.rc_peer_free(self.ptr, self.device.index)

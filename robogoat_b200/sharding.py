@@ -289,11 +289,37 @@ class PointExchange:
         self.capacity = int(capacity)
         self.feature_width = int(feature_width)
         self.group = group
-        self.ids = PeerBuffer(max(16, 4 * self.capacity))
-        self.features = PeerBuffer(max(16, 4 * self.capacity * max(1, self.feature_width)))
-        self.ids.connect(group)
-        self.features.connect(group)
-        self._token = torch.zeros(1, dtype=torch.int32, device=self.ids.device)
+        dev = torch.device("cuda", torch.cuda.current_device())
+        self._token = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.ids = self.features = None
+        error = None
+        try:
+            self.ids = PeerBuffer(max(16, 4 * self.capacity), dev)
+            self.features = PeerBuffer(max(16, 4 * self.capacity * max(1, self.feature_width)), dev)
+        except RuntimeError as e:           # allocation failed here: tell everyone before anybody waits on a handle
+            error = e
+        if not self._everyone(error is None):
+            self._drop()
+            raise RuntimeError(f"PointExchange: receive buffers could not be allocated on every rank ({error})")
+        for buf in (self.ids, self.features):       # one collective per buffer, agreed on before the next
+            try:
+                buf.connect(group)
+            except RuntimeError as e:               # no peer access / IPC not permitted
+                error = e
+            if not self._everyone(error is None):
+                self._drop()
+                raise RuntimeError(f"PointExchange: peer buffers could not be mapped on every rank ({error})")
+
+    def _everyone(self, ok: bool) -> bool:
+        flag = torch.tensor([1 if ok else 0], dtype=torch.int32, device=self._token.device)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=self.group)
+        return bool(flag.item())
+
+    def _drop(self) -> None:
+        for b in (self.ids, self.features):
+            if b is not None:
+                b.close()
+        self.ids = self.features = None
 
     def stream_barrier(self) -> None:
         """Orders, on the current stream, everything the other ranks enqueued before their call of this
@@ -301,8 +327,7 @@ class PointExchange:
         dist.all_reduce(self._token, group=self.group)
 
     def close(self) -> None:
-        self.ids.close()
-        self.features.close()
+        self._drop()
 
 
 def voxelize_sharded_exchange(points_local: torch.Tensor, features_local: Optional[torch.Tensor] = None,
