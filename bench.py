@@ -562,6 +562,16 @@ def run_extras(L, dev, local, rank, world, peak):
                 r = fn(); del r
             e1.record(); torch.cuda.synchronize()
             ms = max_over_ranks(e0.elapsed_time(e1) / 5, world, dev)
+            L.rc_set_option(2, 0)                   # per-thread feature stores instead of bulk copies over NVLink
+            for _ in range(2):
+                r = fn(); del r
+            barrier(world)
+            e0.record()
+            for _ in range(5):
+                r = fn(); del r
+            e1.record(); torch.cuda.synchronize()
+            ms_plain = max_over_ranks(e0.elapsed_time(e1) / 5, world, dev)
+            L.rc_set_option(2, 1)
             barrier(world)
             ev[0].record()
             pc, scratch = ops.voxel_partition_count_cuda(pts, kw["grid_min"], kw["voxel_size"], kw["grid_size"], world, K)
@@ -582,6 +592,7 @@ def run_extras(L, dev, local, rank, world, peak):
             sent_remote = sum(c for d, c in enumerate(plan["send_counts"]) if d != rank) * 20
             ex["voxel_mean_sharded_point_exchange_direct"] = {
                 "ms": ms, "Gpts/s_total": N * world / (ms * 1e-3) / 1e9, "fits_receive_buffers": fits,
+                "ms_with_per_thread_feature_stores": ms_plain,
                 "stage_ms": {"count_and_count_matrix": stages[0], "move_over_nvlink_and_barrier": stages[1], "scatter_normalise": stages[2]},
                 "nvlink_GB/s_out_per_gpu_during_move": sent_remote / (stages[1] * 1e-3) / 1e9 if fits else None,
                 "note": "same, but the partition kernel stores its sorted chunks straight into the owners' receive buffers "

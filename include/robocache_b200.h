@@ -195,7 +195,7 @@ RC_API int rc_voxel_normalize(float* grid, const int32_t* counts, int64_t voxel_
  *   buffer).  dest_features may be NULL (ids only).
  * rc_voxel_partition: count + move into local buffers ids_out [N] / features_out [N, F], parts back to
  *   back; only the first sum(part_counts) entries are written.
- * Limits: N and gx*gy*gz below 2^31.  Everything runs on `stream`.
+ * Limits: N at most 2^31 - 4096, gx*gy*gz below 2^31.  Everything runs on `stream`.
  *
  * rc_voxel_scatter_ids: accumulates points given as (voxel id, feature row) into the slab of
  * voxels [id_begin, id_end); ids outside the range (and -1) are ignored.
@@ -274,10 +274,15 @@ RC_API int rc_voxelize_mean_static(const float* points, const float* features, f
  * RC_OPT_VOXEL_PASSES (default 0 = choose automatically): number of slab passes of the count /
  * mean / max scatter; each pass re-reads the coordinates but scatters into only 1/passes of the
  * grid, which keeps the touched part of large sparse grids resident in L2.
+ * RC_OPT_PART_BULK_STORE: how rc_voxel_partition_move writes 4-wide feature rows.  1 (default): with bulk
+ * asynchronous copies from shared memory (one request per run of sorted records) when a destination lies
+ * on another GPU, with per-thread stores otherwise; 0: always per-thread stores; 2: always bulk copies.
+ * All produce identical bytes.
  * No counterpart in the reference.
  */
 #define RC_OPT_BLOCK_KERNEL 0
 #define RC_OPT_VOXEL_PASSES 1
+#define RC_OPT_PART_BULK_STORE 2
 RC_API int rc_set_option(int option, int value);
 
 /*

@@ -549,7 +549,19 @@ __device__ __forceinline__ int voxel_id32(float x, float y, float z, const Voxel
     return (static_cast<int>(fz) * g.gy + static_cast<int>(fy)) * g.gx + static_cast<int>(fx);
 }
 
-template <bool MOVE>
+// Bulk asynchronous copy shared -> global (the TMA engine moves a whole run of sorted records with one
+// request, to local or peer memory alike).  Both addresses 16-byte aligned, size a multiple of 16 bytes.
+__device__ __forceinline__ void bulk_store(void* dst_global, const void* src_shared, unsigned int bytes) {
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+                 :: "l"(__cvta_generic_to_global(dst_global)),
+                    "r"(static_cast<unsigned int>(__cvta_generic_to_shared(src_shared))), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read_all_but_one() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_shared() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+template <bool MOVE, bool BULK>
 __global__ void __launch_bounds__(kThreads, 5)
 voxel_part_kernel(const float* __restrict__ pts, const float* __restrict__ feats, long long N, int F, VoxelGeom g,
                   bool pts_aligned, bool vec4, PartRule rule, long long chunks_per_cta, int* __restrict__ table,
@@ -565,10 +577,17 @@ voxel_part_kernel(const float* __restrict__ pts, const float* __restrict__ feats
     __shared__ int s_total;
     __shared__ int s_sid[MOVE ? kChunk : 1];                 // the chunk's voxel ids, sorted by part
     __shared__ unsigned short s_meta[MOVE ? kChunk : 1];     // (index in chunk << 6) | part
+    // feature rows of the sorted chunk, staged for the bulk stores; two buffers so that a chunk is staged
+    // while the previous one is still being read by the copy engine
+    __shared__ __align__(16) float4 s_feat[BULK ? 2 : 1][BULK ? kChunk : 1];
+    constexpr bool bulk = MOVE && BULK;                      // callers pass BULK only together with vec4
+    float* pend_dst[2] = {nullptr, nullptr};                 // warp 0: the runs of the previous chunk, not yet issued
+    int pend_src[2] = {0, 0}, pend_cnt[2] = {0, 0}, pend_buf = 0;
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
     const unsigned int lt_mask = (1u << lane) - 1u;
     const int P = rule.P;
+    const int nbits = 32 - __clz(P - 1 > 0 ? P - 1 : 1);                 // bits that tell the parts apart
     int* wcnt = s_wcnt[warp];
     for (int p = lane; p < P; p += 32) wcnt[p] = 0;
     if (MOVE) {
@@ -584,50 +603,70 @@ voxel_part_kernel(const float* __restrict__ pts, const float* __restrict__ feats
         }
     }
     __syncthreads();
-    const long long nchunks = (N + kChunk - 1) / kChunk;
-    const long long c0 = static_cast<long long>(blockIdx.x) * chunks_per_cta;
-    const long long c1 = (c0 + chunks_per_cta < nchunks) ? c0 + chunks_per_cta : nchunks;
+    // N < 2^31 (checked by the host): point and chunk indices are 32-bit
+    const int n_pts = static_cast<int>(N);
+    const int nchunks = (n_pts + kChunk - 1) / kChunk;                  // n_pts + 1023 cannot overflow: N <= 2^31 - 1024 is enforced
+    const int per_cta = static_cast<int>(chunks_per_cta);
+    const int c0 = (static_cast<long long>(blockIdx.x) * per_cta < nchunks) ? static_cast<int>(blockIdx.x) * per_cta : nchunks;
+    const int c1 = (nchunks - c0 > per_cta) ? c0 + per_cta : nchunks;
+    const int toff = warp * kPointsPerWarp + lane;                      // this lane's first point inside a chunk
     float4 ahead[3];
     int ids_ahead[kPointsPerLane];
-    {
-        const long long tbase = c0 * kChunk + warp * kPointsPerWarp;
+    if (c0 < c1) {
+        const int tbase = c0 * kChunk + warp * kPointsPerWarp;
         if (MOVE) {
 #pragma unroll
             for (int i = 0; i < kPointsPerLane; ++i) {
-                const long long pi = tbase + i * 32 + lane;
-                ids_ahead[i] = (c0 < c1 && pi < N) ? __ldcs(ids_tmp + pi) : -1;
+                const int pi = c0 * kChunk + toff + i * 32;
+                ids_ahead[i] = (pi < n_pts) ? __ldcs(ids_tmp + pi) : -1;
             }
-        } else if (pts_aligned && c0 < c1 && tbase + kPointsPerWarp <= N) {
+        } else if (pts_aligned && tbase + kPointsPerWarp <= n_pts) {
             tile_issue(pts, tbase, lane, ahead);
         }
     }
-    for (long long chunk = c0; chunk < c1; ++chunk) {
-        const long long cbase = chunk * kChunk;
-        const long long base = cbase + warp * kPointsPerWarp;
+    for (int chunk = c0; chunk < c1; ++chunk) {
+        const int cbase = chunk * kChunk;
+        const int base = cbase + warp * kPointsPerWarp;
+        const bool full = cbase + kChunk <= n_pts;                      // uniform: no per-point bound checks in full chunks
+        const bool next_full = chunk + 1 < c1 && cbase + 2 * kChunk <= n_pts;
         int id[kPointsPerLane], part[kPointsPerLane], rank[kPointsPerLane];
         if (MOVE) {
             // the voxel ids were left behind by the count pass; fetch the next chunk's while this one is sorted
 #pragma unroll
-            for (int i = 0; i < kPointsPerLane; ++i) {
-                id[i] = ids_ahead[i];
-                const long long pn = base + kChunk + i * 32 + lane;
-                ids_ahead[i] = (chunk + 1 < c1 && pn < N) ? __ldcs(ids_tmp + pn) : -1;
+            for (int i = 0; i < kPointsPerLane; ++i) id[i] = ids_ahead[i];
+            if (next_full) {
+#pragma unroll
+                for (int i = 0; i < kPointsPerLane; ++i) ids_ahead[i] = __ldcs(ids_tmp + cbase + kChunk + toff + i * 32);
+            } else {
+#pragma unroll
+                for (int i = 0; i < kPointsPerLane; ++i) {
+                    const int pn = cbase + kChunk + toff + i * 32;
+                    ids_ahead[i] = (chunk + 1 < c1 && pn < n_pts) ? __ldcs(ids_tmp + pn) : -1;
+                }
             }
         } else {
             float x[kPointsPerLane], y[kPointsPerLane], z[kPointsPerLane];
-            if (pts_aligned && base + kPointsPerWarp <= N) {
+            if (pts_aligned && (full || base + kPointsPerWarp <= n_pts)) {
                 float4 now[3] = {ahead[0], ahead[1], ahead[2]};
-                const long long nbase = base + kChunk;
-                if (chunk + 1 < c1 && nbase + kPointsPerWarp <= N) tile_issue(pts, nbase, lane, ahead);
+                const int nbase = base + kChunk;
+                if (next_full || (chunk + 1 < c1 && nbase + kPointsPerWarp <= n_pts)) tile_issue(pts, nbase, lane, ahead);
                 tile_unpack(now, s_xyz[warp], lane, x, y, z);
             } else {
                 tile_load_slow(pts, base, N, lane, x, y, z);
             }
+            if (full) {
 #pragma unroll
-            for (int i = 0; i < kPointsPerLane; ++i) {
-                const long long pi = base + i * 32 + lane;
-                id[i] = (pi < N) ? voxel_id32(x[i], y[i], z[i], g) : -1;
-                if (pi < N) __stcs(ids_tmp + pi, id[i]);
+                for (int i = 0; i < kPointsPerLane; ++i) {
+                    id[i] = voxel_id32(x[i], y[i], z[i], g);
+                    __stcs(ids_tmp + cbase + toff + i * 32, id[i]);
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < kPointsPerLane; ++i) {
+                    const int pi = cbase + toff + i * 32;
+                    id[i] = (pi < n_pts) ? voxel_id32(x[i], y[i], z[i], g) : -1;
+                    if (pi < n_pts) __stcs(ids_tmp + pi, id[i]);
+                }
             }
         }
 #pragma unroll
@@ -646,9 +685,11 @@ voxel_part_kernel(const float* __restrict__ pts, const float* __restrict__ feats
             unsigned int same = __ballot_sync(0xffffffffu, part[i] >= 0);
 #pragma unroll
             for (int bit = 0; bit < 6; ++bit) {
-                const bool on = (part[i] >> bit) & 1;
-                const unsigned int b = __ballot_sync(0xffffffffu, on);
-                same &= on ? b : ~b;
+                if (bit < nbits) {                                       // uniform
+                    const bool on = (part[i] >> bit) & 1;
+                    const unsigned int b = __ballot_sync(0xffffffffu, on);
+                    same &= on ? b : ~b;
+                }
             }
             rank[i] = 0;
             if (part[i] >= 0) rank[i] = wcnt[part[i]] + __popc(same & lt_mask);
@@ -661,6 +702,14 @@ voxel_part_kernel(const float* __restrict__ pts, const float* __restrict__ feats
         // lane p, and p + 32 when there are more than 32 parts, sums part p over the warps, the totals are
         // prefixed over the parts with shuffles, and the lane keeps the first sorted slot of this warp's
         // points of its part(s) in registers.
+        if (bulk && warp == 0) {
+            // the previous chunk's feature rows are staged (its threads fenced before the barrier): one bulk
+            // store per part and lane
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+                if (pend_cnt[h] > 0) bulk_store(pend_dst[h], &s_feat[pend_buf][pend_src[h]], static_cast<unsigned int>(pend_cnt[h]) * 16u);
+            bulk_commit();
+        }
         const bool wide = P > 32;                                   // uniform: the upper half is skipped for <= 32 parts
         int tot[2] = {0, 0}, mine[2] = {0, 0};
 #pragma unroll
@@ -700,9 +749,16 @@ voxel_part_kernel(const float* __restrict__ pts, const float* __restrict__ feats
                     const long long first = s_cur[p] - lstart[h];
                     s_adj_ids[p] = dest.ids[p] + first;
                     s_adj_feats[p] = (dest.feats[p] != nullptr) ? dest.feats[p] + first * F : nullptr;
+                    pend_dst[h] = bulk ? dest.feats[p] + s_cur[p] * 4 : nullptr;
+                    pend_src[h] = lstart[h];
+                    pend_cnt[h] = tot[h];
                     s_cur[p] += tot[h];
+                } else {
+                    pend_cnt[h] = 0;
                 }
             }
+            pend_buf = chunk & 1;
+            if (bulk) bulk_wait_read_all_but_one();   // the buffer this chunk stages into was read two chunks ago
         }
 #pragma unroll
         for (int i = 0; i < kPointsPerLane; ++i) {
@@ -725,7 +781,7 @@ voxel_part_kernel(const float* __restrict__ pts, const float* __restrict__ feats
             for (int m = 0; m < kPointsPerLane; ++m) {
                 const int j = threadIdx.x + m * kThreads;
                 meta[m] = (j < n) ? s_meta[j] : -1;
-                if (j < n) f4[m] = __ldcs(reinterpret_cast<const float4*>(feats) + cbase + (meta[m] >> 6));
+                if (j < n) f4[m] = __ldcs(reinterpret_cast<const float4*>(feats) + (cbase + (meta[m] >> 6)));
             }
 #pragma unroll
             for (int m = 0; m < kPointsPerLane; ++m) {
@@ -733,9 +789,11 @@ voxel_part_kernel(const float* __restrict__ pts, const float* __restrict__ feats
                 if (meta[m] >= 0) {
                     const int p = meta[m] & 63;
                     s_adj_ids[p][j] = s_sid[j];
-                    reinterpret_cast<float4*>(s_adj_feats[p])[j] = f4[m];
+                    if (bulk) s_feat[chunk & 1][j] = f4[m];
+                    else reinterpret_cast<float4*>(s_adj_feats[p])[j] = f4[m];
                 }
             }
+            if (bulk) fence_async_shared();   // staged rows become visible to the copy engine; issued after the next barrier
         } else {
             for (int j = threadIdx.x; j < n; j += kThreads) {
                 const int meta = s_meta[j];
@@ -743,12 +801,22 @@ voxel_part_kernel(const float* __restrict__ pts, const float* __restrict__ feats
                 s_adj_ids[p][j] = s_sid[j];
                 float* fo = s_adj_feats[p];
                 if (fo != nullptr) {
-                    const float* fi = feats + (cbase + (meta >> 6)) * F;
+                    const float* fi = feats + static_cast<long long>(cbase + (meta >> 6)) * F;
                     for (int c = 0; c < F; ++c) fo[static_cast<long long>(j) * F + c] = __ldg(fi + c);
                 }
             }
         }
         // no barrier here: the next chunk's first barrier comes before anything above is overwritten
+    }
+    if (MOVE && bulk) {
+        __syncthreads();
+        if (warp == 0) {
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+                if (pend_cnt[h] > 0) bulk_store(pend_dst[h], &s_feat[pend_buf][pend_src[h]], static_cast<unsigned int>(pend_cnt[h]) * 16u);
+            bulk_commit();
+            bulk_wait_all();                  // shared memory must outlive the copies
+        }
     }
     if (!MOVE) {
         __syncthreads();
@@ -1116,7 +1184,7 @@ int rc_voxel_partition_count(const float* points, int64_t N, const float grid_mi
     if (rc_geom != RC_OK) return rc_geom;
     if (part_counts == nullptr) return RC_ERR_NULL_POINTER;
     if (N < 0) return RC_ERR_BAD_SHAPE;
-    if (N >= (1ll << 31)) return RC_ERR_TOO_LARGE;
+    if (N > (1ll << 31) - 4096) return RC_ERR_TOO_LARGE;   // 32-bit point indices with room for one chunk of look-ahead
     if (N > 0 && points == nullptr) return RC_ERR_NULL_POINTER;
     if (!rc::aligned_to(points, 4) || !rc::aligned_to(part_counts, 8)) return RC_ERR_BAD_ALIGNMENT;
     rc::DeviceScope scope(device);
@@ -1134,7 +1202,7 @@ int rc_voxel_partition_count(const float* points, int64_t N, const float grid_mi
     int* table = static_cast<int*>(scratch);
     int* ids_tmp = reinterpret_cast<int*>(static_cast<unsigned char*>(scratch) + partition_table_bytes(blocks, rule.P));
     PartDest none{};
-    voxel_part_kernel<false><<<static_cast<unsigned int>(blocks), kThreads, 0, st>>>(
+    voxel_part_kernel<false, false><<<static_cast<unsigned int>(blocks), kThreads, 0, st>>>(
         points, nullptr, N, 0, g, rc::aligned_to(points, 16), false, rule, per, table, ids_tmp, nullptr, none);
     voxel_part_scan_kernel<<<rule.P, 1024, 0, st>>>(table, blocks, rule.P, reinterpret_cast<long long*>(part_counts));
     return rc::check_launch();
@@ -1151,7 +1219,7 @@ int rc_voxel_partition_move(const float* points, const float* features, int64_t 
     const int rc_geom = partition_geometry(grid_min_host, voxel_size, grid_size_host, n_groups, parts_per_group, &g, &rule, &V);
     if (rc_geom != RC_OK) return rc_geom;
     if (N < 0 || F < 0) return RC_ERR_BAD_SHAPE;
-    if (N >= (1ll << 31)) return RC_ERR_TOO_LARGE;
+    if (N > (1ll << 31) - 4096) return RC_ERR_TOO_LARGE;   // 32-bit point indices with room for one chunk of look-ahead
     if (N == 0 || V == 0) return RC_OK;
     if (points == nullptr || dest_ids == nullptr || scratch == nullptr) return RC_ERR_NULL_POINTER;
     if (dest_start == nullptr && part_counts_device == nullptr) return RC_ERR_NULL_POINTER;
@@ -1175,12 +1243,31 @@ int rc_voxel_partition_move(const float* points, const float* features, int64_t 
     partition_plan(N, device, &blocks, &per);
     if (scratch_bytes < partition_table_bytes(blocks, rule.P) + static_cast<uint64_t>(N) * 4u) return RC_ERR_BAD_SHAPE;
     const bool vec4 = move_feats && F == 4 && all16;
+    // bulk (TMA) stores of the feature runs pay off over NVLink, per-thread stores in local memory
+    const int bulk_opt = rc::g_part_bulk_store.load(std::memory_order_relaxed);
+    bool bulk = vec4 && bulk_opt == 2;
+    if (vec4 && bulk_opt == 1) {
+        const float* seen = nullptr;
+        for (int p = 0; p < rule.P && !bulk; ++p) {
+            if (dest.feats[p] == seen) continue;
+            seen = dest.feats[p];
+            cudaPointerAttributes attr{};
+            if (cudaPointerGetAttributes(&attr, seen) != cudaSuccess) { cudaGetLastError(); continue; }
+            bulk = attr.type == cudaMemoryTypeDevice && attr.device != device;
+        }
+    }
     int* table = const_cast<int*>(static_cast<const int*>(scratch));
     int* ids_tmp = reinterpret_cast<int*>(const_cast<unsigned char*>(static_cast<const unsigned char*>(scratch)) +
                                           partition_table_bytes(blocks, rule.P));
-    voxel_part_kernel<true><<<static_cast<unsigned int>(blocks), kThreads, 0, st>>>(
-        points, move_feats ? features : nullptr, N, F, g, rc::aligned_to(points, 16), vec4, rule, per, table, ids_tmp,
-        reinterpret_cast<const long long*>(part_counts_device), dest);
+    const unsigned int nb = static_cast<unsigned int>(blocks);
+    const float* f_in = move_feats ? features : nullptr;
+    const long long* pc_dev = reinterpret_cast<const long long*>(part_counts_device);
+    if (bulk)
+        voxel_part_kernel<true, true><<<nb, kThreads, 0, st>>>(points, f_in, N, F, g, rc::aligned_to(points, 16), vec4, rule, per,
+                                                               table, ids_tmp, pc_dev, dest);
+    else
+        voxel_part_kernel<true, false><<<nb, kThreads, 0, st>>>(points, f_in, N, F, g, rc::aligned_to(points, 16), vec4, rule, per,
+                                                                table, ids_tmp, pc_dev, dest);
     return rc::check_launch();
 }
 

@@ -180,3 +180,27 @@ def test_exchange_entry_points_reject_bad_arguments(cuda_lib):
         ops.voxel_scatter_ids_cuda(torch.zeros(4, dtype=torch.int32, device=DEV), None, 0, 8, "max")
     with pytest.raises(RuntimeError):
         ops.voxel_scatter_ids_cuda(torch.zeros(8, dtype=torch.int32, device=DEV)[1:5], None, 0, 8, "count")  # misaligned ids
+
+
+@pytest.mark.parametrize("groups,per_group", [(2, 1), (8, 4), (4, 16)])
+def test_bulk_and_per_thread_feature_stores_write_the_same_bytes(groups, per_group, cuda_lib):
+    from robogoat_b200 import _lib
+    kw = dict(grid_min=[-2.0, -2.0, -2.0], voxel_size=0.125, grid_size=[32, 32, 32])
+    pts, feats = _cloud(150_001, 77)
+    p, f = pts.to(DEV), feats.to(DEV)
+    L = _lib.load()
+    outs = []
+    try:
+        for bulk in (2, 0):
+            assert L.rc_set_option(2, bulk) == 0
+            ids, fb, pc = ops.voxel_partition_cuda(p, f, kw["grid_min"], kw["voxel_size"], kw["grid_size"], groups, per_group)
+            n = int(pc.sum())
+            outs.append((ids[:n].clone(), fb[:n].clone(), pc.clone()))
+    finally:
+        L.rc_set_option(2, 1)
+    assert torch.equal(outs[0][2], outs[1][2]) and torch.equal(outs[0][0], outs[1][0])
+    assert torch.equal(outs[0][1], outs[1][1])
+    exp_ids = oracle.voxel_ids(pts, **kw)
+    keep = exp_ids >= 0
+    order = torch.sort(_owner(exp_ids[keep], 32 ** 3, groups, per_group), stable=True).indices
+    assert torch.equal(outs[0][1].cpu(), feats[keep][order])
