@@ -662,6 +662,17 @@ def run_profile_case(name: str):
         kw = workloads.VOXEL_MIXTURE_GEOMETRY
         fn = lambda: ops.voxel_partition_cuda(pts, feats, kw["grid_min"], kw["voxel_size"], kw["grid_size"], 8, 4)
         units = {"N": N, "parts": 32}
+    elif name == "voxel_scatter_runs":
+        # what one of 2 owners receives from a 2^24-point cloud, cut into 14 L2-sized sub-ranges of its slab
+        N = 1 << 24
+        pts, feats = workloads.voxel_mixture_inputs(N, seed=0, device=dev)
+        kw = workloads.VOXEL_MIXTURE_GEOMETRY
+        ids, fbk, pc = ops.voxel_partition_cuda(pts, feats, kw["grid_min"], kw["voxel_size"], kw["grid_size"], 2, 14)
+        cnts = pc.tolist()
+        runs = [(sum(cnts[:k]), cnts[k], k) for k in range(14)]
+        del pts, feats
+        fn = lambda: ops.voxel_scatter_runs_cuda(ids.data_ptr(), fbk.data_ptr(), dev, 4, 0, 512 ** 3 // 2, runs, 14, "mean")
+        units = {"N": sum(cnts[:14]), "sub_ranges": 14}
     elif name == "voxel_occupancy":
         pts = workloads.voxel_uniform_inputs(500_000, seed=0, device=dev)
         fn = lambda: robocache.voxelize_pointcloud(pts, mode="occupancy", **workloads.VOXEL_OCCUPANCY_GEOMETRY)
@@ -684,7 +695,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extras", action="store_true")
     ap.add_argument("--profile-case", default=None,
-                    help="run 4 launches of one kernel on a small case (resample, fusion, voxel_mean, voxel_count, voxel_occupancy, voxel_partition; voxel_mean_full = headline size)")
+                    help="run 4 launches of one kernel on a small case (resample, fusion, voxel_mean, voxel_count, voxel_occupancy, voxel_partition, voxel_scatter_runs; voxel_mean_full = headline size)")
     args = ap.parse_args()
     if args.profile_case:
         run_profile_case(args.profile_case)
