@@ -357,32 +357,42 @@ def voxel_partition_move_cuda(points: torch.Tensor, features: Optional[torch.Ten
     _lib.check(rc, "voxel_partition_move")
 
 
+def voxel_slab_buffers(n_voxels: int, feature_width: int, mode: str, device: torch.device) -> List[torch.Tensor]:
+    """Uninitialised accumulators of a slab: ``[grid]`` (int32 [n]) or, for mean mode, ``[grid fp32 [n, F], counts int32 [n]]``."""
+    if mode == "mean":
+        return [torch.empty((n_voxels, feature_width), dtype=torch.float32, device=device),
+                torch.empty(n_voxels, dtype=torch.int32, device=device)]
+    return [torch.empty(n_voxels, dtype=torch.int32, device=device)]
+
+
 def voxel_scatter_runs_cuda(ids_ptr: int, features_ptr: Optional[int], device: torch.device, feature_width: int,
                             id_begin: int, id_end: int, runs: Sequence[Tuple[int, int, int]], n_passes: int, mode: str,
-                            *, normalize: bool = True) -> List[torch.Tensor]:
+                            *, normalize: bool = True, out: Optional[List[torch.Tensor]] = None) -> List[torch.Tensor]:
     """Accumulate records that arrive as runs into the slab of voxels [id_begin, id_end).
 
     ``ids_ptr`` / ``features_ptr`` are device addresses of the int32 id list and the fp32 [., F] feature rows
     (a torch tensor's ``data_ptr()`` or a ``PeerBuffer``); ``runs`` lists ``(first record, records, pass)``.
     The runs of pass 0 are accumulated first, then pass 1, ...  Returns ``[grid]`` or ``[grid, counts]`` as
-    ``voxel_scatter_ids_cuda``.
+    ``voxel_scatter_ids_cuda``.  ``out``: accumulators from ``voxel_slab_buffers`` that the caller has already
+    cleared (e.g. on another stream while the records were still travelling); they are not cleared again.
     """
     if mode not in ("count", "occupancy", "mean"):
         raise RuntimeError(f"Invalid mode: {mode}. The run scatter supports 'count', 'occupancy' and 'mean'")
     nvox = int(id_end) - int(id_begin)
     _check(nvox >= 0 and id_begin >= 0, "bad voxel range")
     F = int(feature_width) if mode == "mean" else 0
-    counts = None
-    if mode == "mean":
-        grid = torch.empty((nvox, F), dtype=torch.float32, device=device)
-        counts = torch.empty(nvox, dtype=torch.int32, device=device)
+    if out is None:
+        bufs = voxel_slab_buffers(nvox, F, mode, device)
     else:
-        grid = torch.empty(nvox, dtype=torch.int32, device=device)
+        bufs = list(out)
+        _check(bufs[0].is_contiguous() and bufs[0].numel() == (nvox * F if mode == "mean" else nvox), "out does not match the slab")
+    grid = bufs[0]
+    counts = bufs[1] if mode == "mean" else None
     n = len(runs)
     rb = (ctypes.c_int64 * max(n, 1))(*[int(r[0]) for r in runs])
     rcnt = (ctypes.c_int64 * max(n, 1))(*[int(r[1]) for r in runs])
     rp = (ctypes.c_int32 * max(n, 1))(*[int(r[2]) for r in runs])
-    flags = _lib.VOXEL_ZERO_INIT | (0 if normalize else _lib.VOXEL_NO_NORMALIZE)
+    flags = (_lib.VOXEL_ZERO_INIT if out is None else 0) | (0 if normalize else _lib.VOXEL_NO_NORMALIZE)
     rc = _lib.load().rc_voxel_scatter_runs(ids_ptr or None, features_ptr or None, grid.data_ptr() if grid.numel() else None,
                                            counts.data_ptr() if counts is not None and nvox else None, F, int(id_begin),
                                            int(id_end), rb, rcnt, rp, n, int(n_passes), _MODES[mode], flags, device.index,

@@ -81,6 +81,12 @@ def test_two_level_partition_and_run_scatter(groups, per_group, N, cuda_lib):
         grid, cnt = ops.voxel_scatter_runs_cuda(ids.data_ptr(), fb.data_ptr(), p.device, 4, a, b, runs, per_group, "mean")
         assert torch.equal(cnt, full_cnt[a:b])
         assert bool(((grid.cpu() - exp.reshape(V, 4)[a:b]).abs() <= tol[a:b]).all())
+        bufs = ops.voxel_slab_buffers(b - a, 4, "mean", p.device)          # accumulators cleared by the caller
+        for t in bufs:
+            t.zero_()
+        grid2, cnt2 = ops.voxel_scatter_runs_cuda(ids.data_ptr(), fb.data_ptr(), p.device, 4, a, b, runs, per_group, "mean", out=bufs)
+        assert grid2.data_ptr() == bufs[0].data_ptr() and torch.equal(cnt2, cnt)
+        assert bool(((grid2.cpu() - exp.reshape(V, 4)[a:b]).abs() <= tol[a:b]).all())
 
 
 def test_split_count_and_move_into_separate_destinations(cuda_lib):
