@@ -27,6 +27,7 @@ import statistics
 import subprocess
 import sys
 import tempfile
+import threading
 import time
 
 import torch
@@ -36,6 +37,7 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 HEADLINE = dict(B=4096, S=500, D=256, T=250)
+EXTRAS_LIMIT_S = 420          # multi-GPU runs: the side measurements get this long before the line is printed without them
 METRIC = "resample_throughput"
 UNIT = "GB/s"
 WORKLOAD = "resample bf16 B=4096 S=500 D=256 T=250 sorted-uniform targets, per GPU"
@@ -135,6 +137,10 @@ def dist_setup(n_gpus: int):
         import torch.distributed as dist
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         os.environ.setdefault("MASTER_PORT", "29500")
+        # The watchdog of the side measurements may end the processes abruptly, and a process that dies while NCCL has
+        # memory bound to an NVLink multicast object can fault the other GPUs: leave the in-switch reduction off.  The
+        # headline path has no data-path collective; the grid-reduce side measurements run without NVLS.
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         torch.cuda.set_device(local)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     else:
@@ -367,14 +373,13 @@ def run_ours(args):
     extras = {}
     if rank == 0:
         cpu_baseline = cpu_baseline_leg(world)
-    if not args.no_extras:
-        try:
-            extras = run_extras(L, dev, local, rank, world, peak)
-        except Exception as e:  # the headline line must survive a failing side measurement
-            extras = {"error": repr(e)}
-    barrier(world)
 
-    if rank == 0:
+    emitted = threading.Lock()
+
+    def emit():
+        """Rank 0 prints the one JSON line (once, whoever gets here first: the main thread or the watchdog)."""
+        if rank != 0 or not emitted.acquire(blocking=False):
+            return
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
@@ -383,11 +388,34 @@ def run_ours(args):
             "config": {"workload": WORKLOAD,
                        "global_batch": B * world, "parallelism": f"batch-shard x{world}, no collective",
                        "l2": "inputs (1.06 GB) and output (0.52 GB) exceed the 126 MB L2; no flush needed",
-                       "bytes_per_step_per_gpu": step_bytes, "bytes_convention": BYTES_CONVENTION},
+                       "bytes_per_step_per_gpu": step_bytes, "bytes_convention": BYTES_CONVENTION,
+                       "nccl_nvls": os.environ.get("NCCL_NVLS_ENABLE", "default") if world > 1 else "n/a"},
             "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e, "gpu_launches": args.steps, "clocks": clocks,
-            "extras": extras,
+            "extras": dict(extras),
         }
         print(json.dumps(line), flush=True)
+
+    # The side measurements below include collectives.  Should one of them ever stall on some rank, the headline line
+    # above must still come out: a timer prints it with whatever extras exist and ends the process on every rank.
+    watchdog = None
+    if world > 1 and not args.no_extras:
+        def give_up():
+            extras["watchdog"] = f"side measurements did not finish within {EXTRAS_LIMIT_S} s; line printed without the rest"
+            emit()
+            sys.stdout.flush()
+            os._exit(0)
+        watchdog = threading.Timer(EXTRAS_LIMIT_S, give_up)
+        watchdog.daemon = True
+        watchdog.start()
+    if not args.no_extras:
+        try:
+            run_extras(L, dev, local, rank, world, peak, extras)
+        except Exception as e:  # the headline line must survive a failing side measurement
+            extras["error"] = repr(e)
+    barrier(world)
+    if watchdog is not None:
+        watchdog.cancel()
+    emit()
     if world > 1:
         import torch.distributed as dist
         dist.destroy_process_group()
@@ -417,11 +445,11 @@ def cpu_baseline_leg(world: int):
             "host_cores": os.cpu_count()}
 
 
-def run_extras(L, dev, local, rank, world, peak):
-    """Fusion and voxelisation figures for the other headline configurations (device-resident inputs)."""
+def run_extras(L, dev, local, rank, world, peak, ex):
+    """Fusion and voxelisation figures for the other headline configurations (device-resident inputs), added to ``ex``
+    as they are measured."""
     from robogoat_b200 import _lib, ops, workloads
     import robocache
-    ex = {}
     flush = L2Flush(dev)
 
     # fusion throughput, B=16384 per GPU, bf16
