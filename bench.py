@@ -604,12 +604,14 @@ def run_extras(L, dev, local, rank, world, peak, ex):
             ev[0].record()
             pc, scratch = ops.voxel_partition_count_cuda(pts, kw["grid_min"], kw["voxel_size"], kw["grid_size"], world, K)
             plan = sharding.exchange_plan(sharding._gather_counts(pc), rank, K)
+            ev_move = torch.cuda.Event(enable_timing=True)
             ev[1].record()
             fits = max(plan["totals"]) <= px.capacity
             if fits:
                 ops.voxel_partition_move_cuda(pts, feats, kw["grid_min"], kw["voxel_size"], kw["grid_size"], world, K,
                                               [px.ids.peers[p // K] for p in range(world * K)],
                                               [px.features.peers[p // K] for p in range(world * K)], plan["dest_start"], scratch)
+                ev_move.record()
                 px.stream_barrier()
             ev[2].record()
             if fits:
@@ -618,11 +620,13 @@ def run_extras(L, dev, local, rank, world, peak, ex):
             ev[3].record(); torch.cuda.synchronize()
             stages = [max_over_ranks(ev[i].elapsed_time(ev[i + 1]), world, dev) for i in range(3)]
             sent_remote = sum(c for d, c in enumerate(plan["send_counts"]) if d != rank) * 20
+            move_ms = max_over_ranks(ev[1].elapsed_time(ev_move), world, dev) if fits else None
             ex["voxel_mean_sharded_point_exchange_direct"] = {
                 "ms": ms, "Gpts/s_total": N * world / (ms * 1e-3) / 1e9, "fits_receive_buffers": fits,
                 "ms_with_per_thread_feature_stores": ms_plain,
                 "stage_ms": {"count_and_count_matrix": stages[0], "move_over_nvlink_and_barrier": stages[1], "scatter_normalise": stages[2]},
-                "nvlink_GB/s_out_per_gpu_during_move": sent_remote / (stages[1] * 1e-3) / 1e9 if fits else None,
+                "move_kernel_ms": move_ms,
+                "nvlink_GB/s_out_per_gpu_during_move": sent_remote / (move_ms * 1e-3) / 1e9 if fits else None,
                 "note": "same, but the partition kernel stores its sorted chunks straight into the owners' receive buffers "
                         "(peer memory over NVLink); collectives left: the count matrix and one barrier"}
             px.close()
