@@ -521,6 +521,20 @@ def run_extras(L, dev, local, rank, world, peak, ex):
                                        "timing": "10 back-to-back calls incl. zero-fill (and normalise for mean); working set > L2"}
     if world > 1:
         from robogoat_b200 import sharding
+        # optional gather of the batch-sharded resample outputs (not on the timed headline path)
+        shard = torch.empty((HEADLINE["B"], HEADLINE["T"], HEADLINE["D"]), dtype=torch.bfloat16, device=dev)
+        for _ in range(2):
+            g = sharding.gather_rows(shard, HEADLINE["B"] * world); del g
+        barrier(world)
+        e0.record()
+        for _ in range(3):
+            g = sharding.gather_rows(shard, HEADLINE["B"] * world); del g
+        e1.record(); torch.cuda.synchronize()
+        ms = max_over_ranks(e0.elapsed_time(e1) / 3, world, dev)
+        ex["resample_output_all_gather"] = {"ms": ms, "bytes_per_gpu_shard": shard.numel() * 2,
+                                            "bus_GB/s": shard.numel() * 2 * (world - 1) / (ms * 1e-3) / 1e9,
+                                            "note": "NCCL all-gather of every rank's [4096,250,256] bf16 output into a full copy on every rank"}
+        del shard
         fn = lambda: sharding.voxelize_sharded(pts, feats, mode="mean", **kw)
         for _ in range(2):
             r = fn(); del r
