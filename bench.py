@@ -129,6 +129,38 @@ def physical_gpu_index(local_rank: int) -> int:
     return local_rank
 
 
+class LineGuard:
+    """Prints the benchmark's one JSON line exactly once: normally from ``finish()``; from a timer thread if
+    ``limit_s`` seconds pass first (the main thread may then be stuck inside a collective), after which the
+    process ends with status 0.  ``printer`` is False on the ranks that print nothing; their timer only ends them."""
+
+    def __init__(self, printer: bool, build_line, extras: dict, limit_s):
+        self.printer, self.build_line, self.extras, self.limit_s = printer, build_line, extras, limit_s
+        self._once = threading.Lock()
+        self._timer = None
+
+    def _emit(self):
+        if self._once.acquire(blocking=False) and self.printer:
+            print(json.dumps(self.build_line()), flush=True)
+
+    def _give_up(self):
+        self.extras["watchdog"] = f"side measurements did not finish within {self.limit_s} s; line printed without the rest"
+        self._emit()
+        sys.stdout.flush()
+        os._exit(0)
+
+    def start(self):
+        if self.limit_s is not None:
+            self._timer = threading.Timer(self.limit_s, self._give_up)
+            self._timer.daemon = True
+            self._timer.start()
+
+    def finish(self):
+        if self._timer is not None:
+            self._timer.cancel()
+        self._emit()
+
+
 def dist_setup(n_gpus: int):
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -374,13 +406,8 @@ def run_ours(args):
     if rank == 0:
         cpu_baseline = cpu_baseline_leg(world)
 
-    emitted = threading.Lock()
-
-    def emit():
-        """Rank 0 prints the one JSON line (once, whoever gets here first: the main thread or the watchdog)."""
-        if rank != 0 or not emitted.acquire(blocking=False):
-            return
-        line = {
+    def build_line():
+        return {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
             "arithmetic": "bf16 rows widened to f32, every product and sum rounded separately, one round-to-nearest back to bf16",
@@ -393,29 +420,18 @@ def run_ours(args):
             "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e, "gpu_launches": args.steps, "clocks": clocks,
             "extras": dict(extras),
         }
-        print(json.dumps(line), flush=True)
 
     # The side measurements below include collectives.  Should one of them ever stall on some rank, the headline line
-    # above must still come out: a timer prints it with whatever extras exist and ends the process on every rank.
-    watchdog = None
-    if world > 1 and not args.no_extras:
-        def give_up():
-            extras["watchdog"] = f"side measurements did not finish within {EXTRAS_LIMIT_S} s; line printed without the rest"
-            emit()
-            sys.stdout.flush()
-            os._exit(0)
-        watchdog = threading.Timer(EXTRAS_LIMIT_S, give_up)
-        watchdog.daemon = True
-        watchdog.start()
+    # must still come out: a timer prints it with whatever extras exist and ends the process on every rank.
+    guard = LineGuard(rank == 0, build_line, extras, EXTRAS_LIMIT_S if (world > 1 and not args.no_extras) else None)
+    guard.start()
     if not args.no_extras:
         try:
             run_extras(L, dev, local, rank, world, peak, extras)
         except Exception as e:  # the headline line must survive a failing side measurement
             extras["error"] = repr(e)
     barrier(world)
-    if watchdog is not None:
-        watchdog.cancel()
-    emit()
+    guard.finish()
     if world > 1:
         import torch.distributed as dist
         dist.destroy_process_group()

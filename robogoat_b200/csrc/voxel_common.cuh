@@ -1,0 +1,121 @@
+// Shared device code of the voxelisation kernels: grid geometry and the voxel id in IEEE fp32,
+// the vector reductions, the 128-point tile loads and the per-point scatter.
+#pragma once
+
+#include "rc_common.cuh"
+
+namespace rc {
+namespace vox {
+
+
+constexpr int kThreads = 256;
+constexpr int kPointsPerLane = 4;
+constexpr int kPointsPerWarp = 32 * kPointsPerLane;            // 128
+constexpr int kPointsPerBlock = kThreads * kPointsPerLane;     // 1024
+constexpr size_t kResidentBytes = 96u << 20;   // accumulators up to this size are treated as L2-resident (one pass)
+constexpr long long kProbeMinPoints = 1ll << 20;  // below this the order probe is not worth its launch
+constexpr int kAutoMeanPasses = 6;             // slab passes of the two-phase mean scatter on larger grids
+constexpr double kSlabPassBytes = 448.0 * 1048576.0;          // accumulator bytes per slab pass of rc_voxel_scatter_ids
+constexpr size_t kSmallGridBytes = 64u << 20;                  // grids up to this size are cleared by voxel_zero_kernel
+
+struct VoxelGeom {
+    float minx, miny, minz, vs;
+    int gx, gy, gz;
+    float fgx, fgy, fgz;
+};
+
+// flat voxel id, or -1 for a dropped point (NaN and infinities fail the range test)
+__device__ __forceinline__ long long voxel_id(float x, float y, float z, const VoxelGeom& g) {
+    const float fx = floorf(__fdiv_rn(__fsub_rn(x, g.minx), g.vs));
+    const float fy = floorf(__fdiv_rn(__fsub_rn(y, g.miny), g.vs));
+    const float fz = floorf(__fdiv_rn(__fsub_rn(z, g.minz), g.vs));
+    const bool in = (fx >= 0.0f) && (fx < g.fgx) && (fy >= 0.0f) && (fy < g.fgy) && (fz >= 0.0f) && (fz < g.fgz);
+    if (!in) return -1;
+    return (static_cast<long long>(fz) * g.gy + static_cast<long long>(fy)) * g.gx + static_cast<long long>(fx);
+}
+
+__device__ __forceinline__ void red_add_v4(float* addr, float4 v) {
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};"
+                 :: "l"(addr), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+}
+__device__ __forceinline__ void red_add_v2(float* addr, float2 v) {
+    asm volatile("red.global.add.v2.f32 [%0], {%1, %2};" :: "l"(addr), "f"(v.x), "f"(v.y) : "memory");
+}
+
+// ordered-integer image of a float: larger float <=> larger signed int
+__device__ __forceinline__ int float_ordered(float f) {
+    const int i = __float_as_int(f);
+    return (i >= 0) ? i : (i ^ 0x7fffffff);
+}
+
+enum : int { kCount = 0, kOccupancy = 1, kMean = 2, kMax = 3, kOccupancyU8 = 4 };
+
+// The xyz of a warp's 128-point tile: point i of a lane is (base + i*32 + lane).
+// Fast tiles (full, 16-byte aligned) are fetched with three coalesced 16-byte loads per lane
+// (tile_issue), issued one tile ahead of their use, and transposed through the warp's slice of
+// shared memory (tile_unpack); other tiles are read with scalar loads (tile_load_slow).
+__device__ __forceinline__ void tile_issue(const float* __restrict__ pts, long long base, int lane, float4 (&v)[3]) {
+    const float4* src = reinterpret_cast<const float4*>(pts + base * 3);
+#pragma unroll
+    for (int k = 0; k < 3; ++k) v[k] = __ldcs(src + k * 32 + lane);
+}
+__device__ __forceinline__ void tile_unpack(const float4 (&v)[3], float* s_warp, int lane,
+                                            float (&x)[kPointsPerLane], float (&y)[kPointsPerLane],
+                                            float (&z)[kPointsPerLane]) {
+    float4* dst = reinterpret_cast<float4*>(s_warp);
+#pragma unroll
+    for (int k = 0; k < 3; ++k) dst[k * 32 + lane] = v[k];
+    __syncwarp();
+#pragma unroll
+    for (int i = 0; i < kPointsPerLane; ++i) {
+        const float* q = s_warp + (i * 32 + lane) * 3;  // stride of three words: conflict free
+        x[i] = q[0]; y[i] = q[1]; z[i] = q[2];
+    }
+    __syncwarp();
+}
+__device__ __forceinline__ void tile_load_slow(const float* __restrict__ pts, long long base, long long N, int lane,
+                                               float (&x)[kPointsPerLane], float (&y)[kPointsPerLane],
+                                               float (&z)[kPointsPerLane]) {
+#pragma unroll
+    for (int i = 0; i < kPointsPerLane; ++i) {
+        const long long pi = base + i * 32 + lane;
+        if (pi < N) {
+            x[i] = __ldg(pts + pi * 3 + 0);
+            y[i] = __ldg(pts + pi * 3 + 1);
+            z[i] = __ldg(pts + pi * 3 + 2);
+        } else {
+            x[i] = y[i] = z[i] = __int_as_float(0x7fc00000);  // NaN: dropped
+        }
+    }
+}
+
+// Programmatic dependent launch (sm_90+): a kernel launched with the programmatic-serialisation
+// attribute may start while its predecessor in the stream is still running; it must execute
+// grid_dependency_wait() before touching memory the predecessor writes.  Launched normally, the
+// wait returns at once.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_dependency_release() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <int MODE>
+__device__ __forceinline__ void scatter_one(int id, long long pi, const float* __restrict__ feats, void* grid_v,
+                                            int* __restrict__ counts, int F) {
+    if (MODE == kCount) {
+        atomicAdd(static_cast<int*>(grid_v) + id, 1);
+    } else if (MODE == kOccupancy) {
+        static_cast<int*>(grid_v)[id] = 1;
+    } else {
+        const float* f = feats + pi * F;
+        float* o = static_cast<float*>(grid_v) + static_cast<long long>(id) * F;
+        if ((F & 3) == 0) {
+            for (int c = 0; c < F; c += 4) red_add_v4(o + c, __ldcs(reinterpret_cast<const float4*>(f + c)));
+        } else if ((F & 1) == 0) {
+            for (int c = 0; c < F; c += 2) red_add_v2(o + c, __ldcs(reinterpret_cast<const float2*>(f + c)));
+        } else {
+            for (int c = 0; c < F; ++c) atomicAdd(o + c, __ldg(f + c));
+        }
+        atomicAdd(counts + id, 1);
+    }
+}
+
+}  // namespace vox
+}  // namespace rc
