@@ -620,7 +620,7 @@ def run_extras(L, dev, local, rank, world, peak, ex):
                 r = fn(); del r
             e1.record(); torch.cuda.synchronize()
             ms = max_over_ranks(e0.elapsed_time(e1) / 5, world, dev)
-            L.rc_set_option(2, 0)                   # per-thread feature stores instead of bulk copies over NVLink
+            L.rc_set_option(2, 0)                   # sorted chunks written as they lie instead of line-aligned groups
             for _ in range(2):
                 r = fn(); del r
             barrier(world)
@@ -640,7 +640,8 @@ def run_extras(L, dev, local, rank, world, peak, ex):
             if fits:
                 ops.voxel_partition_move_cuda(pts, feats, kw["grid_min"], kw["voxel_size"], kw["grid_size"], world, K,
                                               [px.ids.peers[p // K] for p in range(world * K)],
-                                              [px.features.peers[p // K] for p in range(world * K)], plan["dest_start"], scratch)
+                                              [px.features.peers[p // K] for p in range(world * K)], plan["dest_start"], scratch,
+                                              remote=True)
                 ev_move.record()
                 px.stream_barrier()
             ev[2].record()
@@ -653,7 +654,7 @@ def run_extras(L, dev, local, rank, world, peak, ex):
             move_ms = max_over_ranks(ev[1].elapsed_time(ev_move), world, dev) if fits else None
             ex["voxel_mean_sharded_point_exchange_direct"] = {
                 "ms": ms, "Gpts/s_total": N * world / (ms * 1e-3) / 1e9, "fits_receive_buffers": fits,
-                "ms_with_per_thread_feature_stores": ms_plain,
+                "ms_without_line_aligned_stores": ms_plain,
                 "stage_ms": {"count_and_count_matrix": stages[0], "move_over_nvlink_and_barrier": stages[1], "scatter_normalise": stages[2]},
                 "move_kernel_ms": move_ms,
                 "nvlink_GB/s_out_per_gpu_during_move": sent_remote / (move_ms * 1e-3) / 1e9 if fits else None,

@@ -192,7 +192,9 @@ RC_API int rc_voxel_normalize(float* grid, const int32_t* counts, int64_t voxel_
  *   given in HOST arrays of n_parts entries and may be buffers of other GPUs mapped with rc_peer_open;
  *   the caller guarantees room for the counted points.  With dest_start == NULL the parts are packed
  *   back to back in part order using part_counts_device (then all destinations are normally the same
- *   buffer).  dest_features may be NULL (ids only).
+ *   buffer).  dest_features may be NULL (ids only).  flags: RC_PARTITION_REMOTE_DESTINATIONS when destinations
+ *   lie on other GPUs - the kernel then shapes every warp store as one 128-byte-aligned group (see
+ *   RC_OPT_PART_ALIGNED_STORE); the bytes written are the same either way.
  * rc_voxel_partition: count + move into local buffers ids_out [N] / features_out [N, F], parts back to
  *   back; only the first sum(part_counts) entries are written.
  * Limits: N at most 2^31 - 4096, gx*gy*gz below 2^31.  Everything runs on `stream`.
@@ -207,6 +209,7 @@ RC_API int rc_voxel_normalize(float* grid, const int32_t* counts, int64_t voxel_
  *   records; run_pass[r] in [0, n_passes)): the runs of pass 0 are accumulated first, then pass 1, ...
  *   Give every sub-range of the slab its own pass and the atomics of a pass stay within that sub-range.
  */
+#define RC_PARTITION_REMOTE_DESTINATIONS 1u
 RC_API uint64_t rc_voxel_partition_scratch_bytes(int64_t N, int32_t n_parts, int device);
 RC_API int rc_voxel_partition_count(const float* points, int64_t N, const float grid_min_host[3], float voxel_size,
                                     const int32_t grid_size_host[3], int32_t n_groups, int32_t parts_per_group,
@@ -216,8 +219,8 @@ RC_API int rc_voxel_partition_move(const float* points, const float* features, i
                                    const float grid_min_host[3], float voxel_size, const int32_t grid_size_host[3],
                                    int32_t n_groups, int32_t parts_per_group, void* const* dest_ids,
                                    void* const* dest_features, const int64_t* dest_start,
-                                   const int64_t* part_counts_device, const void* scratch, uint64_t scratch_bytes,
-                                   int device, void* stream);
+                                   const int64_t* part_counts_device, uint32_t flags, const void* scratch,
+                                   uint64_t scratch_bytes, int device, void* stream);
 RC_API int rc_voxel_partition(const float* points, const float* features, int64_t N, int32_t F,
                               const float grid_min_host[3], float voxel_size, const int32_t grid_size_host[3],
                               int32_t n_groups, int32_t parts_per_group, int32_t* ids_out, float* features_out,
@@ -274,15 +277,16 @@ RC_API int rc_voxelize_mean_static(const float* points, const float* features, f
  * RC_OPT_VOXEL_PASSES (default 0 = choose automatically): number of slab passes of the count /
  * mean / max scatter; each pass re-reads the coordinates but scatters into only 1/passes of the
  * grid, which keeps the touched part of large sparse grids resident in L2.
- * RC_OPT_PART_BULK_STORE: how rc_voxel_partition_move writes 4-wide feature rows.  1 (default): with bulk
- * asynchronous copies from shared memory (one request per run of sorted records) when a destination lies
- * on another GPU, with per-thread stores otherwise; 0: always per-thread stores; 2: always bulk copies.
- * All produce identical bytes.
+ * RC_OPT_PART_ALIGNED_STORE: how rc_voxel_partition_move lays its warp stores.  1 (default): when the call
+ * carries RC_PARTITION_REMOTE_DESTINATIONS every warp store covers one 32-record-aligned group of the destination
+ * (full 128-byte lines; records that do not fill a group yet wait in shared memory for the next chunk),
+ * otherwise the sorted chunk is written as it lies; 0: never aligned; 2: always aligned.  All produce
+ * identical bytes.
  * No counterpart in the reference.
  */
 #define RC_OPT_BLOCK_KERNEL 0
 #define RC_OPT_VOXEL_PASSES 1
-#define RC_OPT_PART_BULK_STORE 2
+#define RC_OPT_PART_ALIGNED_STORE 2
 RC_API int rc_set_option(int option, int value);
 
 /*

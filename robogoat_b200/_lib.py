@@ -78,7 +78,7 @@ def _declare(L: ctypes.CDLL) -> None:
     L.rc_voxel_partition_count.argtypes = [vp, i64, fp, f32, ip, i32, i32, vp, vp, ctypes.c_uint64, ci, vp]
     L.rc_voxel_partition_count.restype = ci
     L.rc_voxel_partition_move.argtypes = [vp, vp, i64, i32, fp, f32, ip, i32, i32, ctypes.POINTER(vp), ctypes.POINTER(vp),
-                                          ctypes.POINTER(i64), vp, vp, ctypes.c_uint64, ci, vp]
+                                          ctypes.POINTER(i64), vp, u32, vp, ctypes.c_uint64, ci, vp]
     L.rc_voxel_partition_move.restype = ci
     L.rc_voxel_scatter_runs.argtypes = [vp, vp, vp, vp, i32, i64, i64, ctypes.POINTER(i64), ctypes.POINTER(i64), ip, i32, i32,
                                         ci, u32, ci, vp]

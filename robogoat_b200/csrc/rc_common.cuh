@@ -77,6 +77,6 @@ int ensure_dynamic_smem(const void* kernel, int device, size_t bytes);
 // process-wide switches behind rc_set_option
 extern std::atomic<int> g_allow_block_kernel;  // RC_OPT_BLOCK_KERNEL
 extern std::atomic<int> g_voxel_passes;        // RC_OPT_VOXEL_PASSES
-extern std::atomic<int> g_part_bulk_store;     // RC_OPT_PART_BULK_STORE
+extern std::atomic<int> g_part_aligned_store;     // RC_OPT_PART_ALIGNED_STORE
 
 }  // namespace rc

@@ -69,19 +69,7 @@ __device__ __forceinline__ int voxel_id32(float x, float y, float z, const Voxel
     return (static_cast<int>(fz) * g.gy + static_cast<int>(fy)) * g.gx + static_cast<int>(fx);
 }
 
-// Bulk asynchronous copy shared -> global (the TMA engine moves a whole run of sorted records with one
-// request, to local or peer memory alike).  Both addresses 16-byte aligned, size a multiple of 16 bytes.
-__device__ __forceinline__ void bulk_store(void* dst_global, const void* src_shared, unsigned int bytes) {
-    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
-                 :: "l"(__cvta_generic_to_global(dst_global)),
-                    "r"(static_cast<unsigned int>(__cvta_generic_to_shared(src_shared))), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
-__device__ __forceinline__ void bulk_wait_read_all_but_one() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
-__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
-__device__ __forceinline__ void fence_async_shared() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-
-template <bool MOVE, bool BULK>
+template <bool MOVE, bool ALIGNED>
 __global__ void __launch_bounds__(kThreads, 5)
 voxel_part_kernel(const float* __restrict__ pts, const float* __restrict__ feats, long long N, int F, VoxelGeom g,
                   bool pts_aligned, bool vec4, PartRule rule, long long chunks_per_cta, int* __restrict__ table,
@@ -97,12 +85,17 @@ voxel_part_kernel(const float* __restrict__ pts, const float* __restrict__ feats
     __shared__ int s_total;
     __shared__ int s_sid[MOVE ? kChunk : 1];                 // the chunk's voxel ids, sorted by part
     __shared__ unsigned short s_meta[MOVE ? kChunk : 1];     // (index in chunk << 6) | part
-    // feature rows of the sorted chunk, staged for the bulk stores; two buffers so that a chunk is staged
-    // while the previous one is still being read by the copy engine
-    __shared__ __align__(16) float4 s_feat[BULK ? 2 : 1][BULK ? kChunk : 1];
-    constexpr bool bulk = MOVE && BULK;                      // callers pass BULK only together with vec4
-    float* pend_dst[2] = {nullptr, nullptr};                 // warp 0: the runs of the previous chunk, not yet issued
-    int pend_src[2] = {0, 0}, pend_cnt[2] = {0, 0}, pend_buf = 0;
+    // ALIGNED: every warp store covers one 32-slot-aligned group of a destination (a full 128-byte line of ids,
+    // four full lines of feature rows) - what stores to a peer GPU need to run at link rate.  The records of a
+    // part that do not fill a group yet wait here, as (voxel id, point index), for the next chunk.
+    __shared__ int s_cid[ALIGNED ? kMaxParts : 1][ALIGNED ? 32 : 1];
+    __shared__ int s_cpt[ALIGNED ? kMaxParts : 1][ALIGNED ? 32 : 1];
+    __shared__ int s_cc[ALIGNED ? kMaxParts : 1];            // waiting records per part
+    __shared__ int s_w[ALIGNED ? kMaxParts : 1];             // records of the part written with this chunk
+    __shared__ int s_lst[ALIGNED ? kMaxParts : 1];           // start of the part's run in the sorted chunk
+    __shared__ int s_tot[ALIGNED ? kMaxParts : 1];           // length of that run
+    __shared__ int s_gstart[ALIGNED ? kMaxParts + 1 : 1];    // prefix of the parts' group counts
+    __shared__ long long s_D[ALIGNED ? kMaxParts : 1];       // destination slot of the part's first unwritten record
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
     const unsigned int lt_mask = (1u << lane) - 1u;
@@ -120,6 +113,7 @@ voxel_part_kernel(const float* __restrict__ pts, const float* __restrict__ feats
                 start = dest.start[p];
             }
             s_cur[p] = start + table[static_cast<long long>(blockIdx.x) * P + p];
+            if (ALIGNED) s_cc[p] = 0;
         }
     }
     __syncthreads();
@@ -222,14 +216,6 @@ voxel_part_kernel(const float* __restrict__ pts, const float* __restrict__ feats
         // lane p, and p + 32 when there are more than 32 parts, sums part p over the warps, the totals are
         // prefixed over the parts with shuffles, and the lane keeps the first sorted slot of this warp's
         // points of its part(s) in registers.
-        if (bulk && warp == 0) {
-            // the previous chunk's feature rows are staged (its threads fenced before the barrier): one bulk
-            // store per part and lane
-#pragma unroll
-            for (int h = 0; h < 2; ++h)
-                if (pend_cnt[h] > 0) bulk_store(pend_dst[h], &s_feat[pend_buf][pend_src[h]], static_cast<unsigned int>(pend_cnt[h]) * 16u);
-            bulk_commit();
-        }
         const bool wide = P > 32;                                   // uniform: the upper half is skipped for <= 32 parts
         int tot[2] = {0, 0}, mine[2] = {0, 0};
 #pragma unroll
@@ -262,23 +248,48 @@ voxel_part_kernel(const float* __restrict__ pts, const float* __restrict__ feats
         const int first0 = lstart[0] + mine[0], first1 = lstart[1] + mine[1];
         if (warp == 0) {   // destinations of the sorted slots, advanced by this chunk
             if (lane == 31) s_total = sum0 + inc1;
+            if (!ALIGNED) {
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                const int p = lane + 32 * h;
-                if (p < P) {
-                    const long long first = s_cur[p] - lstart[h];
-                    s_adj_ids[p] = dest.ids[p] + first;
-                    s_adj_feats[p] = (dest.feats[p] != nullptr) ? dest.feats[p] + first * F : nullptr;
-                    pend_dst[h] = bulk ? dest.feats[p] + s_cur[p] * 4 : nullptr;
-                    pend_src[h] = lstart[h];
-                    pend_cnt[h] = tot[h];
-                    s_cur[p] += tot[h];
-                } else {
-                    pend_cnt[h] = 0;
+                for (int h = 0; h < 2; ++h) {
+                    const int p = lane + 32 * h;
+                    if (p < P) {
+                        const long long first = s_cur[p] - lstart[h];
+                        s_adj_ids[p] = dest.ids[p] + first;
+                        s_adj_feats[p] = (dest.feats[p] != nullptr) ? dest.feats[p] + first * F : nullptr;
+                        s_cur[p] += tot[h];
+                    }
                 }
+            } else {
+                // per part: the stream to write is the waiting records followed by this chunk's run; everything
+                // up to the last full group goes out now (all of it with the CTA's last chunk)
+                const bool last = chunk == c1 - 1;
+                int groups[2] = {0, 0};
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const int p = lane + 32 * h;
+                    if (p < P) {
+                        const long long D = s_cur[p];
+                        const int hh = static_cast<int>(D & 31);
+                        const int n = s_cc[p] + tot[h];
+                        int w = last ? n : (((hh + n) & ~31) - hh);
+                        if (w < 0) w = 0;
+                        groups[h] = (w > 0) ? ((hh + w + 31) >> 5) : 0;
+                        s_w[p] = w; s_lst[p] = lstart[h]; s_tot[p] = tot[h]; s_D[p] = D;
+                        s_cur[p] = D + w;
+                    }
+                }
+                int g0 = groups[0], g1 = groups[1];
+#pragma unroll
+                for (int off = 1; off < 32; off <<= 1) {
+                    const int a = __shfl_up_sync(0xffffffffu, g0, off);
+                    const int b = __shfl_up_sync(0xffffffffu, g1, off);
+                    if (lane >= off) { g0 += a; g1 += b; }
+                }
+                const int gsum0 = __shfl_sync(0xffffffffu, g0, 31);
+                if (lane < P) s_gstart[lane + 1] = g0;                       // inclusive prefix = start of the next part
+                if (lane + 32 < P) s_gstart[lane + 33] = gsum0 + g1;
+                if (lane == 0) s_gstart[0] = 0;
             }
-            pend_buf = chunk & 1;
-            if (bulk) bulk_wait_read_all_but_one();   // the buffer this chunk stages into was read two chunks ago
         }
 #pragma unroll
         for (int i = 0; i < kPointsPerLane; ++i) {
@@ -293,50 +304,82 @@ voxel_part_kernel(const float* __restrict__ pts, const float* __restrict__ feats
         }
         __syncthreads();
         for (int p = lane; p < P; p += 32) wcnt[p] = 0;      // own row, for the next chunk; every warp has read it
-        const int n = s_total;
-        if (vec4) {
-            float4 f4[kPointsPerLane];
-            int meta[kPointsPerLane];
-#pragma unroll
-            for (int m = 0; m < kPointsPerLane; ++m) {
-                const int j = threadIdx.x + m * kThreads;
-                meta[m] = (j < n) ? s_meta[j] : -1;
-                if (j < n) f4[m] = __ldcs(reinterpret_cast<const float4*>(feats) + (cbase + (meta[m] >> 6)));
-            }
-#pragma unroll
-            for (int m = 0; m < kPointsPerLane; ++m) {
-                const int j = threadIdx.x + m * kThreads;
-                if (meta[m] >= 0) {
-                    const int p = meta[m] & 63;
-                    s_adj_ids[p][j] = s_sid[j];
-                    if (bulk) s_feat[chunk & 1][j] = f4[m];
-                    else reinterpret_cast<float4*>(s_adj_feats[p])[j] = f4[m];
+        if (ALIGNED) {
+            const int G = s_gstart[P];
+            for (int g = warp; g < G; g += kThreads / 32) {
+                // the part whose groups contain g: as many parts end at or before g
+                int p = __popc(__ballot_sync(0xffffffffu, lane < P && s_gstart[lane + 1] <= g));
+                if (P > 32) p += __popc(__ballot_sync(0xffffffffu, lane + 32 < P && s_gstart[lane + 33] <= g));
+                const long long D = s_D[p];
+                const int r = (g - s_gstart[p]) * 32 + lane - static_cast<int>(D & 31);    // record of the part's stream
+                if (r >= 0 && r < s_w[p]) {
+                    const int c = s_cc[p];
+                    int vid, pidx;
+                    if (r < c) {
+                        vid = s_cid[p][r];
+                        pidx = s_cpt[p][r];
+                    } else {
+                        const int j = s_lst[p] + r - c;
+                        vid = s_sid[j];
+                        pidx = cbase + (s_meta[j] >> 6);
+                    }
+                    dest.ids[p][D + r] = vid;
+                    float* fo = dest.feats[p];
+                    if (vec4) {
+                        reinterpret_cast<float4*>(fo)[D + r] = __ldcs(reinterpret_cast<const float4*>(feats) + pidx);
+                    } else if (fo != nullptr) {
+                        const float* fi = feats + static_cast<long long>(pidx) * F;
+                        for (int ch = 0; ch < F; ++ch) fo[(D + r) * F + ch] = __ldg(fi + ch);
+                    }
                 }
             }
-            if (bulk) fence_async_shared();   // staged rows become visible to the copy engine; issued after the next barrier
+            __syncthreads();   // the waiting records have been read; now replace them
+            for (int sl = threadIdx.x; sl < P * 32; sl += kThreads) {
+                const int p = sl >> 5, i = sl & 31;           // one warp per part: its 32 waiting slots
+                const int c = s_cc[p], w = s_w[p], n = c + s_tot[p];
+                const int r = i + w;
+                if (r >= (w > c ? w : c) && r < n) {          // records of this chunk's run that stay behind
+                    const int j = s_lst[p] + r - c;
+                    s_cid[p][i] = s_sid[j];
+                    s_cpt[p][i] = cbase + (s_meta[j] >> 6);
+                }
+                __syncwarp();
+                if (i == 0) s_cc[p] = n - w;
+            }
         } else {
-            for (int j = threadIdx.x; j < n; j += kThreads) {
-                const int meta = s_meta[j];
-                const int p = meta & 63;
-                s_adj_ids[p][j] = s_sid[j];
-                float* fo = s_adj_feats[p];
-                if (fo != nullptr) {
-                    const float* fi = feats + static_cast<long long>(cbase + (meta >> 6)) * F;
-                    for (int c = 0; c < F; ++c) fo[static_cast<long long>(j) * F + c] = __ldg(fi + c);
+            const int n = s_total;
+            if (vec4) {
+                float4 f4[kPointsPerLane];
+                int meta[kPointsPerLane];
+    #pragma unroll
+                for (int m = 0; m < kPointsPerLane; ++m) {
+                    const int j = threadIdx.x + m * kThreads;
+                    meta[m] = (j < n) ? s_meta[j] : -1;
+                    if (j < n) f4[m] = __ldcs(reinterpret_cast<const float4*>(feats) + (cbase + (meta[m] >> 6)));
+                }
+    #pragma unroll
+                for (int m = 0; m < kPointsPerLane; ++m) {
+                    const int j = threadIdx.x + m * kThreads;
+                    if (meta[m] >= 0) {
+                        const int p = meta[m] & 63;
+                        s_adj_ids[p][j] = s_sid[j];
+                        reinterpret_cast<float4*>(s_adj_feats[p])[j] = f4[m];
+                    }
+                }
+            } else {
+                for (int j = threadIdx.x; j < n; j += kThreads) {
+                    const int meta = s_meta[j];
+                    const int p = meta & 63;
+                    s_adj_ids[p][j] = s_sid[j];
+                    float* fo = s_adj_feats[p];
+                    if (fo != nullptr) {
+                        const float* fi = feats + static_cast<long long>(cbase + (meta >> 6)) * F;
+                        for (int c = 0; c < F; ++c) fo[static_cast<long long>(j) * F + c] = __ldg(fi + c);
+                    }
                 }
             }
         }
         // no barrier here: the next chunk's first barrier comes before anything above is overwritten
-    }
-    if (MOVE && bulk) {
-        __syncthreads();
-        if (warp == 0) {
-#pragma unroll
-            for (int h = 0; h < 2; ++h)
-                if (pend_cnt[h] > 0) bulk_store(pend_dst[h], &s_feat[pend_buf][pend_src[h]], static_cast<unsigned int>(pend_cnt[h]) * 16u);
-            bulk_commit();
-            bulk_wait_all();                  // shared memory must outlive the copies
-        }
     }
     if (!MOVE) {
         __syncthreads();
@@ -516,8 +559,8 @@ int rc_voxel_partition_count(const float* points, int64_t N, const float grid_mi
 int rc_voxel_partition_move(const float* points, const float* features, int64_t N, int32_t F,
                             const float grid_min_host[3], float voxel_size, const int32_t grid_size_host[3],
                             int32_t n_groups, int32_t parts_per_group, void* const* dest_ids, void* const* dest_features,
-                            const int64_t* dest_start, const int64_t* part_counts_device, const void* scratch,
-                            uint64_t scratch_bytes, int device, void* stream) {
+                            const int64_t* dest_start, const int64_t* part_counts_device, uint32_t flags,
+                            const void* scratch, uint64_t scratch_bytes, int device, void* stream) {
     VoxelGeom g;
     PartRule rule;
     long long V = 0;
@@ -548,26 +591,16 @@ int rc_voxel_partition_move(const float* points, const float* features, int64_t 
     partition_plan(N, device, &blocks, &per);
     if (scratch_bytes < partition_table_bytes(blocks, rule.P) + static_cast<uint64_t>(N) * 4u) return RC_ERR_BAD_SHAPE;
     const bool vec4 = move_feats && F == 4 && all16;
-    // bulk (TMA) stores of the feature runs pay off over NVLink, per-thread stores in local memory
-    const int bulk_opt = rc::g_part_bulk_store.load(std::memory_order_relaxed);
-    bool bulk = vec4 && bulk_opt == 2;
-    if (vec4 && bulk_opt == 1) {
-        const float* seen = nullptr;
-        for (int p = 0; p < rule.P && !bulk; ++p) {
-            if (dest.feats[p] == seen) continue;
-            seen = dest.feats[p];
-            cudaPointerAttributes attr{};
-            if (cudaPointerGetAttributes(&attr, seen) != cudaSuccess) { cudaGetLastError(); continue; }
-            bulk = attr.type == cudaMemoryTypeDevice && attr.device != device;
-        }
-    }
+    // line-aligned warp stores pay off over NVLink; in local memory L2 merges partial lines anyway
+    const int aligned_opt = rc::g_part_aligned_store.load(std::memory_order_relaxed);
+    const bool line_aligned = aligned_opt == 2 || (aligned_opt == 1 && (flags & RC_PARTITION_REMOTE_DESTINATIONS) != 0);
     int* table = const_cast<int*>(static_cast<const int*>(scratch));
     int* ids_tmp = reinterpret_cast<int*>(const_cast<unsigned char*>(static_cast<const unsigned char*>(scratch)) +
                                           partition_table_bytes(blocks, rule.P));
     const unsigned int nb = static_cast<unsigned int>(blocks);
     const float* f_in = move_feats ? features : nullptr;
     const long long* pc_dev = reinterpret_cast<const long long*>(part_counts_device);
-    if (bulk)
+    if (line_aligned)
         voxel_part_kernel<true, true><<<nb, kThreads, 0, st>>>(points, f_in, N, F, g, rc::aligned_to(points, 16), vec4, rule, per,
                                                                table, ids_tmp, pc_dev, dest);
     else
@@ -589,7 +622,7 @@ int rc_voxel_partition(const float* points, const float* features, int64_t N, in
     for (int p = 0; p < kMaxParts; ++p) { ids_of[p] = ids_out; feats_of[p] = features_out; }
     return rc_voxel_partition_move(points, features, N, F, grid_min_host, voxel_size, grid_size_host, n_groups,
                                    parts_per_group, ids_of, features_out != nullptr ? feats_of : nullptr, nullptr,
-                                   part_counts, scratch, scratch_bytes, device, stream);
+                                   part_counts, 0u, scratch, scratch_bytes, device, stream);
 }
 
 int rc_voxel_scatter_runs(const int32_t* ids, const float* features, void* grid, int32_t* counts, int32_t F,

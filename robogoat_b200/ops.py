@@ -335,10 +335,11 @@ def voxel_partition_count_cuda(points: torch.Tensor, grid_min: Sequence[float], 
 def voxel_partition_move_cuda(points: torch.Tensor, features: Optional[torch.Tensor], grid_min: Sequence[float],
                               voxel_size: float, grid_size: Sequence[int], n_groups: int, parts_per_group: int,
                               dest_ids: Sequence[int], dest_features: Optional[Sequence[int]], dest_start: Sequence[int],
-                              scratch: torch.Tensor) -> None:
+                              scratch: torch.Tensor, remote: bool = False) -> None:
     """Second half: writes part p's voxel ids to the device address ``dest_ids[p]`` (and feature rows to
     ``dest_features[p]``) from slot ``dest_start[p]`` on.  The addresses may belong to peer GPUs' buffers
-    (``PeerBuffer``); the caller guarantees room for the counted points."""
+    (``PeerBuffer``) - say so with ``remote=True`` and every warp store is shaped as one aligned 128-byte group, which is
+    what stores over NVLink need; the caller guarantees room for the counted points."""
     P = _check_parts(int(n_groups), int(parts_per_group))
     _check(len(dest_ids) == P and len(dest_start) == P, "one destination and start slot per part")
     pts, feats = _partition_inputs(points, features if dest_features is not None else None)
@@ -353,7 +354,8 @@ def voxel_partition_move_cuda(points: torch.Tensor, features: Optional[torch.Ten
     gsz = (ctypes.c_int32 * 3)(*[int(v) for v in grid_size])
     rc = L.rc_voxel_partition_move(pts.data_ptr(), feats.data_ptr() if feats is not None else None, N, F, gmin,
                                    float(voxel_size), gsz, int(n_groups), int(parts_per_group), ids_arr, feats_arr,
-                                   start_arr, None, scratch.data_ptr(), scratch.numel(), dev.index, _stream_ptr(dev))
+                                   start_arr, None, 1 if remote else 0, scratch.data_ptr(), scratch.numel(), dev.index,
+                                   _stream_ptr(dev))
     _lib.check(rc, "voxel_partition_move")
 
 

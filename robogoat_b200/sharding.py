@@ -365,7 +365,8 @@ def voxelize_sharded_exchange(points_local: torch.Tensor, features_local: Option
         if max(plan["totals"]) <= direct.capacity:                               # after the owners' previous reads
             dest_ids = [direct.ids.peers[p // K] for p in range(ws * K)]
             dest_f = [direct.features.peers[p // K] for p in range(ws * K)] if feats is not None else None
-            ops.voxel_partition_move_cuda(points_local, feats, *geom, ws, K, dest_ids, dest_f, plan["dest_start"], scratch)
+            ops.voxel_partition_move_cuda(points_local, feats, *geom, ws, K, dest_ids, dest_f, plan["dest_start"], scratch,
+                                          remote=True)
             direct.stream_barrier()
             res = ops.voxel_scatter_runs_cuda(direct.ids.ptr, direct.features.ptr if feats is not None else None, dev, F,
                                               a, b, plan["runs"], K, mode)

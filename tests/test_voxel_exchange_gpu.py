@@ -89,12 +89,14 @@ def test_two_level_partition_and_run_scatter(groups, per_group, N, cuda_lib):
         assert bool(((grid2.cpu() - exp.reshape(V, 4)[a:b]).abs() <= tol[a:b]).all())
 
 
-def test_split_count_and_move_into_separate_destinations(cuda_lib):
+@pytest.mark.parametrize("remote", [False, True])      # True: the line-aligned store path, here with start slots off the line
+@pytest.mark.parametrize("N", [50_000, 6_000_000])
+def test_split_count_and_move_into_separate_destinations(remote, N, cuda_lib):
     """The two halves called separately, every part into a buffer of its own at a chosen slot - the form the
     direct exchange uses with peer buffers."""
     kw = dict(grid_min=[-2.0, -2.0, -2.0], voxel_size=0.25, grid_size=[16, 16, 16])
     V = 16 ** 3
-    pts, feats = _cloud(50_000, 5)
+    pts, feats = _cloud(N, 5)
     p, f = pts.to(DEV), feats.to(DEV)
     groups, per_group = 2, 3
     pc, scratch = ops.voxel_partition_count_cuda(p, kw["grid_min"], kw["voxel_size"], kw["grid_size"], groups, per_group)
@@ -107,7 +109,7 @@ def test_split_count_and_move_into_separate_destinations(cuda_lib):
     bufs_i = [torch.full((c + 2 * pad,), -7, dtype=torch.int32, device=DEV) for c in counts]
     bufs_f = [torch.full((c + 2 * pad, 4), -7.0, device=DEV) for c in counts]
     ops.voxel_partition_move_cuda(p, f, kw["grid_min"], kw["voxel_size"], kw["grid_size"], groups, per_group,
-                                  [t.data_ptr() for t in bufs_i], [t.data_ptr() for t in bufs_f], [pad] * 6, scratch)
+                                  [t.data_ptr() for t in bufs_i], [t.data_ptr() for t in bufs_f], [pad] * 6, scratch, remote=remote)
     for part in range(6):
         sel = owner == part
         assert torch.equal(bufs_i[part][pad:pad + counts[part]].cpu().long(), exp_ids[keep][sel])
@@ -188,17 +190,18 @@ def test_exchange_entry_points_reject_bad_arguments(cuda_lib):
         ops.voxel_scatter_ids_cuda(torch.zeros(8, dtype=torch.int32, device=DEV)[1:5], None, 0, 8, "count")  # misaligned ids
 
 
-@pytest.mark.parametrize("groups,per_group", [(2, 1), (8, 4), (4, 16)])
-def test_bulk_and_per_thread_feature_stores_write_the_same_bytes(groups, per_group, cuda_lib):
+@pytest.mark.parametrize("groups,per_group", [(1, 1), (2, 1), (8, 4), (4, 16), (2, 14), (8, 8)])
+@pytest.mark.parametrize("N", [150_001, 7_000_003])      # the larger cloud gives every CTA several chunks: records wait across chunks
+def test_line_aligned_and_plain_stores_write_the_same_bytes(groups, per_group, N, cuda_lib):
     from robogoat_b200 import _lib
     kw = dict(grid_min=[-2.0, -2.0, -2.0], voxel_size=0.125, grid_size=[32, 32, 32])
-    pts, feats = _cloud(150_001, 77)
+    pts, feats = _cloud(N, 77)
     p, f = pts.to(DEV), feats.to(DEV)
     L = _lib.load()
     outs = []
     try:
-        for bulk in (2, 0):
-            assert L.rc_set_option(2, bulk) == 0
+        for aligned in (2, 0):
+            assert L.rc_set_option(2, aligned) == 0
             ids, fb, pc = ops.voxel_partition_cuda(p, f, kw["grid_min"], kw["voxel_size"], kw["grid_size"], groups, per_group)
             n = int(pc.sum())
             outs.append((ids[:n].clone(), fb[:n].clone(), pc.clone()))
