@@ -70,7 +70,7 @@ __device__ __forceinline__ int voxel_id32(float x, float y, float z, const Voxel
 }
 
 template <bool MOVE, bool ALIGNED>
-__global__ void __launch_bounds__(kThreads, 5)
+__global__ void __launch_bounds__(kThreads, ALIGNED ? 4 : 5)
 voxel_part_kernel(const float* __restrict__ pts, const float* __restrict__ feats, long long N, int F, VoxelGeom g,
                   bool pts_aligned, bool vec4, PartRule rule, long long chunks_per_cta, int* __restrict__ table,
                   int* __restrict__ ids_tmp, const long long* __restrict__ part_counts,
@@ -306,30 +306,58 @@ voxel_part_kernel(const float* __restrict__ pts, const float* __restrict__ feats
         for (int p = lane; p < P; p += 32) wcnt[p] = 0;      // own row, for the next chunk; every warp has read it
         if (ALIGNED) {
             const int G = s_gstart[P];
-            for (int g = warp; g < G; g += kThreads / 32) {
-                // the part whose groups contain g: as many parts end at or before g
-                int p = __popc(__ballot_sync(0xffffffffu, lane < P && s_gstart[lane + 1] <= g));
-                if (P > 32) p += __popc(__ballot_sync(0xffffffffu, lane + 32 < P && s_gstart[lane + 33] <= g));
-                const long long D = s_D[p];
-                const int r = (g - s_gstart[p]) * 32 + lane - static_cast<int>(D & 31);    // record of the part's stream
-                if (r >= 0 && r < s_w[p]) {
-                    const int c = s_cc[p];
-                    int vid, pidx;
-                    if (r < c) {
-                        vid = s_cid[p][r];
-                        pidx = s_cpt[p][r];
-                    } else {
-                        const int j = s_lst[p] + r - c;
-                        vid = s_sid[j];
-                        pidx = cbase + (s_meta[j] >> 6);
+            constexpr int kUnroll = 4;                       // groups per warp in flight: their feature loads overlap
+            for (int g0 = warp; g0 < G; g0 += kUnroll * (kThreads / 32)) {
+                int vid[kUnroll], pidx[kUnroll], pp[kUnroll];
+                long long slot[kUnroll];
+#pragma unroll
+                for (int u = 0; u < kUnroll; ++u) {
+                    const int g = g0 + u * (kThreads / 32);
+                    pp[u] = -1;
+                    if (g < G) {                             // uniform
+                        // the part whose groups contain g: as many parts end at or before g
+                        int p = __popc(__ballot_sync(0xffffffffu, lane < P && s_gstart[lane + 1] <= g));
+                        if (P > 32) p += __popc(__ballot_sync(0xffffffffu, lane + 32 < P && s_gstart[lane + 33] <= g));
+                        const long long D = s_D[p];
+                        const int r = (g - s_gstart[p]) * 32 + lane - static_cast<int>(D & 31);   // record of the part's stream
+                        if (r >= 0 && r < s_w[p]) {
+                            const int c = s_cc[p];
+                            if (r < c) {
+                                vid[u] = s_cid[p][r];
+                                pidx[u] = s_cpt[p][r];
+                            } else {
+                                const int j = s_lst[p] + r - c;
+                                vid[u] = s_sid[j];
+                                pidx[u] = cbase + (s_meta[j] >> 6);
+                            }
+                            slot[u] = D + r;
+                            pp[u] = p;
+                        }
                     }
-                    dest.ids[p][D + r] = vid;
-                    float* fo = dest.feats[p];
-                    if (vec4) {
-                        reinterpret_cast<float4*>(fo)[D + r] = __ldcs(reinterpret_cast<const float4*>(feats) + pidx);
-                    } else if (fo != nullptr) {
-                        const float* fi = feats + static_cast<long long>(pidx) * F;
-                        for (int ch = 0; ch < F; ++ch) fo[(D + r) * F + ch] = __ldg(fi + ch);
+                }
+                if (vec4) {
+                    float4 f4[kUnroll];
+#pragma unroll
+                    for (int u = 0; u < kUnroll; ++u)
+                        if (pp[u] >= 0) f4[u] = __ldcs(reinterpret_cast<const float4*>(feats) + pidx[u]);
+#pragma unroll
+                    for (int u = 0; u < kUnroll; ++u) {
+                        if (pp[u] >= 0) {
+                            dest.ids[pp[u]][slot[u]] = vid[u];
+                            reinterpret_cast<float4*>(dest.feats[pp[u]])[slot[u]] = f4[u];
+                        }
+                    }
+                } else {
+#pragma unroll
+                    for (int u = 0; u < kUnroll; ++u) {
+                        if (pp[u] >= 0) {
+                            dest.ids[pp[u]][slot[u]] = vid[u];
+                            float* fo = dest.feats[pp[u]];
+                            if (fo != nullptr) {
+                                const float* fi = feats + static_cast<long long>(pidx[u]) * F;
+                                for (int ch = 0; ch < F; ++ch) fo[slot[u] * F + ch] = __ldg(fi + ch);
+                            }
+                        }
                     }
                 }
             }
