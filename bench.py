@@ -719,7 +719,10 @@ def run_profile_case(name: str):
         mode = name.split("_")[1]
         fn = lambda: robocache.voxelize_pointcloud(pts, feats if mode == "mean" else None, mode=mode, **kw)
         units = {"N": N}
-    elif name == "voxel_partition":
+    elif name in ("voxel_partition", "voxel_partition_aligned"):
+        if name.endswith("_aligned"):       # the write-out used for peer destinations, here with local ones
+            from robogoat_b200 import _lib
+            _lib.load().rc_set_option(2, 2)
         N = 1 << 24
         pts, feats = workloads.voxel_mixture_inputs(N, seed=0, device=dev)
         kw = workloads.VOXEL_MIXTURE_GEOMETRY
@@ -758,7 +761,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extras", action="store_true")
     ap.add_argument("--profile-case", default=None,
-                    help="run 4 launches of one kernel on a small case (resample, fusion, voxel_mean, voxel_count, voxel_occupancy, voxel_partition, voxel_scatter_runs; voxel_mean_full = headline size)")
+                    help="run 4 launches of one kernel on a small case (resample, fusion, voxel_mean, voxel_count, voxel_occupancy, voxel_partition, voxel_partition_aligned, voxel_scatter_runs; voxel_mean_full = headline size)")
     args = ap.parse_args()
     if args.profile_case:
         run_profile_case(args.profile_case)
