@@ -19,10 +19,12 @@ using namespace rc::vox;
 // part's column of that table into exclusive prefixes over the CTAs (one CTA per part); launch 3
 // (MOVE = true) walks the same chunks again - the count pass leaves every point's voxel id in the
 // scratch, so the coordinates are not read twice -, sorts each chunk by part in shared memory and writes
-// the sorted chunk out, so that every part receives runs of consecutive records: full-width stores
-// whether the destination is local memory or a peer's.  Ranks inside a warp come from
-// __match_any_sync and warps are prefixed in order, so input order is kept inside a part and the
-// result does not depend on scheduling.
+// the sorted chunk out, so that every part receives runs of consecutive records.  Ranks inside a
+// warp come from ballots over the bits of the part number and warps are prefixed in order, so input
+// order is kept inside a part and the result does not depend on scheduling.  For destinations on
+// other GPUs the write-out is line-aligned (ALIGNED = true): every warp store covers one
+// 32-record-aligned group of a destination, and records that do not fill a group yet wait in
+// shared memory for the CTA's next chunk; the bytes that end up in the destinations are the same.
 //
 // Parts are two-level: n_groups owners (ranks) with ceil(V / n_groups) voxel ids each, every owner's
 // range cut into parts_per_group sub-ranges of ceil(range / parts_per_group) ids; part = group *
@@ -76,8 +78,8 @@ voxel_part_kernel(const float* __restrict__ pts, const float* __restrict__ feats
                   int* __restrict__ ids_tmp, const long long* __restrict__ part_counts,
                   const __grid_constant__ PartDest dest) {
     __shared__ __align__(16) float s_xyz[MOVE ? 1 : kThreads / 32][MOVE ? 4 : kPointsPerWarp * 3];
-    // count pass: per-warp totals.  move pass: this chunk's per-warp counts, turned by warp 0 into the
-    // first slot of every (warp, part) in the sorted chunk
+    // count pass: per-warp totals.  move pass: this chunk's per-warp counts (every warp derives the
+    // layout of the sorted chunk from them by itself)
     __shared__ int s_wcnt[kThreads / 32][kMaxParts];
     __shared__ long long s_cur[MOVE ? kMaxParts : 1];        // next slot of each part in its destination
     __shared__ int* s_adj_ids[MOVE ? kMaxParts : 1];         // destination of sorted slot j of part p is s_adj_*[p] + j
