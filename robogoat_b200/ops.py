@@ -380,6 +380,9 @@ def voxel_scatter_runs_cuda(ids_ptr: int, features_ptr: Optional[int], device: t
     """
     if mode not in ("count", "occupancy", "mean"):
         raise RuntimeError(f"Invalid mode: {mode}. The run scatter supports 'count', 'occupancy' and 'mean'")
+    device = torch.device(device)
+    if device.index is None:                # "cuda" without an ordinal: the current device
+        device = torch.device("cuda", torch.cuda.current_device())
     nvox = int(id_end) - int(id_begin)
     _check(nvox >= 0 and id_begin >= 0, "bad voxel range")
     F = int(feature_width) if mode == "mean" else 0
