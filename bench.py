@@ -468,6 +468,25 @@ def run_extras(L, dev, local, rank, world, peak, ex):
     import robocache
     flush = L2Flush(dev)
 
+    # the headline workload generated from other seeds: how much the figure depends on the draw
+    if world == 1:
+        per_seed = {}
+        for seed in (1, 2, 3, 4):
+            s_src, s_st, s_tt = workloads.resample_inputs(B=HEADLINE["B"], S=HEADLINE["S"], D=HEADLINE["D"], T=HEADLINE["T"],
+                                                          dtype=torch.bfloat16, irregular_targets=True, seed=seed, device=dev)
+            fs = lambda: ops.resample_trajectories_cuda(s_src, s_st, s_tt)
+            for _ in range(5):
+                r = fs(); del r
+            a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a0.record()
+            for _ in range(20):
+                r = fs(); del r
+            a1.record(); torch.cuda.synchronize()
+            per_seed[seed] = a0.elapsed_time(a1) / 20
+            del s_src, s_st, s_tt
+        ex["resample_bf16_B4096_other_seeds_ms"] = {"ms_per_call": per_seed,
+                                                   "timing": "20 back-to-back calls through the Python binding (output allocation included)"}
+
     # fusion throughput, B=16384 per GPU, bf16
     Bf = 16384
     a = workloads.fusion_inputs(B=Bf, dtype=torch.bfloat16, seed=rank, device=dev)
