@@ -89,7 +89,9 @@ RC_API int rc_resample(const void* src, const float* source_times, const float* 
  * Resampling of variable-length items without padding.  The source rows of all items are packed
  * back to back: src_rows [sum S_b, D], source_times [sum S_b], and item b owns rows
  * [row_offsets[b], row_offsets[b+1]) (row_offsets: B+1 int64 on the device, ascending).  max_len is
- * an upper bound of the item lengths (host value; it sizes the shared-memory staging).
+ * an upper bound of the item lengths (host value; it sizes the shared-memory staging): an item longer than
+ * max_len is cut to its first max_len rows, and an item whose offsets do not ascend counts as empty.  Every
+ * row_offsets[b] must lie inside the packed rows (the library does not know their number).
  * The result equals padding every item to a common length by repeating its last step — what the
  * reference's loader does before batching (robocache/python/robocache/datasets/rtx_loader.py:214-221)
  * — and calling rc_resample, without materialising the padded batch.  Items with no rows yield zeros.
@@ -282,9 +284,15 @@ RC_API int rc_voxelize_mean_static(const float* points, const float* features, f
  * (full 128-byte lines; records that do not fill a group yet wait in shared memory for the next chunk),
  * otherwise the sorted chunk is written as it lies; 0: never aligned; 2: always aligned.  All produce
  * identical bytes.
+ * RC_OPT_BULK_WAIT_LIMIT (default -1 = built-in limit of 2^22 polls): how many times the TMA-staged kernel
+ * polls for its bulk copies before it gives up, counts the event (rc_bulk_wait_timeouts) and fetches the same
+ * bytes with ordinary loads.  0 makes every CTA give up at once - the way to exercise that fallback without
+ * anything going wrong on the GPU; results are identical.  After the fallback a CTA still waits, with the
+ * built-in limit, for its copies to land before it exits.
  * No counterpart in the reference.
  */
 #define RC_OPT_BLOCK_KERNEL 0
+#define RC_OPT_BULK_WAIT_LIMIT 3
 #define RC_OPT_VOXEL_PASSES 1
 #define RC_OPT_PART_ALIGNED_STORE 2
 RC_API int rc_set_option(int option, int value);

@@ -28,6 +28,11 @@ VOXEL_NO_NORMALIZE = 2
 VOXEL_WARP_AGGREGATE = 4
 STATIC_MAX_VOXELS = 1 << 21
 
+OPT_BLOCK_KERNEL = 0
+OPT_VOXEL_PASSES = 1
+OPT_PART_ALIGNED_STORE = 2
+OPT_BULK_WAIT_LIMIT = 3
+
 # every symbol the header declares; the CPU test-suite checks the built library exports them all
 EXPORTED_SYMBOLS = (
     "rc_resample", "rc_resample_strided", "rc_resample_ragged", "rc_fuse", "rc_fuse_strided", "rc_resample_brackets", "rc_voxelize", "rc_voxel_normalize", "rc_voxelize_mean_static",

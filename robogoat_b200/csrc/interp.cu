@@ -233,8 +233,12 @@ interp_gather_kernel(const __grid_constant__ InterpParams p) {
     auto first_row = [&](int k) -> long long {
         return RAGGED ? __ldg(p.s[k].row_offsets + b) : b * p.s[k].S;
     };
+    // ragged: the caller's bound max_len (held in S) sized the staged row, so an item that is longer than
+    // that, or offsets that do not ascend, are cut to [0, max_len] rows instead of running past the staging
     auto num_rows = [&](int k) -> int {
-        return RAGGED ? static_cast<int>(__ldg(p.s[k].row_offsets + b + 1) - __ldg(p.s[k].row_offsets + b)) : p.s[k].S;
+        if (!RAGGED) return p.s[k].S;
+        const long long n = __ldg(p.s[k].row_offsets + b + 1) - __ldg(p.s[k].row_offsets + b);
+        return static_cast<int>(n < 0 ? 0 : (n > p.s[k].S ? p.s[k].S : n));
     };
 
     if (STAGED) {
@@ -336,6 +340,7 @@ struct BlockParams {
     int brk_base;
     int vec_base;               // table of output-vector descriptors (16-byte path)
     unsigned int tx_bytes;      // sum of block_bytes
+    unsigned int wait_limit;    // polls of the first wait for the bulk copies (RC_OPT_BULK_WAIT_LIMIT)
 };
 
 // how often a CTA gave up waiting for its bulk copies and fetched the data with plain loads
@@ -374,10 +379,10 @@ __device__ __forceinline__ void bulk_load(void* dst_smem, const void* src_gmem, 
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                  :: "r"(smem_u32(dst_smem)), "l"(src_gmem), "r"(bytes), "r"(smem_u32(bar)) : "memory");
 }
-// bounded wait on phase `parity`; false if the limit ran out
-__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned int parity) {
+// bounded wait on phase `parity`: at most `limit` polls; false if they ran out
+__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned int parity, unsigned int limit) {
     const unsigned int addr = smem_u32(bar);
-    for (unsigned int i = 0; i < kMbarSpinLimit; ++i) {
+    for (unsigned int i = 0; i < limit; ++i) {
         unsigned int done;
         asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
                      : "=r"(done) : "r"(addr), "r"(parity) : "memory");
@@ -537,16 +542,24 @@ interp_block_kernel(const __grid_constant__ BlockParams p) {
 
     // One thread waits for the staged data (bounded); the others park at the barrier.  A CTA
     // whose wait runs out records it and fetches the same bytes with ordinary loads instead
-    // (a late bulk copy would only rewrite equal values).
+    // (a late bulk copy only rewrites equal values while this CTA still owns the shared memory).
     bool arrived = true;
-    if (tid == 0) arrived = mbar_wait(bar, 0);
-    if (__syncthreads_or(!arrived)) {
+    if (tid == 0) arrived = mbar_wait(bar, 0, p.wait_limit);
+    const bool gave_up = __syncthreads_or(!arrived);
+    if (gave_up) {
         if (tid == 0) atomicAdd(&g_bulk_wait_timeouts, 1u);
         block_fetch_plain(p, smem, b, tid, nthreads);
         __syncthreads();
     }
     unsigned char* out_tile = p.out + b * p.out_block_bytes + static_cast<long long>(t_begin) * p.out_row_bytes;
     block_compute<ES, V16>(p, smem, s_vec, out_tile, nrows, tid, nthreads);
+    if (gave_up) {
+        // The copies may still be in flight: the CTA must not hand its shared memory to the next CTA on this SM
+        // before they have landed.  Wait again, with the full limit; if even that runs out (a copy that never
+        // completes), the CTA leaves, and the count above is what tells the host.
+        if (tid == 0) mbar_wait(bar, 0, kMbarSpinLimit);
+        __syncthreads();
+    }
 }
 
 // ---------------------------------------------------------------- host side
@@ -649,6 +662,10 @@ bool try_launch_block(const LiveStream* ls, int ns, const float* tt, long long t
     p.tiles_t = static_cast<int>(tiles);
     p.rows_per_tile = static_cast<int>(rpt);
     p.tx_bytes = static_cast<unsigned int>(in_bytes);
+    {
+        const int opt = rc::g_bulk_wait_limit.load(std::memory_order_relaxed);
+        p.wait_limit = opt < 0 ? kMbarSpinLimit : static_cast<unsigned int>(opt);
+    }
     auto* kern = (es == 2) ? (v16 ? interp_block_kernel<2, true> : interp_block_kernel<2, false>)
                            : (v16 ? interp_block_kernel<4, true> : interp_block_kernel<4, false>);
     if (smem > 48 * 1024) {

@@ -27,8 +27,10 @@ using namespace rc::vox;
 
 // Zero-fill for small grids (latency regime): lets the scatter kernel that follows be scheduled
 // right away, so that its point loads and voxel-id arithmetic overlap this fill.
-__global__ void __launch_bounds__(kThreads) voxel_zero_kernel(unsigned char* __restrict__ p, long long bytes) {
+__global__ void __launch_bounds__(kThreads) voxel_zero_kernel(unsigned char* __restrict__ p, long long bytes,
+                                                              const int* __restrict__ gate = nullptr, int gate_want = 0) {
     grid_dependency_release();
+    if (gate != nullptr && *gate != gate_want) return;
     const long long n16 = bytes >> 4;
     uint4* p16 = reinterpret_cast<uint4*>(p);
     const long long stride = static_cast<long long>(gridDim.x) * kThreads;
@@ -277,9 +279,11 @@ voxel_scatter_ids_kernel(const int* __restrict__ ids, const float* __restrict__ 
 // loads in flight; empty regions of a sparse grid cost one streaming read of the counter plane.
 template <bool VEC4>
 __global__ void __launch_bounds__(kThreads)
-voxel_normalize_wide_kernel(float* __restrict__ grid, const int* __restrict__ counts, long long v0, long long v1, int F) {
+voxel_normalize_wide_kernel(float* __restrict__ grid, const int* __restrict__ counts, long long v0, long long v1, int F,
+                            const int* __restrict__ gate, int gate_want) {
     __shared__ int s_vox[kThreads / 32][256];
     __shared__ int s_cnt[kThreads / 32][256];
+    if (gate != nullptr && *gate != gate_want) return;
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
     const unsigned int lt_mask = (1u << lane) - 1u;
@@ -330,7 +334,9 @@ voxel_normalize_wide_kernel(float* __restrict__ grid, const int* __restrict__ co
 
 // mean pass 2, one voxel per thread: ragged ends of a range and unaligned buffers
 __global__ void __launch_bounds__(kThreads)
-voxel_normalize_scalar_kernel(float* __restrict__ grid, const int* __restrict__ counts, long long v0, long long v1, int F) {
+voxel_normalize_scalar_kernel(float* __restrict__ grid, const int* __restrict__ counts, long long v0, long long v1, int F,
+                              const int* __restrict__ gate, int gate_want) {
+    if (gate != nullptr && *gate != gate_want) return;
     const long long v = v0 + blockIdx.x * static_cast<long long>(kThreads) + threadIdx.x;
     if (v >= v1) return;
     const int c = counts[v];
@@ -412,6 +418,44 @@ int static_counts_address(int device, int** out) {
     return RC_OK;
 }
 
+// slabs of the run path: RC_OPT_VOXEL_PASSES when set, else the default
+int mean_runs_parts() {
+    const int forced = rc::g_voxel_passes.load(std::memory_order_relaxed);
+    if (forced > 1) return forced < kMeanRunsMaxParts ? forced : kMeanRunsMaxParts;
+    return kMeanRunsParts;
+}
+
+// Pass 2 over voxels [voxel_begin, voxel_end) on the current device; with a gate the kernels return at once
+// unless *gate == gate_want.
+int normalize_range(float* grid, const int* counts, long long voxel_begin, long long voxel_end, int F, int device,
+                    cudaStream_t st, const int* gate, int gate_want) {
+    // [voxel_begin, head) and [body_end, voxel_end) go voxel by voxel; the body, whose count
+    // pointer is 16-byte aligned and whose length is a multiple of four, goes four per thread
+    long long head = voxel_begin;
+    while (head < voxel_end && !rc::aligned_to(counts + head, 16)) ++head;
+    const long long body_end = head + ((voxel_end - head) & ~3ll);
+    auto scalar = [&](long long a, long long b) {
+        if (b > a) {
+            const long long blocks = (b - a + kThreads - 1) / kThreads;
+            voxel_normalize_scalar_kernel<<<static_cast<unsigned int>(blocks), kThreads, 0, st>>>(grid, counts, a, b, F, gate, gate_want);
+        }
+    };
+    if ((voxel_end - voxel_begin + kThreads - 1) / kThreads >= (1ll << 31)) return RC_ERR_TOO_LARGE;
+    scalar(voxel_begin, head);
+    if (body_end > head) {
+        long long blocks = (((body_end - head) + 255) / 256 + kThreads / 32 - 1) / (kThreads / 32);
+        const long long cap = 16ll * rc::sm_count(device);
+        if (blocks > cap) blocks = cap;
+        const unsigned int nb = static_cast<unsigned int>(blocks);
+        if ((F & 3) == 0 && rc::aligned_to(grid, 16))
+            voxel_normalize_wide_kernel<true><<<nb, kThreads, 0, st>>>(grid, counts, head, body_end, F, gate, gate_want);
+        else
+            voxel_normalize_wide_kernel<false><<<nb, kThreads, 0, st>>>(grid, counts, head, body_end, F, gate, gate_want);
+    }
+    scalar(body_end, voxel_end);
+    return rc::check_launch();
+}
+
 }  // namespace
 
 extern "C" {
@@ -424,32 +468,7 @@ int rc_voxel_normalize(float* grid, const int32_t* counts, int64_t voxel_begin, 
     if (!rc::aligned_to(grid, 4) || !rc::aligned_to(counts, 4)) return RC_ERR_BAD_ALIGNMENT;
     rc::DeviceScope scope(device);
     if (scope.status() != RC_OK) return scope.status();
-    cudaStream_t st = static_cast<cudaStream_t>(stream);
-    // [voxel_begin, head) and [body_end, voxel_end) go voxel by voxel; the body, whose count
-    // pointer is 16-byte aligned and whose length is a multiple of four, goes four per thread
-    long long head = voxel_begin;
-    while (head < voxel_end && !rc::aligned_to(counts + head, 16)) ++head;
-    const long long body_end = head + ((voxel_end - head) & ~3ll);
-    auto scalar = [&](long long a, long long b) {
-        if (b > a) {
-            const long long blocks = (b - a + kThreads - 1) / kThreads;
-            voxel_normalize_scalar_kernel<<<static_cast<unsigned int>(blocks), kThreads, 0, st>>>(grid, counts, a, b, F);
-        }
-    };
-    if ((voxel_end - voxel_begin + kThreads - 1) / kThreads >= (1ll << 31)) return RC_ERR_TOO_LARGE;
-    scalar(voxel_begin, head);
-    if (body_end > head) {
-        long long blocks = (((body_end - head) + 255) / 256 + kThreads / 32 - 1) / (kThreads / 32);
-        const long long cap = 16ll * rc::sm_count(device);
-        if (blocks > cap) blocks = cap;
-        const unsigned int nb = static_cast<unsigned int>(blocks);
-        if ((F & 3) == 0 && rc::aligned_to(grid, 16))
-            voxel_normalize_wide_kernel<true><<<nb, kThreads, 0, st>>>(grid, counts, head, body_end, F);
-        else
-            voxel_normalize_wide_kernel<false><<<nb, kThreads, 0, st>>>(grid, counts, head, body_end, F);
-    }
-    scalar(body_end, voxel_end);
-    return rc::check_launch();
+    return normalize_range(grid, counts, voxel_begin, voxel_end, F, device, static_cast<cudaStream_t>(stream), nullptr, 0);
 }
 
 int rc_voxelize(const float* points, const float* features, void* grid, int32_t* counts, int64_t N,
@@ -465,8 +484,11 @@ uint64_t rc_voxelize_scratch_bytes(int64_t N, int32_t F, const int32_t grid_size
     const double cells = static_cast<double>(grid_size_host[0]) * grid_size_host[1] * grid_size_host[2];
     if (cells <= 0 || cells >= 2147483648.0) return 0;
     const double acc_bytes = cells * 4.0 * (mode == RC_VOXEL_MEAN ? (1 + (F > 0 ? F : 0)) : 1);
-    if (acc_bytes <= static_cast<double>(kResidentBytes)) return 0;  // L2-resident accumulators: one pass
+    const bool forced = rc::g_voxel_passes.load(std::memory_order_relaxed) > 1;
+    if (acc_bytes <= static_cast<double>(kResidentBytes) && !forced) return 0;  // L2-resident accumulators: one pass
     if (mode == RC_VOXEL_COUNT) return (N >= kProbeMinPoints) ? 16 : 0;     // the order probe's flag
+    if (F == 4 && cells < 2147483648.0 && N <= (1ll << 31) - 4096)           // slab-ordered runs + flag
+        return mean_runs_scratch_bytes(N, static_cast<long long>(cells), mean_runs_parts()) + 256u;
     return ((static_cast<uint64_t>(N) * 4u + 15u) & ~static_cast<uint64_t>(15)) + 16u;  // ids + flag
 }
 
@@ -486,6 +508,7 @@ int rc_voxelize_ex(const float* points, const float* features, void* grid, int32
     if (g.gx < 0 || g.gy < 0 || g.gz < 0) return RC_ERR_BAD_SHAPE;
     if (g.gx >= (1 << 24) || g.gy >= (1 << 24) || g.gz >= (1 << 24)) return RC_ERR_TOO_LARGE;
     g.fgx = static_cast<float>(g.gx); g.fgy = static_cast<float>(g.gy); g.fgz = static_cast<float>(g.gz);
+    g.inv_vs = host_reciprocal(voxel_size);
     const long long V = static_cast<long long>(g.gx) * g.gy * g.gz;  // < 2^72 impossible: each < 2^24 -> check below
     if (static_cast<double>(g.gx) * g.gy * g.gz * (feat_mode ? (F > 0 ? F : 1) : 1) >= 1099511627776.0)
         return RC_ERR_TOO_LARGE;
@@ -506,6 +529,42 @@ int rc_voxelize_ex(const float* points, const float* features, void* grid, int32
     const unsigned int fill_blocks =
         static_cast<unsigned int>(fill_blocks_ll < 64ll * rc::sm_count(device) ? (fill_blocks_ll > 0 ? fill_blocks_ll : 1)
                                                                            : 64ll * rc::sm_count(device));
+    // Mean mode, four channels, accumulators beyond L2, enough scratch: slab-ordered runs (voxel_runs.cu), which
+    // clear and normalise inside their own kernels.  With points in coherent order (decided on the device by the
+    // order probe) one plain pass is faster; its kernels are enqueued too and the strategy not chosen returns at once.
+    {
+        const int forced = rc::g_voxel_passes.load(std::memory_order_relaxed);
+        const double acc_bytes = static_cast<double>(V) * 4.0 * (1 + F);
+        const int parts = mean_runs_parts();
+        const uint64_t need = (mode == RC_VOXEL_MEAN && F == 4 && V > 0 && V < (1ll << 31) && N > 0 && N <= (1ll << 31) - 4096)
+                                  ? mean_runs_scratch_bytes(N, V, parts) + 256u : 0;
+        if (need > 0 && (forced > 1 || (forced == 0 && acc_bytes > static_cast<double>(kResidentBytes))) &&
+            scratch != nullptr && rc::aligned_to(scratch, 256) && scratch_bytes >= need && rc::aligned_to(features, 16) &&
+            rc::aligned_to(grid, 16) && rc::aligned_to(counts, 16) && features != nullptr) {
+            const bool clear = (flags & RC_VOXEL_ZERO_INIT) != 0;
+            const bool normalize = !(flags & RC_VOXEL_NO_NORMALIZE);
+            int* flag = nullptr;
+            if (forced == 0 && N >= kProbeMinPoints) {
+                flag = reinterpret_cast<int*>(static_cast<unsigned char*>(scratch) + need - 256u);
+                voxel_order_probe_kernel<<<1, 1024, 0, st>>>(points, N, g, V, flag);
+                const long long cap = 16ll * rc::sm_count(device);
+                if (clear) {
+                    voxel_zero_kernel<<<static_cast<unsigned int>(cap), kThreads, 0, st>>>(static_cast<unsigned char*>(grid), V * 16, flag, 1);
+                    voxel_zero_kernel<<<static_cast<unsigned int>(cap), kThreads, 0, st>>>(reinterpret_cast<unsigned char*>(counts), V * 4, flag, 1);
+                }
+                long long blocks = (N + kPointsPerBlock - 1) / kPointsPerBlock;
+                if (blocks > cap) blocks = cap;
+                launch_bin<kMean>(false, false, static_cast<unsigned int>(blocks), st, points, features, grid, counts, N, F, g,
+                                  rc::aligned_to(points, 16), 0, V, flag, 1);
+                if (normalize) {
+                    const int rc_norm = normalize_range(static_cast<float*>(grid), counts, 0, V, F, device, st, flag, 1);
+                    if (rc_norm != RC_OK) return rc_norm;
+                }
+            }
+            return mean_runs_launch(points, features, static_cast<float*>(grid), counts, N, g, V, parts, clear, normalize, scratch,
+                                    flag, 0, device, st);
+        }
+    }
     bool overlap_fill = false;
     if (mode == RC_VOXEL_MAX) {
         // max mode always starts from "empty": the caller's buffer content is never an operand

@@ -22,16 +22,49 @@ struct VoxelGeom {
     float minx, miny, minz, vs;
     int gx, gy, gz;
     float fgx, fgy, fgz;
+    float inv_vs;   // RN(1 / vs), computed on the host
 };
+
+// RN(1 / vs) for VoxelGeom::inv_vs; NaN when the reciprocal is not a normal float (its relative error would
+// exceed 2^-24), which sends every point of axis_cell through the division
+inline float host_reciprocal(float vs) {
+    const float r = 1.0f / vs;
+    return (r >= 1.1754944e-38f && r <= 3.4028235e38f) ? r : __builtin_nanf("");
+}
+
+// floor((p - lo) / vs) with the reference's rounding (one IEEE subtraction, one IEEE division,
+// floor), at the price of a multiplication for almost every point.  t = a * RN(1/vs) and the
+// exact quotient q = RN(a / vs) differ by less than |t| * 2^-22 (three roundings of 2^-24 each),
+// so floor(t) == floor(q) whenever t is further than that from every integer; only the points
+// that are closer (a few in 10^4 at 512 cells per axis), quotients so small that a product could
+// underflow, NaN and infinities take the division.
+__device__ __forceinline__ float axis_cell(float p, float lo, float vs, float inv_vs) {
+    const float a = __fsub_rn(p, lo);
+    const float t = __fmul_rn(a, inv_vs);
+    float f = floorf(t);
+    const float d = fminf(__fsub_rn(t, f), __fsub_rn(__fadd_rn(f, 1.0f), t));   // distance to the nearest integer
+    if (!(d > fmaxf(__fmul_rn(fabsf(t), 2.5e-7f), 1.0e-30f))) f = floorf(__fdiv_rn(a, vs));
+    return f;
+}
 
 // flat voxel id, or -1 for a dropped point (NaN and infinities fail the range test)
 __device__ __forceinline__ long long voxel_id(float x, float y, float z, const VoxelGeom& g) {
-    const float fx = floorf(__fdiv_rn(__fsub_rn(x, g.minx), g.vs));
-    const float fy = floorf(__fdiv_rn(__fsub_rn(y, g.miny), g.vs));
-    const float fz = floorf(__fdiv_rn(__fsub_rn(z, g.minz), g.vs));
+    const float fx = axis_cell(x, g.minx, g.vs, g.inv_vs);
+    const float fy = axis_cell(y, g.miny, g.vs, g.inv_vs);
+    const float fz = axis_cell(z, g.minz, g.vs, g.inv_vs);
     const bool in = (fx >= 0.0f) && (fx < g.fgx) && (fy >= 0.0f) && (fy < g.fgy) && (fz >= 0.0f) && (fz < g.fgz);
     if (!in) return -1;
     return (static_cast<long long>(fz) * g.gy + static_cast<long long>(fy)) * g.gx + static_cast<long long>(fx);
+}
+
+// voxel_id for grids of fewer than 2^31 voxels: the same float arithmetic, 32-bit index arithmetic
+__device__ __forceinline__ int voxel_id32(float x, float y, float z, const VoxelGeom& g) {
+    const float fx = axis_cell(x, g.minx, g.vs, g.inv_vs);
+    const float fy = axis_cell(y, g.miny, g.vs, g.inv_vs);
+    const float fz = axis_cell(z, g.minz, g.vs, g.inv_vs);
+    const bool in = (fx >= 0.0f) && (fx < g.fgx) && (fy >= 0.0f) && (fy < g.fgy) && (fz >= 0.0f) && (fz < g.fgz);
+    if (!in) return -1;
+    return (static_cast<int>(fz) * g.gy + static_cast<int>(fy)) * g.gx + static_cast<int>(fx);
 }
 
 __device__ __forceinline__ void red_add_v4(float* addr, float4 v) {
@@ -116,6 +149,17 @@ __device__ __forceinline__ void scatter_one(int id, long long pi, const float* _
         atomicAdd(counts + id, 1);
     }
 }
+
+// ---- mean mode by slab-ordered runs (voxel_runs.cu), used by rc_voxelize_ex for F = 4 on grids whose
+// accumulators exceed L2.  `parts` slabs (at most kMeanRunsMaxParts); scratch of mean_runs_scratch_bytes(),
+// 256-byte aligned; grid, counts and features 16-byte aligned; V < 2^31; N <= 2^31 - 4096.  `clear` zero-fills
+// grid and counts inside the kernels, `normalize` turns the sums into means.
+constexpr int kMeanRunsMaxParts = 16;
+constexpr int kMeanRunsParts = 8;
+uint64_t mean_runs_scratch_bytes(long long N, long long V, int parts);
+int mean_runs_launch(const float* points, const float* features, float* grid, int* counts, long long N,
+                     const VoxelGeom& g, long long V, int parts, bool clear, bool normalize, void* scratch,
+                     const int* gate, int gate_want, int device, cudaStream_t st);
 
 }  // namespace vox
 }  // namespace rc

@@ -61,16 +61,6 @@ __device__ __forceinline__ int part_of(int id, const PartRule& r) {
     return static_cast<int>(grp) * r.per_group + static_cast<int>(k);
 }
 
-// voxel_id for grids of fewer than 2^31 voxels: the same float arithmetic, 32-bit index arithmetic
-__device__ __forceinline__ int voxel_id32(float x, float y, float z, const VoxelGeom& g) {
-    const float fx = floorf(__fdiv_rn(__fsub_rn(x, g.minx), g.vs));
-    const float fy = floorf(__fdiv_rn(__fsub_rn(y, g.miny), g.vs));
-    const float fz = floorf(__fdiv_rn(__fsub_rn(z, g.minz), g.vs));
-    const bool in = (fx >= 0.0f) && (fx < g.fgx) && (fy >= 0.0f) && (fy < g.fgy) && (fz >= 0.0f) && (fz < g.fgz);
-    if (!in) return -1;
-    return (static_cast<int>(fz) * g.gy + static_cast<int>(fy)) * g.gx + static_cast<int>(fx);
-}
-
 template <bool MOVE, bool ALIGNED>
 __global__ void __launch_bounds__(kThreads, ALIGNED ? 4 : 5)
 voxel_part_kernel(const float* __restrict__ pts, const float* __restrict__ feats, long long N, int F, VoxelGeom g,
@@ -477,6 +467,7 @@ int partition_geometry(const float grid_min_host[3], float voxel_size, const int
     if (g->gx >= (1 << 24) || g->gy >= (1 << 24) || g->gz >= (1 << 24)) return RC_ERR_TOO_LARGE;
     if (static_cast<double>(g->gx) * g->gy * g->gz >= 2147483648.0) return RC_ERR_TOO_LARGE;
     g->fgx = static_cast<float>(g->gx); g->fgy = static_cast<float>(g->gy); g->fgz = static_cast<float>(g->gz);
+    g->inv_vs = host_reciprocal(voxel_size);
     const long long V = static_cast<long long>(g->gx) * g->gy * g->gz;
     *V_out = V;
     const long long slab = (V + n_groups - 1) / n_groups;

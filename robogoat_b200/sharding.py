@@ -64,7 +64,10 @@ def reduce_partial_grids(grid: torch.Tensor, counts: Optional[torch.Tensor], mod
     """In-place reduce of per-rank partial voxel grids over the group.
 
     occupancy: element-wise MAX (union); count: SUM of int32 counts (exact); mean: SUM of the fp32
-    feature sums and of the int32 counts (call before normalising); max: element-wise MAX.
+    feature sums and of the int32 counts (call before normalising); max: element-wise MAX of grids whose
+    empty voxels hold -inf (``mask_empty_for_max`` / ``unmask_empty_after_max`` around this call: a rank's
+    decoded max grid stores 0.0 for voxels it saw no point in, which would beat a negative maximum
+    found by another rank).
     """
     _, ws = world(group)
     if ws == 1:
@@ -82,6 +85,18 @@ def reduce_partial_grids(grid: torch.Tensor, counts: Optional[torch.Tensor], mod
         dist.all_reduce(grid, op=dist.ReduceOp.MAX, group=group)
     else:
         raise RuntimeError(f"Invalid mode: {mode}. Must be 'count', 'occupancy', 'mean', or 'max'")
+
+
+def mask_empty_for_max(grid: torch.Tensor, occupied: torch.Tensor) -> None:
+    """In place: voxels this rank saw no point in (``occupied`` == 0, shaped like the grid without its feature
+    axis) become -inf, the neutral element of the MAX reduce that follows."""
+    grid.masked_fill_((occupied == 0).unsqueeze(-1), float("-inf"))
+
+
+def unmask_empty_after_max(grid: torch.Tensor, occupied_any: torch.Tensor) -> None:
+    """In place, after the reduce: voxels no rank saw a point in (``occupied_any`` == 0 after its own MAX
+    reduce) go back to 0.0, what the single-GPU operator returns for them."""
+    grid.masked_fill_((occupied_any == 0).unsqueeze(-1), 0.0)
 
 
 # ----------------------------------------------------------------------------- sharded operators (CUDA)
@@ -146,9 +161,17 @@ def voxelize_sharded_slab(points_local: torch.Tensor, features_local: Optional[t
     V = int(grid_size[0]) * int(grid_size[1]) * int(grid_size[2])
     if ws == 1:
         return grid.reshape(V, -1) if grid.dim() == 4 else grid.reshape(V)
+    occ = None
+    if mode == "max":       # a rank's empty voxels must not take part in the maximum with their 0.0
+        occ = ops.voxelize_pointcloud_cuda(points_local, None, list(grid_min), float(voxel_size), list(grid_size),
+                                           "occupancy", occupancy_dtype=torch.uint8)[0]
+        mask_empty_for_max(grid, occ)
     slab, cslab = reduce_scatter_partial_grids(grid, counts, mode, group)
     if mode == "mean":
         ops.voxel_normalize_cuda(slab, cslab, 0, cslab.numel())
+    if mode == "max":
+        occ_slab, _ = reduce_scatter_partial_grids(occ, None, "occupancy", group)
+        unmask_empty_after_max(slab, occ_slab)
     return slab
 
 
@@ -171,7 +194,15 @@ def voxelize_sharded(points_local: torch.Tensor, features_local: Optional[torch.
     counts = res[1] if mode == "mean" else None
     if ws == 1:
         return grid
+    occ = None
+    if mode == "max":       # a rank's empty voxels must not take part in the maximum with their 0.0
+        occ = ops.voxelize_pointcloud_cuda(points_local, None, list(grid_min), float(voxel_size), list(grid_size),
+                                           "occupancy", occupancy_dtype=torch.uint8)[0]
+        mask_empty_for_max(grid, occ)
     reduce_partial_grids(grid, counts, mode, group)
+    if mode == "max":
+        reduce_partial_grids(occ, None, "occupancy", group)
+        unmask_empty_after_max(grid, occ)
     if mode == "occupancy":
         return grid.to(torch.int32)
     if mode == "mean":

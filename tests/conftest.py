@@ -60,6 +60,26 @@ def cuda_lib():
     return _lib.load()
 
 
+# bulk-copy waits that tests made run out on purpose (RC_OPT_BULK_WAIT_LIMIT = 0); any other event is a failure
+DELIBERATE_BULK_TIMEOUTS = [0]
+
+
+def bulk_wait_timeouts(lib) -> int:
+    import ctypes
+    n = ctypes.c_uint32(0)
+    assert lib.rc_bulk_wait_timeouts(0, ctypes.byref(n)) == 0
+    return int(n.value)
+
+
+@pytest.fixture(scope="session", autouse=True)
+def no_unexpected_bulk_wait_timeouts():
+    """At the end of a GPU session: the staged kernel's bounded wait fired only where a test asked it to."""
+    yield
+    if torch.cuda.is_available():
+        from robogoat_b200 import _lib
+        assert bulk_wait_timeouts(_lib.load()) == DELIBERATE_BULK_TIMEOUTS[0]
+
+
 @pytest.fixture(params=["staged-block", "row-gather"])
 def kernel_choice(request, cuda_lib):
     """Runs a test once with the TMA-staged block kernel allowed (it is used where shapes qualify)

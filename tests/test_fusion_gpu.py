@@ -111,12 +111,40 @@ def test_throughput_size_properties(cuda_lib):
     assert torch.equal(vis.view(torch.int16), out[:, :, :512].contiguous().view(torch.int16))
 
 
+def test_bulk_copy_wait_that_runs_out_falls_back_to_plain_loads(kernel_choice, cuda_lib):
+    """Failure detection of the staged kernel, made to happen without anything going wrong on the GPU: with the
+    wait limit set to 0 polls every CTA gives up on its bulk copies at once, counts the event, fetches the same
+    bytes with ordinary loads and still returns the oracle's bits (then waits for the copies before it exits)."""
+    from conftest import DELIBERATE_BULK_TIMEOUTS, bulk_wait_timeouts
+    from robogoat_b200 import _lib
+    before = bulk_wait_timeouts(cuda_lib)
+    assert before == DELIBERATE_BULK_TIMEOUTS[0]
+    args = list(workloads.fusion_inputs(B=64, dtype=torch.bfloat16, seed=11))
+    exp = expected(args)
+    assert cuda_lib.rc_set_option(_lib.OPT_BULK_WAIT_LIMIT, 0) == 0
+    try:
+        got = run(args)
+        got2 = run(args)
+    finally:
+        assert cuda_lib.rc_set_option(_lib.OPT_BULK_WAIT_LIMIT, -1) == 0
+        after = bulk_wait_timeouts(cuda_lib)
+        DELIBERATE_BULK_TIMEOUTS[0] = after
+    assert_exact(got, exp)
+    assert_exact(got2, exp)
+    if kernel_choice == "staged-block":
+        assert after >= before + 2 * 64                  # at least one CTA per item and call gave up
+    else:
+        assert after == before                           # the row-gather kernel has no such wait
+    assert cuda_lib.rc_set_option(_lib.OPT_BULK_WAIT_LIMIT, -2) != 0
+    assert_exact(run(args), exp)                         # built-in limit again: no new events
+    assert bulk_wait_timeouts(cuda_lib) == after
+
+
 def test_no_bulk_copy_wait_ever_ran_out(cuda_lib):
-    """The bounded mbarrier wait of the staged kernel is a safety net; it must not have fired."""
-    import ctypes
-    n = ctypes.c_uint32(12345)
-    assert cuda_lib.rc_bulk_wait_timeouts(0, ctypes.byref(n)) == 0
-    assert n.value == 0
+    """The bounded mbarrier wait of the staged kernel is a safety net; outside the test that sets its limit to 0
+    it must not have fired."""
+    from conftest import DELIBERATE_BULK_TIMEOUTS, bulk_wait_timeouts
+    assert bulk_wait_timeouts(cuda_lib) == DELIBERATE_BULK_TIMEOUTS[0]
 
 
 def test_cuda_graph_replay_matches_direct_calls(cuda_lib):

@@ -201,6 +201,28 @@ def test_ragged_items_equal_per_item_oracle_and_last_step_padding(dtype, D, cuda
     assert_exact(out[keep], dense, "ragged vs last-step padding")
 
 
+def test_ragged_bound_below_an_item_length_truncates_the_item(cuda_lib):
+    """``max_len`` sizes the staged timestamp row.  A bound smaller than an item must cut that item to its first
+    ``max_len`` rows (the result of resampling the truncated item), never read or write past the staging."""
+    g = torch.Generator().manual_seed(5)
+    lens, bound, T, D = [40, 9, 25], 16, 33, 24
+    rows = [torch.randn(n, D, generator=g) for n in lens]
+    times = [workloads.cumsum_times(1, n, g)[0] for n in lens]
+    tt = torch.rand(len(lens), T, generator=g)
+    offs = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int64)
+    out = ops.resample_ragged_cuda(torch.cat(rows).to(DEV), torch.cat(times).to(DEV), offs.to(DEV), tt.to(DEV),
+                                   max_len=bound).cpu()
+    for b, n in enumerate(lens):
+        m = min(n, bound)
+        exp = expected(rows[b][:m].unsqueeze(0), times[b][:m].unsqueeze(0), tt[b:b + 1])
+        assert_exact(out[b:b + 1], exp, f"item {b} (len {n}, bound {bound})")
+    # offsets that do not ascend give an empty item (zeros), not a negative length
+    bad = offs.clone(); bad[2] = bad[1] - 3
+    out = ops.resample_ragged_cuda(torch.cat(rows).to(DEV), torch.cat(times).to(DEV), bad.to(DEV), tt.to(DEV), max_len=64).cpu()
+    assert bool((out[1] == 0).all())
+    torch.cuda.synchronize()
+
+
 def test_expanded_and_strided_time_rows_are_used_in_place(cuda_lib):
     """Timestamps given as stride-0 expanded rows (the reference's usual linspace(...).expand(B, -1)) or as
     row-strided views give the same bits as their materialised copies."""

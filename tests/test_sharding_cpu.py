@@ -98,6 +98,40 @@ def _voxel_job(rank, ws):
     return ok
 
 
+def _max_job(rank, ws):
+    """Max mode with all-negative features and spatially disjoint shards: a rank's decoded max grid holds 0.0
+    where it saw no point, and that 0.0 must not beat the other rank's negative maximum."""
+    g = torch.Generator().manual_seed(17)
+    pts = torch.rand(4_000, 3, generator=g) * 3 - 1.5
+    pts[:, 2] = torch.where(torch.arange(4_000) < 2_000, pts[:, 2].abs() * -1 - 0.01, pts[:, 2].abs() + 0.01)  # rank 0 below z=0, rank 1 above
+    feats = -torch.rand(4_000, 3, generator=g) - 0.5                                                          # all negative
+    kw = dict(grid_min=[-1.5, -1.5, -1.5], voxel_size=0.25, grid_size=[12, 12, 12])
+    V = 12 ** 3
+
+    def decoded_max(p, f):     # what the single-GPU operator returns: true maximum, empty voxels 0.0
+        ids = oracle.voxel_ids(p, **kw)
+        keep = ids >= 0
+        out = torch.full((V, 3), float("-inf")).scatter_reduce_(0, ids[keep].long().unsqueeze(1).expand(-1, 3), f[keep], "amax")
+        occ = torch.zeros(V, dtype=torch.uint8)
+        occ[ids[keep].long()] = 1
+        return torch.where(occ.bool().unsqueeze(1), out, torch.zeros_like(out)), occ
+
+    full, _ = decoded_max(pts, feats)
+    a, b = sharding.shard_bounds(4_000, rank, ws)
+    part, occ = decoded_max(pts[a:b], feats[a:b])
+    naive = part.clone()
+    sharding.reduce_partial_grids(naive, None, "max")          # without the masks: the 0.0 of an empty voxel wins
+    sharding.mask_empty_for_max(part, occ)
+    sharding.reduce_partial_grids(part, None, "max")
+    sharding.reduce_partial_grids(occ, None, "occupancy")
+    sharding.unmask_empty_after_max(part, occ)
+    return bool(torch.equal(part, full)) and not bool(torch.equal(naive, full)) and bool((full < 0).any())
+
+
+def test_sharded_max_keeps_negative_maxima():
+    assert _run(_max_job) == {0: True, 1: True}
+
+
 def test_batch_shards_gather_to_the_unsharded_result():
     assert _run(_batch_job) == {0: True, 1: True}
 
