@@ -129,6 +129,40 @@ def physical_gpu_index(local_rank: int) -> int:
     return local_rank
 
 
+class NumaLocal:
+    """While active, this process runs on the host cores next to GPU ``index`` (sysfs ``local_cpulist`` of the
+    device), so pinned buffers allocated inside land in that socket's memory.  Reads sysfs only; a box without the
+    file is left as it is."""
+
+    def __init__(self, index: int):
+        self.index, self.old, self.cpus = index, None, None
+
+    def __enter__(self):
+        try:
+            bus = torch.cuda.get_device_properties(self.index).pci_bus_id
+            dom = torch.cuda.get_device_properties(self.index).pci_domain_id
+            devid = torch.cuda.get_device_properties(self.index).pci_device_id
+            path = f"/sys/bus/pci/devices/{dom:04x}:{bus:02x}:{devid:02x}.0/local_cpulist"
+            cpus = set()
+            for part in open(path).read().strip().split(","):
+                lo, _, hi = part.partition("-")
+                cpus.update(range(int(lo), int(hi or lo) + 1))
+            allowed = os.sched_getaffinity(0)
+            cpus &= allowed
+            if cpus and cpus != allowed:
+                self.old = allowed
+                os.sched_setaffinity(0, cpus)
+                self.cpus = len(cpus)
+        except Exception:
+            self.old = None
+        return self
+
+    def __exit__(self, *exc):
+        if self.old is not None:
+            os.sched_setaffinity(0, self.old)
+        return False
+
+
 class LineGuard:
     """Prints the benchmark's one JSON line exactly once: normally from ``finish()``; from a timer thread if
     ``limit_s`` seconds pass first (the main thread may then be stuck inside a collective), after which the
@@ -238,14 +272,25 @@ def time_cold(fn, iters: int, warmup: int, flush: L2Flush):
 
 # ----------------------------------------------------------------------------- reference arm
 
+def headline_config(world: int, step_bytes: int) -> dict:
+    """The ``config`` object of the line; both arms print the same keys."""
+    B = HEADLINE["B"]
+    return {"workload": WORKLOAD, "global_batch": B * world, "parallelism": f"batch-shard x{world}, no collective",
+            "l2": "inputs (1.06 GB) and output (0.52 GB) exceed the 126 MB L2; no flush needed",
+            "bytes_per_step_per_gpu": step_bytes, "bytes_convention": BYTES_CONVENTION,
+            "nccl_nvls": os.environ.get("NCCL_NVLS_ENABLE", "default") if world > 1 else "n/a"}
+
+
 def run_reference_arm(args):
+    """The reference's CPU path for the headline workload on the host cores (rank 0 only): the oracle port with all
+    host threads on a bounded sample, timed for at least two seconds, median per step."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     import oracle
-    from robogoat_b200 import workloads
+    import workloads
     threads = host_threads()
-    B_s = 256                                  # bounded sample: 1/16 of the headline batch per step
+    B_s = 1024                                 # bounded sample: 1/4 of the headline batch per step, 390 MB of rows
     src, st, tt = workloads.resample_inputs(B=B_s, dtype=torch.bfloat16, irregular_targets=True, seed=0,
                                             S=HEADLINE["S"], D=HEADLINE["D"], T=HEADLINE["T"])
     left, right, _ = oracle.brackets(st, tt)
@@ -253,21 +298,26 @@ def run_reference_arm(args):
                  workloads.resample_touched_bytes(left, right, HEADLINE["S"], HEADLINE["D"], 2))
     for _ in range(max(args.warmup, 1)):
         oracle.resample_trajectories(src, st, tt, threads=threads)
-    t0 = time.perf_counter()
-    for _ in range(args.steps):
+    # at least K steps and at least two seconds: other ranks' interpreters may still be starting while this runs,
+    # and the median over a longer window is not moved by that
+    ts, t_begin = [], time.perf_counter()
+    while len(ts) < args.steps or (time.perf_counter() - t_begin < 2.0 and len(ts) < 50 * args.steps):
+        t0 = time.perf_counter()
         oracle.resample_trajectories(src, st, tt, threads=threads)
-    dt = time.perf_counter() - t0
-    gbs = nbytes * args.steps / dt / 1e9
-    sample = f"B={B_s} rows of the B=4096 headline batch per step (same S, D, T, generator), oracle port, {threads} threads"
+        ts.append(time.perf_counter() - t0)
+    dt = statistics.median(ts)
+    gbs = nbytes / dt / 1e9
+    sample = (f"B={B_s} rows per step of the B=4096-per-GPU headline batch (same S, D, T and generator; the CPU rate does not "
+              f"depend on B), oracle port, {threads} threads, median of {len(ts)} steps over {time.perf_counter() - t_begin:.1f} s; "
+              f"bytes_per_step_per_gpu is the sample's bytes scaled to 4096 rows")
     line = {
         "impl": "reference", "metric": METRIC, "value": gbs, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
+        "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "sample": "B=256 rows per step (the CPU rate does not depend on B)",
-                   "bytes_per_step": nbytes, "bytes_convention": BYTES_CONVENTION},
+        "config": headline_config(args.gpus, nbytes * (HEADLINE["B"] // B_s)),
         "cpu_baseline": {"value": gbs, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": gbs, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-        "gpu_launches": 0,
+        "gpu_launches": 0, "steps_timed": len(ts),
     }
     ref_gpu = reference_cuda_leg()
     if ref_gpu is not None:
@@ -281,7 +331,7 @@ def reference_cuda_leg():
     is missing.  Their outputs differ from the parity target outside the source time range (they extrapolate)."""
     try:
         import oracle
-        from robogoat_b200 import workloads
+        import workloads
         if oracle.ref_cuda_lib() is None or not torch.cuda.is_available():
             return None
         dev = torch.device("cuda", 0)
@@ -329,7 +379,8 @@ def reference_cuda_leg():
 # ----------------------------------------------------------------------------- our arm
 
 def run_ours(args):
-    from robogoat_b200 import _lib, ops, workloads
+    from robogoat_b200 import _lib, ops
+    import workloads
     import robocache
 
     if not torch.cuda.is_available():
@@ -381,8 +432,13 @@ def run_ours(args):
 
     # ---- end to end through the public API: pinned host inputs -> device -> op -> pinned host output
     e2e_steps = max(3, min(args.steps, 10))
-    h_src, h_st, h_tt = src.cpu().pin_memory(), st.cpu().pin_memory(), tt.cpu().pin_memory()
-    h_out = torch.empty((B, T, D), dtype=torch.bfloat16).pin_memory()
+    with NumaLocal(local) as numa:          # pinned host buffers in the memory of the socket this GPU hangs off
+        h_src = torch.empty((B, S, D), dtype=torch.bfloat16).pin_memory()
+        h_st, h_tt = torch.empty((B, S), dtype=torch.float32).pin_memory(), torch.empty((B, T), dtype=torch.float32).pin_memory()
+        h_out = torch.empty((B, T, D), dtype=torch.bfloat16).pin_memory()
+        h_out.zero_()
+    h_src.copy_(src); h_st.copy_(st); h_tt.copy_(tt)
+    torch.cuda.synchronize()
 
     from robogoat_b200.host_pipeline import resample_trajectories_host
 
@@ -395,9 +451,32 @@ def run_ours(args):
     h2d = h_src.numel() * 2 + h_st.numel() * 4 + h_tt.numel() * 4
     d2h = h_out.numel() * 2
     ok = torch.equal(h_out.view(torch.int16), out.cpu().view(torch.int16))
+    # the floor of that figure: the same bytes moved by plain copies and nothing else, upload and download at the
+    # same time (the link is full duplex), on all ranks at once
+    d_src, d_out = torch.empty_like(src), torch.empty_like(out)
+    d_st, d_tt = torch.empty_like(st), torch.empty_like(tt)
+    up, down = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+
+    def copy_step():
+        ev = torch.cuda.Event(); ev.record()
+        up.wait_event(ev); down.wait_event(ev)
+        with torch.cuda.stream(up):
+            d_src.copy_(h_src, non_blocking=True); d_st.copy_(h_st, non_blocking=True); d_tt.copy_(h_tt, non_blocking=True)
+        with torch.cuda.stream(down):
+            h_out.copy_(d_out, non_blocking=True)
+        torch.cuda.current_stream().wait_stream(up); torch.cuda.current_stream().wait_stream(down)
+
+    floor_ms, _ = timed_region(copy_step, e2e_steps, 2, world, dev)
+    floor_ms /= e2e_steps
+    del d_src, d_out, d_st, d_tt
     e2e = {"value": e2e_val, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps,
            "ms_per_step": e2e_ms / e2e_steps, "matches_device_run": bool(ok),
            "api": "robogoat_b200.host_pipeline.resample_trajectories_host (pinned host in, pinned host out)",
+           "copy_floor_ms": floor_ms, "frac_of_copy_floor": floor_ms / (e2e_ms / e2e_steps),
+           "copy_floor": "one cudaMemcpyAsync per tensor, upload and download on two streams at once, same pinned buffers, "
+                         "all ranks at the same time, max over ranks; link GB/s = (h2d + d2h) / copy_floor_ms",
+           "copy_floor_link_GB/s": (h2d + d2h) / (floor_ms * 1e-3) / 1e9,
+           "pinned_buffers": f"allocated while bound to the {numa.cpus} host cores local to the GPU" if numa.cpus else "allocated without a NUMA binding",
            "pcie_floor_note": "every step moves h2d+d2h bytes over PCIe; that link, not the kernel, bounds this figure"}
     del h_src, h_out
 
@@ -412,11 +491,7 @@ def run_ours(args):
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
             "arithmetic": "bf16 rows widened to f32, every product and sum rounded separately, one round-to-nearest back to bf16",
             "data": "synthetic",
-            "config": {"workload": WORKLOAD,
-                       "global_batch": B * world, "parallelism": f"batch-shard x{world}, no collective",
-                       "l2": "inputs (1.06 GB) and output (0.52 GB) exceed the 126 MB L2; no flush needed",
-                       "bytes_per_step_per_gpu": step_bytes, "bytes_convention": BYTES_CONVENTION,
-                       "nccl_nvls": os.environ.get("NCCL_NVLS_ENABLE", "default") if world > 1 else "n/a"},
+            "config": headline_config(world, step_bytes),
             "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e, "gpu_launches": args.steps, "clocks": clocks,
             "extras": dict(extras),
         }
@@ -437,36 +512,113 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def cpu_seconds(fn, budget_s: float = 1.5, max_reps: int = 25) -> float:
+    """Median wall-clock seconds of ``fn()`` on the host: one warm-up call, then calls until the budget is spent."""
+    t0 = time.perf_counter()
+    fn()
+    first = time.perf_counter() - t0
+    if first >= budget_s:            # one call already spends the budget: take it
+        return first
+    ts, t_end = [], time.perf_counter() + budget_s
+    while len(ts) < 2 or (time.perf_counter() < t_end and len(ts) < max_reps):
+        t0 = time.perf_counter()
+        fn()
+        ts.append(time.perf_counter() - t0)
+    return statistics.median(ts)
+
+
+def torch_threads(k: int, fn):
+    """Runs ``fn`` with torch's intra-op pool set to ``k`` threads."""
+    def run():
+        old = torch.get_num_threads()
+        torch.set_num_threads(k)
+        try:
+            return fn()
+        finally:
+            torch.set_num_threads(old)
+    return run
+
+
+def cpu_records(unit: str, work_per_call: float, scale: float, sample: str, port_fn=None, torch_fn=None,
+                port_threaded: bool = True, budget_s: float = 1.5):
+    """CPU baselines of one configuration: the C oracle port and the torch restatement of the reference's fallback,
+    each with all host threads and with one.  ``work_per_call`` is the sample's work in the unit's numerator
+    (bytes for GB/s, points for Gpts/s); ``scale`` = full configuration / sample, used for the ``ms_full_config`` figure."""
+    out = []
+    threads = host_threads()
+
+    def add(impl, cores, fn):
+        try:
+            sec = cpu_seconds(fn, budget_s)
+        except Exception as e:          # a baseline must never break the line
+            out.append({"impl": impl, "cores": cores, "error": repr(e)[:160]})
+            return
+        out.append({"value": work_per_call / sec / 1e9, "unit": unit, "cores": cores, "kind": "port", "impl": impl,
+                    "ms_sample": sec * 1e3, "ms_full_config": sec * scale * 1e3, "sample": sample})
+
+    if port_fn is not None:
+        if port_threaded:
+            add("C restatement, OpenMP over batch rows", threads, lambda: port_fn(threads))
+        add("C restatement, one thread", 1, lambda: port_fn(1))
+    if torch_fn is not None:
+        add("torch restatement of the reference's Python fallback (oracle/torch_path.py)", threads, torch_threads(threads, torch_fn))
+        add("torch restatement, one thread", 1, torch_threads(1, torch_fn))
+    return out
+
+
 def cpu_baseline_leg(world: int):
-    """Oracle port on the host cores, bounded sample (rank 0, N=1 only)."""
+    """CPU baseline of the headline workload on the host cores, bounded sample (rank 0, N=1 only): the oracle port
+    (headline figure) and, under ``also``, the torch restatement of the reference's Python fallback."""
     if world != 1:
         return None
     import oracle
-    from robogoat_b200 import workloads
+    from oracle import torch_path
+    import workloads
     threads = host_threads()
-    B_s = 512
+    B_s = 1024                                 # 390 MB working set: larger than the host's last-level cache
     src, st, tt = workloads.resample_inputs(B=B_s, dtype=torch.bfloat16, irregular_targets=True, seed=0,
                                             S=HEADLINE["S"], D=HEADLINE["D"], T=HEADLINE["T"])
     left, right, _ = oracle.brackets(st, tt)
     nbytes = min(workloads.resample_bytes(B_s, HEADLINE["S"], HEADLINE["T"], HEADLINE["D"], 2),
                  workloads.resample_touched_bytes(left, right, HEADLINE["S"], HEADLINE["D"], 2))
     oracle.resample_trajectories(src, st, tt, threads=threads)
-    reps, t0 = 0, time.perf_counter()
-    while time.perf_counter() - t0 < 10.0 and reps < 200:
+    ts, t_end = [], time.perf_counter() + 8.0
+    while time.perf_counter() < t_end and len(ts) < 200:
+        t0 = time.perf_counter()
         oracle.resample_trajectories(src, st, tt, threads=threads)
-        reps += 1
-    dt = (time.perf_counter() - t0) / reps
+        ts.append(time.perf_counter() - t0)
+    dt = statistics.median(ts)
+    scale = HEADLINE["B"] / 256
+    s256 = (src[:256], st[:256], tt[:256])
+    also = cpu_records(UNIT, nbytes / 4, scale, "B=256 rows of the headline batch (the fallback loops over rows: linear in B)",
+                       port_fn=lambda k: oracle.resample_trajectories(*s256, threads=k),
+                       torch_fn=lambda: torch_path.interpolate_stream(*s256), budget_s=2.0)
     return {"value": nbytes / dt / 1e9, "unit": UNIT, "cores": threads, "kind": "port",
-            "sample": f"B={B_s} rows of the headline batch, {reps} passes (~10 s), oracle port with OpenMP over rows",
-            "host_cores": os.cpu_count()}
+            "sample": f"B={B_s} rows of the headline batch ({B_s * 500 * 256 * 2 >> 20} MB of rows), median of {len(ts)} passes (~8 s), "
+                      f"oracle port with OpenMP over rows",
+            "host_cores": os.cpu_count(), "also": also}
+
+
+def gpu_record(ms: float, work: float, unit: str, nbytes: int, peak: float, timing: str, world: int = 1) -> dict:
+    """One measured configuration: time, rate in the metric's unit (whole job), algorithmic bytes per GPU and the
+    fraction of the measured HBM copy peak those bytes amount to."""
+    rec = {"ms": ms, "rate": work * world / (ms * 1e-3) / 1e9, "unit": unit, "bytes_algorithmic": int(nbytes),
+           "GB/s_per_gpu": nbytes / (ms * 1e-3) / 1e9, "frac_of_hbm_peak": nbytes / (ms * 1e-3) / 1e9 / peak, "timing": timing}
+    return rec
 
 
 def run_extras(L, dev, local, rank, world, peak, ex):
-    """Fusion and voxelisation figures for the other headline configurations (device-resident inputs), added to ``ex``
-    as they are measured."""
-    from robogoat_b200 import _lib, ops, workloads
+    """The other configurations of the headline benchmark (device-resident inputs), added to ``ex`` as they are
+    measured: every record carries ms, rate, algorithmic bytes and their fraction of the HBM peak, and — on one GPU —
+    the CPU baselines of that configuration (the C oracle port and the torch restatement of the reference's fallback)."""
+    from robogoat_b200 import _lib, ops
+    import workloads
     import robocache
     flush = L2Flush(dev)
+    cpu = (world == 1 and rank == 0)
+    if cpu:
+        import oracle
+        from oracle import torch_path
 
     # the headline workload generated from other seeds: how much the figure depends on the draw
     if world == 1:
@@ -487,7 +639,21 @@ def run_extras(L, dev, local, rank, world, peak, ex):
         ex["resample_bf16_B4096_other_seeds_ms"] = {"ms_per_call": per_seed,
                                                    "timing": "20 back-to-back calls through the Python binding (output allocation included)"}
 
-    # fusion throughput, B=16384 per GPU, bf16
+    # configs[0]: fp32 B=32 S=500 D=256 T=250, linspace targets shared by the batch (the reference's own CPU-runnable case)
+    c1 = workloads.resample_inputs(B=32, S=500, D=256, T=250, dtype=torch.float32, irregular_targets=False, seed=rank)
+    d1 = [t.to(dev) for t in c1]
+    b1 = workloads.resample_bytes(32, 500, 250, 256, 4)
+    med, mean = time_cold(lambda: robocache.resample_trajectories(*d1), 200, 20, flush)
+    ex["cfg1_resample_fp32_B32"] = gpu_record(med, b1, "GB/s", b1, peak, "per-call events through the public API incl. output allocation, L2 flushed before each call (median of 200)", world)
+    ex["cfg1_resample_fp32_B32"]["reference_published_h100_ms"] = {"gpu_p50": 2.605, "torch_cpu_p50": 38.385,
+                                                                  "source": "robocache/bench/results/benchmark_h100_20251106_172811.csv:4-5 (bf16, wall-clock harness)"}
+    if cpu:
+        ex["cfg1_resample_fp32_B32"]["cpu_baseline"] = cpu_records(
+            "GB/s", b1, 1.0, "the full configuration", port_fn=lambda k: oracle.resample_trajectories(*c1, threads=k),
+            torch_fn=lambda: torch_path.interpolate_stream(*c1), budget_s=1.0)
+    del d1
+
+    # configs[2]: fusion throughput, B=16384 per GPU, bf16
     Bf = 16384
     a = workloads.fusion_inputs(B=Bf, dtype=torch.bfloat16, seed=rank, device=dev)
     fb = workloads.fusion_bytes(Bf, 50, 2)
@@ -502,13 +668,25 @@ def run_extras(L, dev, local, rank, world, peak, ex):
         f()
     e1.record(); torch.cuda.synchronize()
     ms = max_over_ranks(e0.elapsed_time(e1) / iters, world, dev)
-    ex["fusion_bf16_B16384"] = {"ms": ms, "GB/s": fb * world / (ms * 1e-3) / 1e9, "frac_of_hbm_peak": fb / (ms * 1e-3) / 1e9 / peak,
-                                "bytes_per_gpu": fb, "timing": "50 back-to-back calls incl. output allocation, inputs 0.8 GB > L2"}
+    ex["fusion_bf16_B16384"] = gpu_record(ms, fb, "GB/s", fb, peak, "50 back-to-back calls incl. output allocation, inputs 0.8 GB > L2", world)
+    if cpu:
+        a256 = [x[:256].cpu() for x in a]
+        ex["fusion_bf16_B16384"]["cpu_baseline"] = cpu_records(
+            "GB/s", fb / 64, 64.0, "B=256 items of the batch (the fallback loops over items: linear in B)",
+            port_fn=lambda k: oracle.fuse_multimodal(*a256, threads=k), torch_fn=lambda: torch_path.fuse_multimodal(*a256))
     del a
     # fusion latency, B=4
     a4 = workloads.fusion_inputs(B=4, dtype=torch.bfloat16, seed=rank, device=dev)
     med, mean = time_cold(lambda: ops.fuse_multimodal_cuda(*a4), 200, 20, flush)
-    ex["fusion_bf16_B4_latency_us"] = {"median": med * 1e3, "mean": mean * 1e3, "timing": "per-call events, L2 flushed before each call"}
+    fb4 = workloads.fusion_bytes(4, 50, 2)
+    ex["fusion_bf16_B4"] = gpu_record(med, fb4, "GB/s", fb4, peak, "per-call events, L2 flushed before each call (median of 200); a latency case: "
+                                      "434 560 B take 0.07 us at the HBM peak, the call is launch-bound", world)
+    ex["fusion_bf16_B4"]["latency_us"] = {"median": med * 1e3, "mean": mean * 1e3}
+    if cpu:
+        a4c = [x.cpu() for x in a4]
+        ex["fusion_bf16_B4"]["cpu_baseline"] = cpu_records(
+            "GB/s", fb4, 1.0, "the full configuration", port_fn=lambda k: oracle.fuse_multimodal(*a4c, threads=k),
+            torch_fn=lambda: torch_path.fuse_multimodal(*a4c), budget_s=0.5)
     from robogoat_b200.graphs import GraphedOp
     gop = GraphedOp(ops.fuse_multimodal_cuda, a4)
     torch.cuda.synchronize()
@@ -522,25 +700,34 @@ def run_extras(L, dev, local, rank, world, peak, ex):
         ops.fuse_multimodal_cuda(*a4)
     torch.cuda.synchronize()
     eager_us = (time.perf_counter() - t0) / 1000 * 1e6
-    ex["fusion_bf16_B4_wall_us_per_call"] = {"cuda_graph_replay": graph_us, "direct_call": eager_us,
-                                             "timing": "host wall clock over 1000 back-to-back calls (warm L2): what a caller in a loop sees"}
+    ex["fusion_bf16_B4"]["wall_us_per_call"] = {"cuda_graph_replay": graph_us, "direct_call": eager_us,
+                                                "timing": "host wall clock over 1000 back-to-back calls (warm L2): what a caller in a loop sees"}
 
-    # voxel occupancy, 500k points, 128^3 (public API: int32 grid; harness format: uint8 grid)
+    # configs[3]: voxel occupancy, 500k points, 128^3 (public API: int32 grid; harness format: uint8 grid)
     pts = workloads.voxel_uniform_inputs(500_000, seed=rank, device=dev)
     kw = workloads.VOXEL_OCCUPANCY_GEOMETRY
     med, mean = time_cold(lambda: robocache.voxelize_pointcloud(pts, mode="occupancy", **kw), 200, 20, flush)
-    ex["voxel_occupancy_500k_128"] = {"median_us": med * 1e3, "Gpts/s": 500_000 / (med * 1e-3) / 1e9,
-                                      "timing": "per-call events incl. grid allocation and zero-fill, L2 flushed before each call"}
-    med, mean = time_cold(lambda: ops.voxelize_pointcloud_cuda(pts, None, kw["grid_min"], kw["voxel_size"], kw["grid_size"],
-                                                               "occupancy", occupancy_dtype=torch.uint8), 200, 20, flush)
-    ex["voxel_occupancy_u8_500k_128"] = {"median_us": med * 1e3, "Gpts/s": 500_000 / (med * 1e-3) / 1e9,
-                                         "timing": "same, uint8 occupancy plane (2 MiB zero-fill instead of 8 MiB)"}
+    vb = workloads.voxel_bytes(500_000, 0, 128 ** 3, "occupancy")["total"]
+    ex["voxel_occupancy_500k_128"] = gpu_record(med, 500_000, "Gpts/s", vb, peak,
+                                                "per-call events incl. grid allocation and zero-fill, L2 flushed before each call; "
+                                                "14.4 MB take 2.2 us at the HBM peak: launch-bound", world)
+    med8, _ = time_cold(lambda: ops.voxelize_pointcloud_cuda(pts, None, kw["grid_min"], kw["voxel_size"], kw["grid_size"],
+                                                             "occupancy", occupancy_dtype=torch.uint8), 200, 20, flush)
+    ex["voxel_occupancy_u8_500k_128"] = gpu_record(med8, 500_000, "Gpts/s", 6_000_000 + 128 ** 3, peak,
+                                                   "same, uint8 occupancy plane (2 MiB zero-fill instead of 8 MiB)", world)
+    if cpu:
+        pc = pts.cpu()
+        ex["voxel_occupancy_500k_128"]["cpu_baseline"] = cpu_records(
+            "Gpts/s", 500_000, 1.0, "the full configuration (the torch fallback clamps out-of-grid points and is x-major: a timed baseline, not the oracle)",
+            port_fn=lambda k: oracle.voxelize_pointcloud(pc, None, mode="occupancy", **kw), port_threaded=False,
+            torch_fn=lambda: torch_path.voxelize_pointcloud(pc, None, mode="occupancy", **kw), budget_s=1.0)
     del pts
 
-    # voxel count + mean at scale: N = 2^26 points per GPU, 512^3, F=4
+    # configs[4]: voxel count + mean at scale: N = 2^26 points per GPU, 512^3, F=4
     N = 1 << 26
     pts, feats = workloads.voxel_mixture_inputs(N, seed=rank, device=dev)
     kw = workloads.VOXEL_MIXTURE_GEOMETRY
+    occupied = int((robocache.voxelize_pointcloud(pts, mode="count", **kw) > 0).sum().item())
     for mode in ("count", "mean"):
         fn = (lambda: robocache.voxelize_pointcloud(pts, feats if mode == "mean" else None, mode=mode, **kw))
         for _ in range(3):
@@ -552,134 +739,21 @@ def run_extras(L, dev, local, rank, world, peak, ex):
             r = fn(); del r
         e1.record(); torch.cuda.synchronize()
         ms = max_over_ranks(e0.elapsed_time(e1) / iters, world, dev)
-        ex[f"voxel_{mode}_64M_512"] = {"ms": ms, "Gpts/s_per_gpu": N / (ms * 1e-3) / 1e9,
-                                       "timing": "10 back-to-back calls incl. zero-fill (and normalise for mean); working set > L2"}
+        vb = workloads.voxel_bytes(N, 4, 512 ** 3, mode, occupied)["total"]
+        ex[f"voxel_{mode}_64M_512"] = gpu_record(ms, N, "Gpts/s", vb, peak,
+                                                 "10 back-to-back calls incl. zero-fill (and normalise for mean); working set > L2", world)
+        ex[f"voxel_{mode}_64M_512"]["Gpts/s_per_gpu"] = N / (ms * 1e-3) / 1e9
+        ex[f"voxel_{mode}_64M_512"]["occupied_voxels"] = occupied
+        if cpu:
+            Ns = 1 << 22
+            ps, fs_ = pts[:Ns].cpu(), feats[:Ns].cpu()
+            ex[f"voxel_{mode}_64M_512"]["cpu_baseline"] = cpu_records(
+                "Gpts/s", Ns, N / Ns, "the first 2^22 points of the cloud into the same 512^3 grid, scaled linearly in N",
+                port_fn=lambda k: oracle.voxelize_pointcloud(ps, fs_ if mode == "mean" else None, mode=mode, **kw), port_threaded=False,
+                torch_fn=lambda: torch_path.voxelize_pointcloud(ps, fs_ if mode == "mean" else None, mode=mode, **kw), budget_s=2.0)
     if world > 1:
-        from robogoat_b200 import sharding
-        # optional gather of the batch-sharded resample outputs (not on the timed headline path)
-        shard = torch.empty((HEADLINE["B"], HEADLINE["T"], HEADLINE["D"]), dtype=torch.bfloat16, device=dev)
-        for _ in range(2):
-            g = sharding.gather_rows(shard, HEADLINE["B"] * world); del g
-        barrier(world)
-        e0.record()
-        for _ in range(3):
-            g = sharding.gather_rows(shard, HEADLINE["B"] * world); del g
-        e1.record(); torch.cuda.synchronize()
-        ms = max_over_ranks(e0.elapsed_time(e1) / 3, world, dev)
-        ex["resample_output_all_gather"] = {"ms": ms, "bytes_per_gpu_shard": shard.numel() * 2,
-                                            "bus_GB/s": shard.numel() * 2 * (world - 1) / (ms * 1e-3) / 1e9,
-                                            "note": "NCCL all-gather of every rank's [4096,250,256] bf16 output into a full copy on every rank"}
-        del shard
-        fn = lambda: sharding.voxelize_sharded(pts, feats, mode="mean", **kw)
-        for _ in range(2):
-            r = fn(); del r
-        barrier(world)
-        e0.record()
-        for _ in range(5):
-            r = fn(); del r
-        e1.record(); torch.cuda.synchronize()
-        ms = max_over_ranks(e0.elapsed_time(e1) / 5, world, dev)
-        ex["voxel_mean_sharded_with_grid_reduce"] = {"ms": ms, "Gpts/s_total": N * world / (ms * 1e-3) / 1e9,
-                                                     "note": "point shards + NCCL all-reduce of the 2.68 GB partial grids + normalise; every rank holds the full grid"}
-        fn = lambda: sharding.voxelize_sharded_slab(pts, feats, mode="mean", **kw)
-        for _ in range(2):
-            r = fn(); del r
-        barrier(world)
-        e0.record()
-        for _ in range(5):
-            r = fn(); del r
-        e1.record(); torch.cuda.synchronize()
-        ms = max_over_ranks(e0.elapsed_time(e1) / 5, world, dev)
-        ex["voxel_mean_sharded_slab_output"] = {"ms": ms, "Gpts/s_total": N * world / (ms * 1e-3) / 1e9,
-                                                "note": "point shards + NCCL reduce-scatter; each rank keeps the reduced, normalised 1/N slab of z-planes"}
-        # point exchange: bucket by owner slab, all-to-all of (id, features) records, scatter into the own slab
-        fn = lambda: sharding.voxelize_sharded_exchange(pts, feats, mode="mean", **kw)
-        for _ in range(2):
-            r = fn(); del r
-        barrier(world)
-        e0.record()
-        for _ in range(5):
-            r = fn(); del r
-        e1.record(); torch.cuda.synchronize()
-        ms = max_over_ranks(e0.elapsed_time(e1) / 5, world, dev)
-        K = sharding.sub_parts(512 ** 3, 4, world, "mean")
-        ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
-        barrier(world)
-        ev[0].record()
-        ids, fbk, pc = ops.voxel_partition_cuda(pts, feats, kw["grid_min"], kw["voxel_size"], kw["grid_size"], world, K)
-        ev[1].record()
-        plan = sharding.exchange_plan(sharding._gather_counts(pc), rank, K)
-        (ids_in, f_in), _ = sharding.exchange_buckets([ids, fbk], plan["send_counts"], recv_counts=plan["recv_counts"])
-        ev[2].record()
-        lo_v, hi_v = sharding.slab_bounds(512 ** 3, rank, world)
-        r = ops.voxel_scatter_runs_cuda(ids_in.data_ptr(), f_in.data_ptr(), dev, 4, lo_v, hi_v, plan["runs"], K, "mean")
-        ev[3].record(); torch.cuda.synchronize()
-        stages = [max_over_ranks(ev[i].elapsed_time(ev[i + 1]), world, dev) for i in range(3)]
-        received = int(ids_in.numel())
-        del r, ids, fbk, ids_in, f_in
-        ex["voxel_mean_sharded_point_exchange"] = {
-            "ms": ms, "Gpts/s_total": N * world / (ms * 1e-3) / 1e9, "sub_ranges_per_slab": K,
-            "stage_ms": {"partition": stages[0], "counts_and_all_to_all": stages[1], "scatter_normalise": stages[2]},
-            "points_received_rank0": received,
-            "note": "stable partition by owner slab and sub-range + NCCL all-to-all of 20-byte (id, features) records + scatter "
-                    "into the rank's own 1/N slab, one L2-sized sub-range per pass; no rank holds a dense grid"}
-        # direct form: the partition kernel stores into the owners' buffers over NVLink
-        try:
-            px = sharding.PointExchange(capacity=int(1.25 * N), feature_width=4)
-        except RuntimeError as e:       # raised on every rank alike
-            px = None
-            ex["voxel_mean_sharded_point_exchange_direct"] = {"unavailable": str(e)[:200]}
-        if px is not None:
-            fn = lambda: sharding.voxelize_sharded_exchange(pts, feats, mode="mean", direct=px, **kw)
-            for _ in range(2):
-                r = fn(); del r
-            barrier(world)
-            e0.record()
-            for _ in range(5):
-                r = fn(); del r
-            e1.record(); torch.cuda.synchronize()
-            ms = max_over_ranks(e0.elapsed_time(e1) / 5, world, dev)
-            L.rc_set_option(2, 0)                   # sorted chunks written as they lie instead of line-aligned groups
-            for _ in range(2):
-                r = fn(); del r
-            barrier(world)
-            e0.record()
-            for _ in range(5):
-                r = fn(); del r
-            e1.record(); torch.cuda.synchronize()
-            ms_plain = max_over_ranks(e0.elapsed_time(e1) / 5, world, dev)
-            L.rc_set_option(2, 1)
-            barrier(world)
-            ev[0].record()
-            pc, scratch = ops.voxel_partition_count_cuda(pts, kw["grid_min"], kw["voxel_size"], kw["grid_size"], world, K)
-            plan = sharding.exchange_plan(sharding._gather_counts(pc), rank, K)
-            ev_move = torch.cuda.Event(enable_timing=True)
-            ev[1].record()
-            fits = max(plan["totals"]) <= px.capacity
-            if fits:
-                ops.voxel_partition_move_cuda(pts, feats, kw["grid_min"], kw["voxel_size"], kw["grid_size"], world, K,
-                                              [px.ids.peers[p // K] for p in range(world * K)],
-                                              [px.features.peers[p // K] for p in range(world * K)], plan["dest_start"], scratch,
-                                              remote=True)
-                ev_move.record()
-                px.stream_barrier()
-            ev[2].record()
-            if fits:
-                r = ops.voxel_scatter_runs_cuda(px.ids.ptr, px.features.ptr, dev, 4, lo_v, hi_v, plan["runs"], K, "mean")
-                del r
-            ev[3].record(); torch.cuda.synchronize()
-            stages = [max_over_ranks(ev[i].elapsed_time(ev[i + 1]), world, dev) for i in range(3)]
-            sent_remote = sum(c for d, c in enumerate(plan["send_counts"]) if d != rank) * 20
-            move_ms = max_over_ranks(ev[1].elapsed_time(ev_move), world, dev) if fits else None
-            ex["voxel_mean_sharded_point_exchange_direct"] = {
-                "ms": ms, "Gpts/s_total": N * world / (ms * 1e-3) / 1e9, "fits_receive_buffers": fits,
-                "ms_without_line_aligned_stores": ms_plain,
-                "stage_ms": {"count_and_count_matrix": stages[0], "move_over_nvlink_and_barrier": stages[1], "scatter_normalise": stages[2]},
-                "move_kernel_ms": move_ms,
-                "nvlink_GB/s_out_per_gpu_during_move": sent_remote / (move_ms * 1e-3) / 1e9 if fits else None,
-                "note": "same, but the partition kernel stores its sorted chunks straight into the owners' receive buffers "
-                        "(peer memory over NVLink); collectives left: the count matrix and one barrier"}
-            px.close()
+        multi_gpu_extras(L, dev, rank, world, ex, pts, feats, kw, N,
+                         {m: ex[f"voxel_{m}_64M_512"]["ms"] for m in ("count", "mean")})
     else:
         # the two kernels of the point exchange on one GPU: partition for 8 owners, then one owner's bucket into its slab
         ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
@@ -715,10 +789,183 @@ def run_extras(L, dev, local, rank, world, peak, ex):
     return ex
 
 
+def sharded_parity(dev, rank, world, px) -> dict:
+    """Every sharded voxel form on a cloud small enough for the CPU oracle (2^20 mixture points into 128^3), checked
+    on every rank against the oracle run on the whole cloud: occupancy and counts exact, means within the oracle's
+    tolerance.  Returns one flag per form, true only if it held on all ranks."""
+    import oracle
+    import workloads
+    from robogoat_b200 import sharding
+    import torch.distributed as dist
+    n = 1 << 20
+    p_h, f_h = workloads.voxel_mixture_inputs(n, seed=99)
+    p_h = p_h * 0.25
+    kw = dict(grid_min=[-6.4, -6.4, -6.4], voxel_size=0.1, grid_size=[128, 128, 128])
+    V = 128 ** 3
+    occ = oracle.voxelize_pointcloud(p_h, None, mode="occupancy", **kw).reshape(V)
+    cnt = oracle.voxelize_pointcloud(p_h, None, mode="count", **kw).reshape(V)
+    mean, mcnt, sabs = oracle.voxelize_pointcloud(p_h, f_h, mode="mean", return_aux=True, **kw)
+    tol = oracle.mean_tolerance(mcnt, sabs, mean).reshape(V, 4)
+    mean = mean.reshape(V, 4)
+    lo, hi = sharding.shard_bounds(n, rank, world)
+    pl, fl = p_h[lo:hi].to(dev), f_h[lo:hi].to(dev)
+
+    def count_ok(got, a=0, b=V):
+        return bool(torch.equal(got.reshape(-1).cpu(), cnt[a:b]))
+
+    def mean_ok(got, a=0, b=V):
+        return bool(((got.reshape(-1, 4).cpu() - mean[a:b]).abs() <= tol[a:b]).all())
+
+    sa, sb = rank * V // world, (rank + 1) * V // world       # reduce-scatter slabs
+    xa, xb = sharding.slab_bounds(V, rank, world)             # point-exchange slabs
+    flags = {}
+    flags["all_reduce"] = (bool(torch.equal(sharding.voxelize_sharded(pl, None, mode="occupancy", **kw).reshape(V).cpu(), occ))
+                           and count_ok(sharding.voxelize_sharded(pl, None, mode="count", **kw))
+                           and mean_ok(sharding.voxelize_sharded(pl, fl, mode="mean", **kw)))
+    flags["slab"] = (count_ok(sharding.voxelize_sharded_slab(pl, None, mode="count", **kw), sa, sb)
+                     and mean_ok(sharding.voxelize_sharded_slab(pl, fl, mode="mean", **kw), sa, sb))
+    flags["exchange"] = (count_ok(sharding.voxelize_sharded_exchange(pl, None, mode="count", **kw), xa, xb)
+                         and mean_ok(sharding.voxelize_sharded_exchange(pl, fl, mode="mean", **kw), xa, xb))
+    if px is not None:
+        flags["exchange_direct"] = (count_ok(sharding.voxelize_sharded_exchange(pl, None, mode="count", direct=px, **kw), xa, xb)
+                                    and mean_ok(sharding.voxelize_sharded_exchange(pl, fl, mode="mean", direct=px, **kw), xa, xb))
+        flags["exchange_direct_batched"] = (
+            count_ok(sharding.voxelize_sharded_exchange(pl, None, mode="count", direct=px, batches=4, **kw), xa, xb)
+            and mean_ok(sharding.voxelize_sharded_exchange(pl, fl, mode="mean", direct=px, batches=4, **kw), xa, xb))
+    names = sorted(flags)
+    t = torch.tensor([1 if flags[k] else 0 for k in names], dtype=torch.int32, device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MIN)
+    return {k: bool(v) for k, v in zip(names, t.tolist())}
+
+
+def multi_gpu_extras(L, dev, rank, world, ex, pts, feats, kw, N, single_ms):
+    """Voxelisation over point shards (2^26 points per GPU into 512^3), every form timed in count and mean mode and
+    checked against the oracle on a small cloud first; occupancy at the 500 k / 128^3 configuration with the
+    reference's all_reduce(MAX).  ``efficiency`` = one GPU's time for its 2^26 points / this time (weak scaling)."""
+    from robogoat_b200 import sharding, ops
+    import workloads
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+    def timed(fn, iters=5, warm=2):
+        for _ in range(warm):
+            r = fn(); del r
+        barrier(world)
+        e0.record()
+        for _ in range(iters):
+            r = fn(); del r
+        e1.record(); torch.cuda.synchronize()
+        return max_over_ranks(e0.elapsed_time(e1) / iters, world, dev)
+
+    # optional gather of the batch-sharded resample outputs (not on the timed headline path)
+    shard = torch.empty((HEADLINE["B"], HEADLINE["T"], HEADLINE["D"]), dtype=torch.bfloat16, device=dev)
+    ms = timed(lambda: sharding.gather_rows(shard, HEADLINE["B"] * world), 3)
+    ex["resample_output_all_gather"] = {"ms": ms, "bytes_per_gpu_shard": shard.numel() * 2,
+                                        "bus_GB/s": shard.numel() * 2 * (world - 1) / (ms * 1e-3) / 1e9,
+                                        "note": "NCCL all-gather of every rank's [4096,250,256] bf16 output into a full copy on every rank"}
+    del shard
+
+    try:
+        px = sharding.PointExchange(capacity=int(1.25 * N), feature_width=4)
+    except RuntimeError as e:       # raised on every rank alike
+        px = None
+        ex["voxel_sharded_direct_unavailable"] = str(e)[:200]
+    parity = sharded_parity(dev, rank, world, px)
+    ex["voxel_sharded_parity"] = {"parity": parity,
+                                  "checked": "2^20 mixture points into 128^3 on every rank against the CPU oracle run on the whole cloud: "
+                                             "occupancy and counts exact, means within 1e-5 relative + 1e-6 of the mean summand"}
+
+    # configs[3] over point shards: 500 000 points in all, private uint8 planes, all_reduce(MAX) as the reference's
+    # multi-GPU test does (robocache/tests/test_multi_gpu.py:60-81)
+    okw = workloads.VOXEL_OCCUPANCY_GEOMETRY
+    allp = workloads.voxel_uniform_inputs(500_000, seed=0, device=dev)
+    lo, hi = sharding.shard_bounds(500_000, rank, world)
+    mine = allp[lo:hi].contiguous()
+    ms = timed(lambda: sharding.voxelize_sharded(mine, None, mode="occupancy", **okw), 50, 10)
+    ex["voxel_occupancy_500k_128_sharded_max_reduce"] = {
+        "ms": ms, "Gpts/s_total": (500_000 / (ms * 1e-3) / 1e9) if parity.get("all_reduce") else 0.0, "parity": parity.get("all_reduce"),
+        "note": "500 000 points split over the ranks, private uint8 occupancy planes, NCCL all_reduce(MAX) of 2 MiB, int32 result on every rank; "
+                "50 back-to-back calls (warm L2): the collective's latency bounds it"}
+    del allp, mine
+
+    forms = [("all_reduce", "all_reduce", lambda m: sharding.voxelize_sharded(pts, feats if m == "mean" else None, mode=m, **kw),
+              "point shards + NCCL all-reduce of the dense partial grids (+ normalise); every rank holds the full grid"),
+             ("reduce_scatter_slab", "slab", lambda m: sharding.voxelize_sharded_slab(pts, feats if m == "mean" else None, mode=m, **kw),
+              "point shards + NCCL reduce-scatter; each rank keeps the reduced (normalised) 1/N slab of z-planes"),
+             ("point_exchange", "exchange", lambda m: sharding.voxelize_sharded_exchange(pts, feats if m == "mean" else None, mode=m, **kw),
+              "stable partition by owner slab and sub-range + NCCL all-to-all of (id, features) records + scatter into the own slab")]
+    if px is not None:
+        forms += [("point_exchange_direct", "exchange_direct",
+                   lambda m: sharding.voxelize_sharded_exchange(pts, feats if m == "mean" else None, mode=m, direct=px, **kw),
+                   "the partition kernel stores its sorted chunks straight into the owners' receive buffers (peer memory over NVLink)"),
+                  ("point_exchange_direct_batched", "exchange_direct_batched",
+                   lambda m: sharding.voxelize_sharded_exchange(pts, feats if m == "mean" else None, mode=m, direct=px, batches=4, **kw),
+                   "same in four slices of the local cloud: the stores of slice i+1 overlap the owners' accumulation of slice i")]
+    for mode in ("mean", "count"):
+        for name, pkey, fn, note in forms:
+            ms = timed(lambda: fn(mode))
+            ok = bool(parity.get(pkey))
+            ex[f"voxel_{mode}_sharded_{name}"] = {"ms": ms, "Gpts/s_total": (N * world / (ms * 1e-3) / 1e9) if ok else 0.0, "parity": ok,
+                                                  "efficiency": single_ms[mode] / ms, "single_gpu_ms": single_ms[mode], "note": note}
+
+    # stages of the all-to-all and of the direct form (mean mode), each max over ranks
+    K = sharding.sub_parts(512 ** 3, 4, world, "mean")
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+    barrier(world)
+    ev[0].record()
+    ids, fbk, pc = ops.voxel_partition_cuda(pts, feats, kw["grid_min"], kw["voxel_size"], kw["grid_size"], world, K)
+    ev[1].record()
+    plan = sharding.exchange_plan(sharding._gather_counts(pc), rank, K)
+    (ids_in, f_in), _ = sharding.exchange_buckets([ids, fbk], plan["send_counts"], recv_counts=plan["recv_counts"])
+    ev[2].record()
+    lo_v, hi_v = sharding.slab_bounds(512 ** 3, rank, world)
+    r = ops.voxel_scatter_runs_cuda(ids_in.data_ptr(), f_in.data_ptr(), dev, 4, lo_v, hi_v, plan["runs"], K, "mean")
+    ev[3].record(); torch.cuda.synchronize()
+    stages = [max_over_ranks(ev[i].elapsed_time(ev[i + 1]), world, dev) for i in range(3)]
+    ex["voxel_mean_sharded_point_exchange"].update({
+        "sub_ranges_per_slab": K, "points_received_rank0": int(ids_in.numel()),
+        "stage_ms": {"partition": stages[0], "counts_and_all_to_all": stages[1], "scatter_normalise": stages[2]}})
+    del r, ids, fbk, ids_in, f_in
+    if px is not None:
+        L.rc_set_option(2, 0)                   # sorted chunks written as they lie instead of line-aligned groups
+        ms_plain = timed(lambda: sharding.voxelize_sharded_exchange(pts, feats, mode="mean", direct=px, **kw))
+        L.rc_set_option(2, 1)
+        barrier(world)
+        ev[0].record()
+        pc, scratch = ops.voxel_partition_count_cuda(pts, kw["grid_min"], kw["voxel_size"], kw["grid_size"], world, K)
+        plan = sharding.exchange_plan(sharding._gather_counts(pc), rank, K)
+        ev_move = torch.cuda.Event(enable_timing=True)
+        ev[1].record()
+        fits = max(plan["totals"]) <= px.capacity
+        if fits:
+            ops.voxel_partition_move_cuda(pts, feats, kw["grid_min"], kw["voxel_size"], kw["grid_size"], world, K,
+                                          [px.ids.peers[p // K] for p in range(world * K)],
+                                          [px.features.peers[p // K] for p in range(world * K)], plan["dest_start"], scratch,
+                                          remote=True)
+            ev_move.record()
+            px.stream_barrier()
+        ev[2].record()
+        if fits:
+            r = ops.voxel_scatter_runs_cuda(px.ids.ptr, px.features.ptr, dev, 4, lo_v, hi_v, plan["runs"], K, "mean")
+            del r
+        ev[3].record(); torch.cuda.synchronize()
+        stages = [max_over_ranks(ev[i].elapsed_time(ev[i + 1]), world, dev) for i in range(3)]
+        sent_remote = sum(c for d, c in enumerate(plan["send_counts"]) if d != rank) * 20
+        move_ms = max_over_ranks(ev[1].elapsed_time(ev_move), world, dev) if fits else None
+        ex["voxel_mean_sharded_point_exchange_direct"].update({
+            "fits_receive_buffers": fits, "ms_without_line_aligned_stores": ms_plain,
+            "stage_ms": {"count_and_count_matrix": stages[0], "move_over_nvlink_and_barrier": stages[1], "scatter_normalise": stages[2]},
+            "move_kernel_ms": move_ms,
+            "nvlink_GB/s_out_per_gpu_during_move": sent_remote / (move_ms * 1e-3) / 1e9 if fits else None,
+            "bound": "the move kernel (NVLink, measured 770 GB/s per direction) and the owner's atomics run back to back here; "
+                     "the batched form overlaps them"})
+        px.close()
+
+
 def run_profile_case(name: str):
     """A few launches of one kernel on a case sized for a profiler capture: larger than L2, well under
     a GB on the device.  Prints one JSON line with the CUDA-event time of the last launch."""
-    from robogoat_b200 import ops, workloads
+    from robogoat_b200 import ops
+    import workloads
     import robocache
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(0)
@@ -738,6 +985,14 @@ def run_profile_case(name: str):
         mode = name.split("_")[1]
         fn = lambda: robocache.voxelize_pointcloud(pts, feats if mode == "mean" else None, mode=mode, **kw)
         units = {"N": N}
+    elif name == "voxel_mean_runs":
+        # the slab-ordered run path on a capture-sized case: 2^24 mixture points into 256^3 voxels of 0.2 m
+        # (accumulators 335 MB > L2, 1.2 GB on the device in all)
+        N = 1 << 24
+        pts, feats = workloads.voxel_mixture_inputs(N, seed=0, device=dev)
+        kw = dict(grid_min=[-25.6, -25.6, -25.6], voxel_size=0.2, grid_size=[256, 256, 256])
+        fn = lambda: robocache.voxelize_pointcloud(pts, feats, mode="mean", **kw)
+        units = {"N": N, "grid": "256^3"}
     elif name in ("voxel_partition", "voxel_partition_aligned"):
         if name.endswith("_aligned"):       # the write-out used for peer destinations, here with local ones
             from robogoat_b200 import _lib
@@ -780,7 +1035,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extras", action="store_true")
     ap.add_argument("--profile-case", default=None,
-                    help="run 4 launches of one kernel on a small case (resample, fusion, voxel_mean, voxel_count, voxel_occupancy, voxel_partition, voxel_partition_aligned, voxel_scatter_runs; voxel_mean_full = headline size)")
+                    help="run 4 launches of one kernel on a small case (resample, fusion, voxel_mean, voxel_count, voxel_occupancy, voxel_partition, voxel_partition_aligned, voxel_scatter_runs, voxel_mean_runs; voxel_mean_full = headline size)")
     args = ap.parse_args()
     if args.profile_case:
         run_profile_case(args.profile_case)

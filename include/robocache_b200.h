@@ -149,11 +149,14 @@ RC_API int rc_voxelize(const float* points, const float* features, void* grid, i
 
 /*
  * rc_voxelize with an optional device scratch buffer.  Mean mode on grids whose accumulators do not
- * fit in L2 then runs in two phases (voxel ids written once to the scratch, then several passes that
- * each scatter into one slab of the grid), which keeps the atomics L2-resident.  Results are the
- * same as rc_voxelize's (counts exact, sums equal up to fp32 summation order).
- *   scratch, scratch_bytes : device buffer, 16-byte aligned, at least rc_voxelize_scratch_bytes()
- *                            (4 bytes per point when the two-phase path applies, else 0); may be NULL.
+ * fit in L2 then runs in phases that keep the atomics L2-resident: with four feature channels the
+ * points are first bucketed by slab of the grid into (voxel id, feature row) records in the scratch
+ * and the slabs are then accumulated one after the other from those records; with other widths the
+ * voxel ids are written once to the scratch and several passes each scatter into one slab.  Results
+ * are the same as rc_voxelize's (counts exact, sums equal up to fp32 summation order).
+ *   scratch, scratch_bytes : device buffer, 256-byte aligned, at least rc_voxelize_scratch_bytes()
+ *                            (about 21.5 bytes per point for four channels, 4 bytes per point for other
+ *                            widths, 0 when the plain path applies); may be NULL (plain path).
  * The scratch is only used during the call's own work on `stream`.  No counterpart in the reference.
  */
 RC_API uint64_t rc_voxelize_scratch_bytes(int64_t N, int32_t F, const int32_t grid_size_host[3], int mode);
@@ -170,6 +173,24 @@ RC_API int rc_voxelize_ex(const float* points, const float* features, void* grid
  */
 RC_API int rc_voxel_normalize(float* grid, const int32_t* counts, int64_t voxel_begin, int64_t voxel_end,
                        int32_t F, int device, void* stream);
+
+/*
+ * Batched voxel grids in one launch: points [B,N,3] fp32 -> grid fp32 [B, D, H, W] (occupancy 0/1, density =
+ * points per voxel) or [B, D, H, W, F] (feature mean; features [B,N,F] fp32, counts int32 [B, D, H, W] as work
+ * space and second output).  depth/height/width are the z/y/x extents; cell (vz, vy, vx) of item b sits at
+ * ((b*D + vz)*H + vy)*W + vx, the item index being folded into the voxel id so that one launch bins the whole batch.
+ * Cell arithmetic, dropping of out-of-grid points and flags as rc_voxelize.
+ * Replaces voxelize_occupancy / voxelize_density / voxelize_feature_mean
+ * (robocache/kernels/cutlass/point_cloud_voxelization.h:59-136; kernels point_cloud_voxelization.cu:41-300).
+ * rc_point_cloud_bounds: per item the minimum and maximum of every coordinate, [B,3] each, starting from +-1e10
+ * (compute_point_cloud_bounds, point_cloud_voxelization.h:218-227, .cu:386-449).
+ */
+typedef enum rc_batched_mode { RC_BATCHED_OCCUPANCY = 0, RC_BATCHED_DENSITY = 1, RC_BATCHED_FEATURE_MEAN = 2 } rc_batched_mode;
+RC_API int rc_voxelize_batched(const float* points, const float* features, float* grid, int32_t* counts, int64_t B,
+                               int64_t N, int32_t F, const float origin_host[3], float voxel_size,
+                               const int32_t dhw_host[3], int mode, uint32_t flags, int device, void* stream);
+RC_API int rc_point_cloud_bounds(const float* points, float* min_bounds, float* max_bounds, int64_t B, int64_t N,
+                                 int device, void* stream);
 
 /*
  * Point exchange for multi-GPU voxelisation: instead of reducing dense partial grids, every rank
@@ -263,8 +284,12 @@ RC_API int rc_peer_free(void* ptr, int device);
  *   - All calls on a device share the one counter array: two calls that overlap on the GPU
  *     (different streams, or different threads) race.  Serialise them on one stream.
  *   - The first call on each device looks up the array's device address; make that call before
- *     any stream capture begins.
- *   - No cudaMalloc, cudaFree or other allocating routine is called.
+ *     any stream capture begins.  Under CUDA's lazy module loading that first call (or the first
+ *     launch of any kernel of this library on the device) is also what makes the driver place the
+ *     library's image, the 8 MiB array included, on the GPU: a caller with a no-allocation region
+ *     makes one warm-up call before entering it.
+ *   - Apart from that one-time module load, no cudaMalloc, cudaFree or other allocating routine is
+ *     called, by this function or on its behalf.
  * Results equal rc_voxelize(..., RC_VOXEL_MEAN, RC_VOXEL_ZERO_INIT) up to fp32 summation order.
  */
 #define RC_STATIC_MAX_VOXELS (1 << 21)

@@ -190,7 +190,7 @@ voxel_ids_kernel(const float* __restrict__ pts, long long N, VoxelGeom g, bool p
 // often two consecutive points fall into the same 1/64 slab of the grid; *flag = 1 (coherent) if at
 // least 15 % do.  The kernels of both strategies are launched behind it and the ones that were not
 // chosen return at once, so the decision never leaves the device.
-constexpr int kProbeTiles = 256;
+constexpr int kProbeTiles = 64;
 __global__ void __launch_bounds__(1024)
 voxel_order_probe_kernel(const float* __restrict__ pts, long long N, VoxelGeom g, long long V, int* __restrict__ flag) {
     __shared__ int s_same, s_pairs;
@@ -332,6 +332,41 @@ voxel_normalize_wide_kernel(float* __restrict__ grid, const int* __restrict__ co
     }
 }
 
+// mean pass 2 for four channels, streaming form: counts + v0 and grid are 16-byte aligned, (v1 - v0) % 4 == 0.  A warp
+// reads 512 consecutive counters per step (four 16-byte loads per lane, all in flight together) and rescales the
+// occupied voxels among its own sixteen; on a sparse grid almost all of the work is the counter stream.
+__global__ void __launch_bounds__(kThreads)
+voxel_normalize_stream_kernel(float4* __restrict__ grid4, const int* __restrict__ counts, long long v0, long long v1,
+                              const int* __restrict__ gate, int gate_want) {
+    if (gate != nullptr && *gate != gate_want) return;
+    const int lane = threadIdx.x & 31;
+    const long long warps_total = static_cast<long long>(gridDim.x) * (kThreads / 32);
+    const long long steps = (v1 - v0 + 511) >> 9;
+    for (long long step = static_cast<long long>(blockIdx.x) * (kThreads / 32) + (threadIdx.x >> 5); step < steps; step += warps_total) {
+        const long long base = v0 + (step << 9) + lane * 4;
+        int4 c[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+            c[k] = (base + k * 128 < v1) ? __ldcs(reinterpret_cast<const int4*>(counts + base + k * 128)) : make_int4(0, 0, 0, 0);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int cc[4] = {c[k].x, c[k].y, c[k].z, c[k].w};
+            if ((cc[0] | cc[1] | cc[2] | cc[3]) == 0) continue;     // counters are never negative
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                if (cc[j] > 0) {                                    // empty voxels stay exactly 0
+                    const float inv = __fdiv_rn(1.0f, static_cast<float>(cc[j]));
+                    float4* o = grid4 + base + k * 128 + j;
+                    float4 x = *o;
+                    x.x = __fmul_rn(x.x, inv); x.y = __fmul_rn(x.y, inv);
+                    x.z = __fmul_rn(x.z, inv); x.w = __fmul_rn(x.w, inv);
+                    *o = x;
+                }
+            }
+        }
+    }
+}
+
 // mean pass 2, one voxel per thread: ragged ends of a range and unaligned buffers
 __global__ void __launch_bounds__(kThreads)
 voxel_normalize_scalar_kernel(float* __restrict__ grid, const int* __restrict__ counts, long long v0, long long v1, int F,
@@ -447,7 +482,12 @@ int normalize_range(float* grid, const int* counts, long long voxel_begin, long 
         const long long cap = 16ll * rc::sm_count(device);
         if (blocks > cap) blocks = cap;
         const unsigned int nb = static_cast<unsigned int>(blocks);
-        if ((F & 3) == 0 && rc::aligned_to(grid, 16))
+        if (F == 4 && rc::aligned_to(grid, 16)) {
+            long long sb = (((body_end - head) + 511) / 512 + kThreads / 32 - 1) / (kThreads / 32);
+            if (sb > cap) sb = cap;
+            voxel_normalize_stream_kernel<<<static_cast<unsigned int>(sb), kThreads, 0, st>>>(reinterpret_cast<float4*>(grid), counts, head,
+                                                                                            body_end, gate, gate_want);
+        } else if ((F & 3) == 0 && rc::aligned_to(grid, 16))
             voxel_normalize_wide_kernel<true><<<nb, kThreads, 0, st>>>(grid, counts, head, body_end, F, gate, gate_want);
         else
             voxel_normalize_wide_kernel<false><<<nb, kThreads, 0, st>>>(grid, counts, head, body_end, F, gate, gate_want);
@@ -529,9 +569,9 @@ int rc_voxelize_ex(const float* points, const float* features, void* grid, int32
     const unsigned int fill_blocks =
         static_cast<unsigned int>(fill_blocks_ll < 64ll * rc::sm_count(device) ? (fill_blocks_ll > 0 ? fill_blocks_ll : 1)
                                                                            : 64ll * rc::sm_count(device));
-    // Mean mode, four channels, accumulators beyond L2, enough scratch: slab-ordered runs (voxel_runs.cu), which
-    // clear and normalise inside their own kernels.  With points in coherent order (decided on the device by the
-    // order probe) one plain pass is faster; its kernels are enqueued too and the strategy not chosen returns at once.
+    // Mean mode, four channels, accumulators beyond L2, enough scratch: slab-ordered runs (voxel_runs.cu) between
+    // one clear and one normalise pass.  With points in coherent order (decided on the device by the order probe)
+    // one plain pass is faster; its kernel is enqueued too and the strategy not chosen returns at once.
     {
         const int forced = rc::g_voxel_passes.load(std::memory_order_relaxed);
         const double acc_bytes = static_cast<double>(V) * 4.0 * (1 + F);
@@ -540,29 +580,27 @@ int rc_voxelize_ex(const float* points, const float* features, void* grid, int32
                                   ? mean_runs_scratch_bytes(N, V, parts) + 256u : 0;
         if (need > 0 && (forced > 1 || (forced == 0 && acc_bytes > static_cast<double>(kResidentBytes))) &&
             scratch != nullptr && rc::aligned_to(scratch, 256) && scratch_bytes >= need && rc::aligned_to(features, 16) &&
-            rc::aligned_to(grid, 16) && rc::aligned_to(counts, 16) && features != nullptr) {
-            const bool clear = (flags & RC_VOXEL_ZERO_INIT) != 0;
-            const bool normalize = !(flags & RC_VOXEL_NO_NORMALIZE);
+            rc::aligned_to(grid, 16) && features != nullptr) {
+            if (flags & RC_VOXEL_ZERO_INIT) {
+                RC_CUDA_TRY(cudaMemsetAsync(grid, 0, static_cast<size_t>(V) * 16, st));
+                RC_CUDA_TRY(cudaMemsetAsync(counts, 0, static_cast<size_t>(V) * 4, st));
+            }
             int* flag = nullptr;
             if (forced == 0 && N >= kProbeMinPoints) {
                 flag = reinterpret_cast<int*>(static_cast<unsigned char*>(scratch) + need - 256u);
                 voxel_order_probe_kernel<<<1, 1024, 0, st>>>(points, N, g, V, flag);
                 const long long cap = 16ll * rc::sm_count(device);
-                if (clear) {
-                    voxel_zero_kernel<<<static_cast<unsigned int>(cap), kThreads, 0, st>>>(static_cast<unsigned char*>(grid), V * 16, flag, 1);
-                    voxel_zero_kernel<<<static_cast<unsigned int>(cap), kThreads, 0, st>>>(reinterpret_cast<unsigned char*>(counts), V * 4, flag, 1);
-                }
                 long long blocks = (N + kPointsPerBlock - 1) / kPointsPerBlock;
                 if (blocks > cap) blocks = cap;
                 launch_bin<kMean>(false, false, static_cast<unsigned int>(blocks), st, points, features, grid, counts, N, F, g,
                                   rc::aligned_to(points, 16), 0, V, flag, 1);
-                if (normalize) {
-                    const int rc_norm = normalize_range(static_cast<float*>(grid), counts, 0, V, F, device, st, flag, 1);
-                    if (rc_norm != RC_OK) return rc_norm;
-                }
             }
-            return mean_runs_launch(points, features, static_cast<float*>(grid), counts, N, g, V, parts, clear, normalize, scratch,
-                                    flag, 0, device, st);
+            const int rc_runs = mean_runs_launch(points, features, static_cast<float*>(grid), counts, N, g, V, parts, scratch,
+                                                 flag, 0, device, st);
+            if (rc_runs != RC_OK) return rc_runs;
+            if (!(flags & RC_VOXEL_NO_NORMALIZE))
+                return normalize_range(static_cast<float*>(grid), counts, 0, V, F, device, st, nullptr, 0);
+            return RC_OK;
         }
     }
     bool overlap_fill = false;

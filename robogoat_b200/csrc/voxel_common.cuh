@@ -35,15 +35,16 @@ inline float host_reciprocal(float vs) {
 // floor((p - lo) / vs) with the reference's rounding (one IEEE subtraction, one IEEE division,
 // floor), at the price of a multiplication for almost every point.  t = a * RN(1/vs) and the
 // exact quotient q = RN(a / vs) differ by less than |t| * 2^-22 (three roundings of 2^-24 each),
-// so floor(t) == floor(q) whenever t is further than that from every integer; only the points
-// that are closer (a few in 10^4 at 512 cells per axis), quotients so small that a product could
-// underflow, NaN and infinities take the division.
+// so floor(t) == floor(q) whenever t is further than that from every integer, i.e. when its
+// fractional part is closer to 0.5 than 0.5 - |t| * 2.5e-7.  Only the points that fail the test (a
+// few in 10^4 at 512 cells per axis), quotients so small that the product could underflow (their
+// fractional part rounds to 0 or 1), NaN and infinities take the division.
 __device__ __forceinline__ float axis_cell(float p, float lo, float vs, float inv_vs) {
     const float a = __fsub_rn(p, lo);
     const float t = __fmul_rn(a, inv_vs);
     float f = floorf(t);
-    const float d = fminf(__fsub_rn(t, f), __fsub_rn(__fadd_rn(f, 1.0f), t));   // distance to the nearest integer
-    if (!(d > fmaxf(__fmul_rn(fabsf(t), 2.5e-7f), 1.0e-30f))) f = floorf(__fdiv_rn(a, vs));
+    const float off = fabsf(__fsub_rn(__fsub_rn(t, f), 0.5f));          // |frac(t) - 0.5|, in [0, 0.5]
+    if (!(off < __fmaf_rn(fabsf(t), -2.5e-7f, 0.5f))) f = floorf(__fdiv_rn(a, vs));
     return f;
 }
 
@@ -152,14 +153,14 @@ __device__ __forceinline__ void scatter_one(int id, long long pi, const float* _
 
 // ---- mean mode by slab-ordered runs (voxel_runs.cu), used by rc_voxelize_ex for F = 4 on grids whose
 // accumulators exceed L2.  `parts` slabs (at most kMeanRunsMaxParts); scratch of mean_runs_scratch_bytes(),
-// 256-byte aligned; grid, counts and features 16-byte aligned; V < 2^31; N <= 2^31 - 4096.  `clear` zero-fills
-// grid and counts inside the kernels, `normalize` turns the sums into means.
+// 256-byte aligned; grid and features 16-byte aligned; V < 2^31; N <= 2^31 - 4096.  The grid and the counters
+// must be clear; the grid holds feature sums afterwards.
 constexpr int kMeanRunsMaxParts = 16;
-constexpr int kMeanRunsParts = 8;
+constexpr int kMeanRunsParts = 12;
 uint64_t mean_runs_scratch_bytes(long long N, long long V, int parts);
 int mean_runs_launch(const float* points, const float* features, float* grid, int* counts, long long N,
-                     const VoxelGeom& g, long long V, int parts, bool clear, bool normalize, void* scratch,
-                     const int* gate, int gate_want, int device, cudaStream_t st);
+                     const VoxelGeom& g, long long V, int parts, void* scratch, const int* gate, int gate_want,
+                     int device, cudaStream_t st);
 
 }  // namespace vox
 }  // namespace rc

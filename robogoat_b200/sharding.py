@@ -322,6 +322,9 @@ class PointExchange:
         self.group = group
         dev = torch.device("cuda", torch.cuda.current_device())
         self._token = torch.zeros(1, dtype=torch.int32, device=dev)
+        # the batched form runs the stores over NVLink and the owner's accumulation side by side
+        self.move_stream = torch.cuda.Stream(dev)
+        self.scatter_stream = torch.cuda.Stream(dev, priority=-1)
         self.ids = self.features = None
         error = None
         try:
@@ -361,9 +364,70 @@ class PointExchange:
         self._drop()
 
 
+def batched_exchange_plans(counts, rank: int, per_group: int):
+    """Bookkeeping of the batched direct exchange from ``counts[s][i][p]`` = points rank ``s`` holds for part ``p`` in
+    its batch ``i``.  An owner's receive buffer is laid out batch by batch, inside a batch source rank by source rank,
+    sub-ranges in order inside.  Returns ``(plans, totals)``: per batch the ``exchange_plan`` of that batch with
+    ``dest_start`` and the runs' first records shifted to the batch's place in the buffers, and the records every rank
+    receives over all batches."""
+    R, nb = len(counts), len(counts[0])
+    totals = [0] * R
+    plans = []
+    for i in range(nb):
+        plan = exchange_plan([counts[s][i] for s in range(R)], rank, per_group)
+        base = list(totals)
+        plan["dest_start"] = [v + base[p // per_group] for p, v in enumerate(plan["dest_start"])]
+        plan["runs"] = [(off + base[rank], c, k) for off, c, k in plan["runs"]]
+        totals = [t + u for t, u in zip(totals, plan["totals"])]
+        plans.append(plan)
+    return plans, totals
+
+
+def _exchange_direct_batched(points, feats, geom, ws, K, rank, direct, mode, F, a, b, batches, group):
+    """Direct point exchange in ``batches`` slices of the local cloud: while the partition kernel stores slice i+1 into
+    the owners' buffers (NVLink-bound), the owners accumulate slice i (bound by local atomics) on a second stream.  The
+    slices' stores and reads are ordered by one token all-reduce per slice on the storing stream.  Returns the slab, or
+    None when some rank's buffer is too small (decided alike on every rank)."""
+    from . import ops
+    dev = points.device
+    N = points.shape[0]
+    spans = [shard_bounds(N, i, batches) for i in range(batches)]
+    counted = [ops.voxel_partition_count_cuda(points[lo:hi], *geom, ws, K) for lo, hi in spans]
+    table = torch.stack([pc for pc, _ in counted])                               # [batches, parts]
+    plans, totals = batched_exchange_plans(_gather_counts(table, group), rank, K)   # host sync; also orders this call
+    if max(totals) > direct.capacity:                                            # after the owners' previous reads
+        return None
+    out = ops.voxel_slab_buffers(b - a, F, mode, dev)
+    main = torch.cuda.current_stream(dev)
+    fork = torch.cuda.Event()
+    fork.record(main)
+    direct.move_stream.wait_event(fork)
+    direct.scatter_stream.wait_event(fork)
+    with torch.cuda.stream(direct.scatter_stream):
+        for t in out:
+            t.zero_()
+    dest_ids = [direct.ids.peers[p // K] for p in range(ws * K)]
+    dest_f = [direct.features.peers[p // K] for p in range(ws * K)] if feats is not None else None
+    for i, ((lo, hi), plan) in enumerate(zip(spans, plans)):
+        landed = torch.cuda.Event()
+        with torch.cuda.stream(direct.move_stream):
+            ops.voxel_partition_move_cuda(points[lo:hi], feats[lo:hi] if feats is not None else None, *geom, ws, K, dest_ids,
+                                          dest_f, plan["dest_start"], counted[i][1], remote=True)
+            direct.stream_barrier()             # every rank's stores of slice i are done
+            landed.record(direct.move_stream)
+        with torch.cuda.stream(direct.scatter_stream):
+            direct.scatter_stream.wait_event(landed)
+            ops.voxel_scatter_runs_cuda(direct.ids.ptr, direct.features.ptr if feats is not None else None, dev, F, a, b,
+                                        plan["runs"], K, mode, normalize=(i == batches - 1), out=out)
+    main.wait_stream(direct.move_stream)
+    main.wait_stream(direct.scatter_stream)
+    return out[0]
+
+
 def voxelize_sharded_exchange(points_local: torch.Tensor, features_local: Optional[torch.Tensor] = None,
                               grid_min=(-10.0, -10.0, -10.0), voxel_size: float = 0.1, grid_size=(128, 128, 128),
-                              mode: str = "occupancy", group=None, direct: Optional[PointExchange] = None) -> torch.Tensor:
+                              mode: str = "occupancy", group=None, direct: Optional[PointExchange] = None,
+                              batches: int = 1) -> torch.Tensor:
     """Slab-sharded voxelisation by exchanging points instead of reducing grids.
 
     Every rank buckets its points by the rank that owns their voxel (``slab_bounds``) and, inside an owner, by
@@ -375,7 +439,8 @@ def voxelize_sharded_exchange(points_local: torch.Tensor, features_local: Option
 
     Transport: one NCCL all-to-all per tensor by default; with ``direct`` (a ``PointExchange``) the partition
     kernel stores into the owners' receive buffers itself and only two small collectives remain (the count
-    matrix, and a barrier between the stores and the owners' reads).
+    matrix, and a barrier between the stores and the owners' reads).  ``batches`` > 1 (direct form only) cuts the
+    local cloud into that many slices and overlaps the stores of one slice with the accumulation of the previous.
     """
     from . import ops
     rank, ws = world(group)
@@ -390,7 +455,11 @@ def voxelize_sharded_exchange(points_local: torch.Tensor, features_local: Option
     geom = (list(grid_min), float(voxel_size), list(grid_size))
     a, b = slab_bounds(V, rank, ws)
     dev = points_local.device
-    if direct is not None and ws > 1 and (feats is None or F == direct.feature_width):
+    if direct is not None and ws > 1 and batches > 1 and (feats is None or F == direct.feature_width):
+        res = _exchange_direct_batched(points_local, feats, geom, ws, K, rank, direct, mode, F, a, b, int(batches), group)
+        if res is not None:
+            return res
+    elif direct is not None and ws > 1 and (feats is None or F == direct.feature_width):
         part_counts, scratch = ops.voxel_partition_count_cuda(points_local, *geom, ws, K)
         plan = exchange_plan(_gather_counts(part_counts, group), rank, K)       # host sync; also orders this call
         if max(plan["totals"]) <= direct.capacity:                               # after the owners' previous reads

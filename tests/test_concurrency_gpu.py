@@ -7,7 +7,7 @@ import pytest
 import torch
 
 import robocache
-from robogoat_b200 import workloads
+import workloads
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"

@@ -6,7 +6,8 @@ import torch
 import oracle
 import robocache
 from conftest import golden_names, load_golden
-from robogoat_b200 import ops, workloads
+from robogoat_b200 import ops
+import workloads
 from test_resample_gpu import DEV, assert_exact
 
 pytestmark = [pytest.mark.gpu, pytest.mark.usefixtures("kernel_choice")]

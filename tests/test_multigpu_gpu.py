@@ -16,7 +16,8 @@ CHILD = r'''
 import datetime, os, sys, torch, torch.distributed as dist
 sys.path.insert(0, os.environ["REPO_ROOT"])
 import oracle
-from robogoat_b200 import sharding, workloads, ops
+from robogoat_b200 import sharding, ops
+import workloads
 import robocache
 rank, ws = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
 torch.cuda.set_device(rank)

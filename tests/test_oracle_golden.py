@@ -88,3 +88,40 @@ def test_mean_mode_properties():
     total = (grid * counts.unsqueeze(-1)).double().sum(dim=(0, 1, 2))
     assert torch.allclose(total, feats[ids >= 0].double().sum(0), atol=1e-3)
     assert (grid[counts == 0] == 0).all()
+
+
+# ---- the torch restatement that bench.py times as the CPU baseline (oracle/torch_path.py)
+
+@pytest.mark.parametrize("name", golden_names("resample_"))
+def test_torch_path_resample_reproduces_reference_output(name):
+    from oracle import torch_path
+    g = load_golden(name)
+    src = g["src"].float() if g["_bf16"] else g["src"]          # the fallback widens bf16 rows to fp32
+    out = torch_path.interpolate_stream(g["src"], g["st"], g["tt"])
+    assert torch.equal(bits(out.float()), bits(g["out"])), name
+    assert torch.equal(bits(torch_path.interpolate_stream(src, g["st"], g["tt"])), bits(g["out"])), name
+
+
+@pytest.mark.parametrize("name", golden_names("fusion_"))
+def test_torch_path_fusion_reproduces_reference_output(name):
+    from oracle import torch_path
+    g = load_golden(name)
+    out = torch_path.fuse_multimodal(g["s1"], g["t1"], g["s2"], g["t2"], g["s3"], g["t3"], g["tt"])
+    assert torch.equal(bits(out.float()), bits(g["out"])), name
+
+
+def test_torch_path_voxel_semantics_are_the_fallbacks_own():
+    """Clamped, x-major: in-grid points agree with the oracle after a transpose, out-of-grid points land on the border."""
+    from oracle import torch_path
+    g = torch.Generator().manual_seed(8)
+    pts = torch.rand(4000, 3, generator=g) * 1.8 - 0.9                  # all inside [-1, 1)^3
+    kw = dict(grid_min=[-1.0, -1.0, -1.0], voxel_size=0.25, grid_size=[8, 8, 8])
+    mine = oracle.voxelize_pointcloud(pts, None, mode="count", **kw)    # flat index vz*64 + vy*8 + vx
+    theirs = torch_path.voxelize_pointcloud(pts, None, mode="count", **kw)   # indexed [vx][vy][vz]
+    assert torch.equal(theirs, mine.reshape(8, 8, 8).permute(2, 1, 0))
+    out = torch_path.voxelize_pointcloud(torch.tensor([[5.0, 0.0, 0.0]]), None, mode="occupancy", **kw)
+    assert int(out.sum()) == 1 and int(out[7, 4, 4]) == 1
+    feats = torch.randn(4000, 3, generator=g)
+    m = torch_path.voxelize_pointcloud(pts, feats, mode="mean", **kw)
+    om, oc, _ = oracle.voxelize_pointcloud(pts, feats, mode="mean", return_aux=True, **kw)
+    assert torch.allclose(m, om.reshape(8, 8, 8, 3).permute(2, 1, 0, 3), atol=1e-5)

@@ -8,7 +8,8 @@ import pytest
 import torch
 
 import oracle
-from robogoat_b200 import ops, workloads
+from robogoat_b200 import ops
+import workloads
 from test_resample_gpu import DEV, assert_exact
 
 pytestmark = [pytest.mark.gpu, pytest.mark.usefixtures("kernel_choice")]

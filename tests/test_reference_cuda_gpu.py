@@ -8,7 +8,8 @@ import torch
 
 import oracle
 import robocache
-from robogoat_b200 import ops, workloads
+from robogoat_b200 import ops
+import workloads
 
 pytestmark = [pytest.mark.gpu, pytest.mark.skipif(oracle.ref_cuda_lib() is None, reason="oracle/_ref CUDA library not built")]
 DEV = "cuda:0"

@@ -7,7 +7,8 @@ import torch
 import oracle
 import robocache
 from conftest import bits, golden_names, load_golden
-from robogoat_b200 import ops, workloads
+from robogoat_b200 import ops
+import workloads
 
 pytestmark = [pytest.mark.gpu, pytest.mark.usefixtures("kernel_choice")]
 DEV = "cuda:0"

@@ -12,7 +12,8 @@ import torch.distributed as dist
 import torch.multiprocessing as mp
 
 import oracle
-from robogoat_b200 import sharding, workloads
+from robogoat_b200 import sharding
+import workloads
 
 
 def test_shard_bounds_partition():

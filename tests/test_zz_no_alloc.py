@@ -6,14 +6,16 @@ instead of a caller buffer.
 The file is named to be collected last, so a run that stops at the first failure has already run
 every other test.  It checks, through the C ABI, that two calls in a row (different clouds, so
 stale counters from the first call would corrupt the second) agree with the ordinary entry point
-within the tolerance the other mean-mode tests use, and that a grid beyond the fixed capacity is
-refused.
+and with the CPU oracle within the tolerance the other mean-mode tests use, that the largest grid
+the fixed array covers (128^3) and a feature width that is not a multiple of four work, and that a
+grid beyond the fixed capacity is refused.
 """
 import ctypes
 
 import pytest
 import torch
 
+import oracle
 from robogoat_b200 import _lib
 
 pytestmark = pytest.mark.gpu
@@ -60,6 +62,31 @@ def test_static_counters_match_ordinary_entry_point_twice(cuda_lib):
         assert not torch.isnan(got).any(), f"call {call}: grid not cleared"
         assert bool((err <= tol).all()), f"call {call}: max excess {(err - tol).max().item()}"
         assert bool((got[(counts == 0).repeat_interleave(F)] == 0).all()), f"call {call}: empty voxels must be 0"
+        # and against the CPU oracle, with the oracle's own tolerance
+        em, ec, sabs = oracle.voxelize_pointcloud(pts.cpu(), feats.cpu(), gmin, vs, gs, mode="mean", return_aux=True)
+        assert bool(((got.cpu().reshape(-1, F) - em.reshape(-1, F)).abs() <= oracle.mean_tolerance(ec, sabs, em).reshape(-1, F)).all()), call
+
+
+@pytest.mark.parametrize("gs,F", [([128, 128, 128], 4), ([40, 24, 56], 3), ([16, 16, 16], 5)])
+def test_capacity_edge_and_odd_feature_widths(gs, F, cuda_lib):
+    """128^3 is exactly the fixed array's size and must be accepted; feature widths off the 16-byte path too.
+    Two calls in a row again, each against the ordinary entry point and the oracle."""
+    L = cuda_lib
+    ext = max(gs) * 0.05
+    gmin, vs = [-ext / 2] * 3, 0.05
+    for seed in (21, 22):
+        g = torch.Generator().manual_seed(seed + F)
+        pts_h = torch.rand(50_000, 3, generator=g) * ext * 1.2 - ext * 0.6
+        feats_h = torch.randn(50_000, F, generator=g)
+        pts, feats = pts_h.to(DEV), feats_h.to(DEV)
+        want, counts = _ordinary(L, pts, feats, gmin, vs, gs, F)
+        got = _static(L, pts, feats, gmin, vs, gs, F)
+        torch.cuda.synchronize()
+        em, ec, sabs = oracle.voxelize_pointcloud(pts_h, feats_h, gmin, vs, gs, mode="mean", return_aux=True)
+        tol = oracle.mean_tolerance(ec, sabs, em).reshape(-1, F)
+        assert torch.equal(counts.cpu(), ec.reshape(-1))
+        assert bool(((got.cpu().reshape(-1, F) - em.reshape(-1, F)).abs() <= tol).all()), seed
+        assert bool(((got.cpu().reshape(-1, F) - want.cpu().reshape(-1, F)).abs() <= 2 * tol).all()), seed
 
 
 def test_capacity_is_enforced(cuda_lib):
