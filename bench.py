@@ -41,11 +41,23 @@ EXTRAS_LIMIT_S = 420          # multi-GPU runs: the side measurements get this l
 METRIC = "resample_throughput"
 UNIT = "GB/s"
 WORKLOAD = "resample bf16 B=4096 S=500 D=256 T=250 sorted-uniform targets, per GPU"
-RESAMPLE_DRAM_BYTES_PER_ROW = (169117952 + 88358656) / 1024   # ncu capture, B=1024
+TRAFFIC_CAPTURE = os.path.join(ROOT, "profiles", "resample_gather_bf16_B1024.json")   # DRAM bytes of one captured launch
 BYTES_CONVENTION = "min(all tensors once, touched rows + times + output)"
 
 
 # ----------------------------------------------------------------------------- helpers
+
+def captured_traffic(rows: int):
+    """DRAM bytes per launch of the resample kernel at ``rows`` batch rows, scaled by rows from the committed profiler
+    capture (traffic grows in proportion to the rows); (None, reason) when the capture file is missing."""
+    try:
+        with open(TRAFFIC_CAPTURE) as f:
+            c = json.load(f)
+        per_row = (float(c["dram_bytes_read"]) + float(c["dram_bytes_write"])) / float(c["rows_in_capture"])
+        return int(per_row * rows), f"ncu dram__bytes_read+write of a B={c['rows_in_capture']} capture, scaled by rows"
+    except Exception as e:
+        return None, f"no capture file ({type(e).__name__})"
+
 
 def measured_peak_gbs():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
@@ -426,7 +438,7 @@ def run_ours(args):
     peak, peak_kind = measured_peak_gbs()
     achieved = step_bytes / (kernel_ms * 1e-3) / 1e9
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                "traffic": int(RESAMPLE_DRAM_BYTES_PER_ROW * B), "traffic_source": "ncu dram__bytes_read+write of a B=1024 capture (profiles/resample_gather_bf16_B1024.md), scaled by rows", "peak_source": f"of {peak_kind}", "kernel": "interp_gather_kernel<bf16, 16 B, staged, uniform>",
+                "traffic": captured_traffic(B)[0], "traffic_source": captured_traffic(B)[1], "peak_source": f"of {peak_kind}", "kernel": "interp_gather_kernel<bf16, 16 B, staged, uniform>",
                 "kernel_ms": kernel_ms, "bytes_algorithmic_all_tensors_once": algo_bytes,
                 "bytes_touched_rows": touched_bytes, "achieved_all_tensors_once": algo_bytes / (kernel_ms * 1e-3) / 1e9}
 
@@ -789,7 +801,7 @@ def run_extras(L, dev, local, rank, world, peak, ex):
     return ex
 
 
-def sharded_parity(dev, rank, world, px) -> dict:
+def sharded_parity(dev, rank, world, px, bx=None) -> dict:
     """Every sharded voxel form on a cloud small enough for the CPU oracle (2^20 mixture points into 128^3), checked
     on every rank against the oracle run on the whole cloud: occupancy and counts exact, means within the oracle's
     tolerance.  Returns one flag per form, true only if it held on all ranks."""
@@ -832,6 +844,11 @@ def sharded_parity(dev, rank, world, px) -> dict:
         flags["exchange_direct_batched"] = (
             count_ok(sharding.voxelize_sharded_exchange(pl, None, mode="count", direct=px, batches=4, **kw), xa, xb)
             and mean_ok(sharding.voxelize_sharded_exchange(pl, fl, mode="mean", direct=px, batches=4, **kw), xa, xb))
+    if bx is not None:
+        flags["bucket_exchange"] = True
+        for _ in range(2):          # twice: the second call's stores meet pools the owners have just read
+            got, gcnt = sharding.voxelize_sharded_buckets(pl, fl, bx, return_counts=True, **kw)
+            flags["bucket_exchange"] = flags["bucket_exchange"] and count_ok(gcnt, xa, xb) and mean_ok(got, xa, xb)
     names = sorted(flags)
     t = torch.tensor([1 if flags[k] else 0 for k in names], dtype=torch.int32, device=dev)
     dist.all_reduce(t, op=dist.ReduceOp.MIN)
@@ -869,7 +886,12 @@ def multi_gpu_extras(L, dev, rank, world, ex, pts, feats, kw, N, single_ms):
     except RuntimeError as e:       # raised on every rank alike
         px = None
         ex["voxel_sharded_direct_unavailable"] = str(e)[:200]
-    parity = sharded_parity(dev, rank, world, px)
+    try:
+        bx = sharding.BucketExchange(points_per_rank=N, n_voxels=512 ** 3)
+    except RuntimeError as e:
+        bx = None
+        ex["voxel_sharded_bucket_exchange_unavailable"] = str(e)[:200]
+    parity = sharded_parity(dev, rank, world, px, bx)
     ex["voxel_sharded_parity"] = {"parity": parity,
                                   "checked": "2^20 mixture points into 128^3 on every rank against the CPU oracle run on the whole cloud: "
                                              "occupancy and counts exact, means within 1e-5 relative + 1e-6 of the mean summand"}
@@ -900,8 +922,14 @@ def multi_gpu_extras(L, dev, rank, world, ex, pts, feats, kw, N, single_ms):
                   ("point_exchange_direct_batched", "exchange_direct_batched",
                    lambda m: sharding.voxelize_sharded_exchange(pts, feats if m == "mean" else None, mode=m, direct=px, batches=4, **kw),
                    "same in four slices of the local cloud: the stores of slice i+1 overlap the owners' accumulation of slice i")]
+    if bx is not None:
+        forms.append(("bucket_exchange", "bucket_exchange", lambda m: sharding.voxelize_sharded_buckets(pts, feats, bx, **kw),
+                      "one bucket kernel sorts every chunk by (owner, sub-range) and stores each owner's records into a fixed block of "
+                      "that owner's pool over NVLink; no counts, no host synchronisation, two barriers on the stream; mean mode only"))
     for mode in ("mean", "count"):
         for name, pkey, fn, note in forms:
+            if name == "bucket_exchange" and mode != "mean":
+                continue
             ms = timed(lambda: fn(mode))
             ok = bool(parity.get(pkey))
             ex[f"voxel_{mode}_sharded_{name}"] = {"ms": ms, "Gpts/s_total": (N * world / (ms * 1e-3) / 1e9) if ok else 0.0, "parity": ok,
@@ -959,6 +987,29 @@ def multi_gpu_extras(L, dev, rank, world, ex, pts, feats, kw, N, single_ms):
             "bound": "the move kernel (NVLink, measured 770 GB/s per direction) and the owner's atomics run back to back here; "
                      "the batched form overlaps them"})
         px.close()
+    if bx is not None:
+        # stages of the bucket form, each max over ranks
+        a_v, b_v = sharding.slab_bounds(512 ** 3, rank, world)
+        barrier(world)
+        bx.stream_barrier()
+        ev[0].record()
+        ops.voxel_bucket_exchange_cuda(pts, feats, kw["grid_min"], kw["voxel_size"], kw["grid_size"], world, bx.per_group, rank,
+                                       bx.chunks, bx.ids.peers, bx.features.peers, bx.runs.peers)
+        ev[1].record()
+        bx.stream_barrier()
+        ev[2].record()
+        r = ops.voxel_scatter_buckets_cuda(bx.ids.ptr, bx.features.ptr, bx.runs.ptr, bx.n_blocks, bx.per_group, dev, a_v, b_v)
+        ev[3].record(); torch.cuda.synchronize()
+        stages = [max_over_ranks(ev[i].elapsed_time(ev[i + 1]), world, dev) for i in range(3)]
+        del r
+        remote_bytes = N * 20 * (world - 1) / world
+        ex["voxel_mean_sharded_bucket_exchange"].update({
+            "sub_ranges_per_slab": bx.per_group,
+            "stage_ms": {"bucket_kernel_stores_over_nvlink": stages[0], "barrier": stages[1], "clear_scatter_normalise": stages[2]},
+            "nvlink_GB/s_out_per_gpu_during_bucket_kernel": remote_bytes / (stages[0] * 1e-3) / 1e9,
+            "bound": "bucket kernel: the slower of its own work (0.65 ms on one GPU) and the record bytes that must cross NVLink / 770 GB/s "
+                     "per direction; accumulation: the rate at which L2 retires atomics"})
+        bx.close()
 
 
 def run_profile_case(name: str):

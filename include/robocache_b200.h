@@ -257,6 +257,34 @@ RC_API int rc_voxel_scatter_runs(const int32_t* ids, const float* features, void
                                  int32_t n_passes, int mode, uint32_t flags, int device, void* stream);
 
 /*
+ * Point exchange by buckets (mean mode, four feature channels): the multi-GPU form of the slab-ordered run path,
+ * with no counting pass and no host synchronisation.  The voxel ids are cut into n_groups owner ranges of
+ * ceil(V / n_groups) ids and each range into parts_per_group sub-ranges; n_groups * parts_per_group <= 16.
+ * Every owner has a record pool of n_groups * chunks_per_source blocks of rc_voxel_bucket_block_records() records
+ * (ids int32 and feature rows fp32 [., 4] in two buffers, 128-byte aligned) and a run table uint32
+ * [parts_per_group][n_groups * chunks_per_source].
+ * rc_voxel_bucket_exchange: rank source_rank sorts each 1024-point chunk of its cloud by (owner, sub-range) and
+ *   stores every owner's segment into block source_rank * chunks_per_source + chunk of that owner's pool, and the
+ *   sub-ranges' (first slot, length) into that owner's table.  dest_ids / dest_features / dest_runs are HOST arrays
+ *   of n_groups device pointers, which may be other GPUs' buffers mapped with rc_peer_open (plain stores; nothing
+ *   is read from a peer, no multicast).  N <= chunks_per_source * 1024; all of the source's blocks are written on
+ *   every call (empty ones as empty).  The caller orders the stores against the owners' reads with a barrier on
+ *   the stream before and after.
+ * rc_voxel_scatter_buckets: the owner accumulates its pool into its slab [id_begin, id_end) of the grid (fp32
+ *   [., 4], first cell of voxel id_begin) and counts, one sub-range after the other; flags as rc_voxelize.
+ * No counterpart in the reference.
+ */
+RC_API int32_t rc_voxel_bucket_block_records(int32_t parts_per_group);
+RC_API int rc_voxel_bucket_exchange(const float* points, const float* features, int64_t N, const float grid_min_host[3],
+                                    float voxel_size, const int32_t grid_size_host[3], int32_t n_groups,
+                                    int32_t parts_per_group, int32_t source_rank, int64_t chunks_per_source,
+                                    void* const* dest_ids, void* const* dest_features, void* const* dest_runs, int device,
+                                    void* stream);
+RC_API int rc_voxel_scatter_buckets(const int32_t* pool_ids, const float* pool_features, const uint32_t* runs,
+                                    int64_t n_blocks, int32_t parts_per_group, float* grid, int32_t* counts,
+                                    int64_t id_begin, int64_t id_end, uint32_t flags, int device, void* stream);
+
+/*
  * Device buffers that the other processes of a node can map, for rc_voxel_partition_move's remote
  * destinations.  rc_peer_alloc allocates `bytes` on `device` (cudaMalloc) and fills the 64-byte CUDA IPC
  * handle to hand to the other processes; rc_peer_open maps such a handle into this process on `device`

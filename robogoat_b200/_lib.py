@@ -42,7 +42,7 @@ EXPORTED_SYMBOLS = (
     "rc_resample", "rc_resample_strided", "rc_resample_ragged", "rc_fuse", "rc_fuse_strided", "rc_resample_brackets", "rc_voxelize", "rc_voxel_normalize", "rc_voxelize_mean_static",
     "rc_voxelize_ex", "rc_voxelize_scratch_bytes", "rc_voxel_partition", "rc_voxel_partition_count", "rc_voxel_partition_move", "rc_voxel_partition_scratch_bytes",
     "rc_voxel_scatter_ids", "rc_voxel_scatter_runs", "rc_peer_alloc", "rc_peer_open", "rc_peer_close", "rc_peer_free",
-    "rc_voxelize_batched", "rc_point_cloud_bounds", "rc_set_option", "rc_bulk_wait_timeouts", "rc_strerror", "rc_last_cuda_error", "rc_abi_version",
+    "rc_voxelize_batched", "rc_point_cloud_bounds", "rc_voxel_bucket_block_records", "rc_voxel_bucket_exchange", "rc_voxel_scatter_buckets", "rc_set_option", "rc_bulk_wait_timeouts", "rc_strerror", "rc_last_cuda_error", "rc_abi_version",
 )
 
 
@@ -105,6 +105,13 @@ def _declare(L: ctypes.CDLL) -> None:
     L.rc_voxelize_batched.restype = ci
     L.rc_point_cloud_bounds.argtypes = [vp, vp, vp, i64, i64, ci, vp]
     L.rc_point_cloud_bounds.restype = ci
+    L.rc_voxel_bucket_block_records.argtypes = [i32]
+    L.rc_voxel_bucket_block_records.restype = i32
+    L.rc_voxel_bucket_exchange.argtypes = [vp, vp, i64, ctypes.POINTER(f32), f32, ctypes.POINTER(i32), i32, i32, i32, i64,
+                                           ctypes.POINTER(vp), ctypes.POINTER(vp), ctypes.POINTER(vp), ci, vp]
+    L.rc_voxel_bucket_exchange.restype = ci
+    L.rc_voxel_scatter_buckets.argtypes = [vp, vp, vp, i64, i32, vp, vp, i64, i64, u32, ci, vp]
+    L.rc_voxel_scatter_buckets.restype = ci
     for name in ("rc_resample", "rc_resample_strided", "rc_resample_ragged", "rc_fuse", "rc_fuse_strided", "rc_resample_brackets", "rc_voxelize", "rc_voxel_normalize", "rc_voxelize_mean_static",
                  "rc_last_cuda_error", "rc_abi_version"):
         getattr(L, name).restype = ci

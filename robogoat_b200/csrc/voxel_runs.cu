@@ -47,16 +47,34 @@ __device__ __forceinline__ int slab_of(int id, const RunRule& r) {
     return q;
 }
 
-// runs[p * nchunks + c] = (first slot of slab p's run in chunk c's block) << 16 | records in the run
+// Multi-GPU form (EXCH): the slabs are grouped by owner - `groups` owners with `per_group` slabs each, slab number
+// p = owner * per_group + sub - and every owner has its own record pool and run table, possibly in another GPU's
+// memory (plain stores over NVLink; no multicast, nothing is read from a peer).  A pool holds `nblocks` blocks, this
+// source's chunk c fills block `block0 + c`, and the owner's segment of the sorted chunk goes to the start of that
+// block as one contiguous piece, so every warp store covers whole 128-byte lines up to the segment's tail.
+struct ExchangeDest {
+    int* ids[kMeanRunsMaxParts];
+    float4* feats[kMeanRunsMaxParts];
+    unsigned int* runs[kMeanRunsMaxParts];      // [per_group][nblocks] each
+    long long block0, nblocks;
+    int groups, per_group;
+    unsigned int owner_span;                    // voxel ids per owner; RunRule::slab is the span of a slab inside it
+    float inv_owner_span;
+};
+
+// Single-GPU form: runs[p * nchunks + c] = (first slot of slab p's run in chunk c's block) << 16 | records in the run.
+// Exchange form: the owner's table, runs[sub * nblocks + block0 + c] = (first slot inside the block) << 16 | records.
+template <bool EXCH>
 __global__ void __launch_bounds__(kThreads, 4)
 voxel_bucket_kernel(const float* __restrict__ pts, const float4* __restrict__ feats, long long N, VoxelGeom g,
                     bool pts_aligned, RunRule rule, long long nchunks, unsigned int* __restrict__ runs,
-                    int* __restrict__ pool_ids, float4* __restrict__ pool_feats, const int* __restrict__ gate,
-                    int gate_want) {
+                    int* __restrict__ pool_ids, float4* __restrict__ pool_feats, const __grid_constant__ ExchangeDest dest,
+                    const int* __restrict__ gate, int gate_want) {
     __shared__ __align__(16) float s_xyz[kThreads / 32][kPointsPerWarp * 3];
     __shared__ __align__(16) int s_sid[kRunBlockMax];
     __shared__ __align__(16) float4 s_sf[kRunBlockMax];
     __shared__ int s_wcnt[kThreads / 32][kMeanRunsMaxParts];
+    __shared__ int s_seg[EXCH ? kMeanRunsMaxParts : 1][2];     // first slot and length of every owner's segment
     if (gate != nullptr && *gate != gate_want) return;
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
@@ -93,7 +111,19 @@ voxel_bucket_kernel(const float* __restrict__ pts, const float4* __restrict__ fe
 #pragma unroll
         for (int i = 0; i < kPointsPerLane; ++i) {
             id[i] = voxel_id32(x[i], y[i], z[i], g);
-            part[i] = (id[i] < 0) ? -1 : slab_of(id[i], rule);
+            if (EXCH) {
+                part[i] = -1;
+                if (id[i] >= 0) {
+                    const unsigned int u = static_cast<unsigned int>(id[i]);
+                    int own = static_cast<int>(__uint2float_rz(u) * dest.inv_owner_span);
+                    unsigned int lo = static_cast<unsigned int>(own) * dest.owner_span;
+                    if (u < lo) { --own; lo -= dest.owner_span; }
+                    else if (u - lo >= dest.owner_span) { ++own; lo += dest.owner_span; }
+                    part[i] = own * dest.per_group + slab_of(static_cast<int>(u - lo), rule);
+                }
+            } else {
+                part[i] = (id[i] < 0) ? -1 : slab_of(id[i], rule);
+            }
         }
         // rank of every point among the warp's points of the same slab: intersect the ballots of the slab number's
         // bits (__match_any_sync in their place ran 5 % slower)
@@ -145,13 +175,34 @@ voxel_bucket_kernel(const float* __restrict__ pts, const float4* __restrict__ fe
                 s_sf[slot] = f[i];
             }
         }
-        if (warp == 0 && lane < P) {
+        if (EXCH) {
+            // lane p's owner segment starts where the owner's first slab starts
+            const int own = lane / dest.per_group;
+            const int seg0 = __shfl_sync(0xffffffffu, start, (own * dest.per_group) & 31);
+            const int seg1 = __shfl_sync(0xffffffffu, inc, (own * dest.per_group + dest.per_group - 1) & 31);
+            if (warp == 0 && lane < P) {
+                for (int j = start + tot; j < start + padded; ++j) s_sid[j] = -1;
+                dest.runs[own][static_cast<long long>(lane - own * dest.per_group) * dest.nblocks + dest.block0 + chunk] =
+                    (static_cast<unsigned int>(start - seg0) << 16) | static_cast<unsigned int>(tot);
+                if (lane == own * dest.per_group) { s_seg[own][0] = seg0; s_seg[own][1] = seg1 - seg0; }
+            }
+        } else if (warp == 0 && lane < P) {
             for (int j = start + tot; j < start + padded; ++j) s_sid[j] = -1;
             runs[static_cast<long long>(lane) * nchunks + chunk] = (static_cast<unsigned int>(start) << 16) | static_cast<unsigned int>(tot);
         }
         __syncthreads();
         if (lane < kMeanRunsMaxParts) wcnt[lane] = 0;     // own row, for the next chunk; every warp has read it
-        {
+        if (EXCH) {
+            for (int own = 0; own < dest.groups; ++own) {
+                const int s0 = s_seg[own][0], len = s_seg[own][1];     // multiples of 8 records
+                const long long o = (dest.block0 + chunk) * rule.blk;
+                int4* dst_i = reinterpret_cast<int4*>(dest.ids[own] + o);
+                const int4* src_i = reinterpret_cast<const int4*>(s_sid + s0);
+                for (int j = threadIdx.x; j < (len >> 2); j += kThreads) dst_i[j] = src_i[j];
+                float4* dst_f = dest.feats[own] + o;
+                for (int j = threadIdx.x; j < len; j += kThreads) dst_f[j] = s_sf[s0 + j];
+            }
+        } else {
             const long long o = chunk * rule.blk;
             int4* dst_i = reinterpret_cast<int4*>(pool_ids + o);
             const int4* src_i = reinterpret_cast<const int4*>(s_sid);
@@ -255,9 +306,10 @@ int mean_runs_launch(const float* points, const float* features, float* grid, in
     rule.blk = l.blk;
     const int sms = rc::sm_count(device);
     const long long nb = l.nchunks < 8ll * sms ? l.nchunks : 8ll * sms;
-    voxel_bucket_kernel<<<static_cast<unsigned int>(nb), kThreads, 0, st>>>(
+    const ExchangeDest none{};
+    voxel_bucket_kernel<false><<<static_cast<unsigned int>(nb), kThreads, 0, st>>>(
         points, reinterpret_cast<const float4*>(features), N, g, rc::aligned_to(points, 16), rule, l.nchunks, runs, pool_ids,
-        pool_feats, gate, gate_want);
+        pool_feats, none, gate, gate_want);
     long long sb = ceil_div(l.nchunks, kThreads / 32);
     if (sb > 8ll * sms) sb = 8ll * sms;
     for (int p = 0; p < l.P; ++p)
@@ -268,3 +320,116 @@ int mean_runs_launch(const float* points, const float* features, float* grid, in
 
 }  // namespace vox
 }  // namespace rc
+
+// ---------------------------------------------------------------- multi-GPU point exchange by buckets
+//
+// The same two kernels across GPUs, with no counting pass and no host synchronisation: every rank buckets its
+// points by (owner, sub-range of the owner's slab) and stores each owner's segment of every chunk straight into
+// that owner's record pool (a buffer of the owner's GPU mapped into this process); after a barrier on the stream
+// every owner accumulates the blocks it received, sub-range after sub-range.  Because a chunk's block in the pool
+// has a fixed place and a fixed capacity (1024 records + padding), nobody needs to know any count in advance.
+// No counterpart in the reference, whose multi-GPU test all-reduces dense grids (robocache/tests/test_multi_gpu.py:76).
+extern "C" {
+
+using namespace rc::vox;
+
+int32_t rc_voxel_bucket_block_records(int32_t parts_per_group) {
+    if (parts_per_group < 1 || parts_per_group > kMeanRunsMaxParts) return 0;
+    return static_cast<int32_t>(round_up(kRunChunk + kRunPad * parts_per_group, 32));
+}
+
+int rc_voxel_bucket_exchange(const float* points, const float* features, int64_t N, const float grid_min_host[3],
+                             float voxel_size, const int32_t grid_size_host[3], int32_t n_groups, int32_t parts_per_group,
+                             int32_t source_rank, int64_t chunks_per_source, void* const* dest_ids,
+                             void* const* dest_features, void* const* dest_runs, int device, void* stream) {
+    if (grid_min_host == nullptr || grid_size_host == nullptr || dest_ids == nullptr || dest_features == nullptr ||
+        dest_runs == nullptr)
+        return RC_ERR_NULL_POINTER;
+    if (n_groups < 1 || parts_per_group < 1 || source_rank < 0 || source_rank >= n_groups || N < 0 || chunks_per_source < 0)
+        return RC_ERR_BAD_SHAPE;
+    if (static_cast<long long>(n_groups) * parts_per_group > kMeanRunsMaxParts) return RC_ERR_TOO_LARGE;
+    if (N > chunks_per_source * kRunChunk || N > (1ll << 31) - 4096) return RC_ERR_TOO_LARGE;
+    if (!(voxel_size > 0.0f) || !(voxel_size <= 3.0e38f)) return RC_ERR_BAD_VALUE;
+    VoxelGeom g;
+    g.minx = grid_min_host[0]; g.miny = grid_min_host[1]; g.minz = grid_min_host[2];
+    g.vs = voxel_size;
+    g.gx = grid_size_host[0]; g.gy = grid_size_host[1]; g.gz = grid_size_host[2];
+    if (g.gx < 0 || g.gy < 0 || g.gz < 0) return RC_ERR_BAD_SHAPE;
+    if (g.gx >= (1 << 24) || g.gy >= (1 << 24) || g.gz >= (1 << 24)) return RC_ERR_TOO_LARGE;
+    if (static_cast<double>(g.gx) * g.gy * g.gz >= 2147483648.0) return RC_ERR_TOO_LARGE;
+    g.fgx = static_cast<float>(g.gx); g.fgy = static_cast<float>(g.gy); g.fgz = static_cast<float>(g.gz);
+    g.inv_vs = host_reciprocal(voxel_size);
+    const long long V = static_cast<long long>(g.gx) * g.gy * g.gz;
+    if (chunks_per_source == 0 || V == 0) return RC_OK;
+    if (N > 0 && (points == nullptr || features == nullptr)) return RC_ERR_NULL_POINTER;
+    if (!rc::aligned_to(points, 4) || !rc::aligned_to(features, 16)) return RC_ERR_BAD_ALIGNMENT;
+    ExchangeDest dest{};
+    for (int d = 0; d < n_groups; ++d) {
+        dest.ids[d] = static_cast<int*>(dest_ids[d]);
+        dest.feats[d] = static_cast<float4*>(dest_features[d]);
+        dest.runs[d] = static_cast<unsigned int*>(dest_runs[d]);
+        if (dest.ids[d] == nullptr || dest.feats[d] == nullptr || dest.runs[d] == nullptr) return RC_ERR_NULL_POINTER;
+        if (!rc::aligned_to(dest.ids[d], 128) || !rc::aligned_to(dest.feats[d], 128) || !rc::aligned_to(dest.runs[d], 4))
+            return RC_ERR_BAD_ALIGNMENT;
+    }
+    const long long owner_span = ceil_div(V, n_groups);          // the ceil-div slabs the owners hold
+    dest.groups = n_groups;
+    dest.per_group = parts_per_group;
+    dest.owner_span = static_cast<unsigned int>(owner_span);
+    dest.inv_owner_span = 1.0f / static_cast<float>(owner_span);
+    dest.block0 = static_cast<long long>(source_rank) * chunks_per_source;
+    dest.nblocks = static_cast<long long>(n_groups) * chunks_per_source;
+    RunRule rule;
+    rule.P = n_groups * parts_per_group;
+    rule.slab = static_cast<unsigned int>(ceil_div(owner_span, parts_per_group));
+    rule.inv_slab = 1.0f / static_cast<float>(rule.slab);
+    rule.blk = rc_voxel_bucket_block_records(parts_per_group);
+    rc::DeviceScope scope(device);
+    if (scope.status() != RC_OK) return scope.status();
+    const int sms = rc::sm_count(device);
+    const long long nb = chunks_per_source < 8ll * sms ? chunks_per_source : 8ll * sms;
+    voxel_bucket_kernel<true><<<static_cast<unsigned int>(nb), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+        points, reinterpret_cast<const float4*>(features), N, g, rc::aligned_to(points, 16), rule, chunks_per_source, nullptr,
+        nullptr, nullptr, dest, nullptr, 0);
+    return rc::check_launch();
+}
+
+int rc_voxel_scatter_buckets(const int32_t* pool_ids, const float* pool_features, const uint32_t* runs, int64_t n_blocks,
+                             int32_t parts_per_group, float* grid, int32_t* counts, int64_t id_begin, int64_t id_end,
+                             uint32_t flags, int device, void* stream) {
+    if (n_blocks < 0 || parts_per_group < 1 || parts_per_group > kMeanRunsMaxParts || id_begin < 0 || id_end < id_begin)
+        return RC_ERR_BAD_SHAPE;
+    if (id_end >= (1ll << 31)) return RC_ERR_TOO_LARGE;
+    const long long nvox = id_end - id_begin;
+    if (nvox > 0 && (grid == nullptr || counts == nullptr)) return RC_ERR_NULL_POINTER;
+    if (n_blocks > 0 && (pool_ids == nullptr || pool_features == nullptr || runs == nullptr)) return RC_ERR_NULL_POINTER;
+    if (!rc::aligned_to(pool_ids, 16) || !rc::aligned_to(pool_features, 16) || !rc::aligned_to(grid, 16) || !rc::aligned_to(counts, 4))
+        return RC_ERR_BAD_ALIGNMENT;
+    rc::DeviceScope scope(device);
+    if (scope.status() != RC_OK) return scope.status();
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if ((flags & RC_VOXEL_ZERO_INIT) && nvox > 0) {
+        RC_CUDA_TRY(cudaMemsetAsync(grid, 0, static_cast<size_t>(nvox) * 16, st));
+        RC_CUDA_TRY(cudaMemsetAsync(counts, 0, static_cast<size_t>(nvox) * 4, st));
+    }
+    if (n_blocks > 0 && nvox > 0) {
+        // the kernel indexes with the global id: hand it the address voxel 0 would have
+        float* grid0 = reinterpret_cast<float*>(reinterpret_cast<uintptr_t>(grid) - static_cast<uintptr_t>(id_begin) * 16u);
+        int* counts0 = reinterpret_cast<int*>(reinterpret_cast<uintptr_t>(counts) - static_cast<uintptr_t>(id_begin) * 4u);
+        const int blk = rc_voxel_bucket_block_records(parts_per_group);
+        const int sms = rc::sm_count(device);
+        long long sb = ceil_div(n_blocks, kThreads / 32);
+        if (sb > 8ll * sms) sb = 8ll * sms;
+        for (int k = 0; k < parts_per_group; ++k)
+            voxel_run_scatter_kernel<<<static_cast<unsigned int>(sb), kThreads, 0, st>>>(
+                runs + static_cast<long long>(k) * n_blocks, pool_ids, reinterpret_cast<const float4*>(pool_features), n_blocks, blk,
+                grid0, counts0, nullptr, 0);
+    }
+    const int rc_launch = rc::check_launch();
+    if (rc_launch != RC_OK) return rc_launch;
+    if (!(flags & RC_VOXEL_NO_NORMALIZE) && nvox > 0)
+        return rc_voxel_normalize(grid, counts, 0, nvox, 4, device, stream);
+    return RC_OK;
+}
+
+}  // extern "C"

@@ -301,7 +301,7 @@ def _gather_counts(part_counts: torch.Tensor, group=None):
     _, ws = world(group)
     if ws == 1:
         return [part_counts.tolist()]
-    allc = torch.empty((ws, part_counts.numel()), dtype=part_counts.dtype, device=part_counts.device)
+    allc = torch.empty((ws,) + tuple(part_counts.shape), dtype=part_counts.dtype, device=part_counts.device)
     dist.all_gather_into_tensor(allc, part_counts.contiguous(), group=group)
     return allc.tolist()
 
@@ -362,6 +362,95 @@ class PointExchange:
 
     def close(self) -> None:
         self._drop()
+
+
+class BucketExchange:
+    """Record pools for the bucket form of the point exchange (mean mode, four feature channels): every rank's bucket
+    kernel stores, chunk by chunk, the records of each owner into that owner's pool over NVLink; a chunk's block has a
+    fixed place and capacity, so the exchange needs no counts, no host synchronisation and no all-to-all - only a
+    barrier on the stream before the stores (the owners have finished with the previous call's records) and after.
+
+    ``points_per_rank`` is the largest cloud a rank may pass per call; the pools hold
+    ``world * ceil(points_per_rank / 1024)`` blocks of about 1 K records of 20 bytes each.  Construction and ``close``
+    are collective."""
+
+    def __init__(self, points_per_rank: int, n_voxels: int, group=None):
+        from .peer import PeerBuffer
+        self.group = group
+        rank, ws = world(group)
+        if ws > 16:
+            raise RuntimeError("the bucket exchange supports at most 16 ranks")
+        self.per_group = max(1, min(16 // ws, sub_parts(int(n_voxels), 4, ws, "mean")))
+        self.chunks = (int(points_per_rank) + 1023) // 1024
+        self.capacity = self.chunks * 1024
+        dev = torch.device("cuda", torch.cuda.current_device())
+        self.block = int(_lib_handle().rc_voxel_bucket_block_records(self.per_group))
+        self.n_blocks = ws * self.chunks
+        self._token = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.ids = self.features = self.runs = None
+        error = None
+        try:
+            self.ids = PeerBuffer(max(128, self.n_blocks * self.block * 4), dev)
+            self.features = PeerBuffer(max(128, self.n_blocks * self.block * 16), dev)
+            self.runs = PeerBuffer(max(128, self.per_group * self.n_blocks * 4), dev)
+        except RuntimeError as e:
+            error = e
+        if not self._everyone(error is None):
+            self.close(collective=False)
+            raise RuntimeError(f"BucketExchange: record pools could not be allocated on every rank ({error})")
+        for buf in (self.ids, self.features, self.runs):
+            try:
+                buf.connect(group)
+            except RuntimeError as e:
+                error = e
+            if not self._everyone(error is None):
+                self.close()
+                raise RuntimeError(f"BucketExchange: peer buffers could not be mapped on every rank ({error})")
+
+    def _everyone(self, ok: bool) -> bool:
+        flag = torch.tensor([1 if ok else 0], dtype=torch.int32, device=self._token.device)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=self.group)
+        return bool(flag.item())
+
+    def stream_barrier(self) -> None:
+        """Orders, on the current stream, everything the other ranks enqueued before their call of this method
+        before everything this rank enqueues after it."""
+        dist.all_reduce(self._token, group=self.group)
+
+    def close(self, collective: bool = True) -> None:
+        for b in (self.ids, self.features, self.runs):
+            if b is not None:
+                b.close()
+        self.ids = self.features = self.runs = None
+
+
+def _lib_handle():
+    from . import _lib
+    return _lib.load()
+
+
+def voxelize_sharded_buckets(points_local: torch.Tensor, features_local: torch.Tensor, exchange: BucketExchange,
+                             grid_min=(-10.0, -10.0, -10.0), voxel_size: float = 0.1, grid_size=(128, 128, 128),
+                             return_counts: bool = False, group=None):
+    """Mean-mode voxelisation of a cloud spread over the ranks, output slab-sharded as ``voxelize_sharded_exchange``
+    returns it ([voxels of this rank's slab, 4]), by the bucket exchange: one bucket kernel that stores into the
+    owners' pools, one barrier, then the owner's accumulation and normalisation - nothing on the host waits."""
+    from . import ops
+    rank, ws = world(group)
+    V = int(grid_size[0]) * int(grid_size[1]) * int(grid_size[2])
+    if features_local is None or features_local.shape[1] != 4:
+        raise RuntimeError("the bucket exchange takes four feature channels")
+    if points_local.shape[0] > exchange.capacity:
+        raise RuntimeError(f"{points_local.shape[0]} points exceed the exchange's capacity of {exchange.capacity} per rank")
+    a, b = slab_bounds(V, rank, ws)
+    exchange.stream_barrier()                   # every owner is done with the records of the previous call
+    ops.voxel_bucket_exchange_cuda(points_local, features_local, list(grid_min), float(voxel_size), list(grid_size), ws,
+                                   exchange.per_group, rank, exchange.chunks, exchange.ids.peers, exchange.features.peers,
+                                   exchange.runs.peers)
+    exchange.stream_barrier()                   # every rank's stores have landed
+    grid, counts = ops.voxel_scatter_buckets_cuda(exchange.ids.ptr, exchange.features.ptr, exchange.runs.ptr, exchange.n_blocks,
+                                                  exchange.per_group, points_local.device, a, b)
+    return (grid, counts) if return_counts else grid
 
 
 def batched_exchange_plans(counts, rank: int, per_group: int):

@@ -85,7 +85,33 @@ for rep in range(2):
             assert mean_ok(slab, a, b), "direct mean"
         else:
             assert torch.equal(slab.cpu(), want[mode].reshape(V)[a:b]), "direct " + mode
+# the same in slices of the local cloud whose stores and accumulation overlap on two streams
+for batches in (2, 3):
+    for mode in ("count", "mean"):
+        slab = sharding.voxelize_sharded_exchange(pts[lo:hi], feats[lo:hi] if mode == "mean" else None, mode=mode, direct=px,
+                                                  batches=batches, **kw)
+        a, b = sharding.slab_bounds(V, rank, ws)
+        if mode == "mean":
+            assert mean_ok(slab, a, b), f"batched direct mean {batches}"
+        else:
+            assert torch.equal(slab.cpu(), want[mode].reshape(V)[a:b]), f"batched direct count {batches}"
 px.close()
+# bucket form: fixed blocks in the owners' pools, no counts and no host synchronisation; three calls in a row with
+# different clouds, so that a call's stores meet pools the owners have just read
+bx = sharding.BucketExchange(points_per_rank=120_000, n_voxels=V)
+spans = [sharding.shard_bounds(pts_h.shape[0], r, ws) for r in range(ws)]
+for rep, frac in enumerate((1, 3, 1)):
+    used = [(l, l + (h - l) // frac) for l, h in spans]                 # every rank passes the first 1/frac of its shard
+    sub_h = torch.cat([pts_h[l:h] for l, h in used])
+    sub_f = torch.cat([feats_h[l:h] for l, h in used])
+    m2, c2, s2 = oracle.voxelize_pointcloud(sub_h, sub_f, mode="mean", return_aux=True, **kw)
+    t2 = oracle.mean_tolerance(c2, s2, m2).reshape(V, 4)
+    l, h = used[rank]
+    slab, cnts = sharding.voxelize_sharded_buckets(pts[l:h], feats[l:h], bx, return_counts=True, **kw)
+    a, b = sharding.slab_bounds(V, rank, ws)
+    assert torch.equal(cnts.cpu(), c2.reshape(V)[a:b]), f"bucket counts {rep}"
+    assert bool(((slab.cpu() - m2.reshape(V, 4)[a:b]).abs() <= t2[a:b]).all()), f"bucket mean {rep}"
+bx.close()
 small = sharding.PointExchange(capacity=10, feature_width=4)
 slab = sharding.voxelize_sharded_exchange(pts[lo:hi], None, mode="count", direct=small, **kw)
 a, b = sharding.slab_bounds(V, rank, ws)

@@ -208,6 +208,30 @@ def test_exchange_plan_bookkeeping():
     assert sharding.sub_parts(10 ** 9, 16, 2, "mean") == 32 and sharding.sub_parts(512 ** 3, 4, 8, "occupancy") == 1
 
 
+def test_batched_exchange_plans_lay_the_batches_out_back_to_back():
+    """Batched direct exchange: per batch the plan of that batch, shifted behind the records of the batches before
+    it in every owner's buffer; replaying all stores hits every slot once, and the owner's runs name the right slots."""
+    R, K, nb = 3, 2, 4
+    g = torch.Generator().manual_seed(6)
+    C = torch.randint(0, 40, (R, nb, R * K), generator=g).tolist()          # [source][batch][part]
+    per_rank = [sharding.batched_exchange_plans(C, r, K) for r in range(R)]
+    assert all(t == per_rank[0][1] for _, t in per_rank)
+    totals = per_rank[0][1]
+    for d in range(R):
+        slots = [None] * totals[d]
+        for s in range(R):
+            for i in range(nb):
+                starts = per_rank[s][0][i]["dest_start"]
+                for k in range(K):
+                    for j in range(C[s][i][d * K + k]):
+                        assert slots[starts[d * K + k] + j] is None
+                        slots[starts[d * K + k] + j] = (i, s, k)
+        assert all(x is not None for x in slots)
+        for i in range(nb):
+            for (off, cnt, k), (s, kk) in zip(per_rank[d][0][i]["runs"], [(s, k) for s in range(R) for k in range(K)]):
+                assert k == kk and all(slots[off + j] == (i, s, k) for j in range(cnt))
+
+
 def _lonely_rank(port, q):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)

@@ -213,3 +213,45 @@ def test_line_aligned_and_plain_stores_write_the_same_bytes(groups, per_group, N
     keep = exp_ids >= 0
     order = torch.sort(_owner(exp_ids[keep], 32 ** 3, groups, per_group), stable=True).indices
     assert torch.equal(outs[0][1].cpu(), feats[keep][order])
+
+
+@pytest.mark.parametrize("R,K", [(1, 1), (2, 8), (3, 2), (4, 4), (8, 2), (16, 1)])
+@pytest.mark.parametrize("N", [0, 1, 2500, 40_001])
+def test_bucket_exchange_with_every_owner_on_one_gpu(R, K, N, cuda_lib):
+    """The bucket form of the exchange, all owners' pools in this GPU's memory: every source rank buckets its shard
+    into the owners' pools (fixed block per chunk, no counts), every owner accumulates its pool, and each slab must
+    equal the oracle's grid of the whole cloud.  The pools start out full of garbage: whatever a source does not write
+    must not be read.  The shards are uneven and one more chunk than needed is reserved per source (empty blocks)."""
+    import ctypes
+    kw = dict(grid_min=[-2.0, -2.0, -2.0], voxel_size=0.25, grid_size=[16, 15, 13])       # 3120 voxels: not a multiple of 16
+    V = 16 * 15 * 13
+    pts, feats = _cloud(N, 500 + R * K + N)
+    cuts = [0] + sorted(torch.randint(0, N + 1, (R - 1,), generator=torch.Generator().manual_seed(R + N)).tolist()) + [N]
+    chunks = (max(b - a for a, b in zip(cuts, cuts[1:])) + 1023) // 1024 + 1
+    blk = int(cuda_lib.rc_voxel_bucket_block_records(K))
+    assert blk % 32 == 0 and blk >= 1024 + 8 * K
+    nblocks = R * chunks
+    pools = [dict(ids=torch.full((nblocks * blk,), 123456789, dtype=torch.int32, device=DEV),
+                  feats=torch.full((nblocks * blk, 4), float("nan"), device=DEV),
+                  runs=torch.full((K * nblocks,), 0x7fff7fff, dtype=torch.int32, device=DEV)) for _ in range(R)]
+    for s in range(R):
+        a, b = cuts[s], cuts[s + 1]
+        ops.voxel_bucket_exchange_cuda(pts[a:b].to(DEV), feats[a:b].to(DEV), kw["grid_min"], kw["voxel_size"], kw["grid_size"],
+                                       R, K, s, chunks, [p["ids"].data_ptr() for p in pools], [p["feats"].data_ptr() for p in pools],
+                                       [p["runs"].data_ptr() for p in pools])
+    if N:
+        exp, ecnt, sabs = oracle.voxelize_pointcloud(pts, feats, mode="mean", return_aux=True, **kw)
+        tol = oracle.mean_tolerance(ecnt, sabs, exp).reshape(V, 4)
+        exp, ecnt = exp.reshape(V, 4), ecnt.reshape(V)
+    else:
+        exp, ecnt, tol = torch.zeros(V, 4), torch.zeros(V, dtype=torch.int32), torch.zeros(V, 4)
+    total = 0
+    for d in range(R):
+        lo, hi = sharding.slab_bounds(V, d, R)
+        grid, counts = ops.voxel_scatter_buckets_cuda(pools[d]["ids"].data_ptr(), pools[d]["feats"].data_ptr(),
+                                                      pools[d]["runs"].data_ptr(), nblocks, K, DEV, lo, hi)
+        assert torch.equal(counts.cpu(), ecnt[lo:hi]), (d, R, K)
+        assert bool(((grid.cpu() - exp[lo:hi]).abs() <= tol[lo:hi]).all()), (d, R, K)
+        total += int(counts.sum())
+    assert total == int(ecnt.sum())
+    torch.cuda.synchronize()
