@@ -57,6 +57,8 @@ struct InterpParams {
     int ns;
     int T;
     int tiles_per_row;          // ceil(T / (32*W))
+    int bulk_stage;             // 1: the timestamp rows are staged by bulk asynchronous copies (RC_OPT_GATHER_BULK_STAGE)
+    unsigned int wait_limit;    // polls of the wait for those copies (RC_OPT_BULK_WAIT_LIMIT)
     int pad_;
 };
 
@@ -216,132 +218,7 @@ __device__ __forceinline__ void interp_chunk(const StreamArg& s, const unsigned 
 
 // ---------------------------------------------------------------- gather kernel
 
-// STAGED: timestamp rows live in shared memory; otherwise lanes search global memory
-// (rows too long for shared memory).  Four CTAs of 256 threads per SM (64 registers).
-template <int ES, int VEC, bool STAGED, bool UNIFORM, bool RAGGED>
-__global__ void __launch_bounds__(32 * kMaxWarps, 4)
-interp_gather_kernel(const __grid_constant__ InterpParams p) {
-    extern __shared__ __align__(16) float s_times[];
-
-    const int lane = threadIdx.x & 31;
-    const int warp = threadIdx.x >> 5;
-    const int nwarps = blockDim.x >> 5;
-    const long long b = blockIdx.x / p.tiles_per_row;
-    const int tile = static_cast<int>(blockIdx.x - b * p.tiles_per_row);
-
-    // item b of stream k: first row and number of rows (dense: b*S and S)
-    auto first_row = [&](int k) -> long long {
-        return RAGGED ? __ldg(p.s[k].row_offsets + b) : b * p.s[k].S;
-    };
-    // ragged: the caller's bound max_len (held in S) sized the staged row, so an item that is longer than
-    // that, or offsets that do not ascend, are cut to [0, max_len] rows instead of running past the staging
-    auto num_rows = [&](int k) -> int {
-        if (!RAGGED) return p.s[k].S;
-        const long long n = __ldg(p.s[k].row_offsets + b + 1) - __ldg(p.s[k].row_offsets + b);
-        return static_cast<int>(n < 0 ? 0 : (n > p.s[k].S ? p.s[k].S : n));
-    };
-
-    if (STAGED) {
-        for (int k = 0; k < p.ns; ++k) {
-            const float* g = p.s[k].times + (RAGGED ? first_row(k) : b * p.s[k].time_stride);
-            float* d = s_times + p.s[k].smem_off;
-            const int n = num_rows(k);
-            for (int i = threadIdx.x; i < n; i += blockDim.x) d[i] = __ldg(g + i);
-        }
-        __syncthreads();
-    }
-
-    const int t0 = (tile * nwarps + warp) * 32;
-    if (t0 >= p.T) return;
-    const int nt = min(32, p.T - t0);
-    const float tq = (lane < nt) ? __ldg(p.tt + b * p.tt_stride + t0 + lane) : 0.0f;
-    unsigned char* out_t0 = p.out + (b * p.T + t0) * p.out_row_bytes;
-
-    for (int k = 0; k < p.ns; ++k) {
-        const StreamArg& s = p.s[k];
-        const long long row0 = first_row(k);
-        const int S = num_rows(k);
-        if (RAGGED && S <= 0) {
-            // an item without source rows yields zeros
-            for (int i = lane; i < nt * static_cast<int>(s.row_bytes); i += 32) {
-                const int j = i / static_cast<int>(s.row_bytes);
-                out_t0[static_cast<long long>(j) * p.out_row_bytes + s.col_bytes + (i - j * static_cast<int>(s.row_bytes))] = 0;
-            }
-            continue;
-        }
-        const float* a = STAGED ? (s_times + s.smem_off) : (s.times + (RAGGED ? row0 : b * s.time_stride));
-        int l, r;
-        float w;
-        bracket(a, S, tq, l, r, w);
-        (void)r;
-        interp_chunk<ES, VEC, UNIFORM, UNIFORM ? 2 : 1>(s, s.data + row0 * s.row_bytes, out_t0,
-                                                        p.out_row_bytes, S, l, w, nt, lane);
-    }
-}
-
-// brackets and weights only
-__global__ void __launch_bounds__(256)
-bracket_kernel(const float* __restrict__ st, const float* __restrict__ tt, long long B, int S, int T,
-               int* __restrict__ left, int* __restrict__ right, float* __restrict__ weight) {
-    const long long n = B * T;
-    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
-         i += static_cast<long long>(gridDim.x) * blockDim.x) {
-        const long long b = i / T;
-        int l, r;
-        float w;
-        bracket(st + b * S, S, __ldg(tt + i), l, r, w);
-        if (left) left[i] = l;
-        if (right) right[i] = r;
-        if (weight) weight[i] = w;
-    }
-}
-
-// ---------------------------------------------------------------- block kernel (TMA-staged inputs)
-//
-// When the inputs of one batch item are small enough to sit in shared memory (the fusion
-// shapes: 48 KB for 30x512 + 100x64 + 200x12 bf16) a CTA fetches them whole with one bulk
-// asynchronous copy (TMA, cp.async.bulk) per stream, completes them on an mbarrier, and
-// computes its output rows out of shared memory.  Global memory then sees only large
-// contiguous reads (every input byte exactly once per CTA) and fully coalesced writes;
-// rows narrower than a warp access (24-byte IMU rows) and output rows that are only
-// 8-byte aligned cost nothing extra.  Work is cut into 8-byte pieces of output rows (4 bf16
-// or 2 fp32), written two at a time as 16-byte vectors where the row geometry allows, so
-// every stream width must be a multiple of 8 bytes.
-
-constexpr int kBlockThreads = 512;  // 4 CTAs x 16 warps per SM at the fusion headline shape (measured best of 256/512/1024)
-constexpr int kBlockSmemLimit = 100 * 1024;     // keeps at least two CTAs per SM
 constexpr unsigned int kMbarSpinLimit = 1u << 22;
-
-struct BlockStream {
-    const unsigned char* data;
-    const float* times;
-    int S;
-    int row_bytes;
-    int half_off;       // first 8-byte piece of this stream inside an output row
-    int data_off;       // byte offset of the staged data in shared memory
-    int time_off;       // float offset of the staged time row
-    int block_bytes;    // S * row_bytes
-    long long time_stride;  // floats between the time rows of consecutive items (0: shared row)
-};
-
-struct BlockParams {
-    BlockStream s[RC_MAX_STREAMS];
-    const float* tt;
-    long long tt_stride;        // floats between target rows of consecutive items (0: shared row)
-    unsigned char* out;
-    long long out_block_bytes;  // T * out_row_bytes
-    int out_row_bytes;
-    int hpr;                    // 8-byte pieces per output row
-    int ns;
-    int T;
-    int tiles_t;
-    int rows_per_tile;
-    int times_base;             // byte offsets of the regions after the staged data
-    int brk_base;
-    int vec_base;               // table of output-vector descriptors (16-byte path)
-    unsigned int tx_bytes;      // sum of block_bytes
-    unsigned int wait_limit;    // polls of the first wait for the bulk copies (RC_OPT_BULK_WAIT_LIMIT)
-};
 
 // how often a CTA gave up waiting for its bulk copies and fetched the data with plain loads
 __device__ unsigned int g_bulk_wait_timeouts = 0;
@@ -391,6 +268,157 @@ __device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned int 
     }
     return false;
 }
+
+// STAGED: timestamp rows live in shared memory; otherwise lanes search global memory
+// (rows too long for shared memory).  Four CTAs of 256 threads per SM (64 registers).
+template <int ES, int VEC, bool STAGED, bool UNIFORM, bool RAGGED>
+__global__ void __launch_bounds__(32 * kMaxWarps, 4)
+interp_gather_kernel(const __grid_constant__ InterpParams p) {
+    extern __shared__ __align__(16) float s_times[];
+
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    const int nwarps = blockDim.x >> 5;
+    const long long b = blockIdx.x / p.tiles_per_row;
+    const int tile = static_cast<int>(blockIdx.x - b * p.tiles_per_row);
+
+    // item b of stream k: first row and number of rows (dense: b*S and S)
+    auto first_row = [&](int k) -> long long {
+        return RAGGED ? __ldg(p.s[k].row_offsets + b) : b * p.s[k].S;
+    };
+    // ragged: the caller's bound max_len (held in S) sized the staged row, so an item that is longer than
+    // that, or offsets that do not ascend, are cut to [0, max_len] rows instead of running past the staging
+    auto num_rows = [&](int k) -> int {
+        if (!RAGGED) return p.s[k].S;
+        const long long n = __ldg(p.s[k].row_offsets + b + 1) - __ldg(p.s[k].row_offsets + b);
+        return static_cast<int>(n < 0 ? 0 : (n > p.s[k].S ? p.s[k].S : n));
+    };
+
+    __shared__ __align__(8) unsigned long long bar;
+    bool gave_up = false;       // thread 0 only: its bounded wait for the bulk copies ran out
+    if (STAGED) {
+        bool staged = false;
+        if (!RAGGED && p.bulk_stage) {
+            // one thread fetches every time row with a bulk asynchronous copy (TMA) and waits for it, bounded;
+            // should the wait run out, the rows are fetched again with ordinary loads below
+            bool arrived = true;
+            if (threadIdx.x == 0) {
+                unsigned int bytes = 0;
+                for (int k = 0; k < p.ns; ++k) bytes += static_cast<unsigned int>(p.s[k].S) * 4u;
+                mbar_init(&bar, 1);
+                mbar_expect_tx(&bar, bytes);
+                for (int k = 0; k < p.ns; ++k)
+                    bulk_load(s_times + p.s[k].smem_off, p.s[k].times + b * p.s[k].time_stride,
+                              static_cast<unsigned int>(p.s[k].S) * 4u, &bar);
+                arrived = mbar_wait(&bar, 0, p.wait_limit);
+                if (!arrived) atomicAdd(&g_bulk_wait_timeouts, 1u);
+                gave_up = !arrived;
+            }
+            staged = !__syncthreads_or(!arrived);
+        }
+        if (!staged) {
+            for (int k = 0; k < p.ns; ++k) {
+                const float* g = p.s[k].times + (RAGGED ? first_row(k) : b * p.s[k].time_stride);
+                float* d = s_times + p.s[k].smem_off;
+                const int n = num_rows(k);
+                for (int i = threadIdx.x; i < n; i += blockDim.x) d[i] = __ldg(g + i);
+            }
+            __syncthreads();
+        }
+    }
+
+    const int t0 = (tile * nwarps + warp) * 32;
+    if (t0 >= p.T) return;
+    const int nt = min(32, p.T - t0);
+    const float tq = (lane < nt) ? __ldg(p.tt + b * p.tt_stride + t0 + lane) : 0.0f;
+    unsigned char* out_t0 = p.out + (b * p.T + t0) * p.out_row_bytes;
+
+    for (int k = 0; k < p.ns; ++k) {
+        const StreamArg& s = p.s[k];
+        const long long row0 = first_row(k);
+        const int S = num_rows(k);
+        if (RAGGED && S <= 0) {
+            // an item without source rows yields zeros
+            for (int i = lane; i < nt * static_cast<int>(s.row_bytes); i += 32) {
+                const int j = i / static_cast<int>(s.row_bytes);
+                out_t0[static_cast<long long>(j) * p.out_row_bytes + s.col_bytes + (i - j * static_cast<int>(s.row_bytes))] = 0;
+            }
+            continue;
+        }
+        const float* a = STAGED ? (s_times + s.smem_off) : (s.times + (RAGGED ? row0 : b * s.time_stride));
+        int l, r;
+        float w;
+        bracket(a, S, tq, l, r, w);
+        (void)r;
+        interp_chunk<ES, VEC, UNIFORM, UNIFORM ? 2 : 1>(s, s.data + row0 * s.row_bytes, out_t0,
+                                                        p.out_row_bytes, S, l, w, nt, lane);
+    }
+    // a CTA that gave up on its bulk copies must not hand its shared memory on while they may still land
+    if (gave_up) mbar_wait(&bar, 0, kMbarSpinLimit);
+}
+
+// brackets and weights only
+__global__ void __launch_bounds__(256)
+bracket_kernel(const float* __restrict__ st, const float* __restrict__ tt, long long B, int S, int T,
+               int* __restrict__ left, int* __restrict__ right, float* __restrict__ weight) {
+    const long long n = B * T;
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const long long b = i / T;
+        int l, r;
+        float w;
+        bracket(st + b * S, S, __ldg(tt + i), l, r, w);
+        if (left) left[i] = l;
+        if (right) right[i] = r;
+        if (weight) weight[i] = w;
+    }
+}
+
+// ---------------------------------------------------------------- block kernel (TMA-staged inputs)
+//
+// When the inputs of one batch item are small enough to sit in shared memory (the fusion
+// shapes: 48 KB for 30x512 + 100x64 + 200x12 bf16) a CTA fetches them whole with one bulk
+// asynchronous copy (TMA, cp.async.bulk) per stream, completes them on an mbarrier, and
+// computes its output rows out of shared memory.  Global memory then sees only large
+// contiguous reads (every input byte exactly once per CTA) and fully coalesced writes;
+// rows narrower than a warp access (24-byte IMU rows) and output rows that are only
+// 8-byte aligned cost nothing extra.  Work is cut into 8-byte pieces of output rows (4 bf16
+// or 2 fp32), written two at a time as 16-byte vectors where the row geometry allows, so
+// every stream width must be a multiple of 8 bytes.
+
+constexpr int kBlockThreads = 512;  // 4 CTAs x 16 warps per SM at the fusion headline shape (measured best of 256/512/1024)
+constexpr int kBlockSmemLimit = 100 * 1024;     // keeps at least two CTAs per SM
+
+struct BlockStream {
+    const unsigned char* data;
+    const float* times;
+    int S;
+    int row_bytes;
+    int half_off;       // first 8-byte piece of this stream inside an output row
+    int data_off;       // byte offset of the staged data in shared memory
+    int time_off;       // float offset of the staged time row
+    int block_bytes;    // S * row_bytes
+    long long time_stride;  // floats between the time rows of consecutive items (0: shared row)
+};
+
+struct BlockParams {
+    BlockStream s[RC_MAX_STREAMS];
+    const float* tt;
+    long long tt_stride;        // floats between target rows of consecutive items (0: shared row)
+    unsigned char* out;
+    long long out_block_bytes;  // T * out_row_bytes
+    int out_row_bytes;
+    int hpr;                    // 8-byte pieces per output row
+    int ns;
+    int T;
+    int tiles_t;
+    int rows_per_tile;
+    int times_base;             // byte offsets of the regions after the staged data
+    int brk_base;
+    int vec_base;               // table of output-vector descriptors (16-byte path)
+    unsigned int tx_bytes;      // sum of block_bytes
+    unsigned int wait_limit;    // polls of the first wait for the bulk copies (RC_OPT_BULK_WAIT_LIMIT)
+};
 
 // pieces of the block kernel ---------------------------------------------------------------
 
@@ -773,6 +801,16 @@ int interp_dispatch(const rc_stream_desc* streams, int ns, const int64_t* time_s
     const size_t smem = static_cast<size_t>(smem_off) * sizeof(float);
     const bool staged = smem <= static_cast<size_t>(kMaxStagedBytes);
     const int threads = warps * 32;
+    // bulk-copy staging of the time rows: every row a whole number of 16-byte pieces at a 16-byte aligned address
+    p.bulk_stage = 0;
+    if (staged && rc::g_gather_bulk_stage.load(std::memory_order_relaxed)) {
+        bool ok = true;
+        for (int k = 0; k < live; ++k)
+            ok = ok && (p.s[k].S % 4 == 0) && rc::aligned_to(p.s[k].times, 16) && (p.s[k].time_stride % 4 == 0);
+        p.bulk_stage = ok ? 1 : 0;
+        const int opt = rc::g_bulk_wait_limit.load(std::memory_order_relaxed);
+        p.wait_limit = opt < 0 ? kMbarSpinLimit : static_cast<unsigned int>(opt);
+    }
     if (es == 2) {
         switch (vec) {
             case 16: return launch_gather<2, 16>(p, grid, threads, smem, staged, uniform, stream);

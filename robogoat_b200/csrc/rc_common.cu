@@ -13,6 +13,7 @@ std::atomic<int> g_allow_block_kernel{1};
 std::atomic<int> g_voxel_passes{0};
 std::atomic<int> g_part_aligned_store{1};
 std::atomic<int> g_bulk_wait_limit{-1};
+std::atomic<int> g_gather_bulk_stage{1};
 
 // SM count per device, filled on first use (immutable hardware facts, not call state).
 static std::atomic<int> g_sm_count[64];
@@ -79,6 +80,10 @@ int rc_set_option(int option, int value) {
     if (option == RC_OPT_PART_ALIGNED_STORE) {
         if (value < 0 || value > 2) return RC_ERR_BAD_VALUE;
         rc::g_part_aligned_store.store(value, std::memory_order_relaxed);
+        return RC_OK;
+    }
+    if (option == RC_OPT_GATHER_BULK_STAGE) {
+        rc::g_gather_bulk_stage.store(value != 0, std::memory_order_relaxed);
         return RC_OK;
     }
     if (option == RC_OPT_BULK_WAIT_LIMIT) {

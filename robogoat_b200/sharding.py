@@ -396,7 +396,7 @@ class BucketExchange:
         except RuntimeError as e:
             error = e
         if not self._everyone(error is None):
-            self.close(collective=False)
+            self.close()
             raise RuntimeError(f"BucketExchange: record pools could not be allocated on every rank ({error})")
         for buf in (self.ids, self.features, self.runs):
             try:
@@ -417,7 +417,7 @@ class BucketExchange:
         before everything this rank enqueues after it."""
         dist.all_reduce(self._token, group=self.group)
 
-    def close(self, collective: bool = True) -> None:
+    def close(self) -> None:
         for b in (self.ids, self.features, self.runs):
             if b is not None:
                 b.close()

@@ -224,6 +224,51 @@ def test_ragged_bound_below_an_item_length_truncates_the_item(cuda_lib):
     torch.cuda.synchronize()
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_bulk_copy_staging_of_time_rows_gives_the_same_bits(dtype, cuda_lib):
+    """RC_OPT_GATHER_BULK_STAGE: the gather kernel's timestamp rows staged by bulk asynchronous copies (S a multiple of 4,
+    so every row is a whole number of 16-byte pieces) against the oracle, and rows that do not qualify (S = 501) too."""
+    from robogoat_b200 import _lib
+    cuda_lib.rc_set_option(_lib.OPT_BLOCK_KERNEL, 0)
+    cuda_lib.rc_set_option(_lib.OPT_GATHER_BULK_STAGE, 1)
+    try:
+        for S in (500, 501, 4):
+            src, st, tt = workloads.resample_inputs(B=70, S=S, D=256, T=250, dtype=dtype, irregular_targets=True, seed=S)
+            out = robocache.resample_trajectories(src.to(DEV), st.to(DEV), tt.to(DEV))
+            torch.cuda.synchronize()
+            assert_exact(out.cpu(), expected(src, st, tt), f"S={S}")
+    finally:
+        cuda_lib.rc_set_option(_lib.OPT_GATHER_BULK_STAGE, 0)
+        cuda_lib.rc_set_option(_lib.OPT_BLOCK_KERNEL, 1)
+
+
+def test_gather_kernel_survives_a_bulk_copy_wait_that_runs_out(cuda_lib):
+    """The row-gather kernel stages its timestamp rows by bulk copy; with the wait limit at 0 polls every CTA gives up at
+    once, counts the event, fetches the rows with ordinary loads and still returns the oracle's bits - nothing on the GPU
+    goes wrong in this test."""
+    from conftest import DELIBERATE_BULK_TIMEOUTS, bulk_wait_timeouts
+    from robogoat_b200 import _lib
+    before = bulk_wait_timeouts(cuda_lib)
+    assert before == DELIBERATE_BULK_TIMEOUTS[0]
+    src, st, tt = workloads.resample_inputs(B=40, S=500, D=256, T=250, dtype=torch.bfloat16, irregular_targets=True, seed=8)
+    exp = expected(src, st, tt)
+    cuda_lib.rc_set_option(_lib.OPT_BLOCK_KERNEL, 0)
+    cuda_lib.rc_set_option(_lib.OPT_BULK_WAIT_LIMIT, 0)
+    try:
+        out = robocache.resample_trajectories(src.to(DEV), st.to(DEV), tt.to(DEV))
+        torch.cuda.synchronize()
+    finally:
+        cuda_lib.rc_set_option(_lib.OPT_BULK_WAIT_LIMIT, -1)
+        cuda_lib.rc_set_option(_lib.OPT_BLOCK_KERNEL, 1)
+        after = bulk_wait_timeouts(cuda_lib)
+        DELIBERATE_BULK_TIMEOUTS[0] = after
+    assert_exact(out.cpu(), exp)
+    assert after >= before + 40                       # at least one CTA per batch row gave up
+    out = robocache.resample_trajectories(src.to(DEV), st.to(DEV), tt.to(DEV))
+    assert_exact(out.cpu(), exp)
+    assert bulk_wait_timeouts(cuda_lib) == after      # built-in limit again: no new events
+
+
 def test_expanded_and_strided_time_rows_are_used_in_place(cuda_lib):
     """Timestamps given as stride-0 expanded rows (the reference's usual linspace(...).expand(B, -1)) or as
     row-strided views give the same bits as their materialised copies."""
