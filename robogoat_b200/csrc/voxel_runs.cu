@@ -126,7 +126,7 @@ voxel_bucket_kernel(const float* __restrict__ pts, const float4* __restrict__ fe
             }
         }
         // rank of every point among the warp's points of the same slab: intersect the ballots of the slab number's
-        // bits (__match_any_sync in their place ran 5 % slower)
+        // bits (__match_any_sync in their place ran 5 % slower, shared-memory atomics on the warp's counters 3 %)
 #pragma unroll
         for (int i = 0; i < kPointsPerLane; ++i) {
             unsigned int same = __ballot_sync(0xffffffffu, part[i] >= 0);

@@ -227,18 +227,20 @@ def test_ragged_bound_below_an_item_length_truncates_the_item(cuda_lib):
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_bulk_copy_staging_of_time_rows_gives_the_same_bits(dtype, cuda_lib):
     """RC_OPT_GATHER_BULK_STAGE: the gather kernel's timestamp rows staged by bulk asynchronous copies (S a multiple of 4,
-    so every row is a whole number of 16-byte pieces) against the oracle, and rows that do not qualify (S = 501) too."""
+    so every row is a whole number of 16-byte pieces) and by ordinary loads, both against the oracle; rows that do not
+    qualify for the bulk copy (S = 501) too."""
     from robogoat_b200 import _lib
     cuda_lib.rc_set_option(_lib.OPT_BLOCK_KERNEL, 0)
-    cuda_lib.rc_set_option(_lib.OPT_GATHER_BULK_STAGE, 1)
     try:
-        for S in (500, 501, 4):
-            src, st, tt = workloads.resample_inputs(B=70, S=S, D=256, T=250, dtype=dtype, irregular_targets=True, seed=S)
-            out = robocache.resample_trajectories(src.to(DEV), st.to(DEV), tt.to(DEV))
-            torch.cuda.synchronize()
-            assert_exact(out.cpu(), expected(src, st, tt), f"S={S}")
+        for staged in (1, 0):
+            cuda_lib.rc_set_option(_lib.OPT_GATHER_BULK_STAGE, staged)
+            for S in (500, 501, 4):
+                src, st, tt = workloads.resample_inputs(B=70, S=S, D=256, T=250, dtype=dtype, irregular_targets=True, seed=S)
+                out = robocache.resample_trajectories(src.to(DEV), st.to(DEV), tt.to(DEV))
+                torch.cuda.synchronize()
+                assert_exact(out.cpu(), expected(src, st, tt), f"S={S} bulk staging {staged}")
     finally:
-        cuda_lib.rc_set_option(_lib.OPT_GATHER_BULK_STAGE, 0)
+        cuda_lib.rc_set_option(_lib.OPT_GATHER_BULK_STAGE, 1)
         cuda_lib.rc_set_option(_lib.OPT_BLOCK_KERNEL, 1)
 
 
