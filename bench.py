@@ -801,7 +801,7 @@ def run_extras(L, dev, local, rank, world, peak, ex):
     return ex
 
 
-def sharded_parity(dev, rank, world, px, bx=None) -> dict:
+def sharded_parity(dev, rank, world, px, bx=None, bxs=None) -> dict:
     """Every sharded voxel form on a cloud small enough for the CPU oracle (2^20 mixture points into 128^3), checked
     on every rank against the oracle run on the whole cloud: occupancy and counts exact, means within the oracle's
     tolerance.  Returns one flag per form, true only if it held on all ranks."""
@@ -844,11 +844,13 @@ def sharded_parity(dev, rank, world, px, bx=None) -> dict:
         flags["exchange_direct_batched"] = (
             count_ok(sharding.voxelize_sharded_exchange(pl, None, mode="count", direct=px, batches=4, **kw), xa, xb)
             and mean_ok(sharding.voxelize_sharded_exchange(pl, fl, mode="mean", direct=px, batches=4, **kw), xa, xb))
-    if bx is not None:
-        flags["bucket_exchange"] = True
-        for _ in range(2):          # twice: the second call's stores meet pools the owners have just read
-            got, gcnt = sharding.voxelize_sharded_buckets(pl, fl, bx, return_counts=True, **kw)
-            flags["bucket_exchange"] = flags["bucket_exchange"] and count_ok(gcnt, xa, xb) and mean_ok(got, xa, xb)
+    for key, ex_ in (("bucket_exchange", bx), ("bucket_exchange_store", bxs)):
+        if ex_ is None:
+            continue
+        flags[key] = True
+        for _ in range(2):          # twice: the second call's records meet pools that have just been read
+            got, gcnt = sharding.voxelize_sharded_buckets(pl, fl, ex_, return_counts=True, **kw)
+            flags[key] = flags[key] and count_ok(gcnt, xa, xb) and mean_ok(got, xa, xb)
     names = sorted(flags)
     t = torch.tensor([1 if flags[k] else 0 for k in names], dtype=torch.int32, device=dev)
     dist.all_reduce(t, op=dist.ReduceOp.MIN)
@@ -886,12 +888,12 @@ def multi_gpu_extras(L, dev, rank, world, ex, pts, feats, kw, N, single_ms):
     except RuntimeError as e:       # raised on every rank alike
         px = None
         ex["voxel_sharded_direct_unavailable"] = str(e)[:200]
+    bx = bxs = None         # bxs: the fetching transport (measured slower; not timed by default)
     try:
         bx = sharding.BucketExchange(points_per_rank=N, n_voxels=512 ** 3)
     except RuntimeError as e:
-        bx = None
         ex["voxel_sharded_bucket_exchange_unavailable"] = str(e)[:200]
-    parity = sharded_parity(dev, rank, world, px, bx)
+    parity = sharded_parity(dev, rank, world, px, bx, bxs)
     ex["voxel_sharded_parity"] = {"parity": parity,
                                   "checked": "2^20 mixture points into 128^3 on every rank against the CPU oracle run on the whole cloud: "
                                              "occupancy and counts exact, means within 1e-5 relative + 1e-6 of the mean summand"}
@@ -926,9 +928,12 @@ def multi_gpu_extras(L, dev, rank, world, ex, pts, feats, kw, N, single_ms):
         forms.append(("bucket_exchange", "bucket_exchange", lambda m: sharding.voxelize_sharded_buckets(pts, feats, bx, **kw),
                       "one bucket kernel sorts every chunk by (owner, sub-range) and stores each owner's records into a fixed block of "
                       "that owner's pool over NVLink; no counts, no host synchronisation, two barriers on the stream; mean mode only"))
+    if bxs is not None:
+        forms.append(("bucket_exchange_fetch", "bucket_exchange_store", lambda m: sharding.voxelize_sharded_buckets(pts, feats, bxs, **kw),
+                      "same pools in the sources' own memory; every owner's accumulation kernel fetches its blocks over NVLink as it goes"))
     for mode in ("mean", "count"):
         for name, pkey, fn, note in forms:
-            if name == "bucket_exchange" and mode != "mean":
+            if name.startswith("bucket_exchange") and mode != "mean":
                 continue
             ms = timed(lambda: fn(mode))
             ok = bool(parity.get(pkey))
@@ -987,29 +992,34 @@ def multi_gpu_extras(L, dev, rank, world, ex, pts, feats, kw, N, single_ms):
             "bound": "the move kernel (NVLink, measured 770 GB/s per direction) and the owner's atomics run back to back here; "
                      "the batched form overlaps them"})
         px.close()
-    if bx is not None:
-        # stages of the bucket form, each max over ranks
+    for key, ex_ in (("bucket_exchange", bx), ("bucket_exchange_fetch", bxs)):
+        if ex_ is None:
+            continue
+        # stages of the bucket forms, each max over ranks
         a_v, b_v = sharding.slab_bounds(512 ** 3, rank, world)
+        d_ids, d_feats, d_runs, first_block, pool_blocks = ex_.destinations()
+        s_ids, s_feats, s_runs, per_source = ex_.sources()
         barrier(world)
-        bx.stream_barrier()
+        ex_.stream_barrier()
         ev[0].record()
-        ops.voxel_bucket_exchange_cuda(pts, feats, kw["grid_min"], kw["voxel_size"], kw["grid_size"], world, bx.per_group, rank,
-                                       bx.chunks, bx.ids.peers, bx.features.peers, bx.runs.peers)
+        ops.voxel_bucket_exchange_cuda(pts, feats, kw["grid_min"], kw["voxel_size"], kw["grid_size"], world, ex_.per_group, ex_.chunks,
+                                       first_block, pool_blocks, d_ids, d_feats, d_runs)
         ev[1].record()
-        bx.stream_barrier()
+        ex_.stream_barrier()
         ev[2].record()
-        r = ops.voxel_scatter_buckets_cuda(bx.ids.ptr, bx.features.ptr, bx.runs.ptr, bx.n_blocks, bx.per_group, dev, a_v, b_v)
+        r = ops.voxel_scatter_buckets_cuda(s_ids, s_feats, s_runs, per_source, ex_.per_group, dev, a_v, b_v)
         ev[3].record(); torch.cuda.synchronize()
         stages = [max_over_ranks(ev[i].elapsed_time(ev[i + 1]), world, dev) for i in range(3)]
         del r
         remote_bytes = N * 20 * (world - 1) / world
-        ex["voxel_mean_sharded_bucket_exchange"].update({
-            "sub_ranges_per_slab": bx.per_group,
-            "stage_ms": {"bucket_kernel_stores_over_nvlink": stages[0], "barrier": stages[1], "clear_scatter_normalise": stages[2]},
-            "nvlink_GB/s_out_per_gpu_during_bucket_kernel": remote_bytes / (stages[0] * 1e-3) / 1e9,
-            "bound": "bucket kernel: the slower of its own work (0.65 ms on one GPU) and the record bytes that must cross NVLink / 770 GB/s "
-                     "per direction; accumulation: the rate at which L2 retires atomics"})
-        bx.close()
+        link_stage = stages[2] if ex_.fetch else stages[0]
+        ex[f"voxel_mean_sharded_{key}"].update({
+            "sub_ranges_per_slab": ex_.per_group,
+            "stage_ms": {"bucket_kernel": stages[0], "barrier": stages[1], "clear_accumulate_normalise": stages[2]},
+            "nvlink_GB/s_per_gpu_during_the_stage_that_crosses_it": remote_bytes / (link_stage * 1e-3) / 1e9,
+            "bound": "bucket kernel: its own work (0.65 ms on one GPU) and, when it stores remotely, the record bytes that must cross NVLink / "
+                     "770 GB/s per direction; accumulation: the rate at which L2 retires atomics and, when it fetches, the same link bound"})
+        ex_.close()
 
 
 def run_profile_case(name: str):

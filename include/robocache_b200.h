@@ -260,29 +260,33 @@ RC_API int rc_voxel_scatter_runs(const int32_t* ids, const float* features, void
  * Point exchange by buckets (mean mode, four feature channels): the multi-GPU form of the slab-ordered run path,
  * with no counting pass and no host synchronisation.  The voxel ids are cut into n_groups owner ranges of
  * ceil(V / n_groups) ids and each range into parts_per_group sub-ranges; n_groups * parts_per_group <= 16.
- * Every owner has a record pool of n_groups * chunks_per_source blocks of rc_voxel_bucket_block_records() records
- * (ids int32 and feature rows fp32 [., 4] in two buffers, 128-byte aligned) and a run table uint32
- * [parts_per_group][n_groups * chunks_per_source].
- * rc_voxel_bucket_exchange: rank source_rank sorts each 1024-point chunk of its cloud by (owner, sub-range) and
- *   stores every owner's segment into block source_rank * chunks_per_source + chunk of that owner's pool, and the
- *   sub-ranges' (first slot, length) into that owner's table.  dest_ids / dest_features / dest_runs are HOST arrays
- *   of n_groups device pointers, which may be other GPUs' buffers mapped with rc_peer_open (plain stores; nothing
- *   is read from a peer, no multicast).  N <= chunks_per_source * 1024; all of the source's blocks are written on
- *   every call (empty ones as empty).  The caller orders the stores against the owners' reads with a barrier on
- *   the stream before and after.
- * rc_voxel_scatter_buckets: the owner accumulates its pool into its slab [id_begin, id_end) of the grid (fp32
- *   [., 4], first cell of voxel id_begin) and counts, one sub-range after the other; flags as rc_voxelize.
+ * A record pool is a sequence of blocks of rc_voxel_bucket_block_records() records (ids int32 and feature rows
+ * fp32 [., 4] in two buffers, 128-byte aligned) with a run table uint32 [parts_per_group][pool_blocks] beside it.
+ * rc_voxel_bucket_exchange: sorts each 1024-point chunk of the cloud by (owner, sub-range) and stores owner d's
+ *   segment of chunk c into block first_block + c of pool d, and the sub-ranges' (first slot, length) into table d.
+ *   dest_ids / dest_features / dest_runs are HOST arrays of n_groups device pointers; pool_blocks is the number of
+ *   blocks of every pool (the row length of its table).  Two layouts are in use: the owners' pools in the owners'
+ *   memory, mapped here with rc_peer_open (plain stores over NVLink; first_block = rank * chunks, pool_blocks =
+ *   n_groups * chunks), or n_groups pools in this GPU's own memory that the owners read later (first_block = 0,
+ *   pool_blocks = chunks).  N <= chunks * 1024; all `chunks` blocks are written on every call (empty ones as
+ *   empty).  Nothing is read from a peer, no multicast.
+ * rc_voxel_scatter_buckets: an owner accumulates the pools of n_sources sources (HOST arrays of device pointers
+ *   to ids, feature rows and tables of blocks_per_source blocks each; they may lie in other GPUs' memory and are
+ *   then read with plain loads over NVLink) into its slab [id_begin, id_end) of the grid (fp32 [., 4], first cell of
+ *   voxel id_begin) and counts, one sub-range after the other; flags as rc_voxelize.
+ * The caller orders writers against readers with a barrier on the stream before and after the exchange call.
  * No counterpart in the reference.
  */
 RC_API int32_t rc_voxel_bucket_block_records(int32_t parts_per_group);
 RC_API int rc_voxel_bucket_exchange(const float* points, const float* features, int64_t N, const float grid_min_host[3],
                                     float voxel_size, const int32_t grid_size_host[3], int32_t n_groups,
-                                    int32_t parts_per_group, int32_t source_rank, int64_t chunks_per_source,
+                                    int32_t parts_per_group, int64_t chunks, int64_t first_block, int64_t pool_blocks,
                                     void* const* dest_ids, void* const* dest_features, void* const* dest_runs, int device,
                                     void* stream);
-RC_API int rc_voxel_scatter_buckets(const int32_t* pool_ids, const float* pool_features, const uint32_t* runs,
-                                    int64_t n_blocks, int32_t parts_per_group, float* grid, int32_t* counts,
-                                    int64_t id_begin, int64_t id_end, uint32_t flags, int device, void* stream);
+RC_API int rc_voxel_scatter_buckets(const void* const* pool_ids, const void* const* pool_features, const void* const* runs,
+                                    int32_t n_sources, int64_t blocks_per_source, int32_t parts_per_group, float* grid,
+                                    int32_t* counts, int64_t id_begin, int64_t id_end, uint32_t flags, int device,
+                                    void* stream);
 
 /*
  * Device buffers that the other processes of a node can map, for rc_voxel_partition_move's remote

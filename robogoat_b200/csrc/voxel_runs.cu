@@ -257,6 +257,57 @@ voxel_run_scatter_kernel(const unsigned int* __restrict__ runs_p, const int* __r
     }
 }
 
+// The owner's side of the bucket exchange: the same accumulation over the blocks of several record pools - one per
+// source rank, in this GPU's memory or, when the owner fetches instead of the sources storing, in the sources' memory
+// (plain loads over NVLink; no multicast).  Step i takes block i / n of source i % n, so that neighbouring warps
+// read from different sources and every link carries its share all the time.
+struct ScatterSources {
+    const int* ids[kMeanRunsMaxParts];
+    const float4* feats[kMeanRunsMaxParts];
+    const unsigned int* runs[kMeanRunsMaxParts];    // the current sub-range's row of every source's table
+    int n;
+};
+
+__global__ void __launch_bounds__(kThreads)
+voxel_bucket_scatter_kernel(const __grid_constant__ ScatterSources src, long long blocks, int blk, float* __restrict__ grid,
+                            int* __restrict__ counts) {
+    const int lane = threadIdx.x & 31;
+    const long long warps_total = static_cast<long long>(gridDim.x) * (kThreads / 32);
+    const long long steps = blocks * src.n;
+    long long it = static_cast<long long>(blockIdx.x) * (kThreads / 32) + (threadIdx.x >> 5);
+    unsigned int desc = (it < steps) ? __ldg(src.runs[it % src.n] + it / src.n) : 0u;
+    for (; it < steps; it += warps_total) {
+        const int s = static_cast<int>(it % src.n);
+        const long long c = it / src.n;
+        const int n = static_cast<int>(desc & 0xffffu);
+        const long long off = c * blk + (desc >> 16);
+        const long long next = it + warps_total;
+        if (next < steps) desc = __ldg(src.runs[next % src.n] + next / src.n);
+        const int* ip = src.ids[s] + off + lane;
+        const float4* fp = src.feats[s] + off + lane;
+        for (int j0 = 0; j0 < n; j0 += 32 * kRunLoads) {
+            int id[kRunLoads];
+            float4 f[kRunLoads];
+#pragma unroll
+            for (int i = 0; i < kRunLoads; ++i) {
+                const int j = j0 + i * 32 + lane;
+                id[i] = -1;
+                if (j < n) {
+                    id[i] = __ldcs(ip + j0 + i * 32);
+                    f[i] = __ldcs(fp + j0 + i * 32);
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < kRunLoads; ++i) {
+                if (id[i] >= 0) {
+                    red_add_v4(grid + static_cast<long long>(id[i]) * 4, f[i]);
+                    atomicAdd(counts + id[i], 1);
+                }
+            }
+        }
+    }
+}
+
 long long ceil_div(long long a, long long b) { return (a + b - 1) / b; }
 long long round_up(long long a, long long m) { return ceil_div(a, m) * m; }
 
@@ -340,15 +391,15 @@ int32_t rc_voxel_bucket_block_records(int32_t parts_per_group) {
 
 int rc_voxel_bucket_exchange(const float* points, const float* features, int64_t N, const float grid_min_host[3],
                              float voxel_size, const int32_t grid_size_host[3], int32_t n_groups, int32_t parts_per_group,
-                             int32_t source_rank, int64_t chunks_per_source, void* const* dest_ids,
+                             int64_t chunks, int64_t first_block, int64_t pool_blocks, void* const* dest_ids,
                              void* const* dest_features, void* const* dest_runs, int device, void* stream) {
     if (grid_min_host == nullptr || grid_size_host == nullptr || dest_ids == nullptr || dest_features == nullptr ||
         dest_runs == nullptr)
         return RC_ERR_NULL_POINTER;
-    if (n_groups < 1 || parts_per_group < 1 || source_rank < 0 || source_rank >= n_groups || N < 0 || chunks_per_source < 0)
+    if (n_groups < 1 || parts_per_group < 1 || N < 0 || chunks < 0 || first_block < 0 || first_block + chunks > pool_blocks)
         return RC_ERR_BAD_SHAPE;
     if (static_cast<long long>(n_groups) * parts_per_group > kMeanRunsMaxParts) return RC_ERR_TOO_LARGE;
-    if (N > chunks_per_source * kRunChunk || N > (1ll << 31) - 4096) return RC_ERR_TOO_LARGE;
+    if (N > chunks * kRunChunk || N > (1ll << 31) - 4096) return RC_ERR_TOO_LARGE;
     if (!(voxel_size > 0.0f) || !(voxel_size <= 3.0e38f)) return RC_ERR_BAD_VALUE;
     VoxelGeom g;
     g.minx = grid_min_host[0]; g.miny = grid_min_host[1]; g.minz = grid_min_host[2];
@@ -360,7 +411,7 @@ int rc_voxel_bucket_exchange(const float* points, const float* features, int64_t
     g.fgx = static_cast<float>(g.gx); g.fgy = static_cast<float>(g.gy); g.fgz = static_cast<float>(g.gz);
     g.inv_vs = host_reciprocal(voxel_size);
     const long long V = static_cast<long long>(g.gx) * g.gy * g.gz;
-    if (chunks_per_source == 0 || V == 0) return RC_OK;
+    if (chunks == 0 || V == 0) return RC_OK;
     if (N > 0 && (points == nullptr || features == nullptr)) return RC_ERR_NULL_POINTER;
     if (!rc::aligned_to(points, 4) || !rc::aligned_to(features, 16)) return RC_ERR_BAD_ALIGNMENT;
     ExchangeDest dest{};
@@ -377,8 +428,8 @@ int rc_voxel_bucket_exchange(const float* points, const float* features, int64_t
     dest.per_group = parts_per_group;
     dest.owner_span = static_cast<unsigned int>(owner_span);
     dest.inv_owner_span = 1.0f / static_cast<float>(owner_span);
-    dest.block0 = static_cast<long long>(source_rank) * chunks_per_source;
-    dest.nblocks = static_cast<long long>(n_groups) * chunks_per_source;
+    dest.block0 = first_block;
+    dest.nblocks = pool_blocks;
     RunRule rule;
     rule.P = n_groups * parts_per_group;
     rule.slab = static_cast<unsigned int>(ceil_div(owner_span, parts_per_group));
@@ -387,24 +438,35 @@ int rc_voxel_bucket_exchange(const float* points, const float* features, int64_t
     rc::DeviceScope scope(device);
     if (scope.status() != RC_OK) return scope.status();
     const int sms = rc::sm_count(device);
-    const long long nb = chunks_per_source < 8ll * sms ? chunks_per_source : 8ll * sms;
+    const long long nb = chunks < 8ll * sms ? chunks : 8ll * sms;
     voxel_bucket_kernel<true><<<static_cast<unsigned int>(nb), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-        points, reinterpret_cast<const float4*>(features), N, g, rc::aligned_to(points, 16), rule, chunks_per_source, nullptr,
+        points, reinterpret_cast<const float4*>(features), N, g, rc::aligned_to(points, 16), rule, chunks, nullptr,
         nullptr, nullptr, dest, nullptr, 0);
     return rc::check_launch();
 }
 
-int rc_voxel_scatter_buckets(const int32_t* pool_ids, const float* pool_features, const uint32_t* runs, int64_t n_blocks,
-                             int32_t parts_per_group, float* grid, int32_t* counts, int64_t id_begin, int64_t id_end,
-                             uint32_t flags, int device, void* stream) {
-    if (n_blocks < 0 || parts_per_group < 1 || parts_per_group > kMeanRunsMaxParts || id_begin < 0 || id_end < id_begin)
+int rc_voxel_scatter_buckets(const void* const* pool_ids, const void* const* pool_features, const void* const* runs,
+                             int32_t n_sources, int64_t blocks_per_source, int32_t parts_per_group, float* grid, int32_t* counts,
+                             int64_t id_begin, int64_t id_end, uint32_t flags, int device, void* stream) {
+    if (n_sources < 0 || n_sources > kMeanRunsMaxParts || blocks_per_source < 0 || parts_per_group < 1 ||
+        parts_per_group > kMeanRunsMaxParts || id_begin < 0 || id_end < id_begin)
         return RC_ERR_BAD_SHAPE;
     if (id_end >= (1ll << 31)) return RC_ERR_TOO_LARGE;
     const long long nvox = id_end - id_begin;
     if (nvox > 0 && (grid == nullptr || counts == nullptr)) return RC_ERR_NULL_POINTER;
-    if (n_blocks > 0 && (pool_ids == nullptr || pool_features == nullptr || runs == nullptr)) return RC_ERR_NULL_POINTER;
-    if (!rc::aligned_to(pool_ids, 16) || !rc::aligned_to(pool_features, 16) || !rc::aligned_to(grid, 16) || !rc::aligned_to(counts, 4))
-        return RC_ERR_BAD_ALIGNMENT;
+    const bool work = n_sources > 0 && blocks_per_source > 0 && nvox > 0;
+    if (work && (pool_ids == nullptr || pool_features == nullptr || runs == nullptr)) return RC_ERR_NULL_POINTER;
+    ScatterSources src{};
+    src.n = n_sources;
+    for (int i = 0; work && i < n_sources; ++i) {
+        src.ids[i] = static_cast<const int*>(pool_ids[i]);
+        src.feats[i] = static_cast<const float4*>(pool_features[i]);
+        src.runs[i] = static_cast<const unsigned int*>(runs[i]);
+        if (src.ids[i] == nullptr || src.feats[i] == nullptr || src.runs[i] == nullptr) return RC_ERR_NULL_POINTER;
+        if (!rc::aligned_to(src.ids[i], 16) || !rc::aligned_to(src.feats[i], 16) || !rc::aligned_to(src.runs[i], 4))
+            return RC_ERR_BAD_ALIGNMENT;
+    }
+    if (!rc::aligned_to(grid, 16) || !rc::aligned_to(counts, 4)) return RC_ERR_BAD_ALIGNMENT;
     rc::DeviceScope scope(device);
     if (scope.status() != RC_OK) return scope.status();
     cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -412,18 +474,19 @@ int rc_voxel_scatter_buckets(const int32_t* pool_ids, const float* pool_features
         RC_CUDA_TRY(cudaMemsetAsync(grid, 0, static_cast<size_t>(nvox) * 16, st));
         RC_CUDA_TRY(cudaMemsetAsync(counts, 0, static_cast<size_t>(nvox) * 4, st));
     }
-    if (n_blocks > 0 && nvox > 0) {
+    if (work) {
         // the kernel indexes with the global id: hand it the address voxel 0 would have
         float* grid0 = reinterpret_cast<float*>(reinterpret_cast<uintptr_t>(grid) - static_cast<uintptr_t>(id_begin) * 16u);
         int* counts0 = reinterpret_cast<int*>(reinterpret_cast<uintptr_t>(counts) - static_cast<uintptr_t>(id_begin) * 4u);
         const int blk = rc_voxel_bucket_block_records(parts_per_group);
         const int sms = rc::sm_count(device);
-        long long sb = ceil_div(n_blocks, kThreads / 32);
+        long long sb = ceil_div(blocks_per_source * n_sources, kThreads / 32);
         if (sb > 8ll * sms) sb = 8ll * sms;
-        for (int k = 0; k < parts_per_group; ++k)
-            voxel_run_scatter_kernel<<<static_cast<unsigned int>(sb), kThreads, 0, st>>>(
-                runs + static_cast<long long>(k) * n_blocks, pool_ids, reinterpret_cast<const float4*>(pool_features), n_blocks, blk,
-                grid0, counts0, nullptr, 0);
+        for (int k = 0; k < parts_per_group; ++k) {     // one launch per sub-range of the slab
+            ScatterSources row = src;
+            for (int i = 0; i < n_sources; ++i) row.runs[i] = src.runs[i] + static_cast<long long>(k) * blocks_per_source;
+            voxel_bucket_scatter_kernel<<<static_cast<unsigned int>(sb), kThreads, 0, st>>>(row, blocks_per_source, blk, grid0, counts0);
+        }
     }
     const int rc_launch = rc::check_launch();
     if (rc_launch != RC_OK) return rc_launch;

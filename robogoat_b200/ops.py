@@ -360,12 +360,12 @@ def voxel_partition_move_cuda(points: torch.Tensor, features: Optional[torch.Ten
 
 
 def voxel_bucket_exchange_cuda(points: torch.Tensor, features: torch.Tensor, grid_min: Sequence[float], voxel_size: float,
-                               grid_size: Sequence[int], n_groups: int, parts_per_group: int, source_rank: int,
-                               chunks_per_source: int, dest_ids: Sequence[int], dest_features: Sequence[int],
+                               grid_size: Sequence[int], n_groups: int, parts_per_group: int, chunks: int, first_block: int,
+                               pool_blocks: int, dest_ids: Sequence[int], dest_features: Sequence[int],
                                dest_runs: Sequence[int]) -> None:
-    """Bucket this rank's points by (owner, sub-range of the owner's slab) and store every owner's records into that
-    owner's pool (device addresses, possibly of peer GPUs' buffers), with the run table beside them.  Mean mode, four
-    feature channels; see ``rc_voxel_bucket_exchange`` in the header for the layout."""
+    """Bucket a cloud by (owner, sub-range of the owner's slab): owner d's records of chunk c go to block
+    ``first_block + c`` of pool d (device addresses, possibly of peer GPUs' buffers), with the run table beside them.
+    Mean mode, four feature channels; see ``rc_voxel_bucket_exchange`` in the header for the layout."""
     _check(int(n_groups) * int(parts_per_group) <= 16, "n_groups * parts_per_group must be at most 16")
     pts, feats = _partition_inputs(points, features)
     _check(feats is not None and feats.shape[1] == 4, "the bucket exchange takes four feature channels")
@@ -376,24 +376,31 @@ def voxel_bucket_exchange_cuda(points: torch.Tensor, features: torch.Tensor, gri
     gmin = (ctypes.c_float * 3)(*[float(v) for v in grid_min])
     gsz = (ctypes.c_int32 * 3)(*[int(v) for v in grid_size])
     rc = _lib.load().rc_voxel_bucket_exchange(pts.data_ptr(), feats.data_ptr(), pts.shape[0], gmin, float(voxel_size), gsz,
-                                              int(n_groups), int(parts_per_group), int(source_rank), int(chunks_per_source),
-                                              VP(*[int(a) for a in dest_ids]), VP(*[int(a) for a in dest_features]),
-                                              VP(*[int(a) for a in dest_runs]), dev.index, _stream_ptr(dev))
+                                              int(n_groups), int(parts_per_group), int(chunks), int(first_block),
+                                              int(pool_blocks), VP(*[int(a) for a in dest_ids]),
+                                              VP(*[int(a) for a in dest_features]), VP(*[int(a) for a in dest_runs]),
+                                              dev.index, _stream_ptr(dev))
     _lib.check(rc, "voxel_bucket_exchange")
 
 
-def voxel_scatter_buckets_cuda(pool_ids_ptr: int, pool_features_ptr: int, runs_ptr: int, n_blocks: int, parts_per_group: int,
-                               device: torch.device, id_begin: int, id_end: int, *, normalize: bool = True) -> List[torch.Tensor]:
-    """The owner's side of the bucket exchange: accumulate the received blocks into the slab [id_begin, id_end);
-    returns ``[grid fp32 [voxels, 4], counts int32 [voxels]]``."""
+def voxel_scatter_buckets_cuda(pool_ids: Sequence[int], pool_features: Sequence[int], runs: Sequence[int],
+                               blocks_per_source: int, parts_per_group: int, device: torch.device, id_begin: int,
+                               id_end: int, *, normalize: bool = True) -> List[torch.Tensor]:
+    """The owner's side of the bucket exchange: accumulate the pools of every source (device addresses of their ids,
+    feature rows and run tables; they may lie in other GPUs' memory) into the slab [id_begin, id_end); returns
+    ``[grid fp32 [voxels, 4], counts int32 [voxels]]``."""
     device = torch.device(device)
     if device.index is None:
         device = torch.device("cuda", torch.cuda.current_device())
+    n = len(pool_ids)
+    _check(len(pool_features) == n and len(runs) == n and 1 <= n <= 16, "one pool and one run table per source (at most 16)")
     nvox = int(id_end) - int(id_begin)
     _check(nvox >= 0 and id_begin >= 0, "bad voxel range")
     grid, counts = voxel_slab_buffers(nvox, 4, "mean", device)
     flags = _lib.VOXEL_ZERO_INIT | (0 if normalize else _lib.VOXEL_NO_NORMALIZE)
-    rc = _lib.load().rc_voxel_scatter_buckets(pool_ids_ptr, pool_features_ptr, runs_ptr, int(n_blocks), int(parts_per_group),
+    VP = ctypes.c_void_p * n
+    rc = _lib.load().rc_voxel_scatter_buckets(VP(*[int(a) for a in pool_ids]), VP(*[int(a) for a in pool_features]),
+                                              VP(*[int(a) for a in runs]), n, int(blocks_per_source), int(parts_per_group),
                                               grid.data_ptr() if nvox else None, counts.data_ptr() if nvox else None,
                                               int(id_begin), int(id_end), flags, device.index, _stream_ptr(device))
     _lib.check(rc, "voxel_scatter_buckets")

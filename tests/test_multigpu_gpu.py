@@ -98,20 +98,21 @@ for batches in (2, 3):
 px.close()
 # bucket form: fixed blocks in the owners' pools, no counts and no host synchronisation; three calls in a row with
 # different clouds, so that a call's stores meet pools the owners have just read
-bx = sharding.BucketExchange(points_per_rank=120_000, n_voxels=V)
 spans = [sharding.shard_bounds(pts_h.shape[0], r, ws) for r in range(ws)]
-for rep, frac in enumerate((1, 3, 1)):
-    used = [(l, l + (h - l) // frac) for l, h in spans]                 # every rank passes the first 1/frac of its shard
-    sub_h = torch.cat([pts_h[l:h] for l, h in used])
-    sub_f = torch.cat([feats_h[l:h] for l, h in used])
-    m2, c2, s2 = oracle.voxelize_pointcloud(sub_h, sub_f, mode="mean", return_aux=True, **kw)
-    t2 = oracle.mean_tolerance(c2, s2, m2).reshape(V, 4)
-    l, h = used[rank]
-    slab, cnts = sharding.voxelize_sharded_buckets(pts[l:h], feats[l:h], bx, return_counts=True, **kw)
-    a, b = sharding.slab_bounds(V, rank, ws)
-    assert torch.equal(cnts.cpu(), c2.reshape(V)[a:b]), f"bucket counts {rep}"
-    assert bool(((slab.cpu() - m2.reshape(V, 4)[a:b]).abs() <= t2[a:b]).all()), f"bucket mean {rep}"
-bx.close()
+for fetch in (True, False):                 # owners fetch the records over NVLink / sources store them over NVLink
+    bx = sharding.BucketExchange(points_per_rank=120_000, n_voxels=V, fetch=fetch)
+    for rep, frac in enumerate((1, 3, 1)):
+        used = [(l, l + (h - l) // frac) for l, h in spans]                 # every rank passes the first 1/frac of its shard
+        sub_h = torch.cat([pts_h[l:h] for l, h in used])
+        sub_f = torch.cat([feats_h[l:h] for l, h in used])
+        m2, c2, s2 = oracle.voxelize_pointcloud(sub_h, sub_f, mode="mean", return_aux=True, **kw)
+        t2 = oracle.mean_tolerance(c2, s2, m2).reshape(V, 4)
+        l, h = used[rank]
+        slab, cnts = sharding.voxelize_sharded_buckets(pts[l:h], feats[l:h], bx, return_counts=True, **kw)
+        a, b = sharding.slab_bounds(V, rank, ws)
+        assert torch.equal(cnts.cpu(), c2.reshape(V)[a:b]), f"bucket counts {rep} fetch={fetch}"
+        assert bool(((slab.cpu() - m2.reshape(V, 4)[a:b]).abs() <= t2[a:b]).all()), f"bucket mean {rep} fetch={fetch}"
+    bx.close()
 small = sharding.PointExchange(capacity=10, feature_width=4)
 slab = sharding.voxelize_sharded_exchange(pts[lo:hi], None, mode="count", direct=small, **kw)
 a, b = sharding.slab_bounds(V, rank, ws)

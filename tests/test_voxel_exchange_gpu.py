@@ -215,14 +215,15 @@ def test_line_aligned_and_plain_stores_write_the_same_bytes(groups, per_group, N
     assert torch.equal(outs[0][1].cpu(), feats[keep][order])
 
 
+@pytest.mark.parametrize("layout", ["owner-pools", "source-pools"])
 @pytest.mark.parametrize("R,K", [(1, 1), (2, 8), (3, 2), (4, 4), (8, 2), (16, 1)])
 @pytest.mark.parametrize("N", [0, 1, 2500, 40_001])
-def test_bucket_exchange_with_every_owner_on_one_gpu(R, K, N, cuda_lib):
-    """The bucket form of the exchange, all owners' pools in this GPU's memory: every source rank buckets its shard
-    into the owners' pools (fixed block per chunk, no counts), every owner accumulates its pool, and each slab must
-    equal the oracle's grid of the whole cloud.  The pools start out full of garbage: whatever a source does not write
-    must not be read.  The shards are uneven and one more chunk than needed is reserved per source (empty blocks)."""
-    import ctypes
+def test_bucket_exchange_with_every_rank_on_one_gpu(R, K, N, layout, cuda_lib):
+    """The bucket form of the exchange with all ranks' pools in this GPU's memory, in both layouts: "owner-pools" (every
+    source stores into the owners' pools, block source * chunks + chunk; an owner reads its one pool) and "source-pools"
+    (every source fills a region per owner of its own pool; an owner reads its region of every source's pool).  Each
+    slab must equal the oracle's grid of the whole cloud.  The pools start out full of garbage: whatever a source does
+    not write must not be read.  The shards are uneven and one more chunk than needed is reserved per source."""
     kw = dict(grid_min=[-2.0, -2.0, -2.0], voxel_size=0.25, grid_size=[16, 15, 13])       # 3120 voxels: not a multiple of 16
     V = 16 * 15 * 13
     pts, feats = _cloud(N, 500 + R * K + N)
@@ -231,14 +232,22 @@ def test_bucket_exchange_with_every_owner_on_one_gpu(R, K, N, cuda_lib):
     blk = int(cuda_lib.rc_voxel_bucket_block_records(K))
     assert blk % 32 == 0 and blk >= 1024 + 8 * K
     nblocks = R * chunks
+    # R pools of R * chunks blocks: pool d belongs to owner d ("owner-pools") or to source d ("source-pools")
     pools = [dict(ids=torch.full((nblocks * blk,), 123456789, dtype=torch.int32, device=DEV),
                   feats=torch.full((nblocks * blk, 4), float("nan"), device=DEV),
                   runs=torch.full((K * nblocks,), 0x7fff7fff, dtype=torch.int32, device=DEV)) for _ in range(R)]
+    rec = chunks * blk
     for s in range(R):
         a, b = cuts[s], cuts[s + 1]
+        if layout == "owner-pools":
+            dest = ([p["ids"].data_ptr() for p in pools], [p["feats"].data_ptr() for p in pools],
+                    [p["runs"].data_ptr() for p in pools], s * chunks, nblocks)
+        else:
+            me = pools[s]
+            dest = ([me["ids"].data_ptr() + d * rec * 4 for d in range(R)], [me["feats"].data_ptr() + d * rec * 16 for d in range(R)],
+                    [me["runs"].data_ptr() + d * K * chunks * 4 for d in range(R)], 0, chunks)
         ops.voxel_bucket_exchange_cuda(pts[a:b].to(DEV), feats[a:b].to(DEV), kw["grid_min"], kw["voxel_size"], kw["grid_size"],
-                                       R, K, s, chunks, [p["ids"].data_ptr() for p in pools], [p["feats"].data_ptr() for p in pools],
-                                       [p["runs"].data_ptr() for p in pools])
+                                       R, K, chunks, dest[3], dest[4], dest[0], dest[1], dest[2])
     if N:
         exp, ecnt, sabs = oracle.voxelize_pointcloud(pts, feats, mode="mean", return_aux=True, **kw)
         tol = oracle.mean_tolerance(ecnt, sabs, exp).reshape(V, 4)
@@ -248,8 +257,12 @@ def test_bucket_exchange_with_every_owner_on_one_gpu(R, K, N, cuda_lib):
     total = 0
     for d in range(R):
         lo, hi = sharding.slab_bounds(V, d, R)
-        grid, counts = ops.voxel_scatter_buckets_cuda(pools[d]["ids"].data_ptr(), pools[d]["feats"].data_ptr(),
-                                                      pools[d]["runs"].data_ptr(), nblocks, K, DEV, lo, hi)
+        if layout == "owner-pools":
+            src = ([pools[d]["ids"].data_ptr()], [pools[d]["feats"].data_ptr()], [pools[d]["runs"].data_ptr()], nblocks)
+        else:
+            src = ([p["ids"].data_ptr() + d * rec * 4 for p in pools], [p["feats"].data_ptr() + d * rec * 16 for p in pools],
+                   [p["runs"].data_ptr() + d * K * chunks * 4 for p in pools], chunks)
+        grid, counts = ops.voxel_scatter_buckets_cuda(src[0], src[1], src[2], src[3], K, DEV, lo, hi)
         assert torch.equal(counts.cpu(), ecnt[lo:hi]), (d, R, K)
         assert bool(((grid.cpu() - exp[lo:hi]).abs() <= tol[lo:hi]).all()), (d, R, K)
         total += int(counts.sum())
