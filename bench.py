@@ -1011,6 +1011,10 @@ def multi_gpu_extras(L, dev, rank, world, ex, pts, feats, kw, N, single_ms):
         ev[3].record(); torch.cuda.synchronize()
         stages = [max_over_ranks(ev[i].elapsed_time(ev[i + 1]), world, dev) for i in range(3)]
         del r
+        L.rc_set_option(5, 0)                   # the bucket kernel's write-out by ordinary stores instead of bulk copies
+        ms_plain = timed(lambda: sharding.voxelize_sharded_buckets(pts, feats, ex_, **kw))
+        L.rc_set_option(5, 1)
+        ex[f"voxel_mean_sharded_{key}"]["ms_with_ordinary_stores"] = ms_plain
         remote_bytes = N * 20 * (world - 1) / world
         link_stage = stages[2] if ex_.fetch else stages[0]
         ex[f"voxel_mean_sharded_{key}"].update({

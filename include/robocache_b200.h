@@ -351,9 +351,14 @@ RC_API int rc_voxelize_mean_static(const float* points, const float* features, f
  * fallback as the staged kernel) where every row is a whole number of 16-byte pieces at a 16-byte aligned
  * address; 0: ordinary loads by all threads.  Same bits either way; 205.0 against 206.1 us on the bf16
  * B=4096 S=500 D=256 T=250 case.
+ * RC_OPT_BUCKET_BULK_STORE (default 1): the bucket kernel (mean mode's run path in rc_voxelize_ex, and
+ * rc_voxel_bucket_exchange) sends every sorted chunk - every owner's segment of it - from shared memory with bulk
+ * asynchronous copies (TMA stores issued by one thread per destination) instead of ordinary stores by all threads.
+ * Same bytes either way; 2.17 against 2.21 ms on the 2^26-point mean case.
  * No counterpart in the reference.
  */
 #define RC_OPT_BLOCK_KERNEL 0
+#define RC_OPT_BUCKET_BULK_STORE 5
 #define RC_OPT_GATHER_BULK_STAGE 4
 #define RC_OPT_BULK_WAIT_LIMIT 3
 #define RC_OPT_VOXEL_PASSES 1

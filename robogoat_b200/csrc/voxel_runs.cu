@@ -58,9 +58,22 @@ struct ExchangeDest {
     unsigned int* runs[kMeanRunsMaxParts];      // [per_group][nblocks] each
     long long block0, nblocks;
     int groups, per_group;
+    int bulk_store;                             // 1: segments leave shared memory by bulk asynchronous copies (TMA)
     unsigned int owner_span;                    // voxel ids per owner; RunRule::slab is the span of a slab inside it
     float inv_owner_span;
 };
+
+// Bulk asynchronous copy shared memory -> global memory (TMA store, no multicast), tracked by the issuing thread's
+// bulk async-group.  A store to a peer GPU issued this way does not hold up the SM's load/store pipeline while NVLink
+// is busy, which ordinary stores do - and with them every other CTA of the SM.
+__device__ __forceinline__ void bulk_store(void* dst_gmem, const void* src_smem, unsigned int bytes) {
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+                 :: "l"(dst_gmem), "r"(static_cast<unsigned int>(__cvta_generic_to_shared(src_smem))), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// until the copies of this thread's groups have read their shared-memory sources (the data may still be on its way)
+__device__ __forceinline__ void bulk_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_shared() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 // Single-GPU form: runs[p * nchunks + c] = (first slot of slab p's run in chunk c's block) << 16 | records in the run.
 // Exchange form: the owner's table, runs[sub * nblocks + block0 + c] = (first slot inside the block) << 16 | records.
@@ -145,6 +158,7 @@ voxel_bucket_kernel(const float* __restrict__ pts, const float4* __restrict__ fe
             if (part[i] >= 0 && below == 0u) wcnt[part[i]] += __popc(same);
             __syncwarp();
         }
+        if (dest.bulk_store && threadIdx.x < (EXCH ? dest.groups : 1)) bulk_store_wait_read();   // the previous chunk has left shared memory
         __syncthreads();   // all counts are in; the previous chunk's block has left shared memory
         // every warp derives the layout of the sorted chunk by itself: lane p owns slab p
         int tot = 0, mine = 0;
@@ -190,9 +204,21 @@ voxel_bucket_kernel(const float* __restrict__ pts, const float4* __restrict__ fe
             for (int j = start + tot; j < start + padded; ++j) s_sid[j] = -1;
             runs[static_cast<long long>(lane) * nchunks + chunk] = (static_cast<unsigned int>(start) << 16) | static_cast<unsigned int>(tot);
         }
+        if (dest.bulk_store) fence_async_shared();   // this thread's shared-memory writes, for the copy engine
         __syncthreads();
         if (lane < kMeanRunsMaxParts) wcnt[lane] = 0;     // own row, for the next chunk; every warp has read it
-        if (EXCH) {
+        if (EXCH && dest.bulk_store) {
+            if (threadIdx.x < dest.groups) {                  // one thread per owner sends that owner's segment
+                const int own = threadIdx.x;
+                const int s0 = s_seg[own][0], len = s_seg[own][1];     // multiples of 8 records
+                const long long o = (dest.block0 + chunk) * rule.blk;
+                if (len > 0) {
+                    bulk_store(dest.ids[own] + o, s_sid + s0, static_cast<unsigned int>(len) * 4u);
+                    bulk_store(dest.feats[own] + o, s_sf + s0, static_cast<unsigned int>(len) * 16u);
+                }
+                bulk_store_commit();
+            }
+        } else if (EXCH) {
             for (int own = 0; own < dest.groups; ++own) {
                 const int s0 = s_seg[own][0], len = s_seg[own][1];     // multiples of 8 records
                 const long long o = (dest.block0 + chunk) * rule.blk;
@@ -201,6 +227,15 @@ voxel_bucket_kernel(const float* __restrict__ pts, const float4* __restrict__ fe
                 for (int j = threadIdx.x; j < (len >> 2); j += kThreads) dst_i[j] = src_i[j];
                 float4* dst_f = dest.feats[own] + o;
                 for (int j = threadIdx.x; j < len; j += kThreads) dst_f[j] = s_sf[s0 + j];
+            }
+        } else if (dest.bulk_store) {
+            if (threadIdx.x == 0) {
+                const long long o = chunk * rule.blk;
+                if (total > 0) {
+                    bulk_store(pool_ids + o, s_sid, static_cast<unsigned int>(total) * 4u);
+                    bulk_store(pool_feats + o, s_sf, static_cast<unsigned int>(total) * 16u);
+                }
+                bulk_store_commit();
             }
         } else {
             const long long o = chunk * rule.blk;
@@ -211,6 +246,7 @@ voxel_bucket_kernel(const float* __restrict__ pts, const float4* __restrict__ fe
             for (int j = threadIdx.x; j < total; j += kThreads) __stcs(dst_f + j, s_sf[j]);
         }
     }
+    if (dest.bulk_store && threadIdx.x < (EXCH ? dest.groups : 1)) bulk_store_wait_read();   // shared memory must outlive the copies' reads
 }
 
 // One slab's runs into the grid (robocache/csrc/cuda/voxelize_kernel.cu:100-143 is the reference's scatter).  A warp
@@ -357,7 +393,8 @@ int mean_runs_launch(const float* points, const float* features, float* grid, in
     rule.blk = l.blk;
     const int sms = rc::sm_count(device);
     const long long nb = l.nchunks < 8ll * sms ? l.nchunks : 8ll * sms;
-    const ExchangeDest none{};
+    ExchangeDest none{};
+    none.bulk_store = rc::g_bucket_bulk_store.load(std::memory_order_relaxed) ? 1 : 0;
     voxel_bucket_kernel<false><<<static_cast<unsigned int>(nb), kThreads, 0, st>>>(
         points, reinterpret_cast<const float4*>(features), N, g, rc::aligned_to(points, 16), rule, l.nchunks, runs, pool_ids,
         pool_feats, none, gate, gate_want);
@@ -430,6 +467,7 @@ int rc_voxel_bucket_exchange(const float* points, const float* features, int64_t
     dest.inv_owner_span = 1.0f / static_cast<float>(owner_span);
     dest.block0 = first_block;
     dest.nblocks = pool_blocks;
+    dest.bulk_store = rc::g_bucket_bulk_store.load(std::memory_order_relaxed) ? 1 : 0;
     RunRule rule;
     rule.P = n_groups * parts_per_group;
     rule.slab = static_cast<unsigned int>(ceil_div(owner_span, parts_per_group));

@@ -215,10 +215,19 @@ def test_line_aligned_and_plain_stores_write_the_same_bytes(groups, per_group, N
     assert torch.equal(outs[0][1].cpu(), feats[keep][order])
 
 
+@pytest.fixture(params=["bulk-stores", "plain-stores"])
+def bucket_store_choice(request, cuda_lib):
+    """The bucket kernel's write-out by bulk asynchronous copies (the default) and by ordinary stores: same bytes."""
+    from robogoat_b200 import _lib
+    cuda_lib.rc_set_option(_lib.OPT_BUCKET_BULK_STORE, 1 if request.param == "bulk-stores" else 0)
+    yield request.param
+    cuda_lib.rc_set_option(_lib.OPT_BUCKET_BULK_STORE, 1)
+
+
 @pytest.mark.parametrize("layout", ["owner-pools", "source-pools"])
 @pytest.mark.parametrize("R,K", [(1, 1), (2, 8), (3, 2), (4, 4), (8, 2), (16, 1)])
 @pytest.mark.parametrize("N", [0, 1, 2500, 40_001])
-def test_bucket_exchange_with_every_rank_on_one_gpu(R, K, N, layout, cuda_lib):
+def test_bucket_exchange_with_every_rank_on_one_gpu(R, K, N, layout, bucket_store_choice, cuda_lib):
     """The bucket form of the exchange with all ranks' pools in this GPU's memory, in both layouts: "owner-pools" (every
     source stores into the owners' pools, block source * chunks + chunk; an owner reads its one pool) and "source-pools"
     (every source fills a region per owner of its own pool; an owner reads its region of every source's pool).  Each
