@@ -38,6 +38,7 @@ OPT_PART_ALIGNED_STORE = 2
 OPT_BULK_WAIT_LIMIT = 3
 OPT_GATHER_BULK_STAGE = 4
 OPT_BUCKET_BULK_STORE = 5
+OPT_SCATTER_OVERLAP = 6
 
 # every symbol the header declares; the CPU test-suite checks the built library exports them all
 EXPORTED_SYMBOLS = (

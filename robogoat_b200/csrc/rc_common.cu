@@ -15,6 +15,7 @@ std::atomic<int> g_part_aligned_store{1};
 std::atomic<int> g_bulk_wait_limit{-1};
 std::atomic<int> g_gather_bulk_stage{1};
 std::atomic<int> g_bucket_bulk_store{1};
+std::atomic<int> g_scatter_overlap{1};
 
 // SM count per device, filled on first use (immutable hardware facts, not call state).
 static std::atomic<int> g_sm_count[64];
@@ -89,6 +90,10 @@ int rc_set_option(int option, int value) {
     }
     if (option == RC_OPT_BUCKET_BULK_STORE) {
         rc::g_bucket_bulk_store.store(value != 0, std::memory_order_relaxed);
+        return RC_OK;
+    }
+    if (option == RC_OPT_SCATTER_OVERLAP) {
+        rc::g_scatter_overlap.store(value != 0, std::memory_order_relaxed);
         return RC_OK;
     }
     if (option == RC_OPT_BULK_WAIT_LIMIT) {

@@ -80,6 +80,7 @@ extern std::atomic<int> g_voxel_passes;        // RC_OPT_VOXEL_PASSES
 extern std::atomic<int> g_part_aligned_store;     // RC_OPT_PART_ALIGNED_STORE
 extern std::atomic<int> g_gather_bulk_stage;      // RC_OPT_GATHER_BULK_STAGE
 extern std::atomic<int> g_bucket_bulk_store;      // RC_OPT_BUCKET_BULK_STORE
+extern std::atomic<int> g_scatter_overlap;        // RC_OPT_SCATTER_OVERLAP
 extern std::atomic<int> g_bulk_wait_limit;        // RC_OPT_BULK_WAIT_LIMIT (-1 = built-in limit)
 
 }  // namespace rc

@@ -156,7 +156,7 @@ __device__ __forceinline__ void scatter_one(int id, long long pi, const float* _
 // 256-byte aligned; grid and features 16-byte aligned; V < 2^31; N <= 2^31 - 4096.  The grid and the counters
 // must be clear; the grid holds feature sums afterwards.
 constexpr int kMeanRunsMaxParts = 16;
-constexpr int kMeanRunsParts = 12;
+constexpr int kMeanRunsParts = 16;
 uint64_t mean_runs_scratch_bytes(long long N, long long V, int parts);
 int mean_runs_launch(const float* points, const float* features, float* grid, int* counts, long long N,
                      const VoxelGeom& g, long long V, int parts, void* scratch, const int* gate, int gate_want,

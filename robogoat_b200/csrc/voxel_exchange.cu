@@ -498,6 +498,9 @@ __global__ void __launch_bounds__(kThreads)
 voxel_scatter_runs_kernel(const int* __restrict__ ids, const float* __restrict__ feats, void* __restrict__ grid_v,
                           int* __restrict__ counts, int F, bool vec4, const __grid_constant__ RunTable rt, int id_lo,
                           unsigned int span) {
+    // the next pass depends on this one's order (L2 locality) only, not on its results: launched as a programmatic
+    // dependent it may fill the SMs this pass's last CTAs leave idle
+    grid_dependency_release();
     const long long total = rt.first_block[rt.n];
     for (long long b = blockIdx.x; b < total; b += gridDim.x) {
         int r = 0;
@@ -527,8 +530,22 @@ voxel_scatter_runs_kernel(const int* __restrict__ ids, const float* __restrict__
 }
 
 template <int MODE>
-void launch_scatter_runs(unsigned int nb, cudaStream_t st, const int* ids, const float* feats, void* grid0, int* counts0,
-                         int F, bool vec4, const RunTable& rt, int id_lo, unsigned int span) {
+void launch_scatter_runs(bool overlap_prev, unsigned int nb, cudaStream_t st, const int* ids, const float* feats, void* grid0,
+                         int* counts0, int F, bool vec4, const RunTable& rt, int id_lo, unsigned int span) {
+    if (overlap_prev && rc::g_scatter_overlap.load(std::memory_order_relaxed)) {
+        cudaLaunchConfig_t cfg{};
+        cfg.gridDim = dim3(nb);
+        cfg.blockDim = dim3(kThreads);
+        cfg.stream = st;
+        cudaLaunchAttribute attr{};
+        attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr.val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = &attr;
+        cfg.numAttrs = 1;
+        if (cudaLaunchKernelEx(&cfg, voxel_scatter_runs_kernel<MODE>, ids, feats, grid0, counts0, F, vec4, rt, id_lo, span) == cudaSuccess)
+            return;
+        cudaGetLastError();  // attribute refused: an ordinary launch
+    }
     voxel_scatter_runs_kernel<MODE><<<nb, kThreads, 0, st>>>(ids, feats, grid0, counts0, F, vec4, rt, id_lo, span);
 }
 
@@ -688,18 +705,20 @@ int rc_voxel_scatter_runs(const int32_t* ids, const float* features, void* grid,
                             : nullptr;
         const bool vec4 = mean && F == 4;
         const long long cap = 16ll * rc::sm_count(device);
+        int launches = 0;       // the first launch waits for whatever precedes it on the stream (the clear); later ones may overlap
         for (int ps = 0; ps < n_passes; ++ps) {
             RunTable rt{};
             auto flush = [&]() {
                 if (rt.n == 0) return;
+                const bool ov = launches++ > 0;
                 long long nb = rt.first_block[rt.n];
                 if (nb > cap) nb = cap;
                 const unsigned int blocks = static_cast<unsigned int>(nb);
                 const int lo = static_cast<int>(id_begin);
                 const unsigned int span = static_cast<unsigned int>(nvox);
-                if (mode == RC_VOXEL_MEAN) launch_scatter_runs<kMean>(blocks, st, ids, features, grid0, counts0, F, vec4, rt, lo, span);
-                else if (mode == RC_VOXEL_COUNT) launch_scatter_runs<kCount>(blocks, st, ids, features, grid0, counts0, F, false, rt, lo, span);
-                else launch_scatter_runs<kOccupancy>(blocks, st, ids, features, grid0, counts0, F, false, rt, lo, span);
+                if (mode == RC_VOXEL_MEAN) launch_scatter_runs<kMean>(ov, blocks, st, ids, features, grid0, counts0, F, vec4, rt, lo, span);
+                else if (mode == RC_VOXEL_COUNT) launch_scatter_runs<kCount>(ov, blocks, st, ids, features, grid0, counts0, F, false, rt, lo, span);
+                else launch_scatter_runs<kOccupancy>(ov, blocks, st, ids, features, grid0, counts0, F, false, rt, lo, span);
                 rt = RunTable{};
             };
             for (int r = 0; r < n_runs; ++r) {

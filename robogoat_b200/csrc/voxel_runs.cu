@@ -258,6 +258,9 @@ __global__ void __launch_bounds__(kThreads)
 voxel_run_scatter_kernel(const unsigned int* __restrict__ runs_p, const int* __restrict__ pool_ids,
                          const float4* __restrict__ pool_feats, long long nchunks, int blk, float* __restrict__ grid,
                          int* __restrict__ counts, const int* __restrict__ gate, int gate_want) {
+    // The next slab's launch does not depend on this one's results, only on the order: launched as a programmatic
+    // dependent it may fill the SMs that this launch's last CTAs leave idle.
+    grid_dependency_release();
     if (gate != nullptr && *gate != gate_want) return;
     const int lane = threadIdx.x & 31;
     const long long warps_total = static_cast<long long>(gridDim.x) * (kThreads / 32);
@@ -307,6 +310,7 @@ struct ScatterSources {
 __global__ void __launch_bounds__(kThreads)
 voxel_bucket_scatter_kernel(const __grid_constant__ ScatterSources src, long long blocks, int blk, float* __restrict__ grid,
                             int* __restrict__ counts) {
+    grid_dependency_release();      // the next sub-range's launch depends on this one's order only (see voxel_run_scatter_kernel)
     const int lane = threadIdx.x & 31;
     const long long warps_total = static_cast<long long>(gridDim.x) * (kThreads / 32);
     const long long steps = blocks * src.n;
@@ -400,9 +404,29 @@ int mean_runs_launch(const float* points, const float* features, float* grid, in
         pool_feats, none, gate, gate_want);
     long long sb = ceil_div(l.nchunks, kThreads / 32);
     if (sb > 8ll * sms) sb = 8ll * sms;
-    for (int p = 0; p < l.P; ++p)
-        voxel_run_scatter_kernel<<<static_cast<unsigned int>(sb), kThreads, 0, st>>>(
-            runs + static_cast<long long>(p) * l.nchunks, pool_ids, pool_feats, l.nchunks, l.blk, grid, counts, gate, gate_want);
+    for (int p = 0; p < l.P; ++p) {
+        const unsigned int* runs_p = runs + static_cast<long long>(p) * l.nchunks;
+        const int* ids_c = pool_ids;
+        const float4* feats_c = pool_feats;
+        bool launched = false;
+        if (p > 0 && rc::g_scatter_overlap.load(std::memory_order_relaxed)) {   // slab p may start while slab p - 1 drains
+            cudaLaunchConfig_t cfg{};
+            cfg.gridDim = dim3(static_cast<unsigned int>(sb));
+            cfg.blockDim = dim3(kThreads);
+            cfg.stream = st;
+            cudaLaunchAttribute attr{};
+            attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            attr.val.programmaticStreamSerializationAllowed = 1;
+            cfg.attrs = &attr;
+            cfg.numAttrs = 1;
+            launched = cudaLaunchKernelEx(&cfg, voxel_run_scatter_kernel, runs_p, ids_c, feats_c, l.nchunks, l.blk, grid, counts, gate,
+                                          gate_want) == cudaSuccess;
+            if (!launched) cudaGetLastError();  // attribute refused: an ordinary launch below
+        }
+        if (!launched)
+            voxel_run_scatter_kernel<<<static_cast<unsigned int>(sb), kThreads, 0, st>>>(runs_p, ids_c, feats_c, l.nchunks, l.blk, grid,
+                                                                                       counts, gate, gate_want);
+    }
     return rc::check_launch();
 }
 
@@ -523,7 +547,22 @@ int rc_voxel_scatter_buckets(const void* const* pool_ids, const void* const* poo
         for (int k = 0; k < parts_per_group; ++k) {     // one launch per sub-range of the slab
             ScatterSources row = src;
             for (int i = 0; i < n_sources; ++i) row.runs[i] = src.runs[i] + static_cast<long long>(k) * blocks_per_source;
-            voxel_bucket_scatter_kernel<<<static_cast<unsigned int>(sb), kThreads, 0, st>>>(row, blocks_per_source, blk, grid0, counts0);
+            bool launched = false;
+            if (k > 0 && rc::g_scatter_overlap.load(std::memory_order_relaxed)) {
+                cudaLaunchConfig_t cfg{};
+                cfg.gridDim = dim3(static_cast<unsigned int>(sb));
+                cfg.blockDim = dim3(kThreads);
+                cfg.stream = st;
+                cudaLaunchAttribute attr{};
+                attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+                attr.val.programmaticStreamSerializationAllowed = 1;
+                cfg.attrs = &attr;
+                cfg.numAttrs = 1;
+                launched = cudaLaunchKernelEx(&cfg, voxel_bucket_scatter_kernel, row, blocks_per_source, blk, grid0, counts0) == cudaSuccess;
+                if (!launched) cudaGetLastError();
+            }
+            if (!launched)
+                voxel_bucket_scatter_kernel<<<static_cast<unsigned int>(sb), kThreads, 0, st>>>(row, blocks_per_source, blk, grid0, counts0);
         }
     }
     const int rc_launch = rc::check_launch();
