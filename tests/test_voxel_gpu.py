@@ -220,6 +220,32 @@ def test_automatic_strategy_equals_single_pass(cluster_sorted, cuda_lib):
         cuda_lib.rc_set_option(1, 0)
 
 
+@pytest.mark.parametrize("overlap,bulk", [(1, 1), (0, 1), (1, 0), (0, 0)])
+@pytest.mark.parametrize("passes", [3, 16])
+def test_run_path_switches_change_no_result(overlap, bulk, passes, cuda_lib):
+    """Mean mode by slab-ordered runs with its launch and store forms switched: per-slab launches overlapped as
+    programmatic dependents or ordinary, sorted chunks written by bulk asynchronous copies or by ordinary stores.
+    Counts must equal the oracle's, means must lie within its tolerance, in every combination."""
+    from robogoat_b200 import _lib
+    N = 300_007
+    pts, feats = workloads.voxel_mixture_inputs(N, seed=9)
+    pts = pts * 0.25
+    kw = dict(grid_min=[-6.4, -6.4, -6.4], voxel_size=0.1, grid_size=[128, 128, 128])
+    exp, ecnt, sabs = oracle.voxelize_pointcloud(pts, feats, mode="mean", return_aux=True, **kw)
+    cuda_lib.rc_set_option(_lib.OPT_VOXEL_PASSES, passes)
+    cuda_lib.rc_set_option(_lib.OPT_SCATTER_OVERLAP, overlap)
+    cuda_lib.rc_set_option(_lib.OPT_BUCKET_BULK_STORE, bulk)
+    try:
+        for _ in range(2):
+            grid, counts = ops.voxelize_pointcloud_cuda(pts.to(DEV), feats.to(DEV), kw["grid_min"], kw["voxel_size"], kw["grid_size"], "mean")
+            assert torch.equal(counts.cpu(), ecnt)
+            assert bool(((grid.cpu() - exp).abs() <= oracle.mean_tolerance(ecnt, sabs, exp)).all())
+    finally:
+        cuda_lib.rc_set_option(_lib.OPT_VOXEL_PASSES, 0)
+        cuda_lib.rc_set_option(_lib.OPT_SCATTER_OVERLAP, 1)
+        cuda_lib.rc_set_option(_lib.OPT_BUCKET_BULK_STORE, 1)
+
+
 def test_batched_float_grids_match_reference_header(cuda_lib):
     """[B,N,3] -> [B,D,H,W] float occupancy / density against the reference's own C++ header, item by item
     (skipped where that header was not compiled); also against the oracle, which is always available."""
