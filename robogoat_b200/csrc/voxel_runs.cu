@@ -28,6 +28,7 @@ namespace {
 constexpr int kRunPad = 8;                                  // records: 32 bytes of ids, 128 bytes of feature rows
 constexpr int kRunChunk = kPointsPerBlock;                  // 1024 points per CTA step
 constexpr int kRunBlockMax = kRunChunk + kRunPad * kMeanRunsMaxParts;
+constexpr int kBucketStageBytes = kRunBlockMax * 20;        // one sorted chunk: feature rows, then ids
 constexpr int kRunLoads = 8;                                // records per lane and step of the scatter: 256 per warp
 
 struct RunRule {
@@ -73,6 +74,8 @@ __device__ __forceinline__ void bulk_store(void* dst_gmem, const void* src_smem,
 __device__ __forceinline__ void bulk_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // until the copies of this thread's groups have read their shared-memory sources (the data may still be on its way)
 __device__ __forceinline__ void bulk_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// the same, but the most recently committed group may still be reading
+__device__ __forceinline__ void bulk_store_wait_read_all_but_one() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
 __device__ __forceinline__ void fence_async_shared() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 // Single-GPU form: runs[p * nchunks + c] = (first slot of slab p's run in chunk c's block) << 16 | records in the run.
@@ -84,8 +87,11 @@ voxel_bucket_kernel(const float* __restrict__ pts, const float4* __restrict__ fe
                     int* __restrict__ pool_ids, float4* __restrict__ pool_feats, const __grid_constant__ ExchangeDest dest,
                     const int* __restrict__ gate, int gate_want) {
     __shared__ __align__(16) float s_xyz[kThreads / 32][kPointsPerWarp * 3];
-    __shared__ __align__(16) int s_sid[kRunBlockMax];
-    __shared__ __align__(16) float4 s_sf[kRunBlockMax];
+    // the sorted chunk; two of them in the exchange form, so that a CTA can sort its next chunk while the copy engine
+    // is still sending the last one over NVLink
+    // (dynamic shared memory: kBucketStageBytes per stage, feature rows first)
+    extern __shared__ __align__(16) unsigned char s_stage[];
+    int stage = 0;
     __shared__ int s_wcnt[kThreads / 32][kMeanRunsMaxParts];
     __shared__ int s_seg[EXCH ? kMeanRunsMaxParts : 1][2];     // first slot and length of every owner's segment
     if (gate != nullptr && *gate != gate_want) return;
@@ -104,6 +110,9 @@ voxel_bucket_kernel(const float* __restrict__ pts, const float4* __restrict__ fe
         if (pts_aligned && blockIdx.x < nchunks && base + kPointsPerWarp <= N) tile_issue(pts, base, lane, ahead);
     }
     for (long long chunk = blockIdx.x; chunk < nchunks; chunk += step) {
+        float4* const s_sf = reinterpret_cast<float4*>(s_stage + stage * kBucketStageBytes);
+        int* const s_sid = reinterpret_cast<int*>(s_stage + stage * kBucketStageBytes + kRunBlockMax * 16);
+        if (EXCH) stage ^= 1;
         const long long base = chunk * kRunChunk + warp * kPointsPerWarp;
         const bool full = base + kPointsPerWarp <= N;
         float4 f[kPointsPerLane];
@@ -158,7 +167,11 @@ voxel_bucket_kernel(const float* __restrict__ pts, const float4* __restrict__ fe
             if (part[i] >= 0 && below == 0u) wcnt[part[i]] += __popc(same);
             __syncwarp();
         }
-        if (dest.bulk_store && threadIdx.x < (EXCH ? dest.groups : 1)) bulk_store_wait_read();   // the previous chunk has left shared memory
+        // the chunk that last used this stage has left shared memory
+        if (dest.bulk_store && threadIdx.x < (EXCH ? dest.groups : 1)) {
+            if (EXCH) bulk_store_wait_read_all_but_one();
+            else bulk_store_wait_read();
+        }
         __syncthreads();   // all counts are in; the previous chunk's block has left shared memory
         // every warp derives the layout of the sorted chunk by itself: lane p owns slab p
         int tot = 0, mine = 0;
@@ -399,7 +412,7 @@ int mean_runs_launch(const float* points, const float* features, float* grid, in
     const long long nb = l.nchunks < 8ll * sms ? l.nchunks : 8ll * sms;
     ExchangeDest none{};
     none.bulk_store = rc::g_bucket_bulk_store.load(std::memory_order_relaxed) ? 1 : 0;
-    voxel_bucket_kernel<false><<<static_cast<unsigned int>(nb), kThreads, 0, st>>>(
+    voxel_bucket_kernel<false><<<static_cast<unsigned int>(nb), kThreads, kBucketStageBytes, st>>>(
         points, reinterpret_cast<const float4*>(features), N, g, rc::aligned_to(points, 16), rule, l.nchunks, runs, pool_ids,
         pool_feats, none, gate, gate_want);
     long long sb = ceil_div(l.nchunks, kThreads / 32);
@@ -501,7 +514,9 @@ int rc_voxel_bucket_exchange(const float* points, const float* features, int64_t
     if (scope.status() != RC_OK) return scope.status();
     const int sms = rc::sm_count(device);
     const long long nb = chunks < 8ll * sms ? chunks : 8ll * sms;
-    voxel_bucket_kernel<true><<<static_cast<unsigned int>(nb), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+    const int rc_smem = rc::ensure_dynamic_smem(reinterpret_cast<const void*>(voxel_bucket_kernel<true>), device, 2 * kBucketStageBytes);
+    if (rc_smem != RC_OK) return rc_smem;
+    voxel_bucket_kernel<true><<<static_cast<unsigned int>(nb), kThreads, 2 * kBucketStageBytes, static_cast<cudaStream_t>(stream)>>>(
         points, reinterpret_cast<const float4*>(features), N, g, rc::aligned_to(points, 16), rule, chunks, nullptr,
         nullptr, nullptr, dest, nullptr, 0);
     return rc::check_launch();
