@@ -798,6 +798,29 @@ def run_extras(L, dev, local, rank, world, peak, ex):
     ms = max_over_ranks(e0.elapsed_time(e1) / 10, world, dev)
     ex["voxel_mean_64M_512_cluster_sorted"] = {"ms": ms, "Gpts/s_per_gpu": N / (ms * 1e-3) / 1e9,
                                                "timing": "same cloud emitted cluster after cluster (spatially coherent order)"}
+    del pts, feats
+    if world == 1:
+        # the older batched surface: 8 clouds of 500 k points -> float density [8,128,128,128] in one launch, and a
+        # truncated signed distance grid from 4 x 65536 surface points (unit sphere, normals outwards)
+        from robogoat_b200 import batched
+        okw = workloads.VOXEL_OCCUPANCY_GEOMETRY
+        bp = torch.stack([workloads.voxel_uniform_inputs(500_000, seed=10 + b) for b in range(8)]).to(dev)
+        origin, dhw = okw["grid_min"], list(reversed(okw["grid_size"]))
+        fn = lambda: batched.voxelize_density_batched(bp, dhw, okw["voxel_size"], origin)
+        med, _ = time_cold(fn, 20, 5, flush)
+        nb = bp.numel() * 4 + 2 * 8 * 128 ** 3 * 4
+        ex["voxel_density_batched_8x500k_128"] = gpu_record(med, 8 * 500_000, "Gpts/s", nb, peak,
+                                                            "median of 20 cold-L2 calls; one launch for the batch, zero-fill included")
+        g = torch.Generator().manual_seed(5)
+        sp = torch.randn(4, 65536, 3, generator=g)
+        sp = sp / sp.norm(dim=2, keepdim=True)
+        spd, nrm = (sp * 2.0).to(dev), sp.to(dev)
+        fn = lambda: batched.voxelize_tsdf(spd, nrm, [128, 128, 128], 0.05, [-3.2, -3.2, -3.2], 0.15)
+        med, _ = time_cold(fn, 20, 5, flush)
+        _, w = fn()
+        pairs = float(w.sum())
+        ex["voxel_tsdf_4x65536_128"] = {"ms": med, "point_voxel_updates": pairs, "G_updates/s": pairs / (med * 1e-3) / 1e9,
+                                        "timing": "median of 20 cold-L2 calls; truncation 3 voxels; clears and decode pass included"}
     return ex
 
 

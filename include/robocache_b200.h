@@ -177,20 +177,39 @@ RC_API int rc_voxel_normalize(float* grid, const int32_t* counts, int64_t voxel_
 /*
  * Batched voxel grids in one launch: points [B,N,3] fp32 -> grid fp32 [B, D, H, W] (occupancy 0/1, density =
  * points per voxel) or [B, D, H, W, F] (feature mean; features [B,N,F] fp32, counts int32 [B, D, H, W] as work
- * space and second output).  depth/height/width are the z/y/x extents; cell (vz, vy, vx) of item b sits at
+ * space and second output; feature max = max(0, largest feature), what the reference's kernel computes by
+ * taking fmaxf against a zero-filled grid, counts unused).  depth/height/width are the z/y/x extents; cell (vz, vy, vx) of item b sits at
  * ((b*D + vz)*H + vy)*W + vx, the item index being folded into the voxel id so that one launch bins the whole batch.
  * Cell arithmetic, dropping of out-of-grid points and flags as rc_voxelize.
- * Replaces voxelize_occupancy / voxelize_density / voxelize_feature_mean
+ * Replaces voxelize_occupancy / voxelize_density / voxelize_feature_max / voxelize_feature_mean
  * (robocache/kernels/cutlass/point_cloud_voxelization.h:59-136; kernels point_cloud_voxelization.cu:41-300).
+ * RC_VOXEL_ZERO_INIT is required for feature max unless the caller cleared the grid.
  * rc_point_cloud_bounds: per item the minimum and maximum of every coordinate, [B,3] each, starting from +-1e10
  * (compute_point_cloud_bounds, point_cloud_voxelization.h:218-227, .cu:386-449).
  */
-typedef enum rc_batched_mode { RC_BATCHED_OCCUPANCY = 0, RC_BATCHED_DENSITY = 1, RC_BATCHED_FEATURE_MEAN = 2 } rc_batched_mode;
+typedef enum rc_batched_mode {
+    RC_BATCHED_OCCUPANCY = 0, RC_BATCHED_DENSITY = 1, RC_BATCHED_FEATURE_MEAN = 2, RC_BATCHED_FEATURE_MAX = 3
+} rc_batched_mode;
 RC_API int rc_voxelize_batched(const float* points, const float* features, float* grid, int32_t* counts, int64_t B,
                                int64_t N, int32_t F, const float origin_host[3], float voxel_size,
                                const int32_t dhw_host[3], int mode, uint32_t flags, int device, void* stream);
 RC_API int rc_point_cloud_bounds(const float* points, float* min_bounds, float* max_bounds, int64_t B, int64_t N,
                                  int device, void* stream);
+
+/*
+ * Truncated signed distance grids: points [B,N,3] fp32, normals [B,N,3] fp32 or NULL -> tsdf_grid fp32 [B,D,H,W] and
+ * weight_grid fp32 [B,D,H,W]; both are cleared by the call.  For every voxel whose centre
+ * origin + (v + 0.5) * voxel_size lies closer than truncation_distance to some point: tsdf = min over those points of
+ * distance / truncation_distance, negative when the closest point's normal has a positive dot product with
+ * (centre - point), which is the reference's sign rule; weight = the number of such points; other voxels 0 / 0.
+ * Distances are single fp32 operations (subtract, multiply, add left to right, sqrt, multiply by 1/truncation).
+ * Replaces voxelize_tsdf (robocache/kernels/cutlass/point_cloud_voxelization.h:146-173, kernel .cu:278-376), whose
+ * compare-and-swap update keeps the sign of whichever point reached the voxel first; the two agree wherever the
+ * reference's result does not depend on thread order.  truncation_distance / voxel_size may not exceed 510.
+ */
+RC_API int rc_voxelize_tsdf(const float* points, const float* normals, float* tsdf_grid, float* weight_grid, int64_t B,
+                            int64_t N, const float origin_host[3], float voxel_size, const int32_t dhw_host[3],
+                            float truncation_distance, int device, void* stream);
 
 /*
  * Point exchange for multi-GPU voxelisation: instead of reducing dense partial grids, every rank

@@ -31,6 +31,7 @@ STATIC_MAX_VOXELS = 1 << 21
 BATCHED_OCCUPANCY = 0
 BATCHED_DENSITY = 1
 BATCHED_FEATURE_MEAN = 2
+BATCHED_FEATURE_MAX = 3
 
 OPT_BLOCK_KERNEL = 0
 OPT_VOXEL_PASSES = 1
@@ -45,7 +46,7 @@ EXPORTED_SYMBOLS = (
     "rc_resample", "rc_resample_strided", "rc_resample_ragged", "rc_fuse", "rc_fuse_strided", "rc_resample_brackets", "rc_voxelize", "rc_voxel_normalize", "rc_voxelize_mean_static",
     "rc_voxelize_ex", "rc_voxelize_scratch_bytes", "rc_voxel_partition", "rc_voxel_partition_count", "rc_voxel_partition_move", "rc_voxel_partition_scratch_bytes",
     "rc_voxel_scatter_ids", "rc_voxel_scatter_runs", "rc_peer_alloc", "rc_peer_open", "rc_peer_close", "rc_peer_free",
-    "rc_voxelize_batched", "rc_point_cloud_bounds", "rc_voxel_bucket_block_records", "rc_voxel_bucket_exchange", "rc_voxel_scatter_buckets", "rc_set_option", "rc_bulk_wait_timeouts", "rc_strerror", "rc_last_cuda_error", "rc_abi_version",
+    "rc_voxelize_batched", "rc_point_cloud_bounds", "rc_voxelize_tsdf", "rc_voxel_bucket_block_records", "rc_voxel_bucket_exchange", "rc_voxel_scatter_buckets", "rc_set_option", "rc_bulk_wait_timeouts", "rc_strerror", "rc_last_cuda_error", "rc_abi_version",
 )
 
 
@@ -108,6 +109,8 @@ def _declare(L: ctypes.CDLL) -> None:
     L.rc_voxelize_batched.restype = ci
     L.rc_point_cloud_bounds.argtypes = [vp, vp, vp, i64, i64, ci, vp]
     L.rc_point_cloud_bounds.restype = ci
+    L.rc_voxelize_tsdf.argtypes = [vp, vp, vp, vp, i64, i64, ctypes.POINTER(f32), f32, ctypes.POINTER(i32), f32, ci, vp]
+    L.rc_voxelize_tsdf.restype = ci
     L.rc_voxel_bucket_block_records.argtypes = [i32]
     L.rc_voxel_bucket_block_records.restype = i32
     L.rc_voxel_bucket_exchange.argtypes = [vp, vp, i64, ctypes.POINTER(f32), f32, ctypes.POINTER(i32), i32, i32, i64, i64, i64,

@@ -2,14 +2,14 @@
 
 The older operator surface of the reference (robocache/kernels/cutlass/point_cloud_voxelization.h:59-157 and
 :218-227, bound in point_cloud_voxelization_torch.cu:17-160) takes a batch of equally sized clouds and returns
-float occupancy (0/1), density (points per voxel) or feature-mean grids laid out ``[batch, depth(z), height(y),
+float occupancy (0/1), density (points per voxel), feature-mean / feature-max or truncated-signed-distance grids laid out ``[batch, depth(z), height(y),
 width(x)]`` — the same z-major order the single-cloud operator uses.  One kernel launch bins the whole batch
 (the item index is folded into the voxel id) into one batch grid that was cleared with one fill.
 """
 from __future__ import annotations
 
 import ctypes
-from typing import Sequence, Tuple
+from typing import Optional, Sequence, Tuple
 
 import torch
 
@@ -41,7 +41,7 @@ def _voxelize_batched(points: torch.Tensor, features, grid_size: Sequence[int], 
     dev = points.device
     pts = points.to(torch.float32).contiguous()
     F, feats, counts = 0, None, None
-    if mode == _lib.BATCHED_FEATURE_MEAN:
+    if mode in (_lib.BATCHED_FEATURE_MEAN, _lib.BATCHED_FEATURE_MAX):
         if features is None:
             raise RuntimeError("features required for mean/max modes")
         if not features.is_cuda or features.device != dev:
@@ -51,7 +51,8 @@ def _voxelize_batched(points: torch.Tensor, features, grid_size: Sequence[int], 
         F = features.shape[2]
         feats = features.to(torch.float32).contiguous()
         grid = torch.empty((B, depth, height, width, F), dtype=torch.float32, device=dev)
-        counts = torch.empty((B, depth, height, width), dtype=torch.int32, device=dev)
+        if mode == _lib.BATCHED_FEATURE_MEAN:
+            counts = torch.empty((B, depth, height, width), dtype=torch.int32, device=dev)
     else:
         grid = torch.empty((B, depth, height, width), dtype=torch.float32, device=dev)
     org = (ctypes.c_float * 3)(*[float(v) for v in origin])
@@ -80,6 +81,14 @@ def voxelize_feature_mean_batched(points, features, grid_size, voxel_size, origi
                              _lib.BATCHED_FEATURE_MEAN)[0]
 
 
+def voxelize_feature_max_batched(points, features, grid_size, voxel_size, origin) -> torch.Tensor:
+    """Per-voxel maximum of the point features floored at 0, ``[B, D, H, W, F]``, empty voxels 0: what the reference's
+    kernel computes by taking ``fmaxf`` against a zero-filled grid (point_cloud_voxelization.h:94-116, .cu:139-195).
+    The single-cloud ``voxelize_pointcloud(..., mode="max")`` returns the true maximum instead."""
+    return _voxelize_batched(points, features, _as_list(grid_size), float(voxel_size), _as_list(origin),
+                             _lib.BATCHED_FEATURE_MAX)[0]
+
+
 def compute_point_cloud_bounds(points: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
     """``(min_bounds, max_bounds)``, each ``[B, 3]``: the bounding box of every cloud of the batch
     (point_cloud_voxelization.h:218-227); an empty cloud yields (+1e10, -1e10) as the reference's kernel does."""
@@ -93,3 +102,32 @@ def compute_point_cloud_bounds(points: torch.Tensor) -> Tuple[torch.Tensor, torc
                                            torch.cuda.current_stream(dev).cuda_stream)
     _lib.check(rc, "point_cloud_bounds")
     return lo, hi
+
+
+def voxelize_tsdf(points: torch.Tensor, normals: Optional[torch.Tensor], grid_size, voxel_size: float, origin,
+                  truncation_distance: float) -> Tuple[torch.Tensor, torch.Tensor]:
+    """``(tsdf, weights)``, each ``[B, D, H, W]`` fp32: for every voxel whose centre lies within ``truncation_distance``
+    of a point, the smallest distance / truncation (negative where ``dot(normal, centre - point) > 0`` for the closest
+    point, the reference kernel's sign rule) and the number of such points; 0 elsewhere
+    (point_cloud_voxelization.h:146-173).  ``normals`` may be ``None`` (unsigned distances)."""
+    _check_cloud(points)
+    B, N, _ = points.shape
+    dev = points.device
+    pts = points.to(torch.float32).contiguous()
+    nrm = None
+    if normals is not None:
+        if normals.shape != points.shape:
+            raise ValueError(f"normals must have the points' shape {tuple(points.shape)}, got {tuple(normals.shape)}")
+        if normals.device != dev:
+            raise ValueError("normals must be on the points' device")
+        nrm = normals.to(torch.float32).contiguous()
+    depth, height, width = (int(v) for v in _as_list(grid_size))
+    tsdf = torch.empty((B, depth, height, width), dtype=torch.float32, device=dev)
+    weights = torch.empty((B, depth, height, width), dtype=torch.float32, device=dev)
+    o = (ctypes.c_float * 3)(*[float(v) for v in _as_list(origin)])
+    dhw = (ctypes.c_int32 * 3)(depth, height, width)
+    rc = _lib.load().rc_voxelize_tsdf(pts.data_ptr(), nrm.data_ptr() if nrm is not None else None, tsdf.data_ptr(),
+                                      weights.data_ptr(), B, N, o, float(voxel_size), dhw, float(truncation_distance),
+                                      dev.index, torch.cuda.current_stream(dev).cuda_stream)
+    _lib.check(rc, "voxelize_tsdf")
+    return tsdf, weights

@@ -1,7 +1,7 @@
 // Batched voxel grids in one launch: [B, N, 3] clouds -> [B, D, H, W(, F)] float grids, and per-item
 // bounding boxes.  This is the older operator surface of the reference
 // (robocache/kernels/cutlass/point_cloud_voxelization.h:59-157, kernels in point_cloud_voxelization.cu):
-// float occupancy (0/1), float density (points per voxel), feature mean, and compute_point_cloud_bounds.
+// float occupancy (0/1), float density (points per voxel), feature mean, feature max, and compute_point_cloud_bounds.
 //
 // The batch is one flat list of B*N points; the item index is folded into the voxel id
 // (id = b * D*H*W + vz*H*W + vy*W + vx), so a single launch bins every item into its slice of one batch
@@ -14,7 +14,7 @@ namespace {
 
 using namespace rc::vox;
 
-enum : int { kBatchOccupancy = 0, kBatchDensity = 1, kBatchMean = 2 };
+enum : int { kBatchOccupancy = 0, kBatchDensity = 1, kBatchMean = 2, kBatchMax = 3 };
 
 __device__ __forceinline__ void red_add_f32(float* addr, float v) {
     asm volatile("red.global.add.f32 [%0], %1;" :: "l"(addr), "f"(v) : "memory");
@@ -58,6 +58,15 @@ voxel_batched_kernel(const float* __restrict__ pts, const float* __restrict__ fe
                 grid[cell] = 1.0f;                           // every writer stores the same value
             } else if (MODE == kBatchDensity) {
                 red_add_f32(grid + cell, 1.0f);              // exact below 2^24 points per voxel
+            } else if (MODE == kBatchMax) {
+                // the reference's kernel takes fmaxf against a grid that starts at zero (point_cloud_voxelization.cu:
+                // 139-195): the result is max(0, max of the features); positive floats order like their bit patterns
+                const float* f = feats + pi * F;
+                int* o = reinterpret_cast<int*>(grid) + cell * F;
+                for (int c = 0; c < F; ++c) {
+                    const float v = __ldg(f + c);
+                    if (v > 0.0f) atomicMax(o + c, __float_as_int(v));
+                }
             } else {
                 const float* f = feats + pi * F;
                 float* o = grid + cell * F;
@@ -119,11 +128,14 @@ extern "C" {
 int rc_voxelize_batched(const float* points, const float* features, float* grid, int32_t* counts, int64_t B, int64_t N,
                         int32_t F, const float origin_host[3], float voxel_size, const int32_t dhw_host[3], int mode,
                         uint32_t flags, int device, void* stream) {
-    if (mode != RC_BATCHED_OCCUPANCY && mode != RC_BATCHED_DENSITY && mode != RC_BATCHED_FEATURE_MEAN) return RC_ERR_BAD_MODE;
+    if (mode != RC_BATCHED_OCCUPANCY && mode != RC_BATCHED_DENSITY && mode != RC_BATCHED_FEATURE_MEAN &&
+        mode != RC_BATCHED_FEATURE_MAX)
+        return RC_ERR_BAD_MODE;
     if (origin_host == nullptr || dhw_host == nullptr) return RC_ERR_NULL_POINTER;
     if (B < 0 || N < 0 || F < 0) return RC_ERR_BAD_SHAPE;
     if (!(voxel_size > 0.0f) || !(voxel_size <= 3.0e38f)) return RC_ERR_BAD_VALUE;
     const bool mean = (mode == RC_BATCHED_FEATURE_MEAN);
+    const bool feat = mean || mode == RC_BATCHED_FEATURE_MAX;
     VoxelGeom g;
     g.minx = origin_host[0]; g.miny = origin_host[1]; g.minz = origin_host[2];
     g.vs = voxel_size;
@@ -132,13 +144,13 @@ int rc_voxelize_batched(const float* points, const float* features, float* grid,
     if (g.gx >= (1 << 24) || g.gy >= (1 << 24) || g.gz >= (1 << 24)) return RC_ERR_TOO_LARGE;
     g.fgx = static_cast<float>(g.gx); g.fgy = static_cast<float>(g.gy); g.fgz = static_cast<float>(g.gz);
     g.inv_vs = host_reciprocal(voxel_size);
-    const double cells_d = static_cast<double>(g.gx) * g.gy * g.gz * static_cast<double>(B) * (mean ? (F > 0 ? F : 1) : 1);
+    const double cells_d = static_cast<double>(g.gx) * g.gy * g.gz * static_cast<double>(B) * (feat ? (F > 0 ? F : 1) : 1);
     if (cells_d >= 1099511627776.0 || static_cast<double>(B) * static_cast<double>(N) >= 4.0e18) return RC_ERR_TOO_LARGE;
     const long long V = static_cast<long long>(g.gx) * g.gy * g.gz;
-    const long long cells = V * B * (mean ? F : 1);
+    const long long cells = V * B * (feat ? F : 1);
     if (cells > 0 && grid == nullptr) return RC_ERR_NULL_POINTER;
     if (mean && V * B > 0 && counts == nullptr) return RC_ERR_NULL_POINTER;
-    if (mean && B * N > 0 && F > 0 && features == nullptr) return RC_ERR_BAD_MODE;
+    if (feat && B * N > 0 && F > 0 && features == nullptr) return RC_ERR_BAD_MODE;
     if (B * N > 0 && points == nullptr) return RC_ERR_NULL_POINTER;
     if (!rc::aligned_to(points, 4) || !rc::aligned_to(features, 4) || !rc::aligned_to(grid, 4) || !rc::aligned_to(counts, 4))
         return RC_ERR_BAD_ALIGNMENT;
@@ -156,7 +168,7 @@ int rc_voxelize_batched(const float* points, const float* features, float* grid,
         if (mean && V * B > 0) RC_CUDA_TRY(cudaMemsetAsync(counts, 0, static_cast<size_t>(V * B) * 4, st));
     }
     const long long total = B * N;
-    if (total > 0 && V > 0 && !(mean && F == 0)) {
+    if (total > 0 && V > 0 && !(feat && F == 0)) {
         long long blocks = (total + kPointsPerBlock - 1) / kPointsPerBlock;
         const long long cap = 16ll * rc::sm_count(device);
         if (blocks > cap) blocks = cap;
@@ -166,6 +178,8 @@ int rc_voxelize_batched(const float* points, const float* features, float* grid,
             voxel_batched_kernel<kBatchOccupancy><<<nb, kThreads, 0, st>>>(points, features, grid, counts, total, N, F, g, V, aligned);
         else if (mode == RC_BATCHED_DENSITY)
             voxel_batched_kernel<kBatchDensity><<<nb, kThreads, 0, st>>>(points, features, grid, counts, total, N, F, g, V, aligned);
+        else if (mode == RC_BATCHED_FEATURE_MAX)
+            voxel_batched_kernel<kBatchMax><<<nb, kThreads, 0, st>>>(points, features, grid, counts, total, N, F, g, V, aligned);
         else
             voxel_batched_kernel<kBatchMean><<<nb, kThreads, 0, st>>>(points, features, grid, counts, total, N, F, g, V, aligned);
     }

@@ -272,8 +272,8 @@ def test_batched_one_launch_against_the_oracle_item_by_item(B, N, F, cuda_lib):
     """The batch kernel folds the item index into the voxel id; tiles of 128 points straddle items (N = 7, 100, 129),
     and every item must equal the single-cloud oracle: density and occupancy exact, feature means in tolerance,
     bounds exact (robocache/kernels/cutlass/point_cloud_voxelization.h:59-136, :218-227)."""
-    from robogoat_b200.batched import (compute_point_cloud_bounds, voxelize_density_batched, voxelize_feature_mean_batched,
-                                       voxelize_occupancy_batched)
+    from robogoat_b200.batched import (compute_point_cloud_bounds, voxelize_density_batched, voxelize_feature_max_batched,
+                                       voxelize_feature_mean_batched, voxelize_occupancy_batched)
     g = torch.Generator().manual_seed(100 * B + N + F)
     pts = torch.rand(B, N, 3, generator=g) * 5 - 2.5
     feats = torch.randn(B, N, F, generator=g)
@@ -282,7 +282,8 @@ def test_batched_one_launch_against_the_oracle_item_by_item(B, N, F, cuda_lib):
     dens = voxelize_density_batched(pts.to(DEV), dhw, vs, origin).cpu()
     occ = voxelize_occupancy_batched(pts.to(DEV), dhw, vs, origin).cpu()
     mean = voxelize_feature_mean_batched(pts.to(DEV), feats.to(DEV), dhw, vs, origin).cpu()
-    assert dens.shape == (B, 9, 14, 17) and mean.shape == (B, 9, 14, 17, F)
+    fmax = voxelize_feature_max_batched(pts.to(DEV), feats.to(DEV), dhw, vs, origin).cpu()
+    assert dens.shape == (B, 9, 14, 17) and mean.shape == (B, 9, 14, 17, F) and fmax.shape == mean.shape
     for b in range(B):
         exp = oracle.voxelize_pointcloud(pts[b], None, origin, vs, xyz, mode="count").flatten().float()
         assert torch.equal(dens[b].flatten(), exp), b
@@ -290,8 +291,56 @@ def test_batched_one_launch_against_the_oracle_item_by_item(B, N, F, cuda_lib):
         em, ec, sabs = oracle.voxelize_pointcloud(pts[b], feats[b], origin, vs, xyz, mode="mean", return_aux=True)
         tol = oracle.mean_tolerance(ec, sabs, em)
         assert bool(((mean[b].reshape(-1, F) - em.reshape(-1, F)).abs() <= tol.reshape(-1, F)).all()), b
+        # feature max as the reference's kernel defines it: fmaxf against a zero-filled grid
+        ids = oracle.voxel_ids(pts[b], origin, vs, xyz) if N else torch.empty(0, dtype=torch.int64)
+        keep = ids >= 0
+        want = torch.zeros(9 * 14 * 17, F)
+        if int(keep.sum()):
+            want.scatter_reduce_(0, ids[keep].unsqueeze(1).expand(-1, F), feats[b][keep], "amax", include_self=True)
+        assert torch.equal(fmax[b].reshape(-1, F), want), b
     lo, hi = compute_point_cloud_bounds(pts.to(DEV))
     if N > 0:
         assert torch.equal(lo.cpu(), pts.amin(dim=1)) and torch.equal(hi.cpu(), pts.amax(dim=1))
     else:
         assert bool((lo == 1e10).all()) and bool((hi == -1e10).all())
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("with_normals", [False, True])
+@pytest.mark.parametrize("B,N", [(1, 1), (2, 300), (3, 45)])
+def test_tsdf_matches_oracle(B, N, with_normals):
+    """Truncated signed distances and weights, bit for bit against the CPU restatement of the reference's kernel rule
+    (point_cloud_voxelization.cu:278-376): points inside, on the border of and outside the grid, a NaN point."""
+    from oracle import tsdf as otsdf
+    from robogoat_b200.batched import voxelize_tsdf
+    g = torch.Generator().manual_seed(100 * B + N + int(with_normals))
+    dhw, vs, origin, trunc = (12, 10, 14), 0.25, (-1.0, -0.5, -1.5), 0.6
+    pts = torch.rand(B, N, 3, generator=g) * torch.tensor([4.5, 3.5, 4.0]) + torch.tensor([-1.5, -1.0, -2.0])
+    if N > 10:
+        pts[0, 3, 1] = float("nan")
+        pts[-1, 5] = torch.tensor([1e30, 0.0, 0.0])
+        pts[0, 7] = torch.tensor([-1.0 + 0.125, -0.5 + 0.125, -1.5 + 0.125])     # exactly on a voxel centre
+    nrm = None
+    if with_normals:
+        nrm = torch.randn(B, N, 3, generator=g)
+        nrm = nrm / nrm.norm(dim=2, keepdim=True)
+    t, w = voxelize_tsdf(pts.to(DEV), nrm.to(DEV) if nrm is not None else None, dhw, vs, origin, trunc)
+    et, ew = otsdf.voxelize_tsdf(pts.numpy(), nrm.numpy() if nrm is not None else None, dhw, vs, origin, trunc)
+    assert t.shape == (B, *dhw) and w.shape == (B, *dhw)
+    assert torch.equal(w.cpu(), torch.from_numpy(ew))
+    assert torch.equal(t.cpu().view(torch.int32), torch.from_numpy(et).view(torch.int32))
+    assert N <= 10 or float(ew.sum()) > 0
+
+
+@pytest.mark.gpu
+def test_tsdf_argument_errors_and_empty():
+    from robogoat_b200.batched import voxelize_tsdf
+    pts = torch.zeros(1, 4, 3, device=DEV)
+    with pytest.raises(RuntimeError):
+        voxelize_tsdf(pts, None, (4, 4, 4), 0.1, (0, 0, 0), 0.0)            # truncation must be positive
+    with pytest.raises(RuntimeError):
+        voxelize_tsdf(pts, None, (4, 4, 4), 0.001, (0, 0, 0), 10.0)         # neighbourhood beyond the supported reach
+    with pytest.raises(ValueError):
+        voxelize_tsdf(pts, torch.zeros(1, 3, 3, device=DEV), (4, 4, 4), 0.1, (0, 0, 0), 0.2)
+    t, w = voxelize_tsdf(torch.zeros(2, 0, 3, device=DEV), None, (3, 3, 3), 0.1, (0, 0, 0), 0.2)
+    assert float(t.abs().sum()) == 0 and float(w.sum()) == 0
