@@ -874,6 +874,14 @@ def sharded_parity(dev, rank, world, px, bx=None, bxs=None) -> dict:
         for _ in range(2):          # twice: the second call's records meet pools that have just been read
             got, gcnt = sharding.voxelize_sharded_buckets(pl, fl, ex_, return_counts=True, **kw)
             flags[key] = flags[key] and count_ok(gcnt, xa, xb) and mean_ok(got, xa, xb)
+        if not ex_.fetch:
+            # sliced form, on pools sized for this cloud so that every slice carries points
+            small = sharding.BucketExchange(points_per_rank=(n + world - 1) // world + 3000, n_voxels=V)
+            flags[key + "_sliced"] = True
+            for slices in (4, 4, 3):
+                got, gcnt = sharding.voxelize_sharded_buckets(pl, fl, small, return_counts=True, slices=slices, **kw)
+                flags[key + "_sliced"] = flags[key + "_sliced"] and count_ok(gcnt, xa, xb) and mean_ok(got, xa, xb)
+            small.close()
     names = sorted(flags)
     t = torch.tensor([1 if flags[k] else 0 for k in names], dtype=torch.int32, device=dev)
     dist.all_reduce(t, op=dist.ReduceOp.MIN)
@@ -951,6 +959,10 @@ def multi_gpu_extras(L, dev, rank, world, ex, pts, feats, kw, N, single_ms):
         forms.append(("bucket_exchange", "bucket_exchange", lambda m: sharding.voxelize_sharded_buckets(pts, feats, bx, **kw),
                       "one bucket kernel sorts every chunk by (owner, sub-range) and stores each owner's records into a fixed block of "
                       "that owner's pool over NVLink; no counts, no host synchronisation, two barriers on the stream; mean mode only"))
+        forms.append(("bucket_exchange_sliced", "bucket_exchange_sliced",
+                      lambda m: sharding.voxelize_sharded_buckets(pts, feats, bx, slices=4, **kw),
+                      "the same in four slices on three streams: while slice s+1 is bucketed and stored over NVLink (a grid of 2 CTAs "
+                      "per SM: the stores are link-bound), the owners accumulate slice s; per-slice barriers on a stream of their own"))
     if bxs is not None:
         forms.append(("bucket_exchange_fetch", "bucket_exchange_store", lambda m: sharding.voxelize_sharded_buckets(pts, feats, bxs, **kw),
                       "same pools in the sources' own memory; every owner's accumulation kernel fetches its blocks over NVLink as it goes"))

@@ -288,11 +288,16 @@ RC_API int rc_voxel_scatter_runs(const int32_t* ids, const float* features, void
  *   memory, mapped here with rc_peer_open (plain stores over NVLink; first_block = rank * chunks, pool_blocks =
  *   n_groups * chunks), or n_groups pools in this GPU's own memory that the owners read later (first_block = 0,
  *   pool_blocks = chunks).  N <= chunks * 1024; all `chunks` blocks are written on every call (empty ones as
- *   empty).  Nothing is read from a peer, no multicast.
+ *   empty).  Nothing is read from a peer, no multicast.  ctas_per_sm (1..8, 0 = 8) sizes the grid: the kernel's
+ *   remote stores are bound by NVLink, not by the SMs, and a small grid (2) leaves SMs to the accumulation of an
+ *   earlier slice running on another stream.
  * rc_voxel_scatter_buckets: an owner accumulates the pools of n_sources sources (HOST arrays of device pointers
  *   to ids, feature rows and tables of blocks_per_source blocks each; they may lie in other GPUs' memory and are
  *   then read with plain loads over NVLink) into its slab [id_begin, id_end) of the grid (fp32 [., 4], first cell of
- *   voxel id_begin) and counts, one sub-range after the other; flags as rc_voxelize.
+ *   voxel id_begin) and counts, one sub-range after the other; flags as rc_voxelize.  table_row_blocks is the row
+ *   length of the sources' run tables (0: blocks_per_source); a larger value lets a "source" be a window of
+ *   blocks_per_source blocks inside a bigger pool - a slice of the cloud that has already arrived while the next
+ *   slice is still travelling.  With n_sources = 0 the call only clears and / or normalises the slab as flags say.
  * The caller orders writers against readers with a barrier on the stream before and after the exchange call.
  * No counterpart in the reference.
  */
@@ -300,12 +305,12 @@ RC_API int32_t rc_voxel_bucket_block_records(int32_t parts_per_group);
 RC_API int rc_voxel_bucket_exchange(const float* points, const float* features, int64_t N, const float grid_min_host[3],
                                     float voxel_size, const int32_t grid_size_host[3], int32_t n_groups,
                                     int32_t parts_per_group, int64_t chunks, int64_t first_block, int64_t pool_blocks,
-                                    void* const* dest_ids, void* const* dest_features, void* const* dest_runs, int device,
-                                    void* stream);
+                                    void* const* dest_ids, void* const* dest_features, void* const* dest_runs,
+                                    int32_t ctas_per_sm, int device, void* stream);
 RC_API int rc_voxel_scatter_buckets(const void* const* pool_ids, const void* const* pool_features, const void* const* runs,
-                                    int32_t n_sources, int64_t blocks_per_source, int32_t parts_per_group, float* grid,
-                                    int32_t* counts, int64_t id_begin, int64_t id_end, uint32_t flags, int device,
-                                    void* stream);
+                                    int32_t n_sources, int64_t blocks_per_source, int64_t table_row_blocks,
+                                    int32_t parts_per_group, float* grid, int32_t* counts, int64_t id_begin,
+                                    int64_t id_end, uint32_t flags, int device, void* stream);
 
 /*
  * Device buffers that the other processes of a node can map, for rc_voxel_partition_move's remote

@@ -114,9 +114,9 @@ def _declare(L: ctypes.CDLL) -> None:
     L.rc_voxel_bucket_block_records.argtypes = [i32]
     L.rc_voxel_bucket_block_records.restype = i32
     L.rc_voxel_bucket_exchange.argtypes = [vp, vp, i64, ctypes.POINTER(f32), f32, ctypes.POINTER(i32), i32, i32, i64, i64, i64,
-                                           ctypes.POINTER(vp), ctypes.POINTER(vp), ctypes.POINTER(vp), ci, vp]
+                                           ctypes.POINTER(vp), ctypes.POINTER(vp), ctypes.POINTER(vp), i32, ci, vp]
     L.rc_voxel_bucket_exchange.restype = ci
-    L.rc_voxel_scatter_buckets.argtypes = [ctypes.POINTER(vp), ctypes.POINTER(vp), ctypes.POINTER(vp), i32, i64, i32, vp, vp,
+    L.rc_voxel_scatter_buckets.argtypes = [ctypes.POINTER(vp), ctypes.POINTER(vp), ctypes.POINTER(vp), i32, i64, i64, i32, vp, vp,
                                            i64, i64, u32, ci, vp]
     L.rc_voxel_scatter_buckets.restype = ci
     for name in ("rc_resample", "rc_resample_strided", "rc_resample_ragged", "rc_fuse", "rc_fuse_strided", "rc_resample_brackets", "rc_voxelize", "rc_voxel_normalize", "rc_voxelize_mean_static",

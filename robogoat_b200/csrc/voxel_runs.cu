@@ -466,12 +466,15 @@ int32_t rc_voxel_bucket_block_records(int32_t parts_per_group) {
 int rc_voxel_bucket_exchange(const float* points, const float* features, int64_t N, const float grid_min_host[3],
                              float voxel_size, const int32_t grid_size_host[3], int32_t n_groups, int32_t parts_per_group,
                              int64_t chunks, int64_t first_block, int64_t pool_blocks, void* const* dest_ids,
-                             void* const* dest_features, void* const* dest_runs, int device, void* stream) {
+                             void* const* dest_features, void* const* dest_runs, int32_t ctas_per_sm, int device,
+                             void* stream) {
     if (grid_min_host == nullptr || grid_size_host == nullptr || dest_ids == nullptr || dest_features == nullptr ||
         dest_runs == nullptr)
         return RC_ERR_NULL_POINTER;
     if (n_groups < 1 || parts_per_group < 1 || N < 0 || chunks < 0 || first_block < 0 || first_block + chunks > pool_blocks)
         return RC_ERR_BAD_SHAPE;
+    if (ctas_per_sm < 0 || ctas_per_sm > 8) return RC_ERR_BAD_VALUE;
+    if (ctas_per_sm == 0) ctas_per_sm = 8;
     if (static_cast<long long>(n_groups) * parts_per_group > kMeanRunsMaxParts) return RC_ERR_TOO_LARGE;
     if (N > chunks * kRunChunk || N > (1ll << 31) - 4096) return RC_ERR_TOO_LARGE;
     if (!(voxel_size > 0.0f) || !(voxel_size <= 3.0e38f)) return RC_ERR_BAD_VALUE;
@@ -513,7 +516,8 @@ int rc_voxel_bucket_exchange(const float* points, const float* features, int64_t
     rc::DeviceScope scope(device);
     if (scope.status() != RC_OK) return scope.status();
     const int sms = rc::sm_count(device);
-    const long long nb = chunks < 8ll * sms ? chunks : 8ll * sms;
+    const long long cap = static_cast<long long>(ctas_per_sm) * sms;
+    const long long nb = chunks < cap ? chunks : cap;
     const int rc_smem = rc::ensure_dynamic_smem(reinterpret_cast<const void*>(voxel_bucket_kernel<true>), device, 2 * kBucketStageBytes);
     if (rc_smem != RC_OK) return rc_smem;
     voxel_bucket_kernel<true><<<static_cast<unsigned int>(nb), kThreads, 2 * kBucketStageBytes, static_cast<cudaStream_t>(stream)>>>(
@@ -523,11 +527,14 @@ int rc_voxel_bucket_exchange(const float* points, const float* features, int64_t
 }
 
 int rc_voxel_scatter_buckets(const void* const* pool_ids, const void* const* pool_features, const void* const* runs,
-                             int32_t n_sources, int64_t blocks_per_source, int32_t parts_per_group, float* grid, int32_t* counts,
-                             int64_t id_begin, int64_t id_end, uint32_t flags, int device, void* stream) {
+                             int32_t n_sources, int64_t blocks_per_source, int64_t table_row_blocks, int32_t parts_per_group,
+                             float* grid, int32_t* counts, int64_t id_begin, int64_t id_end, uint32_t flags, int device,
+                             void* stream) {
     if (n_sources < 0 || n_sources > kMeanRunsMaxParts || blocks_per_source < 0 || parts_per_group < 1 ||
         parts_per_group > kMeanRunsMaxParts || id_begin < 0 || id_end < id_begin)
         return RC_ERR_BAD_SHAPE;
+    if (table_row_blocks == 0) table_row_blocks = blocks_per_source;
+    if (table_row_blocks < blocks_per_source) return RC_ERR_BAD_SHAPE;
     if (id_end >= (1ll << 31)) return RC_ERR_TOO_LARGE;
     const long long nvox = id_end - id_begin;
     if (nvox > 0 && (grid == nullptr || counts == nullptr)) return RC_ERR_NULL_POINTER;
@@ -561,7 +568,7 @@ int rc_voxel_scatter_buckets(const void* const* pool_ids, const void* const* poo
         if (sb > 8ll * sms) sb = 8ll * sms;
         for (int k = 0; k < parts_per_group; ++k) {     // one launch per sub-range of the slab
             ScatterSources row = src;
-            for (int i = 0; i < n_sources; ++i) row.runs[i] = src.runs[i] + static_cast<long long>(k) * blocks_per_source;
+            for (int i = 0; i < n_sources; ++i) row.runs[i] = src.runs[i] + static_cast<long long>(k) * table_row_blocks;
             bool launched = false;
             if (k > 0 && rc::g_scatter_overlap.load(std::memory_order_relaxed)) {
                 cudaLaunchConfig_t cfg{};

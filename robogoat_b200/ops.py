@@ -362,7 +362,7 @@ def voxel_partition_move_cuda(points: torch.Tensor, features: Optional[torch.Ten
 def voxel_bucket_exchange_cuda(points: torch.Tensor, features: torch.Tensor, grid_min: Sequence[float], voxel_size: float,
                                grid_size: Sequence[int], n_groups: int, parts_per_group: int, chunks: int, first_block: int,
                                pool_blocks: int, dest_ids: Sequence[int], dest_features: Sequence[int],
-                               dest_runs: Sequence[int]) -> None:
+                               dest_runs: Sequence[int], ctas_per_sm: int = 0) -> None:
     """Bucket a cloud by (owner, sub-range of the owner's slab): owner d's records of chunk c go to block
     ``first_block + c`` of pool d (device addresses, possibly of peer GPUs' buffers), with the run table beside them.
     Mean mode, four feature channels; see ``rc_voxel_bucket_exchange`` in the header for the layout."""
@@ -379,28 +379,35 @@ def voxel_bucket_exchange_cuda(points: torch.Tensor, features: torch.Tensor, gri
                                               int(n_groups), int(parts_per_group), int(chunks), int(first_block),
                                               int(pool_blocks), VP(*[int(a) for a in dest_ids]),
                                               VP(*[int(a) for a in dest_features]), VP(*[int(a) for a in dest_runs]),
-                                              dev.index, _stream_ptr(dev))
+                                              int(ctas_per_sm), dev.index, _stream_ptr(dev))
     _lib.check(rc, "voxel_bucket_exchange")
 
 
 def voxel_scatter_buckets_cuda(pool_ids: Sequence[int], pool_features: Sequence[int], runs: Sequence[int],
                                blocks_per_source: int, parts_per_group: int, device: torch.device, id_begin: int,
-                               id_end: int, *, normalize: bool = True) -> List[torch.Tensor]:
+                               id_end: int, *, normalize: bool = True, table_row_blocks: int = 0, zero_init: bool = True,
+                               out: Optional[List[torch.Tensor]] = None) -> List[torch.Tensor]:
     """The owner's side of the bucket exchange: accumulate the pools of every source (device addresses of their ids,
     feature rows and run tables; they may lie in other GPUs' memory) into the slab [id_begin, id_end); returns
-    ``[grid fp32 [voxels, 4], counts int32 [voxels]]``."""
+    ``[grid fp32 [voxels, 4], counts int32 [voxels]]``.  ``out``: accumulators from ``voxel_slab_buffers`` to add into
+    (with ``zero_init=False`` they keep what earlier calls accumulated); ``table_row_blocks``: row length of the run
+    tables when a source is a window of a larger pool; an empty source list only clears / normalises."""
     device = torch.device(device)
     if device.index is None:
         device = torch.device("cuda", torch.cuda.current_device())
     n = len(pool_ids)
-    _check(len(pool_features) == n and len(runs) == n and 1 <= n <= 16, "one pool and one run table per source (at most 16)")
+    _check(len(pool_features) == n and len(runs) == n and 0 <= n <= 16, "one pool and one run table per source (at most 16)")
     nvox = int(id_end) - int(id_begin)
     _check(nvox >= 0 and id_begin >= 0, "bad voxel range")
-    grid, counts = voxel_slab_buffers(nvox, 4, "mean", device)
-    flags = _lib.VOXEL_ZERO_INIT | (0 if normalize else _lib.VOXEL_NO_NORMALIZE)
-    VP = ctypes.c_void_p * n
+    grid, counts = out if out is not None else voxel_slab_buffers(nvox, 4, "mean", device)
+    _check(grid.shape == (nvox, 4) and counts.shape == (nvox,) and grid.dtype == torch.float32 and counts.dtype == torch.int32
+           and grid.is_contiguous() and counts.is_contiguous() and grid.device == device and counts.device == device,
+           "out must be the slab's [grid fp32 [voxels, 4], counts int32 [voxels]] on the device")
+    flags = (_lib.VOXEL_ZERO_INIT if zero_init else 0) | (0 if normalize else _lib.VOXEL_NO_NORMALIZE)
+    VP = ctypes.c_void_p * max(n, 1)
     rc = _lib.load().rc_voxel_scatter_buckets(VP(*[int(a) for a in pool_ids]), VP(*[int(a) for a in pool_features]),
-                                              VP(*[int(a) for a in runs]), n, int(blocks_per_source), int(parts_per_group),
+                                              VP(*[int(a) for a in runs]), n, int(blocks_per_source), int(table_row_blocks),
+                                              int(parts_per_group),
                                               grid.data_ptr() if nvox else None, counts.data_ptr() if nvox else None,
                                               int(id_begin), int(id_end), flags, device.index, _stream_ptr(device))
     _lib.check(rc, "voxel_scatter_buckets")

@@ -444,6 +444,30 @@ class BucketExchange:
         return ([p + d * rec * 4 for p in self.ids.peers], [p + d * rec * 16 for p in self.features.peers],
                 [p + d * self.per_group * self.chunks * 4 for p in self.runs.peers], self.chunks)
 
+    def slice_chunks(self, slices: int) -> int:
+        """Chunks per slice when the capacity is cut into ``slices`` equal runs of chunks (the last may be short)."""
+        return (self.chunks + int(slices) - 1) // int(slices)
+
+    def slice_sources(self, s: int, slices: int):
+        """(ids, features, runs, blocks) of slice ``s`` for this rank's accumulation: one window per source rank
+        inside this rank's pool (storing form only); the run tables keep the pool's row length ``n_blocks``."""
+        if self.fetch:
+            raise RuntimeError("sliced accumulation is built for the storing form of the bucket exchange")
+        cs = self.slice_chunks(slices)
+        first = min(s * cs, self.chunks)
+        n = min(cs, self.chunks - first)
+        blocks = [r * self.chunks + first for r in range(self.world)]
+        return ([self.ids.ptr + b * self.block * 4 for b in blocks], [self.features.ptr + b * self.block * 16 for b in blocks],
+                [self.runs.ptr + b * 4 for b in blocks], n)
+
+    def streams(self):
+        """Side streams of the sliced form: (the slices' barriers, the owner's accumulation), both of default priority
+        (with the bucket kernels on a high-priority stream single calls took 11-15 ms instead of 2.4)."""
+        if getattr(self, "_streams", None) is None:
+            dev = self._token.device
+            self._streams = (torch.cuda.Stream(dev), torch.cuda.Stream(dev))
+        return self._streams
+
     def close(self) -> None:
         for b in (self.ids, self.features, self.runs):
             if b is not None:
@@ -458,11 +482,15 @@ def _lib_handle():
 
 def voxelize_sharded_buckets(points_local: torch.Tensor, features_local: torch.Tensor, exchange: BucketExchange,
                              grid_min=(-10.0, -10.0, -10.0), voxel_size: float = 0.1, grid_size=(128, 128, 128),
-                             return_counts: bool = False, group=None):
+                             return_counts: bool = False, group=None, slices: int = 1):
     """Mean-mode voxelisation of a cloud spread over the ranks, output slab-sharded as ``voxelize_sharded_exchange``
     returns it ([voxels of this rank's slab, 4]), by the bucket exchange: one bucket kernel, one barrier, then the
     owner's accumulation (which, in the fetching form, pulls the records over NVLink as it goes) and normalisation -
-    nothing on the host waits."""
+    nothing on the host waits.
+
+    ``slices`` > 1 (storing form): the cloud is bucketed slice after slice on the calling stream, and while slice
+    s+1 is on its way over NVLink the owners already accumulate slice s on a second stream; a third stream carries
+    the per-slice barriers so that the bucket kernels follow one another without waiting for them."""
     from . import ops
     rank, ws = world(group)
     V = int(grid_size[0]) * int(grid_size[1]) * int(grid_size[2])
@@ -471,6 +499,9 @@ def voxelize_sharded_buckets(points_local: torch.Tensor, features_local: torch.T
     if points_local.shape[0] > exchange.capacity:
         raise RuntimeError(f"{points_local.shape[0]} points exceed the exchange's capacity of {exchange.capacity} per rank")
     a, b = slab_bounds(V, rank, ws)
+    if int(slices) > 1 and not exchange.fetch:
+        return _buckets_sliced(points_local, features_local, exchange, list(grid_min), float(voxel_size), list(grid_size),
+                               int(slices), a, b, return_counts)
     d_ids, d_feats, d_runs, first_block, pool_blocks = exchange.destinations()
     s_ids, s_feats, s_runs, blocks_per_source = exchange.sources()
     exchange.stream_barrier()                   # everybody is done with the records of the previous call
@@ -480,6 +511,52 @@ def voxelize_sharded_buckets(points_local: torch.Tensor, features_local: torch.T
     grid, counts = ops.voxel_scatter_buckets_cuda(s_ids, s_feats, s_runs, blocks_per_source, exchange.per_group,
                                                   points_local.device, a, b)
     return (grid, counts) if return_counts else grid
+
+
+def _buckets_sliced(points, feats, exchange: BucketExchange, grid_min, voxel_size, grid_size, slices, a, b, return_counts):
+    """The bucket exchange in ``slices`` slices on three streams (see ``voxelize_sharded_buckets``)."""
+    from . import ops
+    dev = points.device
+    ws, rank = exchange.world, exchange.rank
+    pts = points.to(torch.float32).contiguous()
+    fts = feats.to(torch.float32).contiguous()
+    N = pts.shape[0]
+    cs = exchange.slice_chunks(slices)
+    d_ids, d_feats, d_runs, first_block, pool_blocks = exchange.destinations()
+    main = torch.cuda.current_stream(dev)
+    bar_stream, acc_stream = exchange.streams()
+    out = ops.voxel_slab_buffers(b - a, 4, "mean", dev)
+    exchange.stream_barrier()                   # everybody is done with the records of the previous call
+    start = torch.cuda.Event()
+    start.record(main)
+    acc_stream.wait_event(start)
+    with torch.cuda.stream(acc_stream):         # clear the slab while the first slice is bucketed
+        ops.voxel_scatter_buckets_cuda([], [], [], 0, exchange.per_group, dev, a, b, normalize=False, out=out)
+    for s in range(slices):
+        c0 = min(s * cs, exchange.chunks)
+        nchunks = min(cs, exchange.chunks - c0)
+        p0, p1 = min(N, c0 * 1024), min(N, (c0 + nchunks) * 1024)
+        ops.voxel_bucket_exchange_cuda(pts[p0:p1], fts[p0:p1], grid_min, voxel_size, grid_size, ws, exchange.per_group,
+                                       nchunks, first_block + c0, pool_blocks, d_ids, d_feats, d_runs, ctas_per_sm=2)
+        stored = torch.cuda.Event()
+        stored.record(main)
+        bar_stream.wait_event(stored)
+        with torch.cuda.stream(bar_stream):     # every rank's records of slice s are in place
+            exchange.stream_barrier()
+            arrived = torch.cuda.Event()
+            arrived.record(bar_stream)
+        acc_stream.wait_event(arrived)
+        s_ids, s_feats, s_runs, blocks = exchange.slice_sources(s, slices)
+        with torch.cuda.stream(acc_stream):
+            ops.voxel_scatter_buckets_cuda(s_ids, s_feats, s_runs, blocks, exchange.per_group, dev, a, b,
+                                           normalize=(s == slices - 1), table_row_blocks=exchange.n_blocks,
+                                           zero_init=False, out=out)
+    done = torch.cuda.Event()
+    done.record(acc_stream)
+    main.wait_event(done)
+    for t in out:                               # used on a side stream: keep the allocator from reusing them early
+        t.record_stream(acc_stream)
+    return (out[0], out[1]) if return_counts else out[0]
 
 
 def batched_exchange_plans(counts, rank: int, per_group: int):

@@ -108,10 +108,12 @@ for fetch in (True, False):                 # owners fetch the records over NVLi
         m2, c2, s2 = oracle.voxelize_pointcloud(sub_h, sub_f, mode="mean", return_aux=True, **kw)
         t2 = oracle.mean_tolerance(c2, s2, m2).reshape(V, 4)
         l, h = used[rank]
-        slab, cnts = sharding.voxelize_sharded_buckets(pts[l:h], feats[l:h], bx, return_counts=True, **kw)
         a, b = sharding.slab_bounds(V, rank, ws)
-        assert torch.equal(cnts.cpu(), c2.reshape(V)[a:b]), f"bucket counts {rep} fetch={fetch}"
-        assert bool(((slab.cpu() - m2.reshape(V, 4)[a:b]).abs() <= t2[a:b]).all()), f"bucket mean {rep} fetch={fetch}"
+        # in one piece, then in slices whose accumulation overlaps the next slice's stores (storing form)
+        for slices in ((1,) if fetch else (1, 3, 8)):
+            slab, cnts = sharding.voxelize_sharded_buckets(pts[l:h], feats[l:h], bx, return_counts=True, slices=slices, **kw)
+            assert torch.equal(cnts.cpu(), c2.reshape(V)[a:b]), f"bucket counts {rep} fetch={fetch} slices={slices}"
+            assert bool(((slab.cpu() - m2.reshape(V, 4)[a:b]).abs() <= t2[a:b]).all()), f"bucket mean {rep} fetch={fetch} slices={slices}"
     bx.close()
 small = sharding.PointExchange(capacity=10, feature_width=4)
 slab = sharding.voxelize_sharded_exchange(pts[lo:hi], None, mode="count", direct=small, **kw)

@@ -277,3 +277,56 @@ def test_bucket_exchange_with_every_rank_on_one_gpu(R, K, N, layout, bucket_stor
         total += int(counts.sum())
     assert total == int(ecnt.sum())
     torch.cuda.synchronize()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("R,K,slices", [(2, 4, 3), (4, 2, 4), (3, 1, 2)])
+def test_bucket_exchange_in_slices_on_one_gpu(R, K, slices, cuda_lib):
+    """The sliced form's calls with every rank on this GPU: each source buckets its cloud slice by slice (a small grid
+    per launch), each owner clears its slab with a source-less call, accumulates slice after slice from windows of its
+    pool (one window per source, run tables addressed with the pool's row length) without clearing, and normalises
+    with the last slice.  Every slab must equal the oracle's grid of the whole cloud."""
+    kw = dict(grid_min=[-2.0, -2.0, -2.0], voxel_size=0.25, grid_size=[16, 15, 13])
+    V = 16 * 15 * 13
+    N = 30_000
+    pts, feats = _cloud(N, 900 + R + K)
+    cuts = [N * r // R for r in range(R + 1)]
+    chunks = (N // R + 1023) // 1024 + 2            # capacity per source; the last slice of some sources stays empty
+    cs = (chunks + slices - 1) // slices
+    blk = int(cuda_lib.rc_voxel_bucket_block_records(K))
+    nblocks = R * chunks
+    pools = [dict(ids=torch.full((nblocks * blk,), 123456789, dtype=torch.int32, device=DEV),
+                  feats=torch.full((nblocks * blk, 4), float("nan"), device=DEV),
+                  runs=torch.full((K * nblocks,), 0x7fff7fff, dtype=torch.int32, device=DEV)) for _ in range(R)]
+    dest = ([p["ids"].data_ptr() for p in pools], [p["feats"].data_ptr() for p in pools], [p["runs"].data_ptr() for p in pools])
+    for r in range(R):
+        p_r, f_r = pts[cuts[r]:cuts[r + 1]].to(DEV), feats[cuts[r]:cuts[r + 1]].to(DEV)
+        n_r = p_r.shape[0]
+        for s in range(slices):
+            c0 = min(s * cs, chunks)
+            nch = min(cs, chunks - c0)
+            p0, p1 = min(n_r, c0 * 1024), min(n_r, (c0 + nch) * 1024)
+            ops.voxel_bucket_exchange_cuda(p_r[p0:p1], f_r[p0:p1], kw["grid_min"], kw["voxel_size"], kw["grid_size"], R, K, nch,
+                                           r * chunks + c0, nblocks, *dest, ctas_per_sm=1 + s % 3)
+    exp, ecnt, sabs = oracle.voxelize_pointcloud(pts, feats, mode="mean", return_aux=True, **kw)
+    tol = oracle.mean_tolerance(ecnt, sabs, exp).reshape(V, 4)
+    exp, ecnt = exp.reshape(V, 4), ecnt.reshape(V)
+    for d in range(R):
+        lo, hi = sharding.slab_bounds(V, d, R)
+        out = ops.voxel_slab_buffers(hi - lo, 4, "mean", torch.device(DEV))
+        out[0].fill_(float("nan")); out[1].fill_(77)
+        ops.voxel_scatter_buckets_cuda([], [], [], 0, K, DEV, lo, hi, normalize=False, out=out)      # clears only
+        assert int(out[1].abs().sum()) == 0 and float(out[0].abs().sum()) == 0.0
+        for s in range(slices):
+            c0 = min(s * cs, chunks)
+            nch = min(cs, chunks - c0)
+            first = [r * chunks + c0 for r in range(R)]
+            ops.voxel_scatter_buckets_cuda([pools[d]["ids"].data_ptr() + b * blk * 4 for b in first],
+                                           [pools[d]["feats"].data_ptr() + b * blk * 16 for b in first],
+                                           [pools[d]["runs"].data_ptr() + b * 4 for b in first], nch, K, DEV, lo, hi,
+                                           normalize=(s == slices - 1), table_row_blocks=nblocks, zero_init=False, out=out)
+        assert torch.equal(out[1].cpu(), ecnt[lo:hi]), (d, R, K)
+        assert bool(((out[0].cpu() - exp[lo:hi]).abs() <= tol[lo:hi]).all()), (d, R, K)
+    with pytest.raises(RuntimeError):
+        ops.voxel_bucket_exchange_cuda(pts[:10].to(DEV), feats[:10].to(DEV), kw["grid_min"], kw["voxel_size"], kw["grid_size"], R, K, 1,
+                                       0, nblocks, *dest, ctas_per_sm=9)
