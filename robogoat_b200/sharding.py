@@ -380,7 +380,8 @@ class BucketExchange:
     ``world * ceil(points_per_rank / 1024)`` blocks of about 1 K records of 20 bytes.  Construction and ``close`` are
     collective."""
 
-    def __init__(self, points_per_rank: int, n_voxels: int, group=None, fetch: bool = False):
+    def __init__(self, points_per_rank: int, n_voxels: int, group=None, fetch: bool = False,
+                 sub_ranges: Optional[int] = None):
         from .peer import PeerBuffer
         self.group = group
         self.fetch = bool(fetch)
@@ -389,6 +390,10 @@ class BucketExchange:
             raise RuntimeError("the bucket exchange supports at most 16 ranks")
         self.rank, self.world = rank, ws
         self.per_group = max(1, min(16 // ws, sub_parts(int(n_voxels), 4, ws, "mean")))
+        if sub_ranges is not None:          # fewer sub-ranges: larger pieces on the link, less locality for the owner's atomics
+            if not 1 <= int(sub_ranges) <= 16 // ws:
+                raise ValueError(f"sub_ranges must be between 1 and {16 // ws} for {ws} ranks")
+            self.per_group = int(sub_ranges)
         self.chunks = (int(points_per_rank) + 1023) // 1024
         self.capacity = self.chunks * 1024
         dev = torch.device("cuda", torch.cuda.current_device())
