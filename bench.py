@@ -882,6 +882,17 @@ def sharded_parity(dev, rank, world, px, bx=None, bxs=None) -> dict:
                 got, gcnt = sharding.voxelize_sharded_buckets(pl, fl, small, return_counts=True, slices=slices, **kw)
                 flags[key + "_sliced"] = flags[key + "_sliced"] and count_ok(gcnt, xa, xb) and mean_ok(got, xa, xb)
             small.close()
+    sr = None
+    try:
+        sr = sharding.SparseReduce(records_per_pair=V // world + 4096)
+    except RuntimeError:
+        pass
+    if sr is not None:
+        flags["sparse_reduce"] = True
+        for _ in range(2):
+            got, gcnt = sharding.voxelize_sharded_sparse(pl, fl, sr, return_counts=True, **kw)
+            flags["sparse_reduce"] = flags["sparse_reduce"] and count_ok(gcnt, xa, xb) and mean_ok(got, xa, xb)
+        sr.close()
     names = sorted(flags)
     t = torch.tensor([1 if flags[k] else 0 for k in names], dtype=torch.int32, device=dev)
     dist.all_reduce(t, op=dist.ReduceOp.MIN)
@@ -963,12 +974,22 @@ def multi_gpu_extras(L, dev, rank, world, ex, pts, feats, kw, N, single_ms):
                       lambda m: sharding.voxelize_sharded_buckets(pts, feats, bx, slices=4, **kw),
                       "the same in four slices on three streams: while slice s+1 is bucketed and stored over NVLink (a grid of 2 CTAs "
                       "per SM: the stores are link-bound), the owners accumulate slice s; per-slice barriers on a stream of their own"))
+    sr = None
+    try:
+        sr = sharding.SparseReduce(records_per_pair=(12 << 20) // world)
+    except RuntimeError as e:
+        ex["voxel_sharded_sparse_reduce_unavailable"] = str(e)[:200]
+    if sr is not None:
+        forms.append(("sparse_reduce", "sparse_reduce", lambda m: sharding.voxelize_sharded_sparse(pts, feats, sr, check=False, **kw),
+                      "every rank bins its own points into a private full grid, then only the occupied voxels of the other ranks' slabs "
+                      "travel (24 B per occupied voxel instead of 20 B per point) and the owners add them to their own slab; pays "
+                      "because this cloud puts 13 points into an occupied voxel on average - data dependent, unlike the exchanges"))
     if bxs is not None:
         forms.append(("bucket_exchange_fetch", "bucket_exchange_store", lambda m: sharding.voxelize_sharded_buckets(pts, feats, bxs, **kw),
                       "same pools in the sources' own memory; every owner's accumulation kernel fetches its blocks over NVLink as it goes"))
     for mode in ("mean", "count"):
         for name, pkey, fn, note in forms:
-            if name.startswith("bucket_exchange") and mode != "mean":
+            if (name.startswith("bucket_exchange") or name == "sparse_reduce") and mode != "mean":
                 continue
             ms = timed(lambda: fn(mode))
             ok = bool(parity.get(pkey))
@@ -1027,6 +1048,37 @@ def multi_gpu_extras(L, dev, rank, world, ex, pts, feats, kw, N, single_ms):
             "bound": "the move kernel (NVLink, measured 770 GB/s per direction) and the owner's atomics run back to back here; "
                      "the batched form overlaps them"})
         px.close()
+    if sr is not None:
+        rec = ex["voxel_mean_sharded_sparse_reduce"]
+        overflowed = bool(int(sr.overflow.item()))       # reduced over the ranks by the last call
+        rec["record_lists_overflowed"] = overflowed
+        if overflowed:
+            rec["Gpts/s_total"], rec["parity"] = 0.0, False
+        # stages, each max over ranks
+        Vv = 512 ** 3
+        a_v, b_v = sharding.slab_bounds(Vv, rank, world)
+        others = [(rank + k) % world for k in range(1, world)]
+        d_ids, d_sums, d_counts, d_nrec = sr.destinations(others)
+        s_ids, s_sums, s_counts, s_nrec = sr.sources(others)
+        barrier(world)
+        sr.stream_barrier()
+        ev[0].record()
+        g_, c_ = ops.voxelize_pointcloud_cuda(pts, feats, kw["grid_min"], kw["voxel_size"], kw["grid_size"], "mean", normalize=False)
+        g_, c_ = g_.view(Vv, 4), c_.view(Vv)
+        ev[1].record()
+        ops.voxel_sparse_send_cuda(g_, c_, [sharding.slab_bounds(Vv, d, world) for d in others], sr.capacity, d_ids, d_sums, d_counts,
+                                   d_nrec, sr.cursors, sr.overflow)
+        ev[2].record()
+        sr.stream_barrier()
+        ops.voxel_sparse_merge_cuda(s_ids, s_sums, s_counts, s_nrec, sr.capacity, g_, c_, a_v, b_v)
+        ev[3].record(); torch.cuda.synchronize()
+        sent = int(sr.cursors[:len(others)].sum().item())
+        stages = [max_over_ranks(ev[i].elapsed_time(ev[i + 1]), world, dev) for i in range(3)]
+        rec.update({"stage_ms": {"private_full_grid": stages[0], "send_occupied_voxels": stages[1], "barrier_merge_normalise": stages[2]},
+                    "records_sent_rank0": sent, "bytes_sent_rank0": sent * 24, "capacity_per_pair": sr.capacity,
+                    "nvlink_GB/s_out_during_send": sent * 24 / (stages[1] * 1e-3) / 1e9})
+        del g_, c_
+        sr.close()
     for key, ex_ in (("bucket_exchange", bx), ("bucket_exchange_fetch", bxs)):
         if ex_ is None:
             continue

@@ -313,6 +313,34 @@ RC_API int rc_voxel_scatter_buckets(const void* const* pool_ids, const void* con
                                     int64_t id_end, uint32_t flags, int device, void* stream);
 
 /*
+ * Sparse reduction of partial grids (mean mode, four feature channels): when a cloud puts many points into every
+ * occupied voxel, a rank that has binned its own points into a private full-size grid (feature sums + counts, not
+ * normalised) sends every other rank only the occupied voxels of that rank's slab - 24 bytes per occupied voxel
+ * instead of 20 bytes per point.
+ * rc_voxel_sparse_send: for each of n_dest (<= 16) voxel ranges [id_begin_host[r], id_end_host[r]) of grid (fp32
+ *   [V,4] sums) / counts (int32 [V]), appends (voxel id, sums, count) of every voxel with a non-zero count to record
+ *   list r: dest_ids[r] int32 [capacity], dest_sums[r] fp32 [capacity,4], dest_counts[r] int32 [capacity] (HOST
+ *   arrays of device pointers; the lists may lie in peer memory and are written with plain stores), in no particular
+ *   order; then stores the number of records to *dest_nrec[r].  Records beyond `capacity` are dropped - the stored
+ *   number still counts them, and *overflow (int32 on this GPU, may be NULL) is set to 1: the caller must check it
+ *   (after reducing it over the ranks) before trusting the result.  cursors: int32 [n_dest] scratch on this GPU.
+ * rc_voxel_sparse_merge: the owner adds the record lists of n_src sources (HOST arrays of device pointers; the
+ *   record numbers are read on the device from *src_nrec[i], clamped to capacity) to its slab [id_begin, id_end) of
+ *   its own partial grid (grid / counts point at voxel id_begin) and normalises the slab unless flags has
+ *   RC_VOXEL_NO_NORMALIZE.
+ * The caller orders senders against owners with a barrier on the stream between the two calls and before the next
+ * send.  No counterpart in the reference.
+ */
+RC_API int rc_voxel_sparse_send(const float* grid, const int32_t* counts, int32_t n_dest, const int64_t* id_begin_host,
+                                const int64_t* id_end_host, int64_t capacity, void* const* dest_ids,
+                                void* const* dest_sums, void* const* dest_counts, void* const* dest_nrec,
+                                int32_t* cursors, int32_t* overflow, int device, void* stream);
+RC_API int rc_voxel_sparse_merge(int32_t n_src, const void* const* src_ids, const void* const* src_sums,
+                                 const void* const* src_counts, const void* const* src_nrec, int64_t capacity,
+                                 float* grid, int32_t* counts, int64_t id_begin, int64_t id_end, uint32_t flags,
+                                 int device, void* stream);
+
+/*
  * Device buffers that the other processes of a node can map, for rc_voxel_partition_move's remote
  * destinations.  rc_peer_alloc allocates `bytes` on `device` (cudaMalloc) and fills the 64-byte CUDA IPC
  * handle to hand to the other processes; rc_peer_open maps such a handle into this process on `device`

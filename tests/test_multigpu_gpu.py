@@ -115,6 +115,22 @@ for fetch in (True, False):                 # owners fetch the records over NVLi
             assert torch.equal(cnts.cpu(), c2.reshape(V)[a:b]), f"bucket counts {rep} fetch={fetch} slices={slices}"
             assert bool(((slab.cpu() - m2.reshape(V, 4)[a:b]).abs() <= t2[a:b]).all()), f"bucket mean {rep} fetch={fetch} slices={slices}"
     bx.close()
+# sparse reduction: private full grids, only occupied voxels travel; twice in a row, then with lists that are too small
+sr = sharding.SparseReduce(records_per_pair=V)
+for rep in range(2):
+    l, h = spans[rank]
+    slab, cnts = sharding.voxelize_sharded_sparse(pts[l:h], feats[l:h], sr, return_counts=True, **kw)
+    a, b = sharding.slab_bounds(V, rank, ws)
+    assert torch.equal(cnts.cpu(), cnt.reshape(V)[a:b]), f"sparse counts {rep}"
+    assert mean_ok(slab, a, b), f"sparse mean {rep}"
+sr.close()
+tiny = sharding.SparseReduce(records_per_pair=8)
+try:
+    sharding.voxelize_sharded_sparse(pts[l:h], feats[l:h], tiny, **kw)
+    raise AssertionError("overflow not reported")
+except RuntimeError as e:
+    assert "overflowed" in str(e), e
+tiny.close()
 small = sharding.PointExchange(capacity=10, feature_width=4)
 slab = sharding.voxelize_sharded_exchange(pts[lo:hi], None, mode="count", direct=small, **kw)
 a, b = sharding.slab_bounds(V, rank, ws)

@@ -330,3 +330,86 @@ def test_bucket_exchange_in_slices_on_one_gpu(R, K, slices, cuda_lib):
     with pytest.raises(RuntimeError):
         ops.voxel_bucket_exchange_cuda(pts[:10].to(DEV), feats[:10].to(DEV), kw["grid_min"], kw["voxel_size"], kw["grid_size"], R, K, 1,
                                        0, nblocks, *dest, ctas_per_sm=9)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("R", [1, 2, 3, 8])
+@pytest.mark.parametrize("N", [0, 1, 5000, 60_000])
+def test_sparse_reduce_with_every_rank_on_one_gpu(R, N, cuda_lib):
+    """The sparse reduction's two calls with all ranks on this GPU: every source bins its shard into a private full
+    grid (sums + counts), appends the occupied voxels of every other owner's slab to that owner's list, and every owner
+    adds the lists to its own slab and normalises.  Each slab must equal the oracle's grid of the whole cloud.  The
+    grid's voxel count is not a multiple of 4 or of the rank count, so ranges start at odd offsets."""
+    kw = dict(grid_min=[-2.0, -2.0, -2.0], voxel_size=0.25, grid_size=[17, 15, 13])
+    V = 17 * 15 * 13
+    pts, feats = _cloud(N, 700 + R + N)
+    cuts = [N * r // R for r in range(R + 1)]
+    cap = V
+    lists = [dict(ids=torch.full((R * cap,), -7, dtype=torch.int32, device=DEV), sums=torch.full((R * cap, 4), float("nan"), device=DEV),
+                  cnts=torch.full((R * cap,), -1, dtype=torch.int32, device=DEV),
+                  nrec=torch.full((R,), 12345, dtype=torch.int32, device=DEV)) for _ in range(R)]
+    cursors = torch.zeros(16, dtype=torch.int32, device=DEV)
+    overflow = torch.zeros(1, dtype=torch.int32, device=DEV)
+    partial = []
+    for r in range(R):
+        g, c = ops.voxelize_pointcloud_cuda(pts[cuts[r]:cuts[r + 1]].to(DEV), feats[cuts[r]:cuts[r + 1]].to(DEV), kw["grid_min"],
+                                            kw["voxel_size"], kw["grid_size"], "mean", normalize=False)
+        g, c = g.view(V, 4), c.view(V)
+        partial.append((g, c))
+        others = [(r + k) % R for k in range(1, R)]
+        ops.voxel_sparse_send_cuda(g, c, [sharding.slab_bounds(V, d, R) for d in others], cap,
+                                   [lists[d]["ids"].data_ptr() + r * cap * 4 for d in others],
+                                   [lists[d]["sums"].data_ptr() + r * cap * 16 for d in others],
+                                   [lists[d]["cnts"].data_ptr() + r * cap * 4 for d in others],
+                                   [lists[d]["nrec"].data_ptr() + r * 4 for d in others], cursors, overflow)
+        assert int(overflow.item()) == 0
+    if N:
+        exp, ecnt, sabs = oracle.voxelize_pointcloud(pts, feats, mode="mean", return_aux=True, **kw)
+        tol = oracle.mean_tolerance(ecnt, sabs, exp).reshape(V, 4)
+        exp, ecnt = exp.reshape(V, 4), ecnt.reshape(V)
+    else:
+        exp, ecnt, tol = torch.zeros(V, 4), torch.zeros(V, dtype=torch.int32), torch.zeros(V, 4)
+    for d in range(R):
+        lo, hi = sharding.slab_bounds(V, d, R)
+        srcs = [(d + k) % R for k in range(1, R)]
+        g, c = partial[d]
+        ops.voxel_sparse_merge_cuda([lists[d]["ids"].data_ptr() + s * cap * 4 for s in srcs],
+                                    [lists[d]["sums"].data_ptr() + s * cap * 16 for s in srcs],
+                                    [lists[d]["cnts"].data_ptr() + s * cap * 4 for s in srcs],
+                                    [lists[d]["nrec"].data_ptr() + s * 4 for s in srcs], cap, g, c, lo, hi)
+        assert torch.equal(c[lo:hi].cpu(), ecnt[lo:hi]), (d, R)
+        assert bool(((g[lo:hi].cpu() - exp[lo:hi]).abs() <= tol[lo:hi]).all()), (d, R)
+        # the number of records a source sent is the number of voxels it occupies in this slab
+        for s_ in srcs:
+            sent = int(lists[d]["nrec"][s_].item())
+            # partial[s_] counts outside its own slab are untouched by any merge
+            assert sent == int((partial[s_][1][lo:hi] > 0).sum()), (d, s_)
+
+
+@pytest.mark.gpu
+def test_sparse_reduce_overflow_is_reported_and_harmless(cuda_lib):
+    """A record list that is too small: the published number still counts every occupied voxel, the overflow flag is
+    raised, nothing is written past the list, and the merge reads no more than the capacity."""
+    kw = dict(grid_min=[-2.0, -2.0, -2.0], voxel_size=0.25, grid_size=[16, 16, 16])
+    V = 16 ** 3
+    pts, feats = _cloud(20_000, 31)
+    g, c = ops.voxelize_pointcloud_cuda(pts.to(DEV), feats.to(DEV), kw["grid_min"], kw["voxel_size"], kw["grid_size"], "mean",
+                                        normalize=False)
+    g, c = g.view(V, 4), c.view(V)
+    cap = 100
+    ids = torch.full((cap + 64,), -7, dtype=torch.int32, device=DEV)
+    sums = torch.zeros(cap + 64, 4, device=DEV)
+    cnts = torch.full((cap + 64,), -1, dtype=torch.int32, device=DEV)
+    nrec = torch.zeros(1, dtype=torch.int32, device=DEV)
+    cursors = torch.zeros(16, dtype=torch.int32, device=DEV)
+    overflow = torch.zeros(1, dtype=torch.int32, device=DEV)
+    ops.voxel_sparse_send_cuda(g, c, [(0, V)], cap, [ids.data_ptr()], [sums.data_ptr()], [cnts.data_ptr()], [nrec.data_ptr()],
+                               cursors, overflow)
+    occupied = int((c > 0).sum())
+    assert occupied > cap and int(nrec.item()) == occupied and int(overflow.item()) == 1
+    assert bool((ids[cap:] == -7).all()) and bool((cnts[cap:] == -1).all())
+    assert bool((ids[:cap] >= 0).all())
+    g2, c2 = torch.zeros(V, 4, device=DEV), torch.zeros(V, dtype=torch.int32, device=DEV)
+    ops.voxel_sparse_merge_cuda([ids.data_ptr()], [sums.data_ptr()], [cnts.data_ptr()], [nrec.data_ptr()], cap, g2, c2, 0, V,
+                                normalize=False)
+    assert int((c2 > 0).sum()) == cap and int(c2.sum()) == int(cnts[:cap].sum())
