@@ -905,6 +905,7 @@ def multi_gpu_extras(L, dev, rank, world, ex, pts, feats, kw, N, single_ms):
     reference's all_reduce(MAX).  ``efficiency`` = one GPU's time for its 2^26 points / this time (weak scaling)."""
     from robogoat_b200 import sharding, ops
     import workloads
+    import torch.distributed as dist
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
 
     def timed(fn, iters=5, warm=2):
@@ -1048,6 +1049,28 @@ def multi_gpu_extras(L, dev, rank, world, ex, pts, feats, kw, N, single_ms):
             "bound": "the move kernel (NVLink, measured 770 GB/s per direction) and the owner's atomics run back to back here; "
                      "the batched form overlaps them"})
         px.close()
+    if sr is not None and bx is not None:
+        # full size, where no CPU oracle is affordable: the two fastest forms share no kernel after the points are read
+        # (sorted records over NVLink against private grids + occupied voxels), so their slabs must agree - counts
+        # exactly, means to rounding - and the counts of all slabs must add up to the points inside the grid
+        g1, c1 = sharding.voxelize_sharded_buckets(pts, feats, bx, return_counts=True, slices=4, **kw)
+        g2, c2 = sharding.voxelize_sharded_sparse(pts, feats, sr, return_counts=True, check=False, **kw)
+        same_counts = bool(torch.equal(c1, c2))
+        worst = float(((g1 - g2).abs() - 1e-5 * g1.abs()).max().item()) if g1.numel() else 0.0
+        inside = torch.tensor([int(c2.sum(dtype=torch.int64).item()), int(c1.sum(dtype=torch.int64).item())], dtype=torch.int64, device=dev)
+        dist.all_reduce(inside)
+        cgrid = sharding.voxelize_sharded_slab(pts, None, mode="count", **kw)
+        total = torch.tensor([int(cgrid.sum(dtype=torch.int64).item())], dtype=torch.int64, device=dev)
+        dist.all_reduce(total)
+        okf = torch.tensor([1 if (same_counts and worst <= 1e-5) else 0], dtype=torch.int32, device=dev)
+        dist.all_reduce(okf, op=dist.ReduceOp.MIN)
+        ex["voxel_mean_sharded_full_scale_agreement"] = {
+            "bucket_exchange_sliced_vs_sparse_reduce": bool(okf.item()) and inside[0].item() == inside[1].item() == total[0].item(),
+            "points_inside_grid_all_ranks": int(total[0].item()), "counted_by_sparse_reduce": int(inside[0].item()),
+            "counted_by_bucket_exchange": int(inside[1].item()),
+            "checked": "per rank: slab counts identical, |mean difference| <= 1e-5 (1 + |mean|); over all ranks: counts add up to the "
+                       "reduce-scatter count grid's total"}
+        del g1, c1, g2, c2, cgrid
     if sr is not None:
         rec = ex["voxel_mean_sharded_sparse_reduce"]
         overflowed = bool(int(sr.overflow.item()))       # reduced over the ranks by the last call
