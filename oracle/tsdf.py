@@ -48,7 +48,8 @@ def voxelize_tsdf(points, normals: Optional[object], grid_size: Sequence[int], v
             dx = (cx - x)[None, None, :]
             dy = (cy - y)[None, :, None]
             dz = (cz - z)[:, None, None]
-            dist = np.sqrt((dx * dx + dy * dy) + dz * dz)
+            with np.errstate(over="ignore"):                      # a far-away point squares to inf, as on the GPU
+                dist = np.sqrt((dx * dx + dy * dy) + dz * dz)
             hit = dist < trunc
             if not hit.any():
                 continue

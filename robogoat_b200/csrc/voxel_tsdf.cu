@@ -69,10 +69,16 @@ voxel_tsdf_kernel(const float* __restrict__ pts, const float* __restrict__ norma
             const unsigned int wx = x1 - x0 + 1, wy = y1 - y0 + 1;
             const unsigned int ncell = wx * wy * static_cast<unsigned int>(z1 - z0 + 1);   // <= 1025^3 < 2^31
             const long long item = ((base + j) / N) * V;
+            // c / w for the whole neighbourhood from one reciprocal per point: floor(c * ceil(2^32 / w) / 2^32) is
+            // exact while c * w < 2^32; w <= 1025, so neighbourhoods of up to 2^20 cells qualify (w = 1 has no 32-bit
+            // reciprocal); larger ones divide
+            const bool fast = ncell <= (1u << 20);
+            const unsigned int mx = static_cast<unsigned int>((0x100000000ull + wx - 1) / wx);
+            const unsigned int my = static_cast<unsigned int>((0x100000000ull + wy - 1) / wy);
             for (unsigned int c = lane; c < ncell; c += 32) {
-                const unsigned int r = c / wx;
+                const unsigned int r = (wx == 1) ? c : (fast ? __umulhi(c, mx) : c / wx);
                 const int vx = x0 + static_cast<int>(c - r * wx);
-                const unsigned int q = r / wy;
+                const unsigned int q = (wy == 1) ? r : (fast ? __umulhi(r, my) : r / wy);
                 const int vy = y0 + static_cast<int>(r - q * wy);
                 const int vz = z0 + static_cast<int>(q);
                 // voxel centre and distance: single fp32 operations in this order (no contraction)

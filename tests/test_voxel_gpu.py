@@ -333,6 +333,21 @@ def test_tsdf_matches_oracle(B, N, with_normals):
 
 
 @pytest.mark.gpu
+def test_tsdf_neighbourhood_larger_than_2_pow_20_cells():
+    """A truncation distance that covers the whole grid of 1.155 M voxels: neighbourhoods above 2^20 cells index their
+    cells by division instead of the reciprocal multiply."""
+    from oracle import tsdf as otsdf
+    from robogoat_b200.batched import voxelize_tsdf
+    dhw, vs, origin, trunc = (100, 105, 110), 1.0, (0.0, 0.0, 0.0), 200.0
+    pts = torch.tensor([[[3.2, 50.1, 97.7], [60.5, 10.25, 20.0], [109.9, 104.9, 0.1]]])
+    nrm = torch.tensor([[[1.0, 0.0, 0.0], [0.0, -1.0, 0.0], [0.6, 0.0, 0.8]]])
+    t, w = voxelize_tsdf(pts.to(DEV), nrm.to(DEV), dhw, vs, origin, trunc)
+    et, ew = otsdf.voxelize_tsdf(pts.numpy(), nrm.numpy(), dhw, vs, origin, trunc)
+    assert torch.equal(w.cpu(), torch.from_numpy(ew)) and float(ew.min()) == 3.0
+    assert torch.equal(t.cpu().view(torch.int32), torch.from_numpy(et).view(torch.int32))
+
+
+@pytest.mark.gpu
 def test_tsdf_argument_errors_and_empty():
     from robogoat_b200.batched import voxelize_tsdf
     pts = torch.zeros(1, 4, 3, device=DEV)
