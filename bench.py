@@ -872,7 +872,7 @@ def sharded_parity(dev, rank, world, px, bx=None, bxs=None) -> dict:
             continue
         flags[key] = True
         for _ in range(2):          # twice: the second call's records meet pools that have just been read
-            got, gcnt = sharding.voxelize_sharded_buckets(pl, fl, ex_, return_counts=True, **kw)
+            got, gcnt = sharding.voxelize_sharded_buckets(pl, fl, ex_, return_counts=True, slices=1, **kw)
             flags[key] = flags[key] and count_ok(gcnt, xa, xb) and mean_ok(got, xa, xb)
         if not ex_.fetch:
             # sliced form, on pools sized for this cloud so that every slice carries points
@@ -968,7 +968,7 @@ def multi_gpu_extras(L, dev, rank, world, ex, pts, feats, kw, N, single_ms):
                    lambda m: sharding.voxelize_sharded_exchange(pts, feats if m == "mean" else None, mode=m, direct=px, batches=4, **kw),
                    "same in four slices of the local cloud: the stores of slice i+1 overlap the owners' accumulation of slice i")]
     if bx is not None:
-        forms.append(("bucket_exchange", "bucket_exchange", lambda m: sharding.voxelize_sharded_buckets(pts, feats, bx, **kw),
+        forms.append(("bucket_exchange", "bucket_exchange", lambda m: sharding.voxelize_sharded_buckets(pts, feats, bx, slices=1, **kw),
                       "one bucket kernel sorts every chunk by (owner, sub-range) and stores each owner's records into a fixed block of "
                       "that owner's pool over NVLink; no counts, no host synchronisation, two barriers on the stream; mean mode only"))
         forms.append(("bucket_exchange_sliced", "bucket_exchange_sliced",
@@ -1122,7 +1122,7 @@ def multi_gpu_extras(L, dev, rank, world, ex, pts, feats, kw, N, single_ms):
         stages = [max_over_ranks(ev[i].elapsed_time(ev[i + 1]), world, dev) for i in range(3)]
         del r
         L.rc_set_option(5, 0)                   # the bucket kernel's write-out by ordinary stores instead of bulk copies
-        ms_plain = timed(lambda: sharding.voxelize_sharded_buckets(pts, feats, ex_, **kw))
+        ms_plain = timed(lambda: sharding.voxelize_sharded_buckets(pts, feats, ex_, slices=1, **kw))
         L.rc_set_option(5, 1)
         ex[f"voxel_mean_sharded_{key}"]["ms_with_ordinary_stores"] = ms_plain
         remote_bytes = N * 20 * (world - 1) / world

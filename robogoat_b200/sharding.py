@@ -582,7 +582,7 @@ def _lib_handle():
 
 def voxelize_sharded_buckets(points_local: torch.Tensor, features_local: torch.Tensor, exchange: BucketExchange,
                              grid_min=(-10.0, -10.0, -10.0), voxel_size: float = 0.1, grid_size=(128, 128, 128),
-                             return_counts: bool = False, group=None, slices: int = 1):
+                             return_counts: bool = False, group=None, slices: Optional[int] = None):
     """Mean-mode voxelisation of a cloud spread over the ranks, output slab-sharded as ``voxelize_sharded_exchange``
     returns it ([voxels of this rank's slab, 4]), by the bucket exchange: one bucket kernel, one barrier, then the
     owner's accumulation (which, in the fetching form, pulls the records over NVLink as it goes) and normalisation -
@@ -590,7 +590,8 @@ def voxelize_sharded_buckets(points_local: torch.Tensor, features_local: torch.T
 
     ``slices`` > 1 (storing form): the cloud is bucketed slice after slice on the calling stream, and while slice
     s+1 is on its way over NVLink the owners already accumulate slice s on a second stream; a third stream carries
-    the per-slice barriers so that the bucket kernels follow one another without waiting for them."""
+    the per-slice barriers so that the bucket kernels follow one another without waiting for them.  Default: four
+    slices for exchanges sized for 2^22 points per rank or more (where the overlap pays for the extra launches), else one."""
     from . import ops
     rank, ws = world(group)
     V = int(grid_size[0]) * int(grid_size[1]) * int(grid_size[2])
@@ -599,6 +600,8 @@ def voxelize_sharded_buckets(points_local: torch.Tensor, features_local: torch.T
     if points_local.shape[0] > exchange.capacity:
         raise RuntimeError(f"{points_local.shape[0]} points exceed the exchange's capacity of {exchange.capacity} per rank")
     a, b = slab_bounds(V, rank, ws)
+    if slices is None:
+        slices = 4 if (exchange.chunks >= 4096 and not exchange.fetch) else 1
     if int(slices) > 1 and not exchange.fetch:
         return _buckets_sliced(points_local, features_local, exchange, list(grid_min), float(voxel_size), list(grid_size),
                                int(slices), a, b, return_counts)
