@@ -892,6 +892,7 @@ def sharded_parity(dev, rank, world, px, bx=None, bxs=None) -> dict:
         for _ in range(2):
             got, gcnt = sharding.voxelize_sharded_sparse(pl, fl, sr, return_counts=True, **kw)
             flags["sparse_reduce"] = flags["sparse_reduce"] and count_ok(gcnt, xa, xb) and mean_ok(got, xa, xb)
+            flags["sparse_reduce"] = flags["sparse_reduce"] and count_ok(sharding.voxelize_sharded_sparse(pl, None, sr, mode="count", **kw), xa, xb)
         sr.close()
     names = sorted(flags)
     t = torch.tensor([1 if flags[k] else 0 for k in names], dtype=torch.int32, device=dev)
@@ -981,7 +982,8 @@ def multi_gpu_extras(L, dev, rank, world, ex, pts, feats, kw, N, single_ms):
     except RuntimeError as e:
         ex["voxel_sharded_sparse_reduce_unavailable"] = str(e)[:200]
     if sr is not None:
-        forms.append(("sparse_reduce", "sparse_reduce", lambda m: sharding.voxelize_sharded_sparse(pts, feats, sr, check=False, **kw),
+        forms.append(("sparse_reduce", "sparse_reduce",
+                      lambda m: sharding.voxelize_sharded_sparse(pts, feats if m == "mean" else None, sr, check=False, mode=m, **kw),
                       "every rank bins its own points into a private full grid, then only the occupied voxels of the other ranks' slabs "
                       "travel (24 B per occupied voxel instead of 20 B per point) and the owners add them to their own slab; pays "
                       "because this cloud puts 13 points into an occupied voxel on average - data dependent, unlike the exchanges"))
@@ -990,7 +992,7 @@ def multi_gpu_extras(L, dev, rank, world, ex, pts, feats, kw, N, single_ms):
                       "same pools in the sources' own memory; every owner's accumulation kernel fetches its blocks over NVLink as it goes"))
     for mode in ("mean", "count"):
         for name, pkey, fn, note in forms:
-            if (name.startswith("bucket_exchange") or name == "sparse_reduce") and mode != "mean":
+            if name.startswith("bucket_exchange") and mode != "mean":
                 continue
             ms = timed(lambda: fn(mode))
             ok = bool(parity.get(pkey))
@@ -1075,8 +1077,9 @@ def multi_gpu_extras(L, dev, rank, world, ex, pts, feats, kw, N, single_ms):
         rec = ex["voxel_mean_sharded_sparse_reduce"]
         overflowed = bool(int(sr.overflow.item()))       # reduced over the ranks by the last call
         rec["record_lists_overflowed"] = overflowed
-        if overflowed:
-            rec["Gpts/s_total"], rec["parity"] = 0.0, False
+        if overflowed:              # the same occupied voxels travel in both modes
+            for m_ in ("mean", "count"):
+                ex[f"voxel_{m_}_sharded_sparse_reduce"].update({"Gpts/s_total": 0.0, "parity": False})
         # stages, each max over ranks
         Vv = 512 ** 3
         a_v, b_v = sharding.slab_bounds(Vv, rank, world)

@@ -328,6 +328,7 @@ RC_API int rc_voxel_scatter_buckets(const void* const* pool_ids, const void* con
  *   record numbers are read on the device from *src_nrec[i], clamped to capacity) to its slab [id_begin, id_end) of
  *   its own partial grid (grid / counts point at voxel id_begin) and normalises the slab unless flags has
  *   RC_VOXEL_NO_NORMALIZE.
+ * Count mode: grid = NULL in both calls and NULL entries in dest_sums / src_sums - records are (voxel id, count) only.
  * The caller orders senders against owners with a barrier on the stream between the two calls and before the next
  * send.  No counterpart in the reference.
  */

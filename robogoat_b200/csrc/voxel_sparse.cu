@@ -1,4 +1,4 @@
-// Sparse reduction of partial voxel grids across GPUs (mean mode, four feature channels).
+// Sparse reduction of partial voxel grids across GPUs (mean mode with four feature channels, and count mode).
 //
 // When a cloud puts many points into each occupied voxel, a rank's partial grid holds far fewer occupied voxels than
 // the rank has points (the 2^26-point mixture: 4.8 M of 134 M voxels), so after binning its own points into a private
@@ -48,7 +48,7 @@ __device__ __forceinline__ void sparse_flush(const SparseDests& d, int r, int fi
         const long long slot = base + i;
         if (slot < capacity) {
             d.ids[r][slot] = s_ids[i];
-            d.sums[r][slot] = s_sums[i];
+            if (d.sums[r] != nullptr) d.sums[r][slot] = s_sums[i];
             d.cnts[r][slot] = s_cnts[i];
         }
     }
@@ -99,10 +99,12 @@ voxel_sparse_send_kernel(const float4* __restrict__ grid, const int* __restrict_
             fill = 0;
             fill_r = r;
         }
-        float4 sv[4];
+        float4 sv[4] = {};
+        if (grid != nullptr) {                                    // count mode has no feature sums
 #pragma unroll
-        for (int k = 0; k < 4; ++k)
-            if (c[k] > 0) sv[k] = __ldcs(grid + v0 + k);          // in flight across the prefix sum and its barrier
+            for (int k = 0; k < 4; ++k)
+                if (c[k] > 0) sv[k] = __ldcs(grid + v0 + k);      // in flight across the prefix sum and its barrier
+        }
         const int mine = (c[0] > 0) + (c[1] > 0) + (c[2] > 0) + (c[3] > 0);
         int incl = mine;                                          // inclusive prefix sum over the warp
 #pragma unroll
@@ -167,7 +169,7 @@ voxel_sparse_merge_kernel(SparseSources s, long long capacity, float* __restrict
         for (long long k = static_cast<long long>(blockIdx.x) * kThreads + threadIdx.x; k < n; k += stride) {
             const long long id = s.ids[i][k];
             if (id < id_begin || id >= id_end) continue;          // nothing a well-formed list contains
-            red_add_v4(grid0 + id * 4, __ldcs(s.sums[i] + k));
+            if (s.sums[i] != nullptr) red_add_v4(grid0 + id * 4, __ldcs(s.sums[i] + k));
             atomicAdd(counts0 + id, __ldcs(s.cnts[i] + k));
         }
     }
@@ -199,12 +201,13 @@ int rc_voxel_sparse_send(const float* grid, const int32_t* counts, int32_t n_des
         d.sums[r] = static_cast<float4*>(dest_sums[r]);
         d.cnts[r] = static_cast<int*>(dest_counts[r]);
         d.nrec[r] = static_cast<int*>(dest_nrec[r]);
-        if (d.ids[r] == nullptr || d.sums[r] == nullptr || d.cnts[r] == nullptr || d.nrec[r] == nullptr) return RC_ERR_NULL_POINTER;
+        if (d.ids[r] == nullptr || d.cnts[r] == nullptr || d.nrec[r] == nullptr) return RC_ERR_NULL_POINTER;
+        if ((grid != nullptr) != (d.sums[r] != nullptr)) return RC_ERR_NULL_POINTER;   // sums travel exactly when there is a grid
         if (!rc::aligned_to(d.ids[r], 4) || !rc::aligned_to(d.sums[r], 16) || !rc::aligned_to(d.cnts[r], 4) || !rc::aligned_to(d.nrec[r], 4))
             return RC_ERR_BAD_ALIGNMENT;
     }
     d.tile0[n_dest] = tiles;
-    if (tiles > 0 && (grid == nullptr || counts == nullptr)) return RC_ERR_NULL_POINTER;
+    if (tiles > 0 && counts == nullptr) return RC_ERR_NULL_POINTER;
     if (!rc::aligned_to(grid, 16) || !rc::aligned_to(counts, 16) || !rc::aligned_to(cursors, 4) || !rc::aligned_to(overflow, 4))
         return RC_ERR_BAD_ALIGNMENT;
     rc::DeviceScope scope(device);
@@ -231,24 +234,27 @@ int rc_voxel_sparse_merge(int32_t n_src, const void* const* src_ids, const void*
     if (n_src < 0 || n_src > kSparseMaxPeers || capacity < 0 || id_begin < 0 || id_end < id_begin) return RC_ERR_BAD_SHAPE;
     if (id_end >= (1ll << 31)) return RC_ERR_TOO_LARGE;
     const long long nvox = id_end - id_begin;
-    if (nvox > 0 && (grid == nullptr || counts == nullptr)) return RC_ERR_NULL_POINTER;
+    if (nvox > 0 && counts == nullptr) return RC_ERR_NULL_POINTER;
     if (!rc::aligned_to(grid, 16) || !rc::aligned_to(counts, 4)) return RC_ERR_BAD_ALIGNMENT;
     SparseSources s{};
     s.n = n_src;
     if (n_src > 0 && (src_ids == nullptr || src_sums == nullptr || src_counts == nullptr || src_nrec == nullptr)) return RC_ERR_NULL_POINTER;
+    if (grid == nullptr) flags |= RC_VOXEL_NO_NORMALIZE;          // count mode: nothing to normalise
     for (int i = 0; i < n_src; ++i) {
         s.ids[i] = static_cast<const int*>(src_ids[i]);
         s.sums[i] = static_cast<const float4*>(src_sums[i]);
         s.cnts[i] = static_cast<const int*>(src_counts[i]);
         s.nrec[i] = static_cast<const int*>(src_nrec[i]);
-        if (s.ids[i] == nullptr || s.sums[i] == nullptr || s.cnts[i] == nullptr || s.nrec[i] == nullptr) return RC_ERR_NULL_POINTER;
+        if (s.ids[i] == nullptr || s.cnts[i] == nullptr || s.nrec[i] == nullptr) return RC_ERR_NULL_POINTER;
+        if ((grid != nullptr) != (s.sums[i] != nullptr)) return RC_ERR_NULL_POINTER;
         if (!rc::aligned_to(s.ids[i], 4) || !rc::aligned_to(s.sums[i], 16) || !rc::aligned_to(s.cnts[i], 4) || !rc::aligned_to(s.nrec[i], 4))
             return RC_ERR_BAD_ALIGNMENT;
     }
     rc::DeviceScope scope(device);
     if (scope.status() != RC_OK) return scope.status();
     if (n_src > 0 && nvox > 0 && capacity > 0) {
-        float* grid0 = reinterpret_cast<float*>(reinterpret_cast<uintptr_t>(grid) - static_cast<uintptr_t>(id_begin) * 16u);
+        float* grid0 = grid == nullptr ? nullptr
+                                       : reinterpret_cast<float*>(reinterpret_cast<uintptr_t>(grid) - static_cast<uintptr_t>(id_begin) * 16u);
         int* counts0 = reinterpret_cast<int*>(reinterpret_cast<uintptr_t>(counts) - static_cast<uintptr_t>(id_begin) * 4u);
         long long blocks = (capacity + kThreads - 1) / kThreads;
         const long long cap = 8ll * rc::sm_count(device);

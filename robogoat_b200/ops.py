@@ -414,43 +414,49 @@ def voxel_scatter_buckets_cuda(pool_ids: Sequence[int], pool_features: Sequence[
     return [grid, counts]
 
 
-def voxel_sparse_send_cuda(grid: torch.Tensor, counts: torch.Tensor, ranges: Sequence[Tuple[int, int]], capacity: int,
+def voxel_sparse_send_cuda(grid: Optional[torch.Tensor], counts: torch.Tensor, ranges: Sequence[Tuple[int, int]], capacity: int,
                            dest_ids: Sequence[int], dest_sums: Sequence[int], dest_counts: Sequence[int],
                            dest_nrec: Sequence[int], cursors: torch.Tensor, overflow: Optional[torch.Tensor]) -> None:
     """Append the occupied voxels of every range of a partial grid (``grid`` fp32 [V, 4] feature sums, ``counts`` int32
     [V]) to the record list of that range (device addresses, possibly peer memory) and publish the record numbers;
-    see ``rc_voxel_sparse_send``.  ``cursors``: int32 [len(ranges)] scratch; ``overflow``: int32 [1] flag."""
+    see ``rc_voxel_sparse_send``.  ``cursors``: int32 [len(ranges)] scratch; ``overflow``: int32 [1] flag.  Count mode:
+    ``grid=None`` and ``dest_sums`` all ``None`` - the records are (voxel id, count)."""
     n = len(ranges)
     _check(len(dest_ids) == n and len(dest_sums) == n and len(dest_counts) == n and len(dest_nrec) == n and n <= 16,
            "one record list per range (at most 16)")
-    _check(grid.is_cuda and grid.dtype == torch.float32 and grid.is_contiguous() and grid.numel() == counts.numel() * 4
-           and counts.dtype == torch.int32 and counts.is_contiguous() and counts.device == grid.device,
-           "grid must be fp32 [V, 4] sums and counts int32 [V] on one CUDA device")
-    _check(cursors.dtype == torch.int32 and cursors.numel() >= n and cursors.device == grid.device, "cursors: int32 [ranges]")
-    dev = grid.device
+    _check(counts.is_cuda and counts.dtype == torch.int32 and counts.is_contiguous(), "counts must be int32 [V] on a CUDA device")
+    _check(grid is None or (grid.dtype == torch.float32 and grid.is_contiguous() and grid.numel() == counts.numel() * 4
+                            and counts.device == grid.device), "grid must be fp32 [V, 4] sums on the counts' device")
+    _check(cursors.dtype == torch.int32 and cursors.numel() >= n and cursors.device == counts.device, "cursors: int32 [ranges]")
+    dev = counts.device
     VP = ctypes.c_void_p * max(n, 1)
     I64 = ctypes.c_int64 * max(n, 1)
-    rc = _lib.load().rc_voxel_sparse_send(grid.data_ptr(), counts.data_ptr(), n, I64(*[int(a) for a, _ in ranges]),
+    opt = lambda p: None if p is None else int(p)
+    rc = _lib.load().rc_voxel_sparse_send(grid.data_ptr() if grid is not None else None, counts.data_ptr(), n,
+                                          I64(*[int(a) for a, _ in ranges]),
                                           I64(*[int(b) for _, b in ranges]), int(capacity), VP(*[int(p) for p in dest_ids]),
-                                          VP(*[int(p) for p in dest_sums]), VP(*[int(p) for p in dest_counts]),
+                                          VP(*[opt(p) for p in dest_sums]), VP(*[int(p) for p in dest_counts]),
                                           VP(*[int(p) for p in dest_nrec]), cursors.data_ptr(),
                                           overflow.data_ptr() if overflow is not None else None, dev.index, _stream_ptr(dev))
     _lib.check(rc, "voxel_sparse_send")
 
 
 def voxel_sparse_merge_cuda(src_ids: Sequence[int], src_sums: Sequence[int], src_counts: Sequence[int], src_nrec: Sequence[int],
-                            capacity: int, grid: torch.Tensor, counts: torch.Tensor, id_begin: int, id_end: int, *,
+                            capacity: int, grid: Optional[torch.Tensor], counts: torch.Tensor, id_begin: int, id_end: int, *,
                             normalize: bool = True) -> None:
     """Add the record lists an owner received (device addresses) to its slab [id_begin, id_end) of its own partial grid
-    (``grid`` fp32 [V, 4], ``counts`` int32 [V]: the FULL grid) and normalise the slab; see ``rc_voxel_sparse_merge``."""
+    (``grid`` fp32 [V, 4], ``counts`` int32 [V]: the FULL grid) and normalise the slab; see ``rc_voxel_sparse_merge``.
+    Count mode: ``grid=None`` and ``src_sums`` all ``None``."""
     n = len(src_ids)
     _check(len(src_sums) == n and len(src_counts) == n and len(src_nrec) == n and n <= 16, "one record list per source (at most 16)")
     _check(0 <= id_begin <= id_end <= counts.numel(), "bad voxel range")
-    dev = grid.device
+    dev = counts.device
     VP = ctypes.c_void_p * max(n, 1)
-    rc = _lib.load().rc_voxel_sparse_merge(n, VP(*[int(p) for p in src_ids]), VP(*[int(p) for p in src_sums]),
+    opt = lambda p: None if p is None else int(p)
+    rc = _lib.load().rc_voxel_sparse_merge(n, VP(*[int(p) for p in src_ids]), VP(*[opt(p) for p in src_sums]),
                                            VP(*[int(p) for p in src_counts]), VP(*[int(p) for p in src_nrec]), int(capacity),
-                                           grid.data_ptr() + int(id_begin) * 16, counts.data_ptr() + int(id_begin) * 4,
+                                           grid.data_ptr() + int(id_begin) * 16 if grid is not None else None,
+                                           counts.data_ptr() + int(id_begin) * 4,
                                            int(id_begin), int(id_end), 0 if normalize else _lib.VOXEL_NO_NORMALIZE,
                                            dev.index, _stream_ptr(dev))
     _lib.check(rc, "voxel_sparse_merge")

@@ -546,32 +546,43 @@ class SparseReduce:
 
 def voxelize_sharded_sparse(points_local: torch.Tensor, features_local: torch.Tensor, exchange: SparseReduce,
                             grid_min=(-10.0, -10.0, -10.0), voxel_size: float = 0.1, grid_size=(128, 128, 128),
-                            return_counts: bool = False, check: bool = True):
+                            return_counts: bool = False, check: bool = True, mode: str = "mean"):
     """Mean-mode voxelisation of a cloud spread over the ranks, output slab-sharded ([voxels of this rank's slab, 4], a
     view of this rank's full-size partial grid), by a sparse reduction: every rank bins its own points into a private
     full grid, sends each other rank only the occupied voxels of that rank's slab, and adds what it receives to its own
     slab.  Pays when the ranks' clouds put many points into each occupied voxel (bytes on NVLink: 24 per occupied voxel
     instead of 20 per point); needs the full grid on every rank.  ``check``: wait for the call and raise if a record
-    list overflowed (the result is then incomplete); with ``check=False`` the caller reads ``exchange.overflow``."""
+    list overflowed (the result is then incomplete); with ``check=False`` the caller reads ``exchange.overflow``.
+    ``mode="count"``: points per voxel (int32 [voxels of the slab]); the records are then (voxel id, count) only."""
     from . import ops
     rank, ws = exchange.rank, exchange.world
     V = int(grid_size[0]) * int(grid_size[1]) * int(grid_size[2])
-    if features_local is None or features_local.shape[1] != 4:
-        raise RuntimeError("the sparse reduction takes four feature channels")
-    grid, counts = ops.voxelize_pointcloud_cuda(points_local, features_local, list(grid_min), float(voxel_size), list(grid_size),
-                                                "mean", normalize=False)
-    grid, counts = grid.view(V, 4), counts.view(V)
+    if mode not in ("mean", "count"):
+        raise RuntimeError(f"Invalid mode: {mode}. The sparse reduction supports 'mean' and 'count'")
+    if mode == "count":
+        grid = None
+        counts = ops.voxelize_pointcloud_cuda(points_local, None, list(grid_min), float(voxel_size), list(grid_size), "count")[0].view(V)
+    else:
+        if features_local is None or features_local.shape[1] != 4:
+            raise RuntimeError("the sparse reduction takes four feature channels")
+        grid, counts = ops.voxelize_pointcloud_cuda(points_local, features_local, list(grid_min), float(voxel_size), list(grid_size),
+                                                    "mean", normalize=False)
+        grid, counts = grid.view(V, 4), counts.view(V)
     a, b = slab_bounds(V, rank, ws)
     others = [(rank + k) % ws for k in range(1, ws)]                # start with the neighbour: spreads the link load
     d_ids, d_sums, d_counts, d_nrec = exchange.destinations(others)
+    s_ids, s_sums, s_counts, s_nrec = exchange.sources(others)
+    if grid is None:
+        d_sums, s_sums = [None] * len(others), [None] * len(others)
     exchange.stream_barrier()                   # everybody has merged the records of the previous call
     ops.voxel_sparse_send_cuda(grid, counts, [slab_bounds(V, d, ws) for d in others], exchange.capacity, d_ids, d_sums, d_counts,
                                d_nrec, exchange.cursors, exchange.overflow)
     dist.all_reduce(exchange.overflow, op=dist.ReduceOp.MAX, group=exchange.group)   # barrier: every list is in place
-    s_ids, s_sums, s_counts, s_nrec = exchange.sources(others)
     ops.voxel_sparse_merge_cuda(s_ids, s_sums, s_counts, s_nrec, exchange.capacity, grid, counts, a, b)
     if check and int(exchange.overflow.item()):
         raise RuntimeError(f"sparse reduction: a record list of {exchange.capacity} records overflowed on some rank")
+    if grid is None:
+        return counts[a:b]
     return (grid[a:b], counts[a:b]) if return_counts else grid[a:b]
 
 

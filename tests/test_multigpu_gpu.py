@@ -123,6 +123,8 @@ for rep in range(2):
     a, b = sharding.slab_bounds(V, rank, ws)
     assert torch.equal(cnts.cpu(), cnt.reshape(V)[a:b]), f"sparse counts {rep}"
     assert mean_ok(slab, a, b), f"sparse mean {rep}"
+    cslab = sharding.voxelize_sharded_sparse(pts[l:h], None, sr, mode="count", **kw)
+    assert cslab.dtype == torch.int32 and torch.equal(cslab.cpu(), want["count"].reshape(V)[a:b]), f"sparse count {rep}"
 sr.close()
 tiny = sharding.SparseReduce(records_per_pair=8)
 try:

@@ -413,3 +413,38 @@ def test_sparse_reduce_overflow_is_reported_and_harmless(cuda_lib):
     ops.voxel_sparse_merge_cuda([ids.data_ptr()], [sums.data_ptr()], [cnts.data_ptr()], [nrec.data_ptr()], cap, g2, c2, 0, V,
                                 normalize=False)
     assert int((c2 > 0).sum()) == cap and int(c2.sum()) == int(cnts[:cap].sum())
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("R", [2, 5])
+def test_sparse_reduce_count_mode_on_one_gpu(R, cuda_lib):
+    """Count mode of the sparse reduction: private count grids, (voxel id, count) records, no feature sums anywhere."""
+    kw = dict(grid_min=[-2.0, -2.0, -2.0], voxel_size=0.25, grid_size=[17, 15, 13])
+    V = 17 * 15 * 13
+    N = 40_000
+    pts, _ = _cloud(N, 77 + R)
+    cuts = [N * r // R for r in range(R + 1)]
+    cap = V
+    lists = [dict(ids=torch.full((R * cap,), -7, dtype=torch.int32, device=DEV), cnts=torch.full((R * cap,), -1, dtype=torch.int32, device=DEV),
+                  nrec=torch.zeros(R, dtype=torch.int32, device=DEV)) for _ in range(R)]
+    cursors = torch.zeros(16, dtype=torch.int32, device=DEV)
+    overflow = torch.zeros(1, dtype=torch.int32, device=DEV)
+    partial = []
+    for r in range(R):
+        c = ops.voxelize_pointcloud_cuda(pts[cuts[r]:cuts[r + 1]].to(DEV), None, kw["grid_min"], kw["voxel_size"], kw["grid_size"],
+                                         "count")[0].view(V)
+        partial.append(c)
+        others = [(r + k) % R for k in range(1, R)]
+        ops.voxel_sparse_send_cuda(None, c, [sharding.slab_bounds(V, d, R) for d in others], cap,
+                                   [lists[d]["ids"].data_ptr() + r * cap * 4 for d in others], [None] * len(others),
+                                   [lists[d]["cnts"].data_ptr() + r * cap * 4 for d in others],
+                                   [lists[d]["nrec"].data_ptr() + r * 4 for d in others], cursors, overflow)
+    want = oracle.voxelize_pointcloud(pts, None, mode="count", **kw).reshape(V)
+    for d in range(R):
+        lo, hi = sharding.slab_bounds(V, d, R)
+        srcs = [(d + k) % R for k in range(1, R)]
+        ops.voxel_sparse_merge_cuda([lists[d]["ids"].data_ptr() + s * cap * 4 for s in srcs], [None] * len(srcs),
+                                    [lists[d]["cnts"].data_ptr() + s * cap * 4 for s in srcs],
+                                    [lists[d]["nrec"].data_ptr() + s * 4 for s in srcs], cap, None, partial[d], lo, hi)
+        assert torch.equal(partial[d][lo:hi].cpu(), want[lo:hi]), (d, R)
+    assert int(overflow.item()) == 0
