@@ -1195,6 +1195,38 @@ def run_profile_case(name: str):
         pts = workloads.voxel_uniform_inputs(500_000, seed=0, device=dev)
         fn = lambda: robocache.voxelize_pointcloud(pts, mode="occupancy", **workloads.VOXEL_OCCUPANCY_GEOMETRY)
         units = {"N": 500_000}
+    elif name == "voxel_sparse":
+        # the sparse reduction's send and merge kernels as one of 8 ranks would run them, with the owners' record lists
+        # in this GPU's memory: a private 256^3 grid of 2^24 mixture points (335 MB of sums and counts), the occupied
+        # voxels of the 7 other slabs appended to 7 lists, then 7 such lists merged into this rank's slab
+        from robogoat_b200 import sharding
+        N, Vv, R = 1 << 24, 256 ** 3, 8
+        pts, feats = workloads.voxel_mixture_inputs(N, seed=0, device=dev)
+        kw = dict(grid_min=[-25.6, -25.6, -25.6], voxel_size=0.2, grid_size=[256, 256, 256])
+        g_, c_ = ops.voxelize_pointcloud_cuda(pts, feats, kw["grid_min"], kw["voxel_size"], kw["grid_size"], "mean", normalize=False)
+        g_, c_ = g_.view(Vv, 4), c_.view(Vv)
+        del pts, feats
+        cap = Vv // R
+        ids = torch.empty(R * cap, dtype=torch.int32, device=dev)
+        sums = torch.empty(R * cap, 4, dtype=torch.float32, device=dev)
+        cnts = torch.empty(R * cap, dtype=torch.int32, device=dev)
+        nrec = torch.zeros(R, dtype=torch.int32, device=dev)
+        cursors = torch.zeros(16, dtype=torch.int32, device=dev)
+        overflow = torch.zeros(1, dtype=torch.int32, device=dev)
+        others = list(range(1, R))
+
+        def fn():
+            ops.voxel_sparse_send_cuda(g_, c_, [sharding.slab_bounds(Vv, d, R) for d in others], cap,
+                                       [ids.data_ptr() + d * cap * 4 for d in others], [sums.data_ptr() + d * cap * 16 for d in others],
+                                       [cnts.data_ptr() + d * cap * 4 for d in others], [nrec.data_ptr() + d * 4 for d in others],
+                                       cursors, overflow)
+            # every list holds voxels of ITS slab; shift slab 1's list onto slab 0 would need new ids, so merge list d into
+            # slab d of the private grid itself (same kernel, same access pattern as an owner's merge)
+            for d in others[:1]:
+                lo, hi = sharding.slab_bounds(Vv, d, R)
+                ops.voxel_sparse_merge_cuda([ids.data_ptr() + d * cap * 4], [sums.data_ptr() + d * cap * 16], [cnts.data_ptr() + d * cap * 4],
+                                            [nrec.data_ptr() + d * 4], cap, g_, c_, lo, hi, normalize=False)
+        units = {"N": N, "grid": "256^3", "ranks_emulated": R}
     else:
         raise SystemExit(f"unknown profile case {name}")
     for _ in range(3):
@@ -1213,7 +1245,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extras", action="store_true")
     ap.add_argument("--profile-case", default=None,
-                    help="run 4 launches of one kernel on a small case (resample, fusion, voxel_mean, voxel_count, voxel_occupancy, voxel_partition, voxel_partition_aligned, voxel_scatter_runs, voxel_mean_runs; voxel_mean_full = headline size)")
+                    help="run 4 launches of one kernel on a small case (resample, fusion, voxel_mean, voxel_count, voxel_occupancy, voxel_partition, voxel_partition_aligned, voxel_scatter_runs, voxel_mean_runs, voxel_sparse; voxel_mean_full = headline size)")
     args = ap.parse_args()
     if args.profile_case:
         run_profile_case(args.profile_case)

@@ -6,8 +6,8 @@
 // occupied voxel instead of 20 bytes per point, and nothing at all for empty space.  Two kernels:
 //   voxel_sparse_send_kernel   walks the counter plane of the slabs other ranks own, and appends (voxel id, feature
 //                              sums, count) of every occupied voxel to this rank's region of the owner's record list
-//                              (collected in shared memory, written as contiguous runs of plain stores, possibly
-//                              into peer memory; slots from a counter in local memory);
+//                              (collected per warp in shared memory, written as contiguous runs of plain stores,
+//                              possibly into peer memory; slots from a counter in local memory);
 //   voxel_sparse_merge_kernel  the owner adds the records it received to its own slab of its own partial grid.
 // A one-warp kernel publishes the record counts to the owners.  Record lists have a fixed capacity per (source,
 // owner) pair; records beyond it are dropped and reported through an overflow flag that the caller must check.
@@ -19,11 +19,11 @@ namespace {
 using namespace rc::vox;
 
 constexpr int kSparseMaxPeers = 16;
-constexpr int kSparseTile = kThreads * 4;       // voxels a CTA examines per step
+constexpr int kSparseTile = 128;                // voxels a warp examines per step
 
 struct SparseDests {
     long long begin[kSparseMaxPeers], end[kSparseMaxPeers];     // voxel ranges, one per destination
-    long long tile0[kSparseMaxPeers + 1];                       // first 1024-voxel tile of every range in the flat tile list
+    long long tile0[kSparseMaxPeers + 1];                       // first 128-voxel tile of every range in the flat tile list
     int* ids[kSparseMaxPeers];
     float4* sums[kSparseMaxPeers];
     int* cnts[kSparseMaxPeers];
@@ -31,53 +31,57 @@ struct SparseDests {
     int n;
 };
 
-// A CTA walks a contiguous run of 1024-voxel tiles (four voxels per thread and step), collects the occupied voxels'
-// records in shared memory and, whenever more than kSparseFlush are waiting (or the destination changes), reserves
-// their slots with ONE atomic on the destination's cursor and writes them out as three contiguous runs.  Writing
-// each warp's handful of records straight to the peer cost 0.5 ms for 62 MB: every partial line is a packet of its
-// own on NVLink, and it is the packet rate, not the bytes, that bounded the kernel.
-constexpr int kSparseFlush = 512;
+// A warp walks a contiguous run of 128-voxel tiles (four voxels per lane and step), collects the occupied voxels'
+// records in its own piece of shared memory and, whenever more than kSparseFlush are waiting (or the destination
+// changes), reserves their slots with ONE atomic on the destination's cursor and writes them out as three contiguous
+// runs.  History of this kernel, 2^26-point mixture, 2 GPUs, 62 MB to send: every warp writing its handful of records
+// straight to the peer 0.51 ms (each partial line is a packet of its own on NVLink, and the packet rate bounded it,
+// not the bytes); records collected per CTA of 1024 voxels with two barriers per step 0.15-0.25 ms and issue-bound
+// (220 instructions per warp and step); per warp, no barrier, tiles without an occupied voxel left after one vote:
+// this form.
+constexpr int kSparseFlush = 64;
 constexpr int kSparseStage = kSparseFlush + kSparseTile;
 
 __device__ __forceinline__ void sparse_flush(const SparseDests& d, int r, int fill, int* cursor, long long capacity,
-                                             const int* s_ids, const float4* s_sums, const int* s_cnts, int* s_base) {
-    if (threadIdx.x == 0) *s_base = atomicAdd(cursor + r, fill);
-    __syncthreads();
-    const long long base = *s_base;
-    for (int i = threadIdx.x; i < fill; i += kThreads) {
-        const long long slot = base + i;
+                                             const int* s_ids, const float4* s_sums, const int* s_cnts, int lane) {
+    int base = 0;
+    if (lane == 0) base = atomicAdd(cursor + r, fill);
+    base = __shfl_sync(0xffffffffu, base, 0);
+    for (int i = lane; i < fill; i += 32) {
+        const long long slot = static_cast<long long>(base) + i;
         if (slot < capacity) {
             d.ids[r][slot] = s_ids[i];
             if (d.sums[r] != nullptr) d.sums[r][slot] = s_sums[i];
             d.cnts[r][slot] = s_cnts[i];
         }
     }
-    __syncthreads();                                              // the staging arrays are free again
+    __syncwarp();                                                 // the staging arrays are free again
 }
 
 __global__ void __launch_bounds__(kThreads)
 voxel_sparse_send_kernel(const float4* __restrict__ grid, const int* __restrict__ counts, SparseDests d, int* __restrict__ cursor,
                          long long capacity) {
-    __shared__ __align__(16) float4 s_sums[kSparseStage];
-    __shared__ int s_ids[kSparseStage];
-    __shared__ int s_cnts[kSparseStage];
-    __shared__ int s_warp[kThreads / 32];
-    __shared__ int s_base;
+    __shared__ __align__(16) float4 s_sums_all[kThreads / 32][kSparseStage];
+    __shared__ int s_ids_all[kThreads / 32][kSparseStage];
+    __shared__ int s_cnts_all[kThreads / 32][kSparseStage];
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
+    float4* s_sums = s_sums_all[warp];
+    int* s_ids = s_ids_all[warp];
+    int* s_cnts = s_cnts_all[warp];
     const long long ntiles = d.tile0[d.n];
-    const long long per = (ntiles + gridDim.x - 1) / gridDim.x;
-    const long long t0 = blockIdx.x * per;
+    const long long nwarps = static_cast<long long>(gridDim.x) * (kThreads / 32);
+    const long long per = (ntiles + nwarps - 1) / nwarps;
+    const long long t0 = (static_cast<long long>(blockIdx.x) * (kThreads / 32) + warp) * per;
     const long long t1 = (t0 + per < ntiles) ? t0 + per : ntiles;
-    int fill = 0, fill_r = 0;                                     // staged records and their destination (CTA-uniform)
-    // the counters of the next tile are requested before this tile's are used: a step is a chain of dependent
-    // latencies (counters, feature sums, barriers), and a CTA has only a few dozen steps to hide them in
+    int fill = 0, fill_r = 0;                                     // staged records and their destination (warp-uniform)
+    // the counters of the next tile are requested before this tile's are used
     int rn = 0;
     long long vn = 0;
     int cn[4] = {0, 0, 0, 0};
     auto fetch = [&](long long tile) {
         while (rn + 1 < d.n && tile >= d.tile0[rn + 1]) ++rn;
-        vn = d.begin[rn] + (tile - d.tile0[rn]) * kSparseTile + threadIdx.x * 4;
+        vn = d.begin[rn] + (tile - d.tile0[rn]) * kSparseTile + lane * 4;
         cn[0] = cn[1] = cn[2] = cn[3] = 0;
         if (vn + 4 <= d.end[rn] && ((vn & 3) == 0)) {
             const int4 q = __ldcs(reinterpret_cast<const int4*>(counts + vn));
@@ -94,8 +98,10 @@ voxel_sparse_send_kernel(const float4* __restrict__ grid, const int* __restrict_
         const long long v0 = vn;
         const int c[4] = {cn[0], cn[1], cn[2], cn[3]};
         if (tile + 1 < t1) fetch(tile + 1);
+        const int mine = (c[0] > 0) + (c[1] > 0) + (c[2] > 0) + (c[3] > 0);
+        if (!__any_sync(0xffffffffu, mine)) continue;             // most tiles of a sparse grid hold no occupied voxel
         if (r != fill_r) {
-            if (fill > 0) sparse_flush(d, fill_r, fill, cursor, capacity, s_ids, s_sums, s_cnts, &s_base);
+            if (fill > 0) sparse_flush(d, fill_r, fill, cursor, capacity, s_ids, s_sums, s_cnts, lane);
             fill = 0;
             fill_r = r;
         }
@@ -103,25 +109,16 @@ voxel_sparse_send_kernel(const float4* __restrict__ grid, const int* __restrict_
         if (grid != nullptr) {                                    // count mode has no feature sums
 #pragma unroll
             for (int k = 0; k < 4; ++k)
-                if (c[k] > 0) sv[k] = __ldcs(grid + v0 + k);      // in flight across the prefix sum and its barrier
+                if (c[k] > 0) sv[k] = __ldcs(grid + v0 + k);      // in flight across the prefix sum
         }
-        const int mine = (c[0] > 0) + (c[1] > 0) + (c[2] > 0) + (c[3] > 0);
         int incl = mine;                                          // inclusive prefix sum over the warp
 #pragma unroll
         for (int off = 1; off < 32; off <<= 1) {
             const int up = __shfl_up_sync(0xffffffffu, incl, off);
             if (lane >= off) incl += up;
         }
-        if (lane == 31) s_warp[warp] = incl;
-        __syncthreads();
-        int before = 0, total = 0;
-#pragma unroll
-        for (int w = 0; w < kThreads / 32; ++w) {
-            const int t = s_warp[w];
-            if (w < warp) before += t;
-            total += t;
-        }
-        int at = fill + before + (incl - mine);
+        const int total = __shfl_sync(0xffffffffu, incl, 31);
+        int at = fill + (incl - mine);
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
             if (c[k] > 0) {
@@ -131,14 +128,14 @@ voxel_sparse_send_kernel(const float4* __restrict__ grid, const int* __restrict_
                 ++at;
             }
         }
-        __syncthreads();                                          // records staged; s_warp is free for the next step
+        __syncwarp();                                             // records staged
         fill += total;
         if (fill > kSparseFlush) {                                // the next step may add up to kSparseTile records
-            sparse_flush(d, fill_r, fill, cursor, capacity, s_ids, s_sums, s_cnts, &s_base);
+            sparse_flush(d, fill_r, fill, cursor, capacity, s_ids, s_sums, s_cnts, lane);
             fill = 0;
         }
     }
-    if (fill > 0) sparse_flush(d, fill_r, fill, cursor, capacity, s_ids, s_sums, s_cnts, &s_base);
+    if (fill > 0) sparse_flush(d, fill_r, fill, cursor, capacity, s_ids, s_sums, s_cnts, lane);
 }
 
 // The counts reach the owners after the records (stream order); a count above the capacity raises the local flag.
@@ -216,7 +213,7 @@ int rc_voxel_sparse_send(const float* grid, const int32_t* counts, int32_t n_des
     RC_CUDA_TRY(cudaMemsetAsync(cursors, 0, static_cast<size_t>(n_dest) * 4, st));
     if (overflow != nullptr) RC_CUDA_TRY(cudaMemsetAsync(overflow, 0, 4, st));
     if (tiles > 0) {
-        long long blocks = tiles;
+        long long blocks = (tiles + kThreads / 32 - 1) / (kThreads / 32);
         const long long cap = 16ll * rc::sm_count(device);
         if (blocks > cap) blocks = cap;
         voxel_sparse_send_kernel<<<static_cast<unsigned int>(blocks), kThreads, 0, st>>>(
