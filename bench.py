@@ -1075,7 +1075,7 @@ def multi_gpu_extras(L, dev, rank, world, ex, pts, feats, kw, N, single_ms):
         del g1, c1, g2, c2, cgrid
     if sr is not None:
         rec = ex["voxel_mean_sharded_sparse_reduce"]
-        overflowed = bool(int(sr.overflow.item()))       # reduced over the ranks by the last call
+        overflowed = sr.failed()                # any record list overflowed on any rank since the parity check
         rec["record_lists_overflowed"] = overflowed
         if overflowed:              # the same occupied voxels travel in both modes
             for m_ in ("mean", "count"):

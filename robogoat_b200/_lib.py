@@ -46,7 +46,7 @@ EXPORTED_SYMBOLS = (
     "rc_resample", "rc_resample_strided", "rc_resample_ragged", "rc_fuse", "rc_fuse_strided", "rc_resample_brackets", "rc_voxelize", "rc_voxel_normalize", "rc_voxelize_mean_static",
     "rc_voxelize_ex", "rc_voxelize_scratch_bytes", "rc_voxel_partition", "rc_voxel_partition_count", "rc_voxel_partition_move", "rc_voxel_partition_scratch_bytes",
     "rc_voxel_scatter_ids", "rc_voxel_scatter_runs", "rc_peer_alloc", "rc_peer_open", "rc_peer_close", "rc_peer_free",
-    "rc_voxelize_batched", "rc_point_cloud_bounds", "rc_voxelize_tsdf", "rc_voxel_bucket_block_records", "rc_voxel_bucket_exchange", "rc_voxel_scatter_buckets", "rc_voxel_sparse_send", "rc_voxel_sparse_merge", "rc_set_option", "rc_bulk_wait_timeouts", "rc_strerror", "rc_last_cuda_error", "rc_abi_version",
+    "rc_voxelize_batched", "rc_point_cloud_bounds", "rc_voxelize_tsdf", "rc_voxel_bucket_block_records", "rc_voxel_bucket_exchange", "rc_voxel_scatter_buckets", "rc_voxel_sparse_send", "rc_voxel_sparse_merge", "rc_peer_barrier", "rc_set_option", "rc_bulk_wait_timeouts", "rc_strerror", "rc_last_cuda_error", "rc_abi_version",
 )
 
 
@@ -122,8 +122,10 @@ def _declare(L: ctypes.CDLL) -> None:
     pvp = ctypes.POINTER(vp)
     L.rc_voxel_sparse_send.argtypes = [vp, vp, i32, ctypes.POINTER(i64), ctypes.POINTER(i64), i64, pvp, pvp, pvp, pvp, vp, vp, ci, vp]
     L.rc_voxel_sparse_send.restype = ci
-    L.rc_voxel_sparse_merge.argtypes = [i32, pvp, pvp, pvp, pvp, i64, vp, vp, i64, i64, u32, ci, vp]
+    L.rc_voxel_sparse_merge.argtypes = [i32, pvp, pvp, pvp, pvp, i64, vp, vp, i64, i64, vp, u32, ci, vp]
     L.rc_voxel_sparse_merge.restype = ci
+    L.rc_peer_barrier.argtypes = [pvp, i32, i32, u32, vp, i64, ci, vp]
+    L.rc_peer_barrier.restype = ci
     for name in ("rc_resample", "rc_resample_strided", "rc_resample_ragged", "rc_fuse", "rc_fuse_strided", "rc_resample_brackets", "rc_voxelize", "rc_voxel_normalize", "rc_voxelize_mean_static",
                  "rc_last_cuda_error", "rc_abi_version"):
         getattr(L, name).restype = ci

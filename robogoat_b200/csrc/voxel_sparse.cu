@@ -158,11 +158,14 @@ struct SparseSources {
 
 __global__ void __launch_bounds__(kThreads)
 voxel_sparse_merge_kernel(SparseSources s, long long capacity, float* __restrict__ grid0, int* __restrict__ counts0,
-                          long long id_begin, long long id_end) {
+                          long long id_begin, long long id_end, int* __restrict__ overflow) {
     const long long stride = static_cast<long long>(gridDim.x) * kThreads;
     for (int i = 0; i < s.n; ++i) {
         long long n = *s.nrec[i];
-        if (n > capacity) n = capacity;
+        if (n > capacity) {                                       // the source dropped records: this slab is incomplete
+            if (overflow != nullptr && blockIdx.x == 0 && threadIdx.x == 0) atomicOr(overflow, 1);
+            n = capacity;
+        }
         for (long long k = static_cast<long long>(blockIdx.x) * kThreads + threadIdx.x; k < n; k += stride) {
             const long long id = s.ids[i][k];
             if (id < id_begin || id >= id_end) continue;          // nothing a well-formed list contains
@@ -211,7 +214,6 @@ int rc_voxel_sparse_send(const float* grid, const int32_t* counts, int32_t n_des
     if (scope.status() != RC_OK) return scope.status();
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     RC_CUDA_TRY(cudaMemsetAsync(cursors, 0, static_cast<size_t>(n_dest) * 4, st));
-    if (overflow != nullptr) RC_CUDA_TRY(cudaMemsetAsync(overflow, 0, 4, st));
     if (tiles > 0) {
         long long blocks = (tiles + kThreads / 32 - 1) / (kThreads / 32);
         const long long cap = 16ll * rc::sm_count(device);
@@ -227,7 +229,7 @@ int rc_voxel_sparse_send(const float* grid, const int32_t* counts, int32_t n_des
 
 int rc_voxel_sparse_merge(int32_t n_src, const void* const* src_ids, const void* const* src_sums, const void* const* src_counts,
                           const void* const* src_nrec, int64_t capacity, float* grid, int32_t* counts, int64_t id_begin,
-                          int64_t id_end, uint32_t flags, int device, void* stream) {
+                          int64_t id_end, int32_t* overflow, uint32_t flags, int device, void* stream) {
     if (n_src < 0 || n_src > kSparseMaxPeers || capacity < 0 || id_begin < 0 || id_end < id_begin) return RC_ERR_BAD_SHAPE;
     if (id_end >= (1ll << 31)) return RC_ERR_TOO_LARGE;
     const long long nvox = id_end - id_begin;
@@ -257,7 +259,7 @@ int rc_voxel_sparse_merge(int32_t n_src, const void* const* src_ids, const void*
         const long long cap = 8ll * rc::sm_count(device);
         if (blocks > cap) blocks = cap;
         voxel_sparse_merge_kernel<<<static_cast<unsigned int>(blocks), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-            s, capacity, grid0, counts0, id_begin, id_end);
+            s, capacity, grid0, counts0, id_begin, id_end, overflow);
         const int rc_launch = rc::check_launch();
         if (rc_launch != RC_OK) return rc_launch;
     }

@@ -63,3 +63,42 @@ class PeerBuffer:
         if self.ptr:
             L.rc_peer_free(self.ptr, self.device.index)
             self.ptr = 0
+
+
+class PeerBarrier:
+    """Barrier among the ranks of a node on the current CUDA stream, without NCCL: one 32-thread kernel per call that
+    stores an epoch into every peer's flag array over NVLink and polls its own (``rc_peer_barrier``).  Work enqueued
+    after ``wait()`` on any rank sees what every rank's stream did before its ``wait()``, plain stores into peers'
+    memory included.  The kernel's wait is bounded (about half a second by default): a rank that never arrives raises
+    ``status`` on the others instead of hanging them - read it with ``timed_out()``.  Construction and ``close`` are
+    collective; every rank must call ``wait()`` the same number of times."""
+
+    def __init__(self, group=None, device: Optional[torch.device] = None, poll_limit: int = 0):
+        self.group = group
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        if self.world > 16:
+            raise RuntimeError("the peer barrier supports at most 16 ranks")
+        self.device = device if device is not None else torch.device("cuda", torch.cuda.current_device())
+        self.poll_limit = int(poll_limit)
+        self.epoch = 0
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.flags = PeerBuffer(128, self.device)       # zero-filled by the allocation
+        self.flags.connect(group)
+        dist.barrier(group=group)                       # nobody signals before everybody has mapped
+
+    def wait(self) -> None:
+        self.epoch += 1
+        VP = ctypes.c_void_p * self.world
+        rc = _lib.load().rc_peer_barrier(VP(*self.flags.peers), self.world, self.rank, self.epoch & 0xFFFFFFFF,
+                                         self.status.data_ptr(), self.poll_limit, self.device.index,
+                                         torch.cuda.current_stream(self.device).cuda_stream)
+        _lib.check(rc, "peer_barrier")
+
+    def timed_out(self) -> bool:
+        """True if any ``wait()`` so far gave up (synchronises with the device)."""
+        return bool(int(self.status.item()))
+
+    def close(self) -> None:
+        if self.flags is not None:
+            self.flags.close()
+            self.flags = None

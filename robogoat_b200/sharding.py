@@ -381,8 +381,11 @@ class BucketExchange:
     collective."""
 
     def __init__(self, points_per_rank: int, n_voxels: int, group=None, fetch: bool = False,
-                 sub_ranges: Optional[int] = None):
-        from .peer import PeerBuffer
+                 sub_ranges: Optional[int] = None, barrier: str = "peer"):
+        from .peer import PeerBuffer, PeerBarrier
+        if barrier not in ("peer", "nccl"):
+            raise ValueError("barrier must be 'peer' (flag kernel over NVLink) or 'nccl' (4-byte all-reduce)")
+        self.barrier = None
         self.group = group
         self.fetch = bool(fetch)
         rank, ws = world(group)
@@ -419,6 +422,8 @@ class BucketExchange:
             if not self._everyone(error is None):
                 self.close()
                 raise RuntimeError(f"BucketExchange: peer buffers could not be mapped on every rank ({error})")
+        if barrier == "peer":
+            self.barrier = PeerBarrier(group, dev)
 
     def _everyone(self, ok: bool) -> bool:
         flag = torch.tensor([1 if ok else 0], dtype=torch.int32, device=self._token.device)
@@ -427,8 +432,16 @@ class BucketExchange:
 
     def stream_barrier(self) -> None:
         """Orders, on the current stream, everything the other ranks enqueued before their call of this method
-        before everything this rank enqueues after it."""
-        dist.all_reduce(self._token, group=self.group)
+        before everything this rank enqueues after it: a flag kernel over NVLink (``peer.PeerBarrier``, bounded wait)
+        or, with ``barrier="nccl"``, a 4-byte all-reduce."""
+        if self.barrier is not None:
+            self.barrier.wait()
+        else:
+            dist.all_reduce(self._token, group=self.group)
+
+    def barrier_timed_out(self) -> bool:
+        """True if a flag barrier gave up waiting for a rank (the results since then are not to be trusted)."""
+        return self.barrier is not None and self.barrier.timed_out()
 
     def destinations(self):
         """(ids, features, runs, first_block, pool_blocks) for this rank's bucket kernel."""
@@ -474,10 +487,10 @@ class BucketExchange:
         return self._streams
 
     def close(self) -> None:
-        for b in (self.ids, self.features, self.runs):
+        for b in (self.ids, self.features, self.runs, self.barrier):
             if b is not None:
                 b.close()
-        self.ids = self.features = self.runs = None
+        self.ids = self.features = self.runs = self.barrier = None
 
 
 class SparseReduce:
@@ -485,8 +498,11 @@ class SparseReduce:
     every source rank, a list of ``records_per_pair`` (voxel id, feature sums, count) records that the source fills
     with plain stores over NVLink.  24 bytes per record; construction and ``close`` are collective."""
 
-    def __init__(self, records_per_pair: int, group=None):
-        from .peer import PeerBuffer
+    def __init__(self, records_per_pair: int, group=None, barrier: str = "peer"):
+        from .peer import PeerBuffer, PeerBarrier
+        if barrier not in ("peer", "nccl"):
+            raise ValueError("barrier must be 'peer' (flag kernel over NVLink) or 'nccl' (4-byte all-reduce)")
+        self.barrier = None
         self.group = group
         rank, ws = world(group)
         if ws > 16:
@@ -517,6 +533,8 @@ class SparseReduce:
             if not self._everyone(error is None):
                 self.close()
                 raise RuntimeError(f"SparseReduce: peer buffers could not be mapped on every rank ({error})")
+        if barrier == "peer":
+            self.barrier = PeerBarrier(group, dev)
 
     def _everyone(self, ok: bool) -> bool:
         flag = torch.tensor([1 if ok else 0], dtype=torch.int32, device=self._token.device)
@@ -524,7 +542,21 @@ class SparseReduce:
         return bool(flag.item())
 
     def stream_barrier(self) -> None:
-        dist.all_reduce(self._token, group=self.group)
+        """As ``BucketExchange.stream_barrier``."""
+        if self.barrier is not None:
+            self.barrier.wait()
+        else:
+            dist.all_reduce(self._token, group=self.group)
+
+    def failed(self) -> bool:
+        """Collective, synchronises: true on every rank if, since the last call of this method, a record list
+        overflowed anywhere or a flag barrier gave up waiting - the slabs computed since are then not to be trusted."""
+        flag = self.overflow.clone()
+        self.overflow.zero_()                   # a barrier's time-out stays raised: nothing after it can be trusted
+        if self.barrier is not None:
+            flag |= self.barrier.status
+        dist.all_reduce(flag, op=dist.ReduceOp.MAX, group=self.group)
+        return bool(int(flag.item()))
 
     def destinations(self, owners):
         """Addresses of this rank's list in every owner's memory: (ids, sums, counts, nrec)."""
@@ -538,10 +570,10 @@ class SparseReduce:
                 [self.counts.ptr + s * self.capacity * 4 for s in sources], [self.nrec.ptr + s * 4 for s in sources])
 
     def close(self) -> None:
-        for b in (self.ids, self.sums, self.counts, self.nrec):
+        for b in (self.ids, self.sums, self.counts, self.nrec, self.barrier):
             if b is not None:
                 b.close()
-        self.ids = self.sums = self.counts = self.nrec = None
+        self.ids = self.sums = self.counts = self.nrec = self.barrier = None
 
 
 def voxelize_sharded_sparse(points_local: torch.Tensor, features_local: torch.Tensor, exchange: SparseReduce,
@@ -551,8 +583,9 @@ def voxelize_sharded_sparse(points_local: torch.Tensor, features_local: torch.Te
     view of this rank's full-size partial grid), by a sparse reduction: every rank bins its own points into a private
     full grid, sends each other rank only the occupied voxels of that rank's slab, and adds what it receives to its own
     slab.  Pays when the ranks' clouds put many points into each occupied voxel (bytes on NVLink: 24 per occupied voxel
-    instead of 20 per point); needs the full grid on every rank.  ``check``: wait for the call and raise if a record
-    list overflowed (the result is then incomplete); with ``check=False`` the caller reads ``exchange.overflow``.
+    instead of 20 per point); needs the full grid on every rank.  ``check``: wait for the call and raise on every rank if
+    a record list overflowed anywhere (the result is then incomplete); with ``check=False`` the caller asks
+    ``exchange.failed()`` when it wants to know.
     ``mode="count"``: points per voxel (int32 [voxels of the slab]); the records are then (voxel id, count) only."""
     from . import ops
     rank, ws = exchange.rank, exchange.world
@@ -577,10 +610,12 @@ def voxelize_sharded_sparse(points_local: torch.Tensor, features_local: torch.Te
     exchange.stream_barrier()                   # everybody has merged the records of the previous call
     ops.voxel_sparse_send_cuda(grid, counts, [slab_bounds(V, d, ws) for d in others], exchange.capacity, d_ids, d_sums, d_counts,
                                d_nrec, exchange.cursors, exchange.overflow)
-    dist.all_reduce(exchange.overflow, op=dist.ReduceOp.MAX, group=exchange.group)   # barrier: every list is in place
-    ops.voxel_sparse_merge_cuda(s_ids, s_sums, s_counts, s_nrec, exchange.capacity, grid, counts, a, b)
-    if check and int(exchange.overflow.item()):
-        raise RuntimeError(f"sparse reduction: a record list of {exchange.capacity} records overflowed on some rank")
+    exchange.stream_barrier()                   # every list is in place
+    ops.voxel_sparse_merge_cuda(s_ids, s_sums, s_counts, s_nrec, exchange.capacity, grid, counts, a, b,
+                                overflow=exchange.overflow)       # the owner sees by itself if a source dropped records
+    if check and exchange.failed():
+        raise RuntimeError(f"sparse reduction: a record list of {exchange.capacity} records overflowed on some rank, or a barrier "
+                           f"gave up waiting for a rank")
     if grid is None:
         return counts[a:b]
     return (grid[a:b], counts[a:b]) if return_counts else grid[a:b]

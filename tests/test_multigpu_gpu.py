@@ -114,18 +114,21 @@ for fetch in (True, False):                 # owners fetch the records over NVLi
             slab, cnts = sharding.voxelize_sharded_buckets(pts[l:h], feats[l:h], bx, return_counts=True, slices=slices, **kw)
             assert torch.equal(cnts.cpu(), c2.reshape(V)[a:b]), f"bucket counts {rep} fetch={fetch} slices={slices}"
             assert bool(((slab.cpu() - m2.reshape(V, 4)[a:b]).abs() <= t2[a:b]).all()), f"bucket mean {rep} fetch={fetch} slices={slices}"
+    assert not bx.barrier_timed_out()
     bx.close()
 # sparse reduction: private full grids, only occupied voxels travel; twice in a row, then with lists that are too small
-sr = sharding.SparseReduce(records_per_pair=V)
-for rep in range(2):
-    l, h = spans[rank]
-    slab, cnts = sharding.voxelize_sharded_sparse(pts[l:h], feats[l:h], sr, return_counts=True, **kw)
-    a, b = sharding.slab_bounds(V, rank, ws)
-    assert torch.equal(cnts.cpu(), cnt.reshape(V)[a:b]), f"sparse counts {rep}"
-    assert mean_ok(slab, a, b), f"sparse mean {rep}"
-    cslab = sharding.voxelize_sharded_sparse(pts[l:h], None, sr, mode="count", **kw)
-    assert cslab.dtype == torch.int32 and torch.equal(cslab.cpu(), want["count"].reshape(V)[a:b]), f"sparse count {rep}"
-sr.close()
+for barrier in ("peer", "nccl"):             # the flag kernel over NVLink / a 4-byte all-reduce
+  sr = sharding.SparseReduce(records_per_pair=V, barrier=barrier)
+  for rep in range(2):
+      l, h = spans[rank]
+      slab, cnts = sharding.voxelize_sharded_sparse(pts[l:h], feats[l:h], sr, return_counts=True, **kw)
+      a, b = sharding.slab_bounds(V, rank, ws)
+      assert torch.equal(cnts.cpu(), cnt.reshape(V)[a:b]), f"sparse counts {rep}"
+      assert mean_ok(slab, a, b), f"sparse mean {rep}"
+      cslab = sharding.voxelize_sharded_sparse(pts[l:h], None, sr, mode="count", **kw)
+      assert cslab.dtype == torch.int32 and torch.equal(cslab.cpu(), want["count"].reshape(V)[a:b]), f"sparse count {rep}"
+  assert not (sr.barrier is not None and sr.barrier.timed_out()), barrier
+  sr.close()
 tiny = sharding.SparseReduce(records_per_pair=8)
 try:
     sharding.voxelize_sharded_sparse(pts[l:h], feats[l:h], tiny, **kw)

@@ -448,3 +448,32 @@ def test_sparse_reduce_count_mode_on_one_gpu(R, cuda_lib):
                                     [lists[d]["nrec"].data_ptr() + s * 4 for s in srcs], cap, None, partial[d], lo, hi)
         assert torch.equal(partial[d][lo:hi].cpu(), want[lo:hi]), (d, R)
     assert int(overflow.item()) == 0
+
+
+@pytest.mark.gpu
+def test_peer_barrier_passes_alone_and_gives_up_on_a_rank_that_never_arrives(cuda_lib):
+    """The flag barrier's kernel on one GPU.  A world of one passes at once, epoch after epoch.  In a "world of two"
+    whose second rank does not exist (its flag array is a buffer nobody writes) the wait runs out after the given number
+    of polls, the kernel returns, the status word is raised and the context stays usable - the bounded wait that keeps
+    a missing rank from hanging the others."""
+    import ctypes
+    VP1, VP2 = ctypes.c_void_p * 1, ctypes.c_void_p * 2
+    flags = torch.zeros(32, dtype=torch.int32, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    stream = torch.cuda.current_stream().cuda_stream
+    dev = torch.cuda.current_device()
+    for epoch in (1, 2, 3):
+        assert cuda_lib.rc_peer_barrier(VP1(flags.data_ptr()), 1, 0, epoch, status.data_ptr(), 0, dev, stream) == 0
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0 and int(flags[0].item()) == 3
+    absent = torch.zeros(32, dtype=torch.int32, device=DEV)        # "rank 1": never signals
+    assert cuda_lib.rc_peer_barrier(VP2(flags.data_ptr(), absent.data_ptr()), 2, 0, 4, status.data_ptr(), 2000, dev, stream) == 0
+    torch.cuda.synchronize()
+    assert int(status.item()) == 1                                 # gave up, reported it
+    assert int(absent[0].item()) == 4                              # its own arrival did reach the other array
+    x = torch.arange(10, device=DEV).sum().item()                  # the context is still usable
+    assert x == 45
+    # argument errors are reported before any launch
+    assert cuda_lib.rc_peer_barrier(VP1(flags.data_ptr()), 1, 1, 1, None, 0, dev, stream) != 0
+    assert cuda_lib.rc_peer_barrier(VP1(None), 1, 0, 1, None, 0, dev, stream) != 0
+    assert cuda_lib.rc_peer_barrier(None, 1, 0, 1, None, 0, dev, stream) != 0
