@@ -894,6 +894,19 @@ def sharded_parity(dev, rank, world, px, bx=None, bxs=None) -> dict:
             flags["sparse_reduce"] = flags["sparse_reduce"] and count_ok(gcnt, xa, xb) and mean_ok(got, xa, xb)
             flags["sparse_reduce"] = flags["sparse_reduce"] and count_ok(sharding.voxelize_sharded_sparse(pl, None, sr, mode="count", **kw), xa, xb)
         sr.close()
+    sg = None
+    try:
+        sg = sharding.SparseGather(records_per_rank=V)
+    except RuntimeError:
+        pass
+    if sg is not None:
+        ok = True
+        for _ in range(2):
+            ok = ok and bool(torch.equal(sharding.voxelize_sharded_sparse_full(pl, None, sg, mode="occupancy", **kw).reshape(V).cpu(), occ))
+            ok = ok and count_ok(sharding.voxelize_sharded_sparse_full(pl, None, sg, mode="count", **kw))
+            ok = ok and mean_ok(sharding.voxelize_sharded_sparse_full(pl, fl, sg, mode="mean", **kw))
+        flags["sparse_all_gather"] = ok
+        sg.close()
     names = sorted(flags)
     t = torch.tensor([1 if flags[k] else 0 for k in names], dtype=torch.int32, device=dev)
     dist.all_reduce(t, op=dist.ReduceOp.MIN)
@@ -953,6 +966,18 @@ def multi_gpu_extras(L, dev, rank, world, ex, pts, feats, kw, N, single_ms):
         "ms": ms, "Gpts/s_total": (500_000 / (ms * 1e-3) / 1e9) if parity.get("all_reduce") else 0.0, "parity": parity.get("all_reduce"),
         "note": "500 000 points split over the ranks, private uint8 occupancy planes, NCCL all_reduce(MAX) of 2 MiB, int32 result on every rank; "
                 "50 back-to-back calls (warm L2): the collective's latency bounds it"}
+    try:
+        sg_small = sharding.SparseGather(records_per_rank=1 << 18)
+        ms = timed(lambda: sharding.voxelize_sharded_sparse_full(mine, None, sg_small, mode="occupancy", check=False, **okw), 50, 10)
+        bad = sg_small.failed()
+        ex["voxel_occupancy_500k_128_sharded_sparse_all_gather"] = {
+            "ms": ms, "Gpts/s_total": (500_000 / (ms * 1e-3) / 1e9) if (parity.get("sparse_all_gather") and not bad) else 0.0,
+            "parity": bool(parity.get("sparse_all_gather")) and not bad,
+            "note": "same result (int32 occupancy grid on every rank) without NCCL: every rank lists its occupied voxels in its own memory, "
+                    "a flag barrier over NVLink, every rank merges the others' lists read over NVLink; 50 back-to-back calls (warm L2)"}
+        sg_small.close()
+    except RuntimeError as e:
+        ex["voxel_sharded_sparse_all_gather_unavailable"] = str(e)[:200]
     del allp, mine
 
     forms = [("all_reduce", "all_reduce", lambda m: sharding.voxelize_sharded(pts, feats if m == "mean" else None, mode=m, **kw),
@@ -987,6 +1012,16 @@ def multi_gpu_extras(L, dev, rank, world, ex, pts, feats, kw, N, single_ms):
                       "every rank bins its own points into a private full grid, then only the occupied voxels of the other ranks' slabs "
                       "travel (24 B per occupied voxel instead of 20 B per point) and the owners add them to their own slab; pays "
                       "because this cloud puts 13 points into an occupied voxel on average - data dependent, unlike the exchanges"))
+    sg = None
+    try:
+        sg = sharding.SparseGather(records_per_rank=12 << 20)
+    except RuntimeError as e:
+        ex["voxel_sharded_sparse_all_gather_unavailable"] = str(e)[:200]
+    if sg is not None:
+        forms.append(("sparse_all_gather", "sparse_all_gather",
+                      lambda m: sharding.voxelize_sharded_sparse_full(pts, feats if m == "mean" else None, sg, mode=m, check=False, **kw),
+                      "the full grid on every rank, like the all-reduce form: private full grids, every rank lists its occupied voxels in "
+                      "its own memory and merges the other ranks' lists read over NVLink; data dependent like the sparse reduction"))
     if bxs is not None:
         forms.append(("bucket_exchange_fetch", "bucket_exchange_store", lambda m: sharding.voxelize_sharded_buckets(pts, feats, bxs, **kw),
                       "same pools in the sources' own memory; every owner's accumulation kernel fetches its blocks over NVLink as it goes"))
@@ -1051,6 +1086,13 @@ def multi_gpu_extras(L, dev, rank, world, ex, pts, feats, kw, N, single_ms):
             "bound": "the move kernel (NVLink, measured 770 GB/s per direction) and the owner's atomics run back to back here; "
                      "the batched form overlaps them"})
         px.close()
+    if sg is not None:
+        bad = sg.failed()
+        for m_ in ("mean", "count"):
+            ex[f"voxel_{m_}_sharded_sparse_all_gather"]["record_lists_overflowed_or_barrier_timed_out"] = bad
+            if bad:
+                ex[f"voxel_{m_}_sharded_sparse_all_gather"].update({"Gpts/s_total": 0.0, "parity": False})
+        sg.close()
     if sr is not None and bx is not None:
         # full size, where no CPU oracle is affordable: the two fastest forms share no kernel after the points are read
         # (sorted records over NVLink against private grids + occupied voxels), so their slabs must agree - counts

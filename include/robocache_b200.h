@@ -64,6 +64,7 @@ typedef enum rc_voxel_mode {
 #define RC_VOXEL_ZERO_INIT   1u  /* clear grid (and counts) on `stream` before binning */
 #define RC_VOXEL_NO_NORMALIZE 2u /* mean mode: leave feature SUMS in grid (multi-GPU partials) */
 #define RC_VOXEL_WARP_AGGREGATE 4u /* merge equal voxel ids inside a warp before the atomic */
+#define RC_VOXEL_SPARSE_OCCUPANCY 8u /* rc_voxel_sparse_merge, count mode: store 1 for every received voxel instead of adding its count */
 
 /* one timestamped feature stream: data [B,S,D] (dtype of the call), times [B,S] fp32 */
 typedef struct rc_stream_desc {
@@ -329,7 +330,11 @@ RC_API int rc_voxel_scatter_buckets(const void* const* pool_ids, const void* con
  *   its own partial grid (grid / counts point at voxel id_begin) and normalises the slab unless flags has
  *   RC_VOXEL_NO_NORMALIZE; a record number above the capacity sets *overflow (int32 on this GPU, may be NULL, not
  *   cleared by this call) to 1: the owner learns by itself that its slab is incomplete.
- * Count mode: grid = NULL in both calls and NULL entries in dest_sums / src_sums - records are (voxel id, count) only.
+ * Count mode: grid = NULL in both calls and NULL entries in dest_sums / src_sums - records are (voxel id, count) only;
+ * with RC_VOXEL_SPARSE_OCCUPANCY the merge stores 1 for every received voxel (occupancy grids).
+ * The lists an owner merges may lie in the sources' own memory (plain loads over NVLink): with one list per rank that
+ * holds the occupied voxels of that rank's WHOLE grid, every rank can merge all the others' lists into its own full
+ * grid - the result of an all-reduce of the dense partial grids, for the price of the occupied voxels.
  * The caller orders senders against owners with a barrier on the stream between the two calls and before the next
  * send.  No counterpart in the reference.
  */

@@ -26,6 +26,7 @@ VOXEL_OCCUPANCY_U8 = 4
 VOXEL_ZERO_INIT = 1
 VOXEL_NO_NORMALIZE = 2
 VOXEL_WARP_AGGREGATE = 4
+VOXEL_SPARSE_OCCUPANCY = 8
 STATIC_MAX_VOXELS = 1 << 21
 
 BATCHED_OCCUPANCY = 0

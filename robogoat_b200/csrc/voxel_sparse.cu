@@ -158,7 +158,7 @@ struct SparseSources {
 
 __global__ void __launch_bounds__(kThreads)
 voxel_sparse_merge_kernel(SparseSources s, long long capacity, float* __restrict__ grid0, int* __restrict__ counts0,
-                          long long id_begin, long long id_end, int* __restrict__ overflow) {
+                          long long id_begin, long long id_end, int* __restrict__ overflow, bool occupancy) {
     const long long stride = static_cast<long long>(gridDim.x) * kThreads;
     for (int i = 0; i < s.n; ++i) {
         long long n = *s.nrec[i];
@@ -170,7 +170,8 @@ voxel_sparse_merge_kernel(SparseSources s, long long capacity, float* __restrict
             const long long id = s.ids[i][k];
             if (id < id_begin || id >= id_end) continue;          // nothing a well-formed list contains
             if (s.sums[i] != nullptr) red_add_v4(grid0 + id * 4, __ldcs(s.sums[i] + k));
-            atomicAdd(counts0 + id, __ldcs(s.cnts[i] + k));
+            if (occupancy) counts0[id] = 1;                       // every writer stores the same value
+            else atomicAdd(counts0 + id, __ldcs(s.cnts[i] + k));
         }
     }
 }
@@ -259,7 +260,7 @@ int rc_voxel_sparse_merge(int32_t n_src, const void* const* src_ids, const void*
         const long long cap = 8ll * rc::sm_count(device);
         if (blocks > cap) blocks = cap;
         voxel_sparse_merge_kernel<<<static_cast<unsigned int>(blocks), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-            s, capacity, grid0, counts0, id_begin, id_end, overflow);
+            s, capacity, grid0, counts0, id_begin, id_end, overflow, (flags & RC_VOXEL_SPARSE_OCCUPANCY) != 0);
         const int rc_launch = rc::check_launch();
         if (rc_launch != RC_OK) return rc_launch;
     }

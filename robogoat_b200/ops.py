@@ -443,11 +443,11 @@ def voxel_sparse_send_cuda(grid: Optional[torch.Tensor], counts: torch.Tensor, r
 
 def voxel_sparse_merge_cuda(src_ids: Sequence[int], src_sums: Sequence[int], src_counts: Sequence[int], src_nrec: Sequence[int],
                             capacity: int, grid: Optional[torch.Tensor], counts: torch.Tensor, id_begin: int, id_end: int, *,
-                            normalize: bool = True, overflow: Optional[torch.Tensor] = None) -> None:
+                            normalize: bool = True, overflow: Optional[torch.Tensor] = None, occupancy: bool = False) -> None:
     """Add the record lists an owner received (device addresses) to its slab [id_begin, id_end) of its own partial grid
     (``grid`` fp32 [V, 4], ``counts`` int32 [V]: the FULL grid) and normalise the slab; see ``rc_voxel_sparse_merge``.
     Count mode: ``grid=None`` and ``src_sums`` all ``None``.  ``overflow``: int32 [1] flag that is set (never cleared)
-    when a source reports more records than its list holds."""
+    when a source reports more records than its list holds.  ``occupancy``: count mode storing 1 per received voxel."""
     n = len(src_ids)
     _check(len(src_sums) == n and len(src_counts) == n and len(src_nrec) == n and n <= 16, "one record list per source (at most 16)")
     _check(0 <= id_begin <= id_end <= counts.numel(), "bad voxel range")
@@ -459,7 +459,7 @@ def voxel_sparse_merge_cuda(src_ids: Sequence[int], src_sums: Sequence[int], src
                                            grid.data_ptr() + int(id_begin) * 16 if grid is not None else None,
                                            counts.data_ptr() + int(id_begin) * 4,
                                            int(id_begin), int(id_end), overflow.data_ptr() if overflow is not None else None,
-                                           0 if normalize else _lib.VOXEL_NO_NORMALIZE,
+                                           (0 if normalize else _lib.VOXEL_NO_NORMALIZE) | (_lib.VOXEL_SPARSE_OCCUPANCY if occupancy else 0),
                                            dev.index, _stream_ptr(dev))
     _lib.check(rc, "voxel_sparse_merge")
 

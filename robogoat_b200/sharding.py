@@ -576,6 +576,100 @@ class SparseReduce:
         self.ids = self.sums = self.counts = self.nrec = self.barrier = None
 
 
+class SparseGather:
+    """One record list per rank for the replicated form of the sparse reduction: a rank writes the occupied voxels of
+    its WHOLE partial grid into its own list (local stores), and every other rank reads that list over NVLink while it
+    merges.  ``records_per_rank`` bounds the occupied voxels of one rank's partial grid.  Construction and ``close``
+    are collective."""
+
+    def __init__(self, records_per_rank: int, group=None, barrier: str = "peer"):
+        from .peer import PeerBuffer, PeerBarrier
+        if barrier not in ("peer", "nccl"):
+            raise ValueError("barrier must be 'peer' (flag kernel over NVLink) or 'nccl' (4-byte all-reduce)")
+        self.group = group
+        self.rank, self.world = world(group)
+        if self.world > 16:
+            raise RuntimeError("the sparse reduction supports at most 16 ranks")
+        self.capacity = int(records_per_rank)
+        dev = torch.device("cuda", torch.cuda.current_device())
+        self._token = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.cursors = torch.zeros(16, dtype=torch.int32, device=dev)
+        self.overflow = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.barrier = None
+        self.ids = self.sums = self.counts = self.nrec = None
+        error = None
+        try:
+            self.ids = PeerBuffer(max(128, self.capacity * 4), dev)
+            self.sums = PeerBuffer(max(128, self.capacity * 16), dev)
+            self.counts = PeerBuffer(max(128, self.capacity * 4), dev)
+            self.nrec = PeerBuffer(128, dev)
+        except RuntimeError as e:
+            error = e
+        if not self._everyone(error is None):
+            self.close()
+            raise RuntimeError(f"SparseGather: record lists could not be allocated on every rank ({error})")
+        for buf in (self.ids, self.sums, self.counts, self.nrec):
+            try:
+                buf.connect(group)
+            except RuntimeError as e:
+                error = e
+            if not self._everyone(error is None):
+                self.close()
+                raise RuntimeError(f"SparseGather: peer buffers could not be mapped on every rank ({error})")
+        if barrier == "peer":
+            self.barrier = PeerBarrier(group, dev)
+
+    _everyone = SparseReduce._everyone
+    stream_barrier = SparseReduce.stream_barrier
+    failed = SparseReduce.failed
+
+    def close(self) -> None:
+        for b in (self.ids, self.sums, self.counts, self.nrec, self.barrier):
+            if b is not None:
+                b.close()
+        self.ids = self.sums = self.counts = self.nrec = self.barrier = None
+
+
+def voxelize_sharded_sparse_full(points_local: torch.Tensor, features_local: Optional[torch.Tensor], exchange: SparseGather,
+                                 grid_min=(-10.0, -10.0, -10.0), voxel_size: float = 0.1, grid_size=(128, 128, 128),
+                                 mode: str = "mean", check: bool = True):
+    """Voxelisation of a cloud spread over the ranks with the FULL grid on every rank - what ``voxelize_sharded`` (dense
+    partial grids + NCCL all-reduce, the reference's multi-GPU form) returns - by a sparse all-gather: every rank bins
+    its own points into a private full grid, lists that grid's occupied voxels in its own memory, and after a barrier
+    merges the other ranks' lists, read over NVLink, into its grid.  ``mode``: "mean" (four feature channels; returns the
+    normalised [X,Y,Z,4] grid), "count" or "occupancy" (int32 [X,Y,Z]).  Bytes crossing NVLink: 24 (8 in count and
+    occupancy mode) per occupied voxel of every other rank, instead of the whole dense grid several times."""
+    from . import ops
+    rank, ws = exchange.rank, exchange.world
+    gx, gy, gz = (int(v) for v in grid_size)
+    V = gx * gy * gz
+    if mode not in ("mean", "count", "occupancy"):
+        raise RuntimeError(f"Invalid mode: {mode}. The sparse all-gather supports 'mean', 'count' and 'occupancy'")
+    if mode == "mean":
+        if features_local is None or features_local.shape[1] != 4:
+            raise RuntimeError("the sparse reduction takes four feature channels")
+        grid, counts = ops.voxelize_pointcloud_cuda(points_local, features_local, list(grid_min), float(voxel_size), list(grid_size),
+                                                    "mean", normalize=False)
+        gflat, cflat = grid.view(V, 4), counts.view(V)
+    else:
+        grid = ops.voxelize_pointcloud_cuda(points_local, None, list(grid_min), float(voxel_size), list(grid_size), mode)[0]
+        gflat, cflat = None, grid.view(V)
+    others = [(rank + k) % ws for k in range(1, ws)]
+    exchange.stream_barrier()                   # everybody has finished reading this rank's list of the previous call
+    ops.voxel_sparse_send_cuda(gflat, cflat, [(0, V)], exchange.capacity, [exchange.ids.ptr],
+                               [exchange.sums.ptr if gflat is not None else None], [exchange.counts.ptr], [exchange.nrec.ptr],
+                               exchange.cursors, exchange.overflow)
+    exchange.stream_barrier()                   # every rank's list is complete
+    ops.voxel_sparse_merge_cuda([exchange.ids.peers[s] for s in others],
+                                [exchange.sums.peers[s] if gflat is not None else None for s in others],
+                                [exchange.counts.peers[s] for s in others], [exchange.nrec.peers[s] for s in others],
+                                exchange.capacity, gflat, cflat, 0, V, overflow=exchange.overflow, occupancy=(mode == "occupancy"))
+    if check and exchange.failed():
+        raise RuntimeError(f"sparse all-gather: a record list of {exchange.capacity} records overflowed on some rank, or a barrier "
+                           f"gave up waiting for a rank")
+    return grid
+
+
 def voxelize_sharded_sparse(points_local: torch.Tensor, features_local: torch.Tensor, exchange: SparseReduce,
                             grid_min=(-10.0, -10.0, -10.0), voxel_size: float = 0.1, grid_size=(128, 128, 128),
                             return_counts: bool = False, check: bool = True, mode: str = "mean"):

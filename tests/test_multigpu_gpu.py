@@ -129,6 +129,18 @@ for barrier in ("peer", "nccl"):             # the flag kernel over NVLink / a 4
       assert cslab.dtype == torch.int32 and torch.equal(cslab.cpu(), want["count"].reshape(V)[a:b]), f"sparse count {rep}"
   assert not (sr.barrier is not None and sr.barrier.timed_out()), barrier
   sr.close()
+# replicated output (what the dense all-reduce returns) by a sparse all-gather: lists stay with their sources, every rank
+# merges the others' lists over NVLink into its own full grid
+sg = sharding.SparseGather(records_per_rank=V)
+for rep in range(2):
+    l, h = spans[rank]
+    for mode in ("occupancy", "count"):
+        got = sharding.voxelize_sharded_sparse_full(pts[l:h], None, sg, mode=mode, **kw)
+        assert got.dtype == torch.int32 and torch.equal(got.cpu(), want[mode]), f"sparse all-gather {mode} {rep}"
+    got = sharding.voxelize_sharded_sparse_full(pts[l:h], feats[l:h], sg, mode="mean", **kw)
+    assert mean_ok(got), f"sparse all-gather mean {rep}"
+assert not sg.barrier.timed_out()
+sg.close()
 tiny = sharding.SparseReduce(records_per_pair=8)
 try:
     sharding.voxelize_sharded_sparse(pts[l:h], feats[l:h], tiny, **kw)
