@@ -364,6 +364,33 @@ class PointExchange:
         self._drop()
 
 
+def bucket_slice_windows(chunks: int, ranks: int, slices: int, s: int):
+    """Bookkeeping of the sliced bucket exchange.  Every rank's ``chunks`` blocks of an owner's pool (rank r's start at
+    block ``r * chunks``) are cut into ``slices`` runs of ``ceil(chunks / slices)`` blocks; slice ``s`` of the exchange is
+    run ``s`` of every rank.  Returns ``(first_chunk, n_chunks, first_blocks)``: the slice's first chunk and chunk count
+    inside a rank's cloud (0 chunks for slices beyond the capacity) and, per source rank, the first block of its window
+    in the owner's pool."""
+    chunks, ranks, slices, s = int(chunks), int(ranks), int(slices), int(s)
+    if chunks < 0 or ranks < 1 or slices < 1 or not 0 <= s < slices:
+        raise ValueError("bad slice geometry")
+    per = (chunks + slices - 1) // slices
+    first = min(s * per, chunks)
+    n = min(per, chunks - first)
+    return first, n, [r * chunks + first for r in range(ranks)]
+
+
+def sparse_list_offsets(rank: int, ranks: int, capacity: int):
+    """Bookkeeping of the sparse reduction's record lists: every rank's pool holds one list of ``capacity`` records per
+    source rank, source s at record ``s * capacity``.  Returns ``(others, write_at, read_at)``: the other ranks in the
+    order they are served (starting with the neighbour, which spreads the link load), the record offset of this rank's
+    list inside every other rank's pool, and the record offsets of the others' lists inside this rank's pool."""
+    rank, ranks, capacity = int(rank), int(ranks), int(capacity)
+    if not 0 <= rank < ranks or capacity < 0:
+        raise ValueError("bad rank or capacity")
+    others = [(rank + k) % ranks for k in range(1, ranks)]
+    return others, rank * capacity, [s * capacity for s in others]
+
+
 class BucketExchange:
     """Record pools for the bucket form of the point exchange (mean mode, four feature channels).  A chunk's block in
     a pool has a fixed place and capacity, so the exchange needs no counts, no host synchronisation and no all-to-all -
@@ -462,19 +489,12 @@ class BucketExchange:
         return ([p + d * rec * 4 for p in self.ids.peers], [p + d * rec * 16 for p in self.features.peers],
                 [p + d * self.per_group * self.chunks * 4 for p in self.runs.peers], self.chunks)
 
-    def slice_chunks(self, slices: int) -> int:
-        """Chunks per slice when the capacity is cut into ``slices`` equal runs of chunks (the last may be short)."""
-        return (self.chunks + int(slices) - 1) // int(slices)
-
     def slice_sources(self, s: int, slices: int):
         """(ids, features, runs, blocks) of slice ``s`` for this rank's accumulation: one window per source rank
         inside this rank's pool (storing form only); the run tables keep the pool's row length ``n_blocks``."""
         if self.fetch:
             raise RuntimeError("sliced accumulation is built for the storing form of the bucket exchange")
-        cs = self.slice_chunks(slices)
-        first = min(s * cs, self.chunks)
-        n = min(cs, self.chunks - first)
-        blocks = [r * self.chunks + first for r in range(self.world)]
+        _, n, blocks = bucket_slice_windows(self.chunks, self.world, slices, s)
         return ([self.ids.ptr + b * self.block * 4 for b in blocks], [self.features.ptr + b * self.block * 16 for b in blocks],
                 [self.runs.ptr + b * 4 for b in blocks], n)
 
@@ -560,14 +580,15 @@ class SparseReduce:
 
     def destinations(self, owners):
         """Addresses of this rank's list in every owner's memory: (ids, sums, counts, nrec)."""
-        off = self.rank * self.capacity
+        _, off, _ = sparse_list_offsets(self.rank, self.world, self.capacity)
         return ([self.ids.peers[d] + off * 4 for d in owners], [self.sums.peers[d] + off * 16 for d in owners],
                 [self.counts.peers[d] + off * 4 for d in owners], [self.nrec.peers[d] + self.rank * 4 for d in owners])
 
     def sources(self, sources):
         """Addresses of the lists this rank received from ``sources``: (ids, sums, counts, nrec)."""
-        return ([self.ids.ptr + s * self.capacity * 4 for s in sources], [self.sums.ptr + s * self.capacity * 16 for s in sources],
-                [self.counts.ptr + s * self.capacity * 4 for s in sources], [self.nrec.ptr + s * 4 for s in sources])
+        offs = [s * self.capacity for s in sources]
+        return ([self.ids.ptr + o * 4 for o in offs], [self.sums.ptr + o * 16 for o in offs],
+                [self.counts.ptr + o * 4 for o in offs], [self.nrec.ptr + s * 4 for s in sources])
 
     def close(self) -> None:
         for b in (self.ids, self.sums, self.counts, self.nrec, self.barrier):
@@ -696,7 +717,7 @@ def voxelize_sharded_sparse(points_local: torch.Tensor, features_local: torch.Te
                                                     "mean", normalize=False)
         grid, counts = grid.view(V, 4), counts.view(V)
     a, b = slab_bounds(V, rank, ws)
-    others = [(rank + k) % ws for k in range(1, ws)]                # start with the neighbour: spreads the link load
+    others, _, _ = sparse_list_offsets(rank, ws, exchange.capacity)   # start with the neighbour: spreads the link load
     d_ids, d_sums, d_counts, d_nrec = exchange.destinations(others)
     s_ids, s_sums, s_counts, s_nrec = exchange.sources(others)
     if grid is None:
@@ -764,7 +785,6 @@ def _buckets_sliced(points, feats, exchange: BucketExchange, grid_min, voxel_siz
     pts = points.to(torch.float32).contiguous()
     fts = feats.to(torch.float32).contiguous()
     N = pts.shape[0]
-    cs = exchange.slice_chunks(slices)
     d_ids, d_feats, d_runs, first_block, pool_blocks = exchange.destinations()
     main = torch.cuda.current_stream(dev)
     bar_stream, acc_stream = exchange.streams()
@@ -776,8 +796,7 @@ def _buckets_sliced(points, feats, exchange: BucketExchange, grid_min, voxel_siz
     with torch.cuda.stream(acc_stream):         # clear the slab while the first slice is bucketed
         ops.voxel_scatter_buckets_cuda([], [], [], 0, exchange.per_group, dev, a, b, normalize=False, out=out)
     for s in range(slices):
-        c0 = min(s * cs, exchange.chunks)
-        nchunks = min(cs, exchange.chunks - c0)
+        c0, nchunks, _ = bucket_slice_windows(exchange.chunks, ws, slices, s)
         p0, p1 = min(N, c0 * 1024), min(N, (c0 + nchunks) * 1024)
         ops.voxel_bucket_exchange_cuda(pts[p0:p1], fts[p0:p1], grid_min, voxel_size, grid_size, ws, exchange.per_group,
                                        nchunks, first_block + c0, pool_blocks, d_ids, d_feats, d_runs, ctas_per_sm=2)

@@ -252,3 +252,48 @@ def test_a_rank_that_never_joins_is_reported_not_waited_for_forever():
     p.join(60)
     assert not p.is_alive(), "rendezvous did not time out"
     assert q.get(timeout=5).startswith("error:")
+
+
+def test_bucket_slice_windows_tile_every_ranks_blocks_exactly():
+    """The sliced bucket exchange's bookkeeping: over all slices the windows of a source rank cover its blocks of the
+    owner's pool once, in order, without reaching into the next rank's; points map to chunks 1024 at a time."""
+    for chunks, ranks, slices in [(0, 2, 3), (1, 2, 4), (7, 3, 3), (64, 8, 4), (65, 4, 8), (100, 2, 16), (5, 16, 1)]:
+        covered = {r: [] for r in range(ranks)}
+        chunk_runs = []
+        for s in range(slices):
+            first, n, blocks = sharding.bucket_slice_windows(chunks, ranks, slices, s)
+            assert 0 <= first <= chunks and 0 <= n and first + n <= chunks
+            assert blocks == [r * chunks + first for r in range(ranks)]
+            chunk_runs.append((first, n))
+            for r in range(ranks):
+                covered[r] += list(range(blocks[r], blocks[r] + n))
+        for r in range(ranks):
+            assert covered[r] == list(range(r * chunks, (r + 1) * chunks)), (chunks, ranks, slices, r)
+        assert sum(n for _, n in chunk_runs) == chunks
+        sizes = [n for _, n in chunk_runs]
+        assert sizes == sorted(sizes, reverse=True)                     # full runs first, one short run, then empty slices
+        assert len({n for n in sizes if n and n != sizes[0]}) <= 1
+    import pytest
+    with pytest.raises(ValueError):
+        sharding.bucket_slice_windows(8, 2, 4, 4)
+    with pytest.raises(ValueError):
+        sharding.bucket_slice_windows(8, 0, 4, 0)
+
+
+def test_sparse_list_offsets_pair_every_writer_with_one_reader():
+    """The sparse reduction's bookkeeping: rank a writes its list for owner b where b reads the list of source a; the
+    lists inside a pool do not overlap; everybody starts with its neighbour."""
+    for ranks in (1, 2, 3, 8, 16):
+        cap = 1000
+        views = [sharding.sparse_list_offsets(r, ranks, cap) for r in range(ranks)]
+        for a in range(ranks):
+            others, write_at, read_at = views[a]
+            assert sorted(others) == [r for r in range(ranks) if r != a]
+            assert not others or others[0] == (a + 1) % ranks
+            assert write_at == a * cap and len(set(read_at)) == len(read_at)
+            for b, off in zip(others, read_at):
+                assert off == views[b][1]                      # where a reads b's list is where b wrote it
+                assert off % cap == 0 and off // cap == b
+    import pytest
+    with pytest.raises(ValueError):
+        sharding.sparse_list_offsets(2, 2, 10)
