@@ -777,6 +777,28 @@ def voxelize_sharded_buckets(points_local: torch.Tensor, features_local: torch.T
     return (grid, counts) if return_counts else grid
 
 
+def voxelize_sharded_auto(points_local: torch.Tensor, features_local: torch.Tensor, sparse: SparseReduce, buckets: BucketExchange,
+                          grid_min=(-10.0, -10.0, -10.0), voxel_size: float = 0.1, grid_size=(128, 128, 128),
+                          return_counts: bool = False):
+    """Mean-mode voxelisation with slab output that picks its form by trying: the sparse reduction first, and - if a
+    record list overflowed on any rank, i.e. the clouds hold too few points per occupied voxel for it to pay - the
+    bucket exchange, which takes any cloud.  The lists' capacity is the switch: ``records_per_pair`` below
+    ``points_per_rank / world * 20 / 24`` means the sparse form is only ever used where it moves fewer bytes than the
+    exchange.  Costs one host synchronisation per call (the check); returns what the two forms return.  The last form
+    used is in ``sparse.last_form`` ("sparse" or "buckets")."""
+    try:
+        out = voxelize_sharded_sparse(points_local, features_local, sparse, grid_min, voxel_size, grid_size,
+                                      return_counts=return_counts, check=True)
+        sparse.last_form = "sparse"
+        return out
+    except RuntimeError as e:
+        if "overflowed" not in str(e) or (sparse.barrier is not None and sparse.barrier.timed_out()):
+            raise
+    sparse.last_form = "buckets"
+    return voxelize_sharded_buckets(points_local, features_local, buckets, grid_min, voxel_size, grid_size,
+                                    return_counts=return_counts)
+
+
 def _buckets_sliced(points, feats, exchange: BucketExchange, grid_min, voxel_size, grid_size, slices, a, b, return_counts):
     """The bucket exchange in ``slices`` slices on three streams (see ``voxelize_sharded_buckets``)."""
     from . import ops

@@ -147,6 +147,16 @@ try:
     raise AssertionError("overflow not reported")
 except RuntimeError as e:
     assert "overflowed" in str(e), e
+# the form that picks by trying: lists that hold the cloud -> sparse reduction; lists that do not -> bucket exchange
+roomy = sharding.SparseReduce(records_per_pair=V)
+abx = sharding.BucketExchange(points_per_rank=120_000, n_voxels=V)
+a, b = sharding.slab_bounds(V, rank, ws)
+for lists, form in ((roomy, "sparse"), (tiny, "buckets"), (roomy, "sparse")):
+    slab, cnts = sharding.voxelize_sharded_auto(pts[l:h], feats[l:h], lists, abx, return_counts=True, **kw)
+    assert lists.last_form == form, (lists.last_form, form)
+    assert torch.equal(cnts.cpu(), cnt.reshape(V)[a:b]) and mean_ok(slab, a, b), f"auto form {form}"
+abx.close()
+roomy.close()
 tiny.close()
 small = sharding.PointExchange(capacity=10, feature_width=4)
 slab = sharding.voxelize_sharded_exchange(pts[lo:hi], None, mode="count", direct=small, **kw)
