@@ -1237,6 +1237,15 @@ def run_profile_case(name: str):
         pts = workloads.voxel_uniform_inputs(500_000, seed=0, device=dev)
         fn = lambda: robocache.voxelize_pointcloud(pts, mode="occupancy", **workloads.VOXEL_OCCUPANCY_GEOMETRY)
         units = {"N": 500_000}
+    elif name == "voxel_tsdf":
+        # the benchmark's TSDF case: 4 x 65536 points on a sphere of radius 2 with outward normals into [4,128^3], 3-voxel truncation
+        from robogoat_b200 import batched
+        g = torch.Generator().manual_seed(5)
+        sp = torch.randn(4, 65536, 3, generator=g)
+        sp = sp / sp.norm(dim=2, keepdim=True)
+        spd, nrm = (sp * 2.0).to(dev), sp.to(dev)
+        fn = lambda: batched.voxelize_tsdf(spd, nrm, [128, 128, 128], 0.05, [-3.2, -3.2, -3.2], 0.15)
+        units = {"B": 4, "N": 65536, "grid": "128^3"}
     elif name == "voxel_sparse":
         # the sparse reduction's send and merge kernels as one of 8 ranks would run them, with the owners' record lists
         # in this GPU's memory: a private 256^3 grid of 2^24 mixture points (335 MB of sums and counts), the occupied
@@ -1287,7 +1296,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extras", action="store_true")
     ap.add_argument("--profile-case", default=None,
-                    help="run 4 launches of one kernel on a small case (resample, fusion, voxel_mean, voxel_count, voxel_occupancy, voxel_partition, voxel_partition_aligned, voxel_scatter_runs, voxel_mean_runs, voxel_sparse; voxel_mean_full = headline size)")
+                    help="run 4 launches of one kernel on a small case (resample, fusion, voxel_mean, voxel_count, voxel_occupancy, voxel_partition, voxel_partition_aligned, voxel_scatter_runs, voxel_mean_runs, voxel_sparse, voxel_tsdf; voxel_mean_full = headline size)")
     args = ap.parse_args()
     if args.profile_case:
         run_profile_case(args.profile_case)
