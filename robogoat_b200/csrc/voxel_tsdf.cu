@@ -12,8 +12,8 @@
 // distance and then by side, and one atomicMin per (point, voxel) replaces the compare-and-swap loop.  A last pass
 // turns keys into floats (empty voxels: 0, as in the reference, whose grids start at zero).
 //
-// A warp takes 32 points; for each of them in turn its lanes spread over the voxel neighbourhood (x fastest), so the
-// atomics of one step fall on consecutive addresses.
+// A warp takes 32 points; for each of them in turn its lanes spread over the (y, x) cells of the voxel neighbourhood
+// (x fastest, so the atomics of one step fall on consecutive addresses) and walk their columns in z.
 #include "voxel_common.cuh"
 
 namespace {
@@ -67,32 +67,36 @@ voxel_tsdf_kernel(const float* __restrict__ pts, const float* __restrict__ norma
             if (!axis_range(y, g.oy, g.vs, g.reach, g.gy, y0, y1)) continue;
             if (!axis_range(z, g.oz, g.vs, g.reach, g.gz, z0, z1)) continue;
             const unsigned int wx = x1 - x0 + 1, wy = y1 - y0 + 1;
-            const unsigned int ncell = wx * wy * static_cast<unsigned int>(z1 - z0 + 1);   // <= 1025^3 < 2^31
+            const unsigned int nplane = wx * wy;                                   // <= 1025^2
             const long long item = ((base + j) / N) * V;
-            // c / w for the whole neighbourhood from one reciprocal per point: floor(c * ceil(2^32 / w) / 2^32) is
-            // exact while c * w < 2^32; w <= 1025, so neighbourhoods of up to 2^20 cells qualify (w = 1 has no 32-bit
-            // reciprocal); larger ones divide
-            const bool fast = ncell <= (1u << 20);
+            // lanes over the (y, x) cells of the neighbourhood, z as the inner loop: the cell's x/y offsets, their
+            // squares and the x/y part of the normal's dot product are computed once per column.  c / wx comes from one
+            // reciprocal per point: floor(c * ceil(2^32 / wx) / 2^32) is exact while c * wx < 2^32, and c < 1025^2,
+            // wx <= 1025 (wx = 1 has no 32-bit reciprocal).
             const unsigned int mx = static_cast<unsigned int>((0x100000000ull + wx - 1) / wx);
-            const unsigned int my = static_cast<unsigned int>((0x100000000ull + wy - 1) / wy);
-            for (unsigned int c = lane; c < ncell; c += 32) {
-                const unsigned int r = (wx == 1) ? c : (fast ? __umulhi(c, mx) : c / wx);
+            for (unsigned int c = lane; c < nplane; c += 32) {
+                const unsigned int r = (wx == 1) ? c : __umulhi(c, mx);
                 const int vx = x0 + static_cast<int>(c - r * wx);
-                const unsigned int q = (wy == 1) ? r : (fast ? __umulhi(r, my) : r / wy);
-                const int vy = y0 + static_cast<int>(r - q * wy);
-                const int vz = z0 + static_cast<int>(q);
+                const int vy = y0 + static_cast<int>(r);
                 // voxel centre and distance: single fp32 operations in this order (no contraction)
                 const float dx = (g.ox + (static_cast<float>(vx) + 0.5f) * g.vs) - x;
                 const float dy = (g.oy + (static_cast<float>(vy) + 0.5f) * g.vs) - y;
-                const float dz = (g.oz + (static_cast<float>(vz) + 0.5f) * g.vs) - z;
-                const float dist = sqrtf((dx * dx + dy * dy) + dz * dz);
-                if (!(dist < g.trunc)) continue;
-                unsigned int inside = 0u;
-                if (normals != nullptr && ((ax * dx + ay * dy) + az * dz) > 0.0f) inside = 1u;
-                const float val = fminf(1.0f, dist * g.inv_trunc);
-                const long long cell = item + static_cast<long long>(vz) * plane + static_cast<long long>(vy) * g.gx + vx;
-                atomicMin(keys + cell, (__float_as_uint(val) << 1) | inside);
-                red_add_one(weights + cell);
+                const float dxy2 = dx * dx + dy * dy;
+                // rounded addition and square root are monotonic: a column whose x/y offset alone reaches the
+                // truncation distance has no cell inside it
+                if (!(sqrtf(dxy2) < g.trunc)) continue;
+                const float dotxy = ax * dx + ay * dy;
+                long long cell = item + static_cast<long long>(z0) * plane + static_cast<long long>(vy) * g.gx + vx;
+                for (int vz = z0; vz <= z1; ++vz, cell += plane) {
+                    const float dz = (g.oz + (static_cast<float>(vz) + 0.5f) * g.vs) - z;
+                    const float dist = sqrtf(dxy2 + dz * dz);
+                    if (!(dist < g.trunc)) continue;
+                    unsigned int inside = 0u;
+                    if (normals != nullptr && (dotxy + az * dz) > 0.0f) inside = 1u;
+                    const float val = fminf(1.0f, dist * g.inv_trunc);
+                    atomicMin(keys + cell, (__float_as_uint(val) << 1) | inside);
+                    red_add_one(weights + cell);
+                }
             }
         }
     }
