@@ -297,3 +297,48 @@ def test_sparse_list_offsets_pair_every_writer_with_one_reader():
     import pytest
     with pytest.raises(ValueError):
         sharding.sparse_list_offsets(2, 2, 10)
+
+
+def test_auto_form_falls_back_only_on_overflow(monkeypatch):
+    """Host logic of ``voxelize_sharded_auto`` with the two GPU forms replaced by stand-ins: a record-list overflow sends
+    the call to the bucket exchange, any other error - and an overflow report that comes with a barrier time-out -
+    reaches the caller."""
+    class Lists:
+        barrier = None
+        last_form = None
+
+    class TimedOut:
+        def timed_out(self):
+            return True
+
+    calls = []
+
+    def sparse_ok(*a, **k):
+        calls.append("sparse")
+        return "S"
+
+    def sparse_overflow(*a, **k):
+        calls.append("sparse")
+        raise RuntimeError("sparse reduction: a record list of 8 records overflowed on some rank, or a barrier gave up")
+
+    def sparse_broken(*a, **k):
+        raise RuntimeError("voxel_sparse_send: invalid device pointer")
+
+    def buckets(*a, **k):
+        calls.append("buckets")
+        return "B"
+
+    monkeypatch.setattr(sharding, "voxelize_sharded_buckets", buckets)
+    lists = Lists()
+    monkeypatch.setattr(sharding, "voxelize_sharded_sparse", sparse_ok)
+    assert sharding.voxelize_sharded_auto(None, None, lists, None) == "S" and lists.last_form == "sparse"
+    monkeypatch.setattr(sharding, "voxelize_sharded_sparse", sparse_overflow)
+    assert sharding.voxelize_sharded_auto(None, None, lists, None) == "B" and lists.last_form == "buckets"
+    assert calls == ["sparse", "sparse", "buckets"]
+    monkeypatch.setattr(sharding, "voxelize_sharded_sparse", sparse_broken)
+    with pytest.raises(RuntimeError, match="invalid device pointer"):
+        sharding.voxelize_sharded_auto(None, None, lists, None)
+    lists.barrier = TimedOut()
+    monkeypatch.setattr(sharding, "voxelize_sharded_sparse", sparse_overflow)
+    with pytest.raises(RuntimeError, match="overflowed"):
+        sharding.voxelize_sharded_auto(None, None, lists, None)
