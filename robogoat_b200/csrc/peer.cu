@@ -9,7 +9,7 @@
 namespace {
 
 constexpr int kBarrierMaxRanks = 16;
-constexpr long long kBarrierDefaultPolls = 1ll << 22;      // about half a second of polling
+constexpr long long kBarrierDefaultPolls = 1ll << 25;      // about 8 s of polling (0.26 us per poll): ranks may be seconds apart
 
 struct BarrierFlags {
     unsigned int* arr[kBarrierMaxRanks];    // arr[p]: rank p's flag array (uint32 [n]) as mapped into this process
@@ -20,7 +20,7 @@ struct BarrierFlags {
 // array, after a system-scope fence so that everything this GPU wrote before - including plain stores into peers'
 // memory by earlier kernels of the stream - is performed first), then wait until p's arrival shows up in this rank's
 // own array.  The wait is bounded: after poll_limit polls the thread raises *status and gives up, so a rank that
-// never arrives costs the others half a second and an error code, not a hung GPU.  Epochs only grow (compared as a
+// never arrives costs the others a few seconds and an error code, not a hung GPU.  Epochs only grow (compared as a
 // signed difference, so they may wrap); a fast rank's next epoch satisfies a slow rank's wait for this one.
 __global__ void peer_barrier_kernel(BarrierFlags f, unsigned int epoch, long long poll_limit, int* status) {
     const int p = threadIdx.x;

@@ -69,7 +69,7 @@ class PeerBarrier:
     """Barrier among the ranks of a node on the current CUDA stream, without NCCL: one 32-thread kernel per call that
     stores an epoch into every peer's flag array over NVLink and polls its own (``rc_peer_barrier``).  Work enqueued
     after ``wait()`` on any rank sees what every rank's stream did before its ``wait()``, plain stores into peers'
-    memory included.  The kernel's wait is bounded (about half a second by default): a rank that never arrives raises
+    memory included.  The kernel's wait is bounded (about 8 seconds by default): a rank that never arrives raises
     ``status`` on the others instead of hanging them - read it with ``timed_out()``.  Construction and ``close`` are
     collective; every rank must call ``wait()`` the same number of times."""
 
